@@ -1,0 +1,83 @@
+"""Compile the CUDA sources into ``dynquant_b200/lib/libdynquant_b200.so``.
+
+sm_100a only.  Invoked by ``python -m dynquant_b200.build`` and by the repo's
+build entry point; needs ``nvcc`` but no GPU (it cross-compiles).  The library
+has no dependency on torch or Python: it is the C ABI of ``include/dynquant_b200.h``.
+"""
+
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+ROOT = PKG.parent
+CSRC = PKG / "csrc"
+INCLUDE = ROOT / "include"
+OBJ_DIR = PKG / "lib" / "obj"
+LIB_PATH = PKG / "lib" / "libdynquant_b200.so"
+
+SOURCES = ["dq_capi.cu", "dq_dequant.cu", "dq_gemv.cu", "dq_moe.cu"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "--extended-lambda",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unused-function",
+    "-I", str(INCLUDE), "-I", str(CSRC),
+]
+
+
+def nvcc() -> str:
+    path = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(path).exists():
+        raise RuntimeError("nvcc not found; the CUDA toolkit is required to build dynquant_b200")
+    return path
+
+
+def _stale(target: Path, deps: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(d.stat().st_mtime > t for d in deps)
+
+
+def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(INCLUDE.glob("*.h")) + [Path(__file__)]
+    sources = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
+    jobs = []
+    for src in sources:
+        obj = OBJ_DIR / (src.stem + ".o")
+        if force or _stale(obj, [src, *headers]):
+            cmd = [nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            if ptxas_info:
+                cmd[1:1] = ["-Xptxas", "-v"]
+            jobs.append(cmd)
+
+    def run(cmd: list[str]) -> None:
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0 or ptxas_info:
+            sys.stderr.write(res.stdout + res.stderr)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {cmd[-3]}")
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
+            list(pool.map(run, jobs))
+    objs = [OBJ_DIR / (s.stem + ".o") for s in sources]
+    if jobs or force or _stale(LIB_PATH, objs):
+        run([nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs),
+             "-Xlinker", "-rpath,/usr/local/cuda/lib64"])
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build_library(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas-info" in sys.argv)
+    print(path)

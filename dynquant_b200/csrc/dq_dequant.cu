@@ -1,0 +1,189 @@
+// Packed words -> dense [rows, in_features] matrix, bit-exact against the
+// reference's QuantTensor.dequantize.
+//
+// Replaces dequant_kernel / dequant_cuda
+// (packages/dynquant-kernels/csrc/quant/dequant.cu:47-93, :130-165).  It is the
+// prefill (M > 8) feed for a dense GEMM, the embedding-row decoder, and the
+// anchor of the parity suite: a wrong bit anywhere in the decode shows here as
+// a wrong number, with no accumulation to hide behind.
+//
+// Arithmetic: w = float(q) * scale, then + offset, both rounded to fp32
+// (packages/dynquant-core/src/dynquant/quant/tensor.py:417-426 multiplies and
+// then adds), then one rounding to the output dtype.  With fp16/bf16 scales the
+// product is exact in fp32, so this equals the reference CUDA kernel's single
+// fmaf as well; with fp32 scales it follows the torch definition.  An absent
+// offsets tensor means "no add", not "+0".
+//
+// One thread decodes one block (16/32/8/4 values at 2/3/4/8-bit) per step of a
+// grid-stride loop, so a warp reads 32 consecutive blocks of words and writes
+// 32 * values_per_block consecutive outputs.
+#include <algorithm>
+
+#include "dq_decode.cuh"
+
+namespace dq {
+namespace {
+
+constexpr int kDequantThreads = 256;
+
+struct DequantArgs {
+  const uint32_t* packed;
+  const void* scales;
+  const void* offsets;
+  void* out;
+  int meta_dtype, out_dtype;
+  int rows;
+  int words_per_row, num_groups, words_per_group, group_values, in_features;
+  int blocks_per_group, blocks_per_row;
+};
+
+template <int BITS>
+__global__ void __launch_bounds__(kDequantThreads) dequant_kernel(const DequantArgs a) {
+  constexpr int VB = Block<BITS>::kValues;
+  constexpr int WB = Block<BITS>::kWords;
+  const int64_t total = static_cast<int64_t>(a.rows) * a.blocks_per_row;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const bool has_offsets = a.offsets != nullptr;
+
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += stride) {
+    const int row = static_cast<int>(idx / a.blocks_per_row);
+    const int blk = static_cast<int>(idx - static_cast<int64_t>(row) * a.blocks_per_row);
+    const int g = blk / a.blocks_per_group;
+    const int bg = blk - g * a.blocks_per_group;
+    const int word_base = g * a.words_per_group + (bg * VB * BITS) / 32;
+    const int words_left = a.words_per_row - word_base;
+    const int value_base = g * a.group_values + bg * VB;
+    // Values of this block that exist: bounded by the group (per-row tail) and
+    // by in_features (zero pad of the last group).
+    const int live = min(min(VB, a.group_values - bg * VB), a.in_features - value_base);
+    if (live <= 0) {
+      continue;
+    }
+    const uint32_t* src = a.packed + static_cast<int64_t>(row) * a.words_per_row + word_base;
+    const int64_t meta = static_cast<int64_t>(row) * a.num_groups + g;
+    const float scale = load_f32(a.scales, meta, a.meta_dtype);
+    const float offset = has_offsets ? load_f32(a.offsets, meta, a.meta_dtype) : 0.0f;
+    const int64_t out_base = static_cast<int64_t>(row) * a.in_features + value_base;
+
+    if (live == VB && words_left >= WB) {
+      uint32_t w[WB];
+#pragma unroll
+      for (int i = 0; i < WB; ++i) {
+        w[i] = __ldg(src + i);
+      }
+      float vals[VB];
+      for_each_pair<BITS>(w, [&](int p, float2 q2) {
+        float lo = __fmul_rn(q2.x, scale);
+        float hi = __fmul_rn(q2.y, scale);
+        if (has_offsets) {
+          lo = __fadd_rn(lo, offset);
+          hi = __fadd_rn(hi, offset);
+        }
+        vals[2 * p] = lo;
+        vals[2 * p + 1] = hi;
+      });
+      if (a.out_dtype == DQ_F32) {
+        float* dst = reinterpret_cast<float*>(a.out) + out_base;
+        if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < VB / 4; ++j) {
+            reinterpret_cast<float4*>(dst)[j] =
+                make_float4(vals[4 * j], vals[4 * j + 1], vals[4 * j + 2], vals[4 * j + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < VB; ++j) {
+            dst[j] = vals[j];
+          }
+        }
+      } else {
+        unsigned short* dst = reinterpret_cast<unsigned short*>(a.out) + out_base;
+        uint32_t packed16[VB / 2];
+#pragma unroll
+        for (int j = 0; j < VB / 2; ++j) {
+          packed16[j] = round_to_16(vals[2 * j], a.out_dtype) |
+                        (round_to_16(vals[2 * j + 1], a.out_dtype) << 16);
+        }
+        const uintptr_t addr = reinterpret_cast<uintptr_t>(dst);
+        if (VB % 8 == 0 && (addr & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < VB / 8; ++j) {
+            reinterpret_cast<uint4*>(dst)[j] = make_uint4(packed16[4 * j], packed16[4 * j + 1],
+                                                          packed16[4 * j + 2], packed16[4 * j + 3]);
+          }
+        } else if ((addr & 3) == 0) {
+#pragma unroll
+          for (int j = 0; j < VB / 2; ++j) {
+            reinterpret_cast<uint32_t*>(dst)[j] = packed16[j];
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < VB / 2; ++j) {
+            dst[2 * j] = static_cast<unsigned short>(packed16[j] & 0xFFFFu);
+            dst[2 * j + 1] = static_cast<unsigned short>(packed16[j] >> 16);
+          }
+        }
+      }
+    } else {
+      for (int j = 0; j < live; ++j) {
+        const float q = static_cast<float>(code_at<BITS>(src, j, words_left));
+        float v = __fmul_rn(q, scale);
+        if (has_offsets) {
+          v = __fadd_rn(v, offset);
+        }
+        store_f32(a.out, out_base + j, a.out_dtype, v);
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace dq
+
+extern "C" int32_t dq_dequant(const dq_weight* w, void* out, int32_t out_dtype, void* stream) {
+  dq_geometry g;
+  if (const int32_t rc = dq_resolve_geometry("dequant", w, &g)) return rc;
+  DQ_REQUIRE(dq::dtype_ok(out_dtype), "dequant: unsupported output dtype tag %d", out_dtype);
+  if (w->rows == 0) return DQ_OK;
+  DQ_REQUIRE(out != nullptr, "dequant: null output pointer");
+
+  dq::DequantArgs a = {};
+  a.packed = static_cast<const uint32_t*>(w->packed);
+  a.scales = w->scales;
+  a.offsets = w->offsets;
+  a.out = out;
+  a.meta_dtype = w->meta_dtype;
+  a.out_dtype = out_dtype;
+  a.rows = static_cast<int>(w->rows);
+  a.words_per_row = g.words_per_row;
+  a.num_groups = g.num_groups;
+  a.words_per_group = g.words_per_group;
+  a.group_values = g.group_values;
+  a.in_features = g.in_features;
+  a.blocks_per_group = g.blocks_per_group;
+  a.blocks_per_row = g.blocks_per_row;
+
+  const dq::DeviceInfo* dev = dq::device_info();
+  if (dev == nullptr) return DQ_ERR_CUDA;
+  const int64_t total = static_cast<int64_t>(a.rows) * a.blocks_per_row;
+  const int64_t want = dq::ceil_div(total, dq::kDequantThreads);
+  const int grid = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(dev->sm_count) * 32));
+  auto s = static_cast<cudaStream_t>(stream);
+  switch (w->bits) {
+    case 2:
+      dq::dequant_kernel<2><<<grid, dq::kDequantThreads, 0, s>>>(a);
+      break;
+    case 3:
+      dq::dequant_kernel<3><<<grid, dq::kDequantThreads, 0, s>>>(a);
+      break;
+    case 4:
+      dq::dequant_kernel<4><<<grid, dq::kDequantThreads, 0, s>>>(a);
+      break;
+    default:
+      dq::dequant_kernel<8><<<grid, dq::kDequantThreads, 0, s>>>(a);
+      break;
+  }
+  DQ_CHECK_LAUNCH("dequant");
+  return DQ_OK;
+}

@@ -1,0 +1,594 @@
+// Packed decode GEMV for sm_100a:  out[m, n] = sum_k x[m, k] * (q[n, k] * s[n, g] + o[n, g]).
+//
+// Replaces the reference's gemv_vec_kernel / gemv_kernel / gemv_cuda
+// (packages/dynquant-kernels/csrc/gemv/gemv.cu:275-432, :444-555, :695-756).
+// Same contract -- fp32 accumulation, a fixed summation order so a result is
+// bit-identical run to run, one rounding at the store -- but a different
+// machine in mind:
+//
+//  * The activation is staged ONCE per CTA into shared memory as fp32 (so the
+//    inner loop never converts an activation), in a layout padded by 16 bytes
+//    per lane-chunk so that 32 lanes reading 32 different chunks hit 32
+//    different bank groups.  Per-chunk activation sums are precomputed there
+//    too, which is what lets the affine map be applied once per chunk:
+//        sum_i (q_i*s + o) x_i  =  s * sum_i q_i x_i  +  o * sum_i x_i.
+//  * Weights stream through 128-bit no-allocate loads, software-pipelined one
+//    iteration ahead across row tiles, so every lane always has its next
+//    16..48 bytes in flight while it decodes the current ones.  The first
+//    prefetch is issued BEFORE griddepcontrol.wait: under programmatic
+//    dependent launch the weight stream of layer i+1 starts while layer i is
+//    still draining, and only the activation staging waits for layer i.
+//  * Codes are decoded without conversion instructions and multiplied with
+//    packed fp32 FMAs (dq_decode.cuh).
+//  * CTAs are persistent: the grid is capped at what the device can hold and
+//    warps stride over row tiles, so the staging cost is paid once per CTA.
+//
+// A second kernel covers every geometry the format allows and the fast path
+// refuses (pad tails, per-row tensors, groups smaller than a chunk, unaligned
+// views), like the reference's general kernel.
+#include <algorithm>
+#include <cstdlib>
+
+#include "dq_decode.cuh"
+
+namespace dq {
+namespace {
+
+constexpr int kWarpsPerCta = 8;
+constexpr int kThreads = kWarpsPerCta * kWarp;
+
+struct GemvArgs {
+  const void* x;
+  const uint32_t* packed;
+  const void* scales;
+  const void* offsets;  // may be null
+  const void* bias;     // may be null; [rows] in out_dtype, indexed from out_col0
+  void* out;
+  int64_t out_stride;  // elements between consecutive activation rows of out
+  int64_t out_col0;    // first output column this weight writes
+  int x_dtype, meta_dtype, out_dtype;
+  int m;     // real activation rows
+  int rows;  // output features of this weight
+  int words_per_row, num_groups, words_per_group, group_values, in_features;
+  int chunks_per_row, chunks_per_group;  // fast path only
+};
+
+template <int BITS, int CW>
+struct ChunkCfg {
+  static constexpr int kWords = CW;
+  static constexpr int kValues = CW * 32 / BITS;
+  static constexpr int kBlocks = CW / Block<BITS>::kWords;
+  static constexpr int kPad = 4;  // floats of padding per chunk in shared memory
+  static constexpr int kStride = kValues + kPad;
+};
+
+// CW words of one row's chunk into registers.
+template <int CW>
+__device__ __forceinline__ void load_chunk(const uint32_t* __restrict__ src, uint32_t* w) {
+  if constexpr (CW % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < CW / 4; ++i) {
+      const uint4 v = ldg_stream_128(src + 4 * i);
+      w[4 * i + 0] = v.x;
+      w[4 * i + 1] = v.y;
+      w[4 * i + 2] = v.z;
+      w[4 * i + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < CW; ++i) {
+      w[i] = ldg_stream_32(src + i);
+    }
+  }
+}
+
+__device__ __forceinline__ void store_out(const GemvArgs& a, int m, int row, float v) {
+  const int64_t col = a.out_col0 + row;
+  if (a.bias != nullptr) {
+    v += load_f32(a.bias, col, a.out_dtype);
+  }
+  store_f32(a.out, static_cast<int64_t>(m) * a.out_stride + col, a.out_dtype, v);
+}
+
+// ---------------------------------------------------------------------------
+// Fast path
+// ---------------------------------------------------------------------------
+//
+// MT activation rows are kept in shared memory (rows >= a.m are zero), a warp
+// owns R consecutive output rows per tile and its lanes stride over the row's
+// chunks.
+template <int BITS, int CW, int MT, int R>
+__global__ void __launch_bounds__(kThreads) gemv_fast_kernel(const GemvArgs a) {
+  using Cfg = ChunkCfg<BITS, CW>;
+  constexpr int V = Cfg::kValues;
+  constexpr int VB = Block<BITS>::kValues;
+  constexpr int WB = Block<BITS>::kWords;
+
+  extern __shared__ __align__(16) float smem[];
+  const int C = a.chunks_per_row;
+  const int xs_stride = C * Cfg::kStride;  // floats per activation row
+  float* xs = smem;
+  float* xsum = smem + MT * xs_stride;
+
+  const int lane = threadIdx.x & (kWarp - 1);
+  const int warp = threadIdx.x >> 5;
+  const int total_warps = gridDim.x * kWarpsPerCta;
+  const int first_tile = blockIdx.x * kWarpsPerCta + warp;
+  const int num_tiles = (a.rows + R - 1) / R;
+  const int iters_per_tile = (C + kWarp - 1) / kWarp;
+
+  pdl_launch_dependents();
+
+  // ---- software pipeline state: one (tile, chunk) step ahead ----
+  uint32_t wnext[R][CW];
+  int tile = first_tile;
+  int ci = 0;  // iteration within the tile
+  auto issue_loads = [&](int t, int i) {
+    const int c = i * kWarp + lane;
+    if (t < num_tiles && c < C) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int row = min(t * R + r, a.rows - 1);
+        load_chunk<CW>(a.packed + static_cast<int64_t>(row) * a.words_per_row + c * CW, wnext[r]);
+      }
+    }
+  };
+  issue_loads(tile, ci);
+
+  // ---- stage the activation (this is what depends on the previous kernel) ----
+  pdl_wait_prior_grid();
+  for (int i = threadIdx.x; i < MT * a.in_features; i += kThreads) {
+    const int m = i / a.in_features;
+    const int k = i - m * a.in_features;
+    const float v = m < a.m ? load_f32(a.x, static_cast<int64_t>(m) * a.in_features + k, a.x_dtype) : 0.0f;
+    xs[m * xs_stride + k + Cfg::kPad * (k / V)] = v;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < MT * C; i += kThreads) {
+    const int m = i / C;
+    const int c = i - m * C;
+    const float* p = xs + m * xs_stride + c * Cfg::kStride;
+    float s = 0.0f;
+#pragma unroll 8
+    for (int j = 0; j < V; ++j) {
+      s += p[j];
+    }
+    xsum[i] = s;
+  }
+  __syncthreads();
+
+  float acc[R][MT];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      acc[r][m] = 0.0f;
+    }
+  }
+
+  while (tile < num_tiles) {
+    // Take ownership of the prefetched words, then put the next step in flight.
+    uint32_t w[R][CW];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+      for (int i = 0; i < CW; ++i) {
+        w[r][i] = wnext[r][i];
+      }
+    }
+    const int cur_tile = tile;
+    const int c = ci * kWarp + lane;
+    const bool last_iter = (ci + 1 == iters_per_tile);
+    if (last_iter) {
+      tile += total_warps;
+      ci = 0;
+    } else {
+      ++ci;
+    }
+    issue_loads(tile, ci);
+
+    if (c < C) {
+      const int g = c / a.chunks_per_group;
+      float scale[R], offset[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int row = min(cur_tile * R + r, a.rows - 1);
+        const int64_t meta = static_cast<int64_t>(row) * a.num_groups + g;
+        scale[r] = load_f32(a.scales, meta, a.meta_dtype);
+        offset[r] = a.offsets != nullptr ? load_f32(a.offsets, meta, a.meta_dtype) : 0.0f;
+      }
+
+      float2 qacc[R][MT];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          qacc[r][m] = make_float2(0.0f, 0.0f);
+        }
+      }
+
+      const float* xc = xs + c * Cfg::kStride;
+#pragma unroll
+      for (int b = 0; b < Cfg::kBlocks; ++b) {
+        if constexpr (MT == 1) {
+          // Activations of this block in registers, shared by the R rows.
+          float2 xv[VB / 2];
+#pragma unroll
+          for (int j = 0; j < VB / 4; ++j) {
+            const float4 t = *reinterpret_cast<const float4*>(xc + b * VB + 4 * j);
+            xv[2 * j] = make_float2(t.x, t.y);
+            xv[2 * j + 1] = make_float2(t.z, t.w);
+          }
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            for_each_pair<BITS>(&w[r][b * WB], [&](int p, float2 q2) {
+              qacc[r][0] = __ffma2_rn(q2, xv[p], qacc[r][0]);
+            });
+          }
+        } else {
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            for_each_pair<BITS>(&w[r][b * WB], [&](int p, float2 q2) {
+#pragma unroll
+              for (int m = 0; m < MT; ++m) {
+                const float2 x2 =
+                    *reinterpret_cast<const float2*>(xc + m * xs_stride + b * VB + 2 * p);
+                qacc[r][m] = __ffma2_rn(q2, x2, qacc[r][m]);
+              }
+            });
+          }
+        }
+      }
+
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const float dot = qacc[r][m].x + qacc[r][m].y;
+          acc[r][m] = fmaf(scale[r], dot, fmaf(offset[r], xsum[m * C + c], acc[r][m]));
+        }
+      }
+    }
+
+    if (last_iter) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          float v = acc[r][m];
+#pragma unroll
+          for (int d = kWarp / 2; d > 0; d >>= 1) {
+            v += __shfl_xor_sync(0xffffffffu, v, d);
+          }
+          acc[r][m] = 0.0f;
+          const int row = cur_tile * R + r;
+          if (lane == 0 && row < a.rows && m < a.m) {
+            store_out(a, m, row, v);
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// General path: any legal geometry.  One warp per output row; a lane takes one
+// block (the smallest run of whole words) at a time, word by word, with the
+// pad tail (v >= in_features) skipped as in the reference (gemv.cu:513).
+// ---------------------------------------------------------------------------
+template <int BITS, int MT>
+__global__ void __launch_bounds__(kThreads) gemv_general_kernel(const GemvArgs a) {
+  constexpr int VB = Block<BITS>::kValues;
+  const int lane = threadIdx.x & (kWarp - 1);
+  const int warp = threadIdx.x >> 5;
+  const int total_warps = gridDim.x * kWarpsPerCta;
+  const int blocks_per_group = (a.group_values + VB - 1) / VB;
+  const int blocks_per_row = blocks_per_group * a.num_groups;
+  const uint32_t* packed = a.packed;
+
+  pdl_launch_dependents();
+  pdl_wait_prior_grid();
+
+  for (int row = blockIdx.x * kWarpsPerCta + warp; row < a.rows; row += total_warps) {
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      acc[m] = 0.0f;
+    }
+    const uint32_t* row_words = packed + static_cast<int64_t>(row) * a.words_per_row;
+    for (int blk = lane; blk < blocks_per_row; blk += kWarp) {
+      const int g = blk / blocks_per_group;
+      const int bg = blk - g * blocks_per_group;
+      const int word_base = g * a.words_per_group + (bg * VB * BITS) / 32;
+      const int words_left = a.words_per_row - word_base;
+      const int value_base = g * a.group_values + bg * VB;
+      const int in_group = min(VB, a.group_values - bg * VB);
+      const int64_t meta = static_cast<int64_t>(row) * a.num_groups + g;
+      const float scale = load_f32(a.scales, meta, a.meta_dtype);
+      const float offset = a.offsets != nullptr ? load_f32(a.offsets, meta, a.meta_dtype) : 0.0f;
+      for (int j = 0; j < in_group; ++j) {
+        const int v = value_base + j;
+        if (v >= a.in_features) {
+          break;
+        }
+        const float q = static_cast<float>(code_at<BITS>(row_words + word_base, j, words_left));
+        const float wv = fmaf(q, scale, offset);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          if (m < a.m) {
+            acc[m] = fmaf(wv, load_f32(a.x, static_cast<int64_t>(m) * a.in_features + v, a.x_dtype),
+                          acc[m]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      float v = acc[m];
+#pragma unroll
+      for (int d = kWarp / 2; d > 0; d >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, d);
+      }
+      if (lane == 0 && m < a.m) {
+        store_out(a, m, row, v);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host dispatch
+// ---------------------------------------------------------------------------
+
+bool force_general() {
+  // Same switch the reference reads (DYNQUANT_GEMV_SCALAR, gemv.cu:604-610): an
+  // A/B control that sends every call down the general kernel.  Read once.
+  static const bool forced = [] {
+    const char* v = std::getenv("DYNQUANT_GEMV_SCALAR");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  return forced;
+}
+
+bool use_pdl() {
+  static const bool on = [] {
+    const char* v = std::getenv("DQ_B200_NO_PDL");
+    return !(v != nullptr && v[0] != '\0' && v[0] != '0');
+  }();
+  return on;
+}
+
+// Chunk width (words) of the fast path for this tensor, or 0 if it must take
+// the general kernel.  Host-side twin of the reference's vec_geometry_ok
+// (gemv.cu:566-598).
+int fast_chunk_words(const dq_weight& w, const dq_geometry& g, const void* x, int x_dtype) {
+  if (force_general()) return 0;
+  if (static_cast<int64_t>(g.num_groups) * g.group_values != g.in_features) return 0;  // pad tail
+  (void)x;
+  (void)x_dtype;
+  const auto addr = reinterpret_cast<uintptr_t>(w.packed);
+  if (w.bits == 3) {
+    if (g.words_per_group % 12 == 0 && addr % 16 == 0 && g.words_per_row % 4 == 0) return 12;
+    if (g.words_per_group % 3 == 0 && addr % 4 == 0) return 3;
+    return 0;
+  }
+  if (g.words_per_group % 4 != 0 || addr % 16 != 0) return 0;
+  return 4;
+}
+
+template <typename Kernel>
+int32_t launch(Kernel kernel, const GemvArgs& args, int grid, size_t smem, cudaStream_t stream,
+               const char* what) {
+  if (smem > 48 * 1024) {
+    DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)));
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 1 : 0;
+  DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, args));
+  DQ_CHECK_LAUNCH(what);
+  return DQ_OK;
+}
+
+template <int BITS, int CW, int MT, int R>
+int32_t launch_fast(const GemvArgs& args, cudaStream_t stream) {
+  using Cfg = ChunkCfg<BITS, CW>;
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr) return DQ_ERR_CUDA;
+  const size_t smem =
+      sizeof(float) * static_cast<size_t>(MT) * (static_cast<size_t>(args.chunks_per_row) * Cfg::kStride + args.chunks_per_row);
+  if (smem > static_cast<size_t>(dev->max_smem_optin)) {
+    return fail(DQ_ERR_UNSUPPORTED, "gemv: activation tile of %zu bytes exceeds shared memory", smem);
+  }
+  auto kernel = gemv_fast_kernel<BITS, CW, MT, R>;
+  const int tiles = static_cast<int>(ceil_div(args.rows, R));
+  const int ctas = static_cast<int>(ceil_div(tiles, kWarpsPerCta));
+  // Persistent cap: what fits on the device at once (register / smem limited).
+  const size_t per_sm_smem = 220 * 1024;
+  int per_sm = static_cast<int>(std::min<size_t>(2048 / kThreads, smem ? per_sm_smem / (smem + 1024) : 8));
+  per_sm = std::max(per_sm, 1);
+  const int grid = std::min(ctas, dev->sm_count * per_sm);
+  return launch(kernel, args, grid, smem, stream, "gemv");
+}
+
+template <int BITS, int CW>
+int32_t launch_fast_m(const GemvArgs& args, int rows_per_warp, cudaStream_t stream) {
+  const int m = args.m;
+  if (m == 1) {
+    if (CW <= 4 && rows_per_warp >= 4) return launch_fast<BITS, CW, 1, 4>(args, stream);
+    if (rows_per_warp >= 2) return launch_fast<BITS, CW, 1, 2>(args, stream);
+    return launch_fast<BITS, CW, 1, 1>(args, stream);
+  }
+  if (m == 2) {
+    if (rows_per_warp >= 2) return launch_fast<BITS, CW, 2, 2>(args, stream);
+    return launch_fast<BITS, CW, 2, 1>(args, stream);
+  }
+  if (m <= 4) {
+    if (CW <= 4 && rows_per_warp >= 2) return launch_fast<BITS, CW, 4, 2>(args, stream);
+    return launch_fast<BITS, CW, 4, 1>(args, stream);
+  }
+  return launch_fast<BITS, CW, 8, 1>(args, stream);
+}
+
+template <int BITS>
+int32_t launch_general(const GemvArgs& args, cudaStream_t stream) {
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr) return DQ_ERR_CUDA;
+  const int ctas = static_cast<int>(ceil_div(args.rows, kWarpsPerCta));
+  const int grid = std::min(ctas, dev->sm_count * 8);
+  const int m = args.m;
+  if (m == 1) return launch(gemv_general_kernel<BITS, 1>, args, grid, 0, stream, "gemv");
+  if (m == 2) return launch(gemv_general_kernel<BITS, 2>, args, grid, 0, stream, "gemv");
+  if (m <= 4) return launch(gemv_general_kernel<BITS, 4>, args, grid, 0, stream, "gemv");
+  return launch(gemv_general_kernel<BITS, 8>, args, grid, 0, stream, "gemv");
+}
+
+// Rows per warp: as many as still leave every resident warp a tile.
+int pick_rows_per_warp(int rows, const DeviceInfo& dev) {
+  const int64_t resident_warps = static_cast<int64_t>(dev.sm_count) * (2048 / kWarp) / 2;
+  if (rows >= 4 * resident_warps) return 4;
+  if (rows >= 2 * resident_warps) return 2;
+  return 1;
+}
+
+int32_t gemv_one(const void* x, int32_t x_dtype, int64_t m, const dq_weight& w, const dq_geometry& g,
+                 const void* bias, void* out, int64_t out_stride, int64_t out_col0,
+                 int32_t out_dtype, cudaStream_t stream) {
+  GemvArgs a = {};
+  a.x = x;
+  a.packed = static_cast<const uint32_t*>(w.packed);
+  a.scales = w.scales;
+  a.offsets = w.offsets;
+  a.bias = bias;
+  a.out = out;
+  a.out_stride = out_stride;
+  a.out_col0 = out_col0;
+  a.x_dtype = x_dtype;
+  a.meta_dtype = w.meta_dtype;
+  a.out_dtype = out_dtype;
+  a.m = static_cast<int>(m);
+  a.rows = static_cast<int>(w.rows);
+  a.words_per_row = g.words_per_row;
+  a.num_groups = g.num_groups;
+  a.words_per_group = g.words_per_group;
+  a.group_values = g.group_values;
+  a.in_features = g.in_features;
+
+  const int cw = fast_chunk_words(w, g, x, x_dtype);
+  if (cw == 0) {
+    switch (w.bits) {
+      case 2:
+        return launch_general<2>(a, stream);
+      case 3:
+        return launch_general<3>(a, stream);
+      case 4:
+        return launch_general<4>(a, stream);
+      default:
+        return launch_general<8>(a, stream);
+    }
+  }
+  a.chunks_per_group = g.words_per_group / cw;
+  a.chunks_per_row = g.words_per_row / cw;
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr) return DQ_ERR_CUDA;
+  const int rpw = pick_rows_per_warp(a.rows, *dev);
+  switch (w.bits) {
+    case 2:
+      return launch_fast_m<2, 4>(a, rpw, stream);
+    case 3:
+      return cw == 12 ? launch_fast_m<3, 12>(a, rpw, stream) : launch_fast_m<3, 3>(a, rpw, stream);
+    case 4:
+      return launch_fast_m<4, 4>(a, rpw, stream);
+    default:
+      return launch_fast_m<8, 4>(a, rpw, stream);
+  }
+}
+
+int32_t check_activation(const void* x, int32_t x_dtype, int64_t m, void* out, int32_t out_dtype) {
+  DQ_REQUIRE(dtype_ok(x_dtype), "gemv: unsupported activation dtype tag %d", x_dtype);
+  DQ_REQUIRE(dtype_ok(out_dtype), "gemv: unsupported output dtype tag %d", out_dtype);
+  DQ_REQUIRE(m >= 0, "gemv: x must be 2-D [rows, in_features], got %lld rows", static_cast<long long>(m));
+  DQ_REQUIRE(m <= DQ_GEMV_MAX_ROWS,
+             "gemv: %lld activation rows exceeds the kernel's limit of %d. Above this a quantized "
+             "matmul is compute-bound and the dequant + dense GEMM path is faster; dispatch there "
+             "instead.",
+             static_cast<long long>(m), DQ_GEMV_MAX_ROWS);
+  DQ_REQUIRE(m == 0 || (x != nullptr && out != nullptr), "gemv: null activation or output pointer");
+  return DQ_OK;
+}
+
+}  // namespace
+}  // namespace dq
+
+extern "C" {
+
+int32_t dq_gemv(const void* x, int32_t x_dtype, int64_t m, const dq_weight* w, void* out,
+                int32_t out_dtype, void* stream) {
+  dq_geometry g;
+  if (const int32_t rc = dq_resolve_geometry("gemv", w, &g)) return rc;
+  if (const int32_t rc = dq::check_activation(x, x_dtype, m, out, out_dtype)) return rc;
+  if (m == 0 || w->rows == 0) return DQ_OK;
+  return dq::gemv_one(x, x_dtype, m, *w, g, nullptr, out, w->rows, 0, out_dtype,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const dq_weight* shards,
+                       int32_t num_shards, const void* bias, void* out, int64_t out_stride,
+                       int32_t out_dtype, void* stream) {
+  DQ_REQUIRE(shards != nullptr && num_shards > 0, "gemv_shards: need at least one shard");
+  int64_t total = 0;
+  for (int i = 0; i < num_shards; ++i) {
+    dq_geometry g;
+    if (const int32_t rc = dq_resolve_geometry("gemv_shards", &shards[i], &g)) return rc;
+    DQ_REQUIRE(shards[i].in_features == shards[0].in_features,
+               "gemv_shards: shard %d has in_features=%lld but shard 0 has %lld", i,
+               static_cast<long long>(shards[i].in_features),
+               static_cast<long long>(shards[0].in_features));
+    total += shards[i].rows;
+  }
+  DQ_REQUIRE(out_stride >= total, "gemv_shards: out_stride=%lld is smaller than the %lld rows of the shards",
+             static_cast<long long>(out_stride), static_cast<long long>(total));
+  if (const int32_t rc = dq::check_activation(x, x_dtype, m, out, out_dtype)) return rc;
+  if (m == 0) return DQ_OK;
+  int64_t col0 = 0;
+  for (int i = 0; i < num_shards; ++i) {
+    dq_geometry g;
+    dq_resolve_geometry("gemv_shards", &shards[i], &g);
+    if (shards[i].rows > 0) {
+      const int32_t rc = dq::gemv_one(x, x_dtype, m, shards[i], g, bias, out, out_stride, col0,
+                                      out_dtype, static_cast<cudaStream_t>(stream));
+      if (rc) return rc;
+    }
+    col0 += shards[i].rows;
+  }
+  return DQ_OK;
+}
+
+int32_t dq_gemv_host(const void* x_host, int32_t x_dtype, int64_t m, const dq_weight* w,
+                     void* out_host, int32_t out_dtype, void* x_dev, void* out_dev, void* stream) {
+  dq_geometry g;
+  if (const int32_t rc = dq_resolve_geometry("gemv", w, &g)) return rc;
+  if (const int32_t rc = dq::check_activation(x_host, x_dtype, m, out_host, out_dtype)) return rc;
+  if (m == 0 || w->rows == 0) return DQ_OK;
+  DQ_REQUIRE(x_dev != nullptr && out_dev != nullptr, "gemv_host: device staging buffers are required");
+  auto s = static_cast<cudaStream_t>(stream);
+  const size_t x_bytes = static_cast<size_t>(m) * g.in_features * dq::dtype_size(x_dtype);
+  const size_t out_bytes = static_cast<size_t>(m) * w->rows * dq::dtype_size(out_dtype);
+  DQ_CUDA(cudaMemcpyAsync(x_dev, x_host, x_bytes, cudaMemcpyHostToDevice, s));
+  if (const int32_t rc = dq::gemv_one(x_dev, x_dtype, m, *w, g, nullptr, out_dev, w->rows, 0, out_dtype, s)) {
+    return rc;
+  }
+  DQ_CUDA(cudaMemcpyAsync(out_host, out_dev, out_bytes, cudaMemcpyDeviceToHost, s));
+  DQ_CUDA(cudaStreamSynchronize(s));
+  return DQ_OK;
+}
+
+}  // extern "C"

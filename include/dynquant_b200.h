@@ -1,0 +1,133 @@
+/*
+ * dynquant_b200 -- C ABI of the packed decode path for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers, sizes and a CUDA stream handle; no torch, no C++ types.
+ * Every tensor pointer is a DEVICE pointer unless the parameter name ends in
+ * `_host`.  All entry points are asynchronous on `stream` (a cudaStream_t
+ * passed as void*; NULL is the legacy default stream) except the `_host`
+ * variants, which synchronise that stream before returning.
+ *
+ * Every function that can fail returns a dq_status.  On a non-zero status
+ * dq_last_error() returns a message for the calling thread; the messages keep
+ * the wording the reference's operators raise, so callers that match on them
+ * ("exceeds the kernel's limit", "resolved positive count") keep working.
+ *
+ * "Reference" citations name files of the kambojvikram/dynquant project by
+ * their path inside that project.
+ */
+#ifndef DYNQUANT_B200_H_
+#define DYNQUANT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define DQ_API
+#else
+#define DQ_API __attribute__((visibility("default")))
+#endif
+
+/* Same numbers as packages/dynquant-kernels/csrc/include/dynquant/abi.h:23-39. */
+#define DQ_ABI_VERSION 2
+#define DQ_GROUP_SIZE_ALIGNMENT 32
+#define DQ_GEMV_MAX_ROWS 8
+/* Most tokens one expert may receive in a single dq_moe_* call. */
+#define DQ_MOE_MAX_TOKENS 64
+
+typedef enum dq_status {
+  DQ_OK = 0,
+  DQ_ERR_INVALID = 1,     /* argument / geometry check failed (reference: TORCH_CHECK) */
+  DQ_ERR_CUDA = 2,        /* a CUDA runtime call or the launch failed */
+  DQ_ERR_UNSUPPORTED = 3, /* legal input this build has no kernel for */
+  DQ_ERR_DEVICE = 4       /* a kernel reported an error through its status word */
+} dq_status;
+
+typedef enum dq_dtype { DQ_F16 = 0, DQ_BF16 = 1, DQ_F32 = 2 } dq_dtype;
+
+/*
+ * One packed tensor: the (packed, scales, offsets, bits, group_values,
+ * in_features) tuple the reference passes to every operator
+ * (packages/dynquant-kernels/csrc/bindings.cpp:204-214), plus the shapes that
+ * at::Tensor carries implicitly there.
+ *
+ *   packed   int32 [rows, words_per_row], row-major, bit patterns unsigned
+ *   scales   [rows, num_groups] in meta_dtype
+ *   offsets  same shape and dtype, or NULL meaning zero
+ *   group_values  resolved values per group, never the -1 per-row sentinel
+ *   in_features   unpadded reduction length
+ */
+typedef struct dq_weight {
+  const void* packed;
+  const void* scales;
+  const void* offsets;
+  int64_t rows;
+  int64_t words_per_row;
+  int64_t num_groups;
+  int64_t group_values;
+  int64_t in_features;
+  int32_t bits;
+  int32_t meta_dtype; /* dq_dtype */
+} dq_weight;
+
+/* Derived sizes; mirrors nbit::RowGeometry,
+ * packages/dynquant-kernels/csrc/include/dynquant/geometry.h:47-57. */
+typedef struct dq_geometry {
+  int32_t group_values;
+  int32_t num_groups;
+  int32_t words_per_group;
+  int32_t words_per_row;
+  int32_t in_features;
+  int32_t blocks_per_group;
+  int32_t blocks_per_row;
+} dq_geometry;
+
+/* ---- metadata (reference: bindings.cpp:188-197 abi_version, built_with_cuda,
+ *      compiled_architectures, gemv_max_rows) -------------------------------- */
+DQ_API int32_t dq_abi_version(void);
+DQ_API int32_t dq_built_with_cuda(void);
+DQ_API const char* dq_compiled_architectures(void);
+DQ_API int32_t dq_gemv_max_rows(void);
+DQ_API int32_t dq_moe_max_tokens(void);
+DQ_API const char* dq_last_error(void);
+
+/* ---- geometry (reference: resolve_geometry, geometry.h:63-132) -------------
+ * Host-only validation; reads no device memory.  `op` prefixes the message. */
+DQ_API int32_t dq_resolve_geometry(const char* op, const dq_weight* w, dq_geometry* out);
+
+/* ---- dequant (reference: dequant_cuda, csrc/quant/dequant.cu:130-165) ------
+ * out [rows, in_features] in out_dtype.  The reference writes the scales
+ * dtype; any dq_dtype is accepted here.  w = float(q)*scale, then + offset,
+ * in fp32, one rounding to out_dtype. */
+DQ_API int32_t dq_dequant(const dq_weight* w, void* out, int32_t out_dtype, void* stream);
+
+/* ---- gemv (reference: gemv_cuda, csrc/gemv/gemv.cu:695-756) ----------------
+ * x [m, in_features] in x_dtype, contiguous, m <= DQ_GEMV_MAX_ROWS.
+ * out [m, rows] in out_dtype (the reference writes x's dtype; DQ_F32 gives the
+ * unrounded fp32 accumulators).  x_dtype may differ from w->meta_dtype.
+ * fp32 accumulation, fixed summation order: bit-identical run to run. */
+DQ_API int32_t dq_gemv(const void* x, int32_t x_dtype, int64_t m, const dq_weight* w, void* out,
+                       int32_t out_dtype, void* stream);
+
+/* Several shards of one fused layer in one launch (replaces the per-shard loop
+ * plus concat of integration/vllm_plugin/linear.py:172-186 and
+ * integration/serving_common/fuse.py:41-53).  Shard i writes columns
+ * [sum(rows[0..i)), +rows[i]) of out [m, out_stride]; every shard shares x and
+ * in_features.  bias [sum rows] in out_dtype or NULL. */
+DQ_API int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const dq_weight* shards,
+                              int32_t num_shards, const void* bias, void* out, int64_t out_stride,
+                              int32_t out_dtype, void* stream);
+
+/* Same as dq_gemv with x and out in HOST memory: copies x to the device,
+ * launches, copies the result back and synchronises.  `x_dev` / `out_dev` are
+ * caller-provided device staging buffers of at least the same sizes. */
+DQ_API int32_t dq_gemv_host(const void* x_host, int32_t x_dtype, int64_t m, const dq_weight* w,
+                            void* out_host, int32_t out_dtype, void* x_dev, void* out_dev,
+                            void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DYNQUANT_B200_H_ */
