@@ -51,6 +51,22 @@ class Geometry(ctypes.Structure):
     ]
 
 
+class GemvJob(ctypes.Structure):
+    """``dq_gemv_job``."""
+
+    _fields_ = [
+        ("x", ctypes.c_void_p),
+        ("out", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p),
+        ("m", ctypes.c_int64),
+        ("out_stride", ctypes.c_int64),
+        ("out_col0", ctypes.c_int64),
+        ("x_dtype", ctypes.c_int32),
+        ("out_dtype", ctypes.c_int32),
+        ("weight", Weight),
+    ]
+
+
 class MoeBank(ctypes.Structure):
     """``dq_moe_bank``: a stacked expert tensor folded to rows."""
 
@@ -74,6 +90,7 @@ SIGNATURES = {
     "dq_dequant": (_I32, [_WP, _P, _I32, _P]),
     "dq_gemv": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P]),
     "dq_gemv_shards": (_I32, [_P, _I32, _I64, _WP, _I32, _P, _P, _I64, _I32, _P]),
+    "dq_gemv_sequence": (_I32, [ctypes.POINTER(GemvJob), _I32, _P]),
     "dq_gemv_host": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P, _P, _P]),
 }
 

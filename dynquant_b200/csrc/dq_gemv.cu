@@ -572,6 +572,30 @@ int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const dq_weigh
   return DQ_OK;
 }
 
+int32_t dq_gemv_sequence(const dq_gemv_job* jobs, int32_t num_jobs, void* stream) {
+  DQ_REQUIRE(num_jobs >= 0 && (jobs != nullptr || num_jobs == 0), "gemv_sequence: null job list");
+  for (int i = 0; i < num_jobs; ++i) {
+    const dq_gemv_job& j = jobs[i];
+    dq_geometry g;
+    if (const int32_t rc = dq_resolve_geometry("gemv_sequence", &j.weight, &g)) return rc;
+    if (const int32_t rc = dq::check_activation(j.x, j.x_dtype, j.m, j.out, j.out_dtype)) return rc;
+    DQ_REQUIRE(j.out_col0 >= 0 && j.out_stride >= j.out_col0 + j.weight.rows,
+               "gemv_sequence: job %d writes columns [%lld, %lld) of a row of %lld", i,
+               static_cast<long long>(j.out_col0), static_cast<long long>(j.out_col0 + j.weight.rows),
+               static_cast<long long>(j.out_stride));
+  }
+  for (int i = 0; i < num_jobs; ++i) {
+    const dq_gemv_job& j = jobs[i];
+    if (j.m == 0 || j.weight.rows == 0) continue;
+    dq_geometry g;
+    dq_resolve_geometry("gemv_sequence", &j.weight, &g);
+    const int32_t rc = dq::gemv_one(j.x, j.x_dtype, j.m, j.weight, g, j.bias, j.out, j.out_stride,
+                                    j.out_col0, j.out_dtype, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+  }
+  return DQ_OK;
+}
+
 int32_t dq_gemv_host(const void* x_host, int32_t x_dtype, int64_t m, const dq_weight* w,
                      void* out_host, int32_t out_dtype, void* x_dev, void* out_dev, void* stream) {
   dq_geometry g;

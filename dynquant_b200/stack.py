@@ -1,0 +1,87 @@
+"""Run every packed linear module of a decode step from one host call.
+
+The reference runtime issues one Python ``quantized_matmul`` per module per
+step (``packages/dynquant-core/src/dynquant/runtime/linear.py:211-212`` ->
+``runtime/ops.py:184-231``) and measures 20-45 us of host time per module
+around single-digit-microsecond kernels.  ``StepRunner`` keeps the same
+per-module semantics -- module ``i`` computes ``x_i @ W_i.T`` into its own
+output buffer, in stream order -- but builds the launch list once and replays
+it with a single ``dq_gemv_sequence`` call, optionally from a captured CUDA
+graph.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from .ops import _stream, _tag, weight_descriptor
+from .workloads import LinearStack
+
+
+class StepRunner:
+    """Pre-built launch list for one decode step over a :class:`LinearStack`.
+
+    ``inputs`` maps an activation name (``"hidden"``, ``"attn"``, ``"inter"``)
+    to a resident ``[m, K]`` tensor; every module writes ``outputs[name]``.
+    """
+
+    def __init__(self, stack: LinearStack, m: int, *, act_dtype=torch.bfloat16, out_dtype=None, device="cuda"):
+        self.stack = stack
+        self.m = m
+        self.device = torch.device(device)
+        out_dtype = out_dtype or act_dtype
+        widths = {}
+        for mod in stack.modules:
+            widths.setdefault(mod.input, mod.weight.in_features)
+            if widths[mod.input] != mod.weight.in_features:
+                raise ValueError(f"{mod.name}: activation {mod.input!r} has two widths")
+        gen = torch.Generator(device=self.device).manual_seed(1234)
+        self.inputs = {
+            name: torch.randn(m, k, device=self.device, generator=gen).to(act_dtype) for name, k in widths.items()
+        }
+        self.outputs = {
+            mod.name: torch.empty(m, mod.weight.num_rows, dtype=out_dtype, device=self.device)
+            for mod in stack.modules
+        }
+        self._jobs = (_lib.GemvJob * len(stack.modules))()
+        for i, mod in enumerate(stack.modules):
+            qt = mod.weight
+            x = self.inputs[mod.input]
+            out = self.outputs[mod.name]
+            job = self._jobs[i]
+            job.x = x.data_ptr()
+            job.out = out.data_ptr()
+            job.bias = None
+            job.m = m
+            job.out_stride = qt.num_rows
+            job.out_col0 = 0
+            job.x_dtype = _tag(act_dtype, "x")
+            job.out_dtype = _tag(out_dtype, "out")
+            job.weight = weight_descriptor(
+                "gemv_sequence", qt.packed, qt.scales, qt.offsets, qt.bits, qt.geometry.effective_group, qt.in_features
+            )
+        self._graph: torch.cuda.CUDAGraph | None = None
+        self.launches_per_step = len(stack.modules)
+
+    def run(self) -> None:
+        """Enqueue the whole step on torch's current stream."""
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.dq_gemv_sequence(self._jobs, len(self._jobs), _stream(self.device)))
+
+    def capture(self) -> None:
+        """Record the step into a CUDA graph (programmatic-dependency edges included)."""
+        self.run()  # warm: sets per-kernel attributes outside the capture
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.run()
+        self._graph = graph
+
+    def replay(self) -> None:
+        if self._graph is None:
+            raise RuntimeError("capture() first")
+        self._graph.replay()

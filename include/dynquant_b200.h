@@ -111,7 +111,7 @@ DQ_API int32_t dq_dequant(const dq_weight* w, void* out, int32_t out_dtype, void
 DQ_API int32_t dq_gemv(const void* x, int32_t x_dtype, int64_t m, const dq_weight* w, void* out,
                        int32_t out_dtype, void* stream);
 
-/* Several shards of one fused layer in one launch (replaces the per-shard loop
+/* Several shards of one fused layer from one call (replaces the per-shard loop
  * plus concat of integration/vllm_plugin/linear.py:172-186 and
  * integration/serving_common/fuse.py:41-53).  Shard i writes columns
  * [sum(rows[0..i)), +rows[i]) of out [m, out_stride]; every shard shares x and
@@ -119,6 +119,29 @@ DQ_API int32_t dq_gemv(const void* x, int32_t x_dtype, int64_t m, const dq_weigh
 DQ_API int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const dq_weight* shards,
                               int32_t num_shards, const void* bias, void* out, int64_t out_stride,
                               int32_t out_dtype, void* stream);
+
+/* One GEMV of a sequence; see dq_gemv_sequence. */
+typedef struct dq_gemv_job {
+  const void* x;    /* [m, weight.in_features] in x_dtype */
+  void* out;        /* [m, out_stride] in out_dtype; this job writes columns [out_col0, +rows) */
+  const void* bias; /* [>= out_col0 + rows] in out_dtype, indexed by output column, or NULL */
+  int64_t m;
+  int64_t out_stride;
+  int64_t out_col0;
+  int32_t x_dtype;
+  int32_t out_dtype;
+  dq_weight weight;
+} dq_gemv_job;
+
+/* Launch `num_jobs` GEMVs back to back on `stream`, in order, from one host
+ * call: what one decode step of a model does through the reference runtime's
+ * per-module quantized_matmul calls
+ * (packages/dynquant-core/src/dynquant/runtime/ops.py:184-231), without a
+ * host round trip per module.  Every launch carries the programmatic
+ * dependent-launch attribute, so job i+1 streams its first weights while job
+ * i drains and reads its activation only after job i has completed.  All jobs
+ * are validated before the first launch. */
+DQ_API int32_t dq_gemv_sequence(const dq_gemv_job* jobs, int32_t num_jobs, void* stream);
 
 /* Same as dq_gemv with x and out in HOST memory: copies x to the device,
  * launches, copies the result back and synchronises.  `x_dev` / `out_dev` are
