@@ -30,28 +30,13 @@
 #include <cstdlib>
 
 #include "dq_decode.cuh"
+#include "dq_gemv.cuh"
 
 namespace dq {
 namespace {
 
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * kWarp;
-
-struct GemvArgs {
-  const void* x;
-  const uint32_t* packed;
-  const void* scales;
-  const void* offsets;  // may be null
-  const void* bias;     // may be null; [rows] in out_dtype, indexed from out_col0
-  void* out;
-  int64_t out_stride;  // elements between consecutive activation rows of out
-  int64_t out_col0;    // first output column this weight writes
-  int x_dtype, meta_dtype, out_dtype;
-  int m;     // real activation rows
-  int rows;  // output features of this weight
-  int words_per_row, num_groups, words_per_group, group_values, in_features;
-  int chunks_per_row, chunks_per_group;  // fast path only
-};
 
 template <int BITS, int CW>
 struct ChunkCfg {
@@ -80,14 +65,6 @@ __device__ __forceinline__ void load_chunk(const uint32_t* __restrict__ src, uin
       w[i] = ldg_stream_32(src + i);
     }
   }
-}
-
-__device__ __forceinline__ void store_out(const GemvArgs& a, int m, int row, float v) {
-  const int64_t col = a.out_col0 + row;
-  if (a.bias != nullptr) {
-    v += load_f32(a.bias, col, a.out_dtype);
-  }
-  store_f32(a.out, static_cast<int64_t>(m) * a.out_stride + col, a.out_dtype, v);
 }
 
 // ---------------------------------------------------------------------------
@@ -482,6 +459,9 @@ int32_t gemv_one(const void* x, int32_t x_dtype, int64_t m, const dq_weight& w, 
   a.group_values = g.group_values;
   a.in_features = g.in_features;
 
+  if (!force_general() && mma_path_supports(a, w.bits)) {
+    return launch_gemv_mma(a, w.bits, stream);
+  }
   const int cw = fast_chunk_words(w, g, x, x_dtype);
   if (cw == 0) {
     switch (w.bits) {

@@ -1,0 +1,41 @@
+// Argument block and output store shared by the GEMV kernels.
+#pragma once
+
+#include "dq_common.cuh"
+
+namespace dq {
+
+struct GemvArgs {
+  const void* x;
+  const uint32_t* packed;
+  const void* scales;
+  const void* offsets;  // may be null
+  const void* bias;     // may be null; [rows] in out_dtype, indexed from out_col0
+  void* out;
+  int64_t out_stride;  // elements between consecutive activation rows of out
+  int64_t out_col0;    // first output column this weight writes
+  int x_dtype, meta_dtype, out_dtype;
+  int m;     // real activation rows
+  int rows;  // output features of this weight
+  int words_per_row, num_groups, words_per_group, group_values, in_features;
+  int chunks_per_row, chunks_per_group;  // fast path only
+};
+
+// Tensor-core path (dq_gemv_mma.cu).  Returns DQ_ERR_UNSUPPORTED without touching
+// the error buffer when the geometry or dtype is not one it handles, so the
+// caller can fall through to the SIMT kernels.
+bool mma_path_supports(const GemvArgs& a, int bits);
+int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream);
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void store_out(const GemvArgs& a, int m, int row, float v) {
+  const int64_t col = a.out_col0 + row;
+  if (a.bias != nullptr) {
+    v += load_f32(a.bias, col, a.out_dtype);
+  }
+  store_f32(a.out, static_cast<int64_t>(m) * a.out_stride + col, a.out_dtype, v);
+}
+
+#endif
+
+}  // namespace dq

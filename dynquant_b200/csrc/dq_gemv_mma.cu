@@ -1,0 +1,620 @@
+// Packed decode GEMV on the tensor cores, M = 1..8 activation rows at one price.
+//
+// Same operator as dq_gemv.cu (reference: gemv_cuda,
+// packages/dynquant-kernels/csrc/gemv/gemv.cu:695-756) for 16-bit activations
+// and groups that are a multiple of 128 values.  The SIMT kernel spends about
+// two instructions per weight VALUE (one logic op, half a packed add, half a
+// packed FMA per activation row), which at 2 and 3 bits per value is more
+// instruction issue than the memory system needs time to deliver the bytes;
+// the measured ceiling is in profiles/.  Here a weight value costs 0.6-0.9
+// integer instructions and 1/8 of an mma, whatever M is:
+//
+//   * out tile = 16 weight rows x 8 activation rows = one m16n8k16 accumulator.
+//     The 8 columns are exactly the operator's row limit (DQ_GEMV_MAX_ROWS).
+//   * a thread streams two weight rows (g and g+8 of the tile) and, per step of
+//     128 reduction values (one quantization group, or a 128-value slice of a
+//     larger one), decodes its 32-value unit of each row straight into A
+//     fragments (dq_mma_plan.cuh).  B fragments -- the activation, pre-scaled
+//     and pre-permuted to match -- come from shared memory, staged once per CTA.
+//   * one accumulator covers one step, so the per-(row, group) scale and offset
+//     are applied to it in fp32 right after the step's mmas:
+//         acc += s * (D - MAGIC * sum x')  +  o * sum x
+//   * rows are split over warps, and for short matrices the reduction axis is
+//     split over the warps of a CTA too (summed in a fixed order through shared
+//     memory: results are bit-identical run to run).
+//   * weight words and raw scale/offset bits are loaded a block of steps ahead and
+//     only converted when used, so a warp never stalls on a load it just issued.
+//     The first loads go out BEFORE griddepcontrol.wait: under programmatic
+//     dependent launch the next layer's weights start streaming while the
+//     previous layer is still finishing, and only the activation staging waits.
+//
+// A zero pad past in_features needs no special case: the staged activation is
+// zero there (reference docs/format-spec.md:205-214).
+#include <algorithm>
+#include <cstdlib>
+
+#include "dq_gemv.cuh"
+#include "dq_gemv_mma_stream.cuh"
+#include "dq_mma_plan.cuh"
+#include "dq_mma_stage.cuh"
+
+namespace dq {
+namespace {
+
+constexpr int kStepValues = 128;
+constexpr int kTileRows = 16;
+constexpr int kMaxWarps = 16;
+
+struct MmaParams {
+  int steps;            // padded K / 128
+  int steps_per_group;  // group_values / 128
+  int tiles;            // ceil(rows / 16)
+  int rw, kw;           // warps of a CTA: rw row tiles x kw slices of the reduction axis
+  int steps_per_warp;   // steps of one slice
+  int m_stride_u4;      // uint4 per activation row in the staged B buffer
+  int vec_meta;         // scales/offsets of a whole block of steps may be read with one vector load
+  uint32_t magic;       // 16-bit magic constant in both halves; a parameter so it stays a register operand
+};
+
+template <int BITS>
+struct Depth {
+  static constexpr int value = BITS == 8 ? 2 : 4;  // steps kept in flight per warp
+};
+
+template <int BITS>
+__device__ __forceinline__ void load_unit(const uint32_t* __restrict__ src, uint32_t* w) {
+  if constexpr (BITS == 2) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(src));
+    w[0] = v.x;
+    w[1] = v.y;
+  } else if constexpr (BITS == 3) {
+    // 12 bytes at a 12-byte stride: three 32-bit loads, kept in L1 so the sector a
+    // neighbouring step shares is fetched from L2 once.
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(w[i]) : "l"(src + i));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < BITS / 4; ++i) {
+      const uint4 v = ldg_stream_128(src + 4 * i);
+      w[4 * i + 0] = v.x;
+      w[4 * i + 1] = v.y;
+      w[4 * i + 2] = v.z;
+      w[4 * i + 3] = v.w;
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t ld_u16(const unsigned short* p) {
+  unsigned short v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ld_u64(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+// Element j (0 or 1) of a register holding two 16-bit floats, widened to fp32.
+template <bool BF16>
+__device__ __forceinline__ float half_of(uint32_t reg, int j) {
+  if constexpr (BF16) {
+    return __uint_as_float(j ? (reg & 0xFFFF0000u) : (reg << 16));
+  } else {
+    const __half2 h = *reinterpret_cast<const __half2*>(&reg);
+    return j ? __high2float(h) : __low2float(h);
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t to_raw16(float v) {
+  if constexpr (BF16) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  } else {
+    return __half_as_ushort(__float2half_rn(v));
+  }
+}
+
+// Where one 16-row tile's data starts for this lane.
+struct TilePtr {
+  const uint32_t* wa;  // row g   : words of this lane's unit at step 0
+  const uint32_t* wb;  // row g+8
+  int64_t ma, mb;      // element index of (row, group 0) in scales / offsets
+};
+
+template <int BITS, bool XBF16, bool MBF16>
+__global__ void __launch_bounds__(kMaxWarps* kWarp)
+    gemv_mma_kernel(const GemvArgs a, const MmaParams p) {
+  using Plan = MmaPlan<BITS>;
+  constexpr int P = Depth<BITS>::value;
+  constexpr int NA = Plan::kARegs;
+  constexpr int QU = NA / 4;          // uint4 of B fragments per (step, lane)
+  constexpr int STEP_WORDS = 4 * BITS;  // words one step occupies in a row
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* xb = reinterpret_cast<uint4*>(smem_raw);
+  float* xsum = reinterpret_cast<float*>(xb + a.m * p.m_stride_u4 + QU * 4);  // [steps][8]  sum of x
+  float* xneg = xsum + p.steps * 8;                                  // [steps][8]  -MAGIC * sum of x'
+  float* red = xneg + p.steps * 8;                                   // [kw][rw][16][8]
+
+  const int lane = threadIdx.x & (kWarp - 1);
+  const int warp = threadIdx.x >> 5;
+  const int nthreads = blockDim.x;
+  const int g = lane >> 2;  // row of the tile; also the activation row this lane feeds into B
+  const int t = lane & 3;   // which 32-value unit of a step
+  const int rwi = warp / p.kw;
+  const int kwi = warp - rwi * p.kw;
+  constexpr float kMagicValue = XBF16 ? 128.0f : 1024.0f;
+  const uint32_t magic = p.magic;
+
+  const int s_begin = kwi * p.steps_per_warp;
+  const int s_end = min(p.steps, s_begin + p.steps_per_warp);
+  const int nsteps = max(0, s_end - s_begin);
+  const int tile_stride = gridDim.x * p.rw;
+  const bool has_off = a.offsets != nullptr;
+  const unsigned short* scales16 = reinterpret_cast<const unsigned short*>(a.scales);
+  const unsigned short* offsets16 = reinterpret_cast<const unsigned short*>(a.offsets);
+
+  auto tile_ptr = [&](int tile) {
+    TilePtr tp;
+    const int ra = min(tile * kTileRows + g, a.rows - 1);
+    const int rb = min(tile * kTileRows + g + 8, a.rows - 1);
+    tp.wa = a.packed + static_cast<int64_t>(ra) * a.words_per_row + s_begin * STEP_WORDS + t * BITS;
+    tp.wb = a.packed + static_cast<int64_t>(rb) * a.words_per_row + s_begin * STEP_WORDS + t * BITS;
+    tp.ma = static_cast<int64_t>(ra) * a.num_groups;
+    tp.mb = static_cast<int64_t>(rb) * a.num_groups;
+    return tp;
+  };
+
+  pdl_launch_dependents();
+
+  // ---- prefetch state ----
+  uint32_t raw[P][2][BITS];      // weight words, one slot per step of a block
+  uint32_t mcur[4][P / 2];       // scale_a, offset_a, scale_b, offset_b of the current block (2 x 16 bit / reg)
+  uint32_t mnext[4][P / 2];      // ... of the block after it
+
+  // Weight words of relative step `rs` (counted from s_begin) of a tile into a slot.
+  auto load_weights = [&](const TilePtr& tp, int slot, int rs) {
+    load_unit<BITS>(tp.wa + rs * STEP_WORDS, raw[slot][0]);
+    load_unit<BITS>(tp.wb + rs * STEP_WORDS, raw[slot][1]);
+  };
+  // Scales/offsets of the P steps starting at relative step rs0 (`valid` of them exist).
+  auto load_meta = [&](const TilePtr& tp, int rs0, int valid, uint32_t (&dst)[4][P / 2]) {
+    const int s0 = s_begin + rs0;
+    if (p.vec_meta && valid == P) {
+      // one group per step, block-aligned: P consecutive 16-bit values per array
+      const int64_t ia = tp.ma + s0, ib = tp.mb + s0;
+      if constexpr (P == 4) {
+        const uint2 sa = ld_u64(scales16 + ia), sb = ld_u64(scales16 + ib);
+        dst[0][0] = sa.x, dst[0][1] = sa.y, dst[2][0] = sb.x, dst[2][1] = sb.y;
+        if (has_off) {
+          const uint2 oa = ld_u64(offsets16 + ia), ob = ld_u64(offsets16 + ib);
+          dst[1][0] = oa.x, dst[1][1] = oa.y, dst[3][0] = ob.x, dst[3][1] = ob.y;
+        }
+      } else {
+        dst[0][0] = ld_u32(scales16 + ia), dst[2][0] = ld_u32(scales16 + ib);
+        if (has_off) {
+          dst[1][0] = ld_u32(offsets16 + ia), dst[3][0] = ld_u32(offsets16 + ib);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+        if (j < valid) {
+          const int grp = (s0 + j) / p.steps_per_group;
+          const uint32_t sa = ld_u16(scales16 + tp.ma + grp), sb = ld_u16(scales16 + tp.mb + grp);
+          const uint32_t oa = has_off ? ld_u16(offsets16 + tp.ma + grp) : 0u;
+          const uint32_t ob = has_off ? ld_u16(offsets16 + tp.mb + grp) : 0u;
+          if (j & 1) {
+            dst[0][j / 2] |= sa << 16, dst[1][j / 2] |= oa << 16;
+            dst[2][j / 2] |= sb << 16, dst[3][j / 2] |= ob << 16;
+          } else {
+            dst[0][j / 2] = sa, dst[1][j / 2] = oa, dst[2][j / 2] = sb, dst[3][j / 2] = ob;
+          }
+        }
+      }
+    }
+  };
+
+  int tile = blockIdx.x * p.rw + rwi;
+  TilePtr cur = tile_ptr(min(tile, p.tiles - 1));
+  const bool any_work = tile < p.tiles && nsteps > 0;
+  if (any_work) {
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      if (i < nsteps) load_weights(cur, i, i);
+    }
+    load_meta(cur, 0, min(P, nsteps), mcur);
+  }
+
+  // ---- stage the activation: the only part that depends on the previous kernel ----
+  pdl_wait_prior_grid();
+  stage_activation<BITS, XBF16>(a, p.steps, p.m_stride_u4, xb, xsum, xneg, threadIdx.x, nthreads);
+  __syncthreads();
+
+  // ---- main loop: persistent over row tiles when the reduction axis is not sliced ----
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // (row g; m=2t, 2t+1), (row g+8; m=2t, 2t+1)
+  const bool b_live = g < a.m;
+  // Lanes whose activation row does not exist read a block of zeros, with a zero step stride.
+  const uint4* xb_lane = b_live ? xb + g * p.m_stride_u4 + t : xb + a.m * p.m_stride_u4;
+  const int xb_step_u4 = b_live ? QU * 4 : 0;
+  const int nblocks = (nsteps + P - 1) / P;
+
+  auto store_tile = [&](int tl, const float* v) {
+    const int row_a = tl * kTileRows + g, row_b = row_a + 8;
+    const int m0 = 2 * t;
+    if (m0 < a.m) {
+      if (row_a < a.rows) store_out(a, m0, row_a, v[0]);
+      if (row_b < a.rows) store_out(a, m0, row_b, v[2]);
+    }
+    if (m0 + 1 < a.m) {
+      if (row_a < a.rows) store_out(a, m0 + 1, row_a, v[1]);
+      if (row_b < a.rows) store_out(a, m0 + 1, row_b, v[3]);
+    }
+  };
+
+  // The mmas of one step and the affine map of its group:
+  //   acc += scale * (D - MAGIC * sum x') + offset * sum x      (scalar FMAs: that pipe is idle)
+  auto finish_step = [&](const uint32_t* aa, const uint32_t* ab, int s, int slot,
+                         const uint32_t (&mc)[4][P / 2]) {
+    const uint4* bsrc = xb_lane + s * xb_step_u4;
+    float d[4];
+#pragma unroll
+    for (int q = 0; q < QU; ++q) {
+      const uint4 b = bsrc[q * 4];
+      if (q == 0) {
+        mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
+      } else {
+        mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
+      }
+      mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
+    }
+    const float2 xs2 = *reinterpret_cast<const float2*>(xsum + s * 8 + 2 * t);
+    const float2 xn2 = *reinterpret_cast<const float2*>(xneg + s * 8 + 2 * t);
+    const float sc_a = half_of<MBF16>(mc[0][slot / 2], slot & 1);
+    const float sc_b = half_of<MBF16>(mc[2][slot / 2], slot & 1);
+    acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
+    acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
+    acc[2] = fmaf(sc_b, d[2] + xn2.x, acc[2]);
+    acc[3] = fmaf(sc_b, d[3] + xn2.y, acc[3]);
+    if (has_off) {
+      const float of_a = half_of<MBF16>(mc[1][slot / 2], slot & 1);
+      const float of_b = half_of<MBF16>(mc[3][slot / 2], slot & 1);
+      acc[0] = fmaf(of_a, xs2.x, acc[0]);
+      acc[1] = fmaf(of_a, xs2.y, acc[1]);
+      acc[2] = fmaf(of_b, xs2.x, acc[2]);
+      acc[3] = fmaf(of_b, xs2.y, acc[3]);
+    }
+  };
+
+  if (any_work) {
+    const bool fast = p.vec_meta && (nsteps % P) == 0;
+    while (true) {
+      const int next_tile = tile + tile_stride;
+      const bool has_next = p.kw == 1 && next_tile < p.tiles;
+      const TilePtr nxt = tile_ptr(has_next ? next_tile : tile);
+
+      if (fast) {
+        // Every block is full and block-aligned: no predicates, vector metadata loads, and the
+        // refill of a slot is always a real load (of this tile's next block, the next tile's
+        // first block, or -- at the very end -- a harmless re-read of this tile's first block).
+        for (int blk = 0; blk < nblocks; ++blk) {
+          const int rs0 = blk * P;
+          const bool last_blk = blk + 1 == nblocks;
+          const uint32_t* wa_n = last_blk ? nxt.wa : cur.wa + (rs0 + P) * STEP_WORDS;
+          const uint32_t* wb_n = last_blk ? nxt.wb : cur.wb + (rs0 + P) * STEP_WORDS;
+          TilePtr mp = last_blk ? nxt : cur;
+          load_meta(mp, last_blk ? 0 : rs0 + P, P, mnext);
+#pragma unroll
+          for (int slot = 0; slot < P; ++slot) {
+            uint32_t aa[NA], ab[NA];
+            decode_unit<BITS>(raw[slot][0], magic, aa);
+            decode_unit<BITS>(raw[slot][1], magic, ab);
+            load_unit<BITS>(wa_n + slot * STEP_WORDS, raw[slot][0]);
+            load_unit<BITS>(wb_n + slot * STEP_WORDS, raw[slot][1]);
+            finish_step(aa, ab, s_begin + rs0 + slot, slot, mcur);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int j = 0; j < P / 2; ++j) {
+              mcur[i][j] = mnext[i][j];
+            }
+          }
+        }
+      } else {
+        for (int blk = 0; blk < nblocks; ++blk) {
+          const int rs0 = blk * P;
+          const int valid = min(P, nsteps - rs0);
+          const bool last_blk = blk + 1 == nblocks;
+          if (!last_blk) {
+            load_meta(cur, rs0 + P, min(P, nsteps - rs0 - P), mnext);
+          } else if (has_next) {
+            load_meta(nxt, 0, min(P, nsteps), mnext);
+          }
+#pragma unroll
+          for (int slot = 0; slot < P; ++slot) {
+            if (slot < valid) {
+              uint32_t aa[NA], ab[NA];
+              decode_unit<BITS>(raw[slot][0], magic, aa);
+              decode_unit<BITS>(raw[slot][1], magic, ab);
+              // Refill this slot: P steps ahead in this tile, or the next tile's first block.
+              const int rs_next = rs0 + slot + P;
+              if (rs_next < nsteps) {
+                load_weights(cur, slot, rs_next);
+              } else if (last_blk && has_next) {
+                load_weights(nxt, slot, slot);
+              }
+              finish_step(aa, ab, s_begin + rs0 + slot, slot, mcur);
+            } else if (last_blk && has_next && slot < nsteps) {
+              load_weights(nxt, slot, slot);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int j = 0; j < P / 2; ++j) {
+              mcur[i][j] = mnext[i][j];
+            }
+          }
+        }
+      }
+
+      if (p.kw > 1) {
+        break;  // one tile per warp group; the slices are summed below
+      }
+      store_tile(tile, acc);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i] = 0.0f;
+      }
+      if (!has_next) {
+        break;
+      }
+      tile = next_tile;
+      cur = nxt;
+    }
+  }
+
+  // ---- sliced reduction axis: sum the slices in a fixed order and store ----
+  if (p.kw > 1) {
+    float* mine = red + ((kwi * p.rw + rwi) * kTileRows) * 8;
+    *reinterpret_cast<float2*>(mine + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
+    *reinterpret_cast<float2*>(mine + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
+    __syncthreads();
+    if (kwi == 0 && tile < p.tiles) {
+      float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      for (int k = 0; k < p.kw; ++k) {
+        const float* part = red + ((k * p.rw + rwi) * kTileRows) * 8;
+        const float2 pa = *reinterpret_cast<const float2*>(part + g * 8 + 2 * t);
+        const float2 pb = *reinterpret_cast<const float2*>(part + (g + 8) * 8 + 2 * t);
+        v[0] += pa.x, v[1] += pa.y, v[2] += pb.x, v[3] += pb.y;
+      }
+      store_tile(tile, v);
+    }
+  }
+}
+
+int floor_pow2(int v) {
+  int p = 1;
+  while (2 * p <= v) p *= 2;
+  return p;
+}
+
+bool mma_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("DQ_B200_GEMV_PATH");
+    return !(v != nullptr && v[0] == 's');  // "simt" forces the SIMT kernels
+  }();
+  return on;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("DQ_B200_NO_PDL");
+    return !(v != nullptr && v[0] != '\0' && v[0] != '0');
+  }();
+  return on;
+}
+
+size_t mma_smem_bytes(int m, int steps, int aregs, int rw, int kw, int* m_stride_u4) {
+  const int stride = steps * aregs + 4;  // +4 uint4: consecutive activation rows land 64 B apart mod 128
+  *m_stride_u4 = stride;
+  size_t bytes = (static_cast<size_t>(m) * stride + aregs) * 16;  // + the zero block
+  bytes += static_cast<size_t>(steps) * 8 * 4 * 2;
+  if (kw > 1) bytes += static_cast<size_t>(kw) * rw * kTileRows * 8 * 4;
+  return bytes;
+}
+
+template <typename Kernel>
+int32_t launch_mma_kernel(Kernel kernel, const GemvArgs& a, MmaParams p, int threads, size_t smem,
+                          const DeviceInfo& dev, cudaStream_t stream) {
+  if (smem > 48 * 1024) {
+    DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  }
+  int grid = static_cast<int>(ceil_div(p.tiles, p.rw));
+  if (p.kw == 1) {
+    // persistent: no more CTAs than the device holds at once; warps stride over the tiles
+    int per_sm = 0;
+    DQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem));
+    grid = std::min(grid, std::max(1, per_sm) * dev.sm_count);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(static_cast<unsigned>(threads));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
+  DQ_CHECK_LAUNCH("gemv");
+  return DQ_OK;
+}
+
+template <int BITS>
+int32_t launch_mma_bits(const GemvArgs& a, const MmaParams& p, int threads, size_t smem,
+                        const DeviceInfo& dev, cudaStream_t stream) {
+  const bool xbf = a.x_dtype == DQ_BF16;
+  const bool mbf = a.meta_dtype == DQ_BF16;
+  if (xbf && mbf) return launch_mma_kernel(gemv_mma_kernel<BITS, true, true>, a, p, threads, smem, dev, stream);
+  if (xbf) return launch_mma_kernel(gemv_mma_kernel<BITS, true, false>, a, p, threads, smem, dev, stream);
+  if (mbf) return launch_mma_kernel(gemv_mma_kernel<BITS, false, true>, a, p, threads, smem, dev, stream);
+  return launch_mma_kernel(gemv_mma_kernel<BITS, false, false>, a, p, threads, smem, dev, stream);
+}
+
+// ---- streaming kernel (dq_gemv_mma_stream.cuh) ----
+
+template <int BITS>
+bool stream_ok(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps) {
+  using C = stream::Cfg<BITS>;
+  static const bool off = [] {
+    const char* v = std::getenv("DQ_B200_NO_STREAM");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  if (off) return false;
+  if (a.group_values != kStepValues || steps % C::P != 0 || a.num_groups % C::P != 0) return false;
+  if (tiles < dev.sm_count * stream::kWarps) return false;
+  const auto align = static_cast<uintptr_t>(C::META_BYTES);
+  if (reinterpret_cast<uintptr_t>(a.scales) % align != 0 || reinterpret_cast<uintptr_t>(a.offsets) % align != 0) {
+    return false;
+  }
+  return true;
+}
+
+template <int BITS>
+int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps, cudaStream_t stream_h) {
+  using C = stream::Cfg<BITS>;
+  stream::Params p = {};
+  p.steps = steps;
+  p.tiles = tiles;
+  p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
+  const int aregs = BITS == 8 ? 32 : 16;
+  p.m_stride_u4 = steps * aregs + 4;
+  const size_t smem = C::RING_BYTES + (static_cast<size_t>(a.m) * p.m_stride_u4 + aregs) * 16 +
+                      static_cast<size_t>(steps) * 8 * 4 * 2;
+  if (smem > static_cast<size_t>(dev.max_smem_optin)) {
+    return DQ_ERR_UNSUPPORTED;
+  }
+  auto run = [&](auto kernel) -> int32_t {
+    DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    int per_sm = 0;
+    DQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, stream::kThreads, smem));
+    const int grid = std::min(static_cast<int>(ceil_div(tiles, stream::kWarps)), std::max(1, per_sm) * dev.sm_count);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(stream::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream_h;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
+    DQ_CHECK_LAUNCH("gemv");
+    return DQ_OK;
+  };
+  const bool xbf = a.x_dtype == DQ_BF16;
+  const bool mbf = a.meta_dtype == DQ_BF16;
+  if (xbf && mbf) return run(stream::gemv_mma_stream_kernel<BITS, true, true>);
+  if (xbf) return run(stream::gemv_mma_stream_kernel<BITS, true, false>);
+  if (mbf) return run(stream::gemv_mma_stream_kernel<BITS, false, true>);
+  return run(stream::gemv_mma_stream_kernel<BITS, false, false>);
+}
+
+template <int BITS>
+int32_t try_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps, cudaStream_t stream_h,
+                   bool* taken) {
+  *taken = false;
+  if (!stream_ok<BITS>(a, dev, tiles, steps)) return DQ_OK;
+  const int32_t rc = launch_stream<BITS>(a, dev, tiles, steps, stream_h);
+  if (rc == DQ_ERR_UNSUPPORTED) return DQ_OK;  // does not fit: the generic kernel takes it
+  *taken = true;
+  return rc;
+}
+
+}  // namespace
+
+bool mma_path_supports(const GemvArgs& a, int bits) {
+  if (!mma_enabled()) return false;
+  if (a.x_dtype != DQ_BF16 && a.x_dtype != DQ_F16) return false;
+  if (a.meta_dtype != DQ_BF16 && a.meta_dtype != DQ_F16) return false;
+  if (a.group_values % kStepValues != 0) return false;
+  const auto addr = reinterpret_cast<uintptr_t>(a.packed);
+  const int align = bits == 2 ? 8 : (bits == 3 ? 4 : 16);
+  if (addr % align != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % align != 0) return false;
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr) return false;
+  int stride = 0;
+  const int steps = a.words_per_row / (4 * bits);
+  const size_t smem = mma_smem_bytes(a.m, steps, bits == 8 ? 32 : 16, 1, kMaxWarps, &stride);
+  return smem <= static_cast<size_t>(dev->max_smem_optin);
+}
+
+int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr) return DQ_ERR_CUDA;
+  MmaParams p = {};
+  p.steps = a.words_per_row / (4 * bits);  // a step is 4 units of `bits` words
+  p.steps_per_group = a.group_values / kStepValues;
+  p.tiles = static_cast<int>(ceil_div(a.rows, kTileRows));
+  {
+    bool taken = false;
+    int32_t rc = DQ_OK;
+    switch (bits) {
+      case 2:
+        rc = try_stream<2>(a, *dev, p.tiles, p.steps, stream, &taken);
+        break;
+      case 3:
+        rc = try_stream<3>(a, *dev, p.tiles, p.steps, stream, &taken);
+        break;
+      case 4:
+        rc = try_stream<4>(a, *dev, p.tiles, p.steps, stream, &taken);
+        break;
+      default:
+        rc = try_stream<8>(a, *dev, p.tiles, p.steps, stream, &taken);
+        break;
+    }
+    if (taken || rc != DQ_OK) return rc;
+  }
+  // Few rows: slice the reduction axis over the warps of a CTA until every SM has ~16
+  // warps.  Many rows: several row tiles per CTA, warps persistent over the tiles.
+  const int want = static_cast<int>(ceil_div(static_cast<int64_t>(dev->sm_count) * 16, p.tiles));
+  int kw = 1;
+  while (kw < want && kw < kMaxWarps) kw *= 2;
+  p.kw = std::min(kw, floor_pow2(p.steps));
+  p.rw = p.kw == 1 ? 8 : std::max(1, std::min(8 / p.kw, p.tiles / (2 * dev->sm_count)));
+  p.steps_per_warp = static_cast<int>(ceil_div(p.steps, p.kw));
+  const int depth = bits == 8 ? 2 : 4;
+  const auto meta_align = static_cast<uintptr_t>(2 * depth);
+  p.vec_meta = p.steps_per_group == 1 && a.num_groups % depth == 0 && p.steps_per_warp % depth == 0 &&
+               reinterpret_cast<uintptr_t>(a.scales) % meta_align == 0 &&
+               reinterpret_cast<uintptr_t>(a.offsets) % meta_align == 0;
+  p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
+  const int aregs = bits == 8 ? 32 : 16;
+  const size_t smem = mma_smem_bytes(a.m, p.steps, aregs, p.rw, p.kw, &p.m_stride_u4);
+  const int threads = p.rw * p.kw * kWarp;
+  switch (bits) {
+    case 2:
+      return launch_mma_bits<2>(a, p, threads, smem, *dev, stream);
+    case 3:
+      return launch_mma_bits<3>(a, p, threads, smem, *dev, stream);
+    case 4:
+      return launch_mma_bits<4>(a, p, threads, smem, *dev, stream);
+    default:
+      return launch_mma_bits<8>(a, p, threads, smem, *dev, stream);
+  }
+}
+
+}  // namespace dq

@@ -1,0 +1,272 @@
+// Streaming variant of the tensor-core GEMV: the kernel every large matrix takes.
+//
+// Same arithmetic as gemv_mma_kernel (dq_gemv_mma.cu), different plumbing.  The
+// weights do not wait in registers: each lane copies the words it will decode
+// with cp.async into a slot of shared memory that only it reads back, two to
+// three blocks of four steps ahead.  That keeps ~128 bytes per lane in flight
+// at a cost of zero registers, so three CTAs of eight warps fit on an SM and
+// the copies of one warp cover the load latency of the others.  No barrier is
+// involved for the weights (a lane waits on its own cp.async groups only); the
+// per-(row, group) scales and offsets are fetched the same way, one array per
+// lane of a quad, and shared inside the warp after a __syncwarp.
+//
+// Requirements (the host checks them; anything else takes gemv_mma_kernel):
+// one group per 128-value step, a whole number of blocks per row, block-aligned
+// scale/offset rows, and the reduction axis not sliced over warps.
+#pragma once
+
+#include "dq_gemv.cuh"
+#include "dq_mma_plan.cuh"
+#include "dq_mma_stage.cuh"
+
+namespace dq {
+namespace stream {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * kWarp;
+
+template <int BITS>
+struct Cfg {
+  static constexpr int P = BITS == 8 ? 2 : 4;                  // steps per block
+  static constexpr int NB = BITS == 2 ? 3 : 2;                 // blocks in the ring
+  static constexpr int UNIT = 4 * BITS;                        // bytes of one lane's unit of one row
+  static constexpr int BLOCK_BYTES = P * 2 * UNIT;             // per lane per block
+  static constexpr int META_BYTES = 2 * P;                     // per lane per block (one array, P groups)
+  static constexpr int RING_BYTES = NB * (BLOCK_BYTES + META_BYTES) * kThreads;
+};
+
+template <int BYTES>
+__device__ __forceinline__ void cp_async_n(uint32_t dst, const void* src) {
+  if constexpr (BYTES == 16) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+  } else {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(src), "n"(BYTES) : "memory");
+  }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// One lane's unit of one row: UNIT bytes, global -> shared.
+template <int BITS>
+__device__ __forceinline__ void copy_unit(uint32_t dst, const uint32_t* src) {
+  if constexpr (BITS == 2) {
+    cp_async_n<8>(dst, src);
+  } else if constexpr (BITS == 3) {
+    cp_async_n<4>(dst, src);
+    cp_async_n<4>(dst + 4, src + 1);
+    cp_async_n<4>(dst + 8, src + 2);
+  } else if constexpr (BITS == 4) {
+    cp_async_n<16>(dst, src);
+  } else {
+    cp_async_n<16>(dst, src);
+    cp_async_n<16>(dst + 16, src + 4);
+  }
+}
+
+template <int BITS>
+__device__ __forceinline__ void read_unit(const unsigned char* src, uint32_t* w) {
+  if constexpr (BITS == 2) {
+    const uint2 v = *reinterpret_cast<const uint2*>(src);
+    w[0] = v.x, w[1] = v.y;
+  } else if constexpr (BITS == 3) {
+    const uint32_t* s = reinterpret_cast<const uint32_t*>(src);
+    w[0] = s[0], w[1] = s[1], w[2] = s[2];
+  } else {
+#pragma unroll
+    for (int i = 0; i < BITS / 4; ++i) {
+      const uint4 v = reinterpret_cast<const uint4*>(src)[i];
+      w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+    }
+  }
+}
+
+struct Params {
+  int steps;        // padded K / 128 (a multiple of P)
+  int tiles;        // ceil(rows / 16)
+  int m_stride_u4;  // uint4 per activation row of the staged B buffer
+  uint32_t magic;   // a parameter so it stays a register operand of the decode
+};
+
+template <int BITS, bool XBF16, bool MBF16>
+__global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const GemvArgs a, const Params p) {
+  using Plan = MmaPlan<BITS>;
+  using C = Cfg<BITS>;
+  constexpr int P = C::P;
+  constexpr int NB = C::NB;
+  constexpr int NA = Plan::kARegs;
+  constexpr int QU = NA / 4;
+  constexpr int STEP_WORDS = 4 * BITS;
+  constexpr int kTileRows = 16;
+  constexpr float kMagicValue = XBF16 ? 128.0f : 1024.0f;
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  // [ring weights: NB][P][2 rows][threads][UNIT] [ring meta: NB][threads][META_BYTES] [xb] [zero] [xsum] [xneg]
+  unsigned char* ring_w = smem_raw;
+  unsigned char* ring_m = ring_w + NB * C::BLOCK_BYTES * kThreads;
+  uint4* xb = reinterpret_cast<uint4*>(ring_m + NB * C::META_BYTES * kThreads);
+  float* xsum = reinterpret_cast<float*>(xb + a.m * p.m_stride_u4 + QU * 4);
+  float* xneg = xsum + p.steps * 8;
+
+  const int tid = threadIdx.x;
+  const int lane = tid & (kWarp - 1);
+  const int warp = tid >> 5;
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const uint32_t magic = p.magic;
+  const bool has_off = a.offsets != nullptr;
+  const int nblocks = p.steps / P;
+  const int tile_stride = gridDim.x * kWarps;
+  const int first_tile = blockIdx.x * kWarps + warp;
+
+  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + tid * C::UNIT;
+  const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * C::META_BYTES;
+  const unsigned char* ring_w_mine = ring_w + tid * C::UNIT;
+  // metadata of this lane's quad: arrays 0..3 = scale(row g), offset(row g), scale(row g+8), offset(row g+8)
+  const unsigned char* ring_m_quad = ring_m + (tid & ~3) * C::META_BYTES;
+
+  pdl_launch_dependents();
+
+  // ---- prefetch cursor: walks (tile, block) ahead of the compute loop ----
+  int pf_tile = first_tile;
+  int pf_blk = 0;
+  const uint32_t* pf_wa = nullptr;
+  const uint32_t* pf_wb = nullptr;
+  const unsigned short* pf_meta = nullptr;  // this lane's array (scales or offsets) at its row, group 0
+  auto pf_point = [&]() {
+    const int ra = min(pf_tile * kTileRows + g, a.rows - 1);
+    const int rb = min(pf_tile * kTileRows + g + 8, a.rows - 1);
+    pf_wa = a.packed + static_cast<int64_t>(ra) * a.words_per_row + t * BITS;
+    pf_wb = a.packed + static_cast<int64_t>(rb) * a.words_per_row + t * BITS;
+    const unsigned short* arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
+    pf_meta = arr + static_cast<int64_t>((t & 2) ? rb : ra) * a.num_groups;
+  };
+  if (pf_tile < p.tiles) pf_point();
+  const bool meta_lane = has_off || (t & 1) == 0;
+  int pf_count = 0;  // blocks issued so far (ring slot = count % NB)
+  auto prefetch_block = [&]() {
+    if (pf_tile < p.tiles) {
+      const int slot = pf_count % NB;
+      const uint32_t dst = ring_w_s + slot * (C::BLOCK_BYTES * kThreads);
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+        copy_unit<BITS>(dst + (j * 2 + 0) * (C::UNIT * kThreads), pf_wa + (pf_blk * P + j) * STEP_WORDS);
+        copy_unit<BITS>(dst + (j * 2 + 1) * (C::UNIT * kThreads), pf_wb + (pf_blk * P + j) * STEP_WORDS);
+      }
+      if (meta_lane) {
+        cp_async_n<C::META_BYTES>(ring_m_s + slot * (C::META_BYTES * kThreads), pf_meta + pf_blk * P);
+      }
+      if (++pf_blk == nblocks) {
+        pf_blk = 0;
+        pf_tile += tile_stride;
+        if (pf_tile < p.tiles) pf_point();
+      }
+    }
+    ++pf_count;
+    cp_async_commit();  // an empty group keeps the wait arithmetic uniform
+  };
+#pragma unroll
+  for (int i = 0; i < NB - 1; ++i) {
+    prefetch_block();
+  }
+
+  // ---- stage the activation (the only part that depends on the previous kernel) ----
+  pdl_wait_prior_grid();
+  stage_activation<BITS, XBF16>(a, p.steps, p.m_stride_u4, xb, xsum, xneg, tid, kThreads);
+  __syncthreads();
+
+  // ---- compute loop: one block of P steps per iteration ----
+  const bool b_live = g < a.m;
+  const uint4* xb_lane = b_live ? xb + g * p.m_stride_u4 + t : xb + a.m * p.m_stride_u4;
+  const int xb_step_u4 = b_live ? QU * 4 : 0;
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  int count = 0;
+  for (int tile = first_tile; tile < p.tiles; tile += tile_stride) {
+    for (int blk = 0; blk < nblocks; ++blk, ++count) {
+      __syncwarp();      // every lane is done with the slot about to be refilled
+      prefetch_block();  // refills slot (count + NB - 1) % NB
+      cp_async_wait<NB - 1>();
+      __syncwarp();      // the quad's metadata copies are visible to each other
+      const int slot = count % NB;
+      const unsigned char* wsrc = ring_w_mine + slot * (C::BLOCK_BYTES * kThreads);
+      const unsigned char* msrc = ring_m_quad + slot * (C::META_BYTES * kThreads);
+      uint32_t mc[4][P / 2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (has_off || (i & 1) == 0) {
+          if constexpr (P == 4) {
+            const uint2 v = *reinterpret_cast<const uint2*>(msrc + i * C::META_BYTES);
+            mc[i][0] = v.x, mc[i][1] = v.y;
+          } else {
+            mc[i][0] = *reinterpret_cast<const uint32_t*>(msrc + i * C::META_BYTES);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+        const int s = blk * P + j;
+        uint32_t wa[BITS], wb[BITS];
+        read_unit<BITS>(wsrc + (j * 2 + 0) * (C::UNIT * kThreads), wa);
+        read_unit<BITS>(wsrc + (j * 2 + 1) * (C::UNIT * kThreads), wb);
+        uint32_t aa[NA], ab[NA];
+        decode_unit<BITS>(wa, magic, aa);
+        decode_unit<BITS>(wb, magic, ab);
+        const uint4* bsrc = xb_lane + s * xb_step_u4;
+        float d[4];
+#pragma unroll
+        for (int q = 0; q < QU; ++q) {
+          const uint4 b = bsrc[q * 4];
+          if (q == 0) {
+            mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
+          } else {
+            mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
+          }
+          mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
+        }
+        auto meta_f32 = [&](int i) -> float {
+          const uint32_t reg = mc[i][j / 2];
+          if constexpr (MBF16) {
+            return __uint_as_float((j & 1) ? (reg & 0xFFFF0000u) : (reg << 16));
+          } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&reg);
+            return (j & 1) ? __high2float(h) : __low2float(h);
+          }
+        };
+        const float2 xs2 = *reinterpret_cast<const float2*>(xsum + s * 8 + 2 * t);
+        const float2 xn2 = *reinterpret_cast<const float2*>(xneg + s * 8 + 2 * t);
+        const float sc_a = meta_f32(0), sc_b = meta_f32(2);
+        acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
+        acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
+        acc[2] = fmaf(sc_b, d[2] + xn2.x, acc[2]);
+        acc[3] = fmaf(sc_b, d[3] + xn2.y, acc[3]);
+        if (has_off) {
+          const float of_a = meta_f32(1), of_b = meta_f32(3);
+          acc[0] = fmaf(of_a, xs2.x, acc[0]);
+          acc[1] = fmaf(of_a, xs2.y, acc[1]);
+          acc[2] = fmaf(of_b, xs2.x, acc[2]);
+          acc[3] = fmaf(of_b, xs2.y, acc[3]);
+        }
+      }
+    }
+    const int row_a = tile * kTileRows + g, row_b = row_a + 8;
+    const int m0 = 2 * t;
+    if (m0 < a.m) {
+      if (row_a < a.rows) store_out(a, m0, row_a, acc[0]);
+      if (row_b < a.rows) store_out(a, m0, row_b, acc[2]);
+    }
+    if (m0 + 1 < a.m) {
+      if (row_a < a.rows) store_out(a, m0 + 1, row_a, acc[1]);
+      if (row_b < a.rows) store_out(a, m0 + 1, row_b, acc[3]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[i] = 0.0f;
+    }
+  }
+  cp_async_wait<0>();
+}
+
+}  // namespace stream
+}  // namespace dq
