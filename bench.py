@@ -234,7 +234,7 @@ def run_ours(args) -> None:
         runner = StepRunner(full, m, device=device)
         use_graph = not args.no_graph
         if use_graph:
-            runner.capture()
+            runner.capture(args.graph_mode)
             step_fn = runner.replay
         else:
             step_fn = runner.run
@@ -313,7 +313,8 @@ def run_ours(args) -> None:
             "m": m, "activations": "bf16", "scales": "fp16", "group_size": 128,
             "weight_bytes": full.weight_bytes, "algorithmic_bytes_per_step": step_bytes,
             "l2": "working set (1.1 GB of weights per step) is larger than L2; no flush needed",
-            "launch": "cuda graph of one step, programmatic dependent launch" if use_graph else "dq_gemv_sequence per step",
+            "launch": (f"cuda graph of one step, {args.graph_mode} edges, programmatic dependent launch"
+                       if use_graph else "dq_gemv_sequence per step"),
             "parallelism": "single gpu" if world == 1 else f"column-sharded x{world}, NCCL all-gather",
             "peak": f"{peak} GB/s ({peak_kind})",
         },
@@ -344,6 +345,9 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=28, help="reduce the stack (profiling only)")
     ap.add_argument("--no-graph", action="store_true", help="launch with dq_gemv_sequence instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph-mode", choices=["dataflow", "chain", "independent"], default="dataflow",
+                    help="edges of the captured step: a decoder layer's data dependencies (default), "
+                         "a strict chain, or none")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -318,6 +318,8 @@ __global__ void __launch_bounds__(kMaxWarps* kWarp)
             uint32_t aa[NA], ab[NA];
             decode_unit<BITS>(raw[slot][0], magic, aa);
             decode_unit<BITS>(raw[slot][1], magic, ab);
+            unbias_fragments<XBF16, NA>(aa);
+            unbias_fragments<XBF16, NA>(ab);
             load_unit<BITS>(wa_n + slot * STEP_WORDS, raw[slot][0]);
             load_unit<BITS>(wb_n + slot * STEP_WORDS, raw[slot][1]);
             finish_step(aa, ab, s_begin + rs0 + slot, slot, mcur);
@@ -346,6 +348,8 @@ __global__ void __launch_bounds__(kMaxWarps* kWarp)
               uint32_t aa[NA], ab[NA];
               decode_unit<BITS>(raw[slot][0], magic, aa);
               decode_unit<BITS>(raw[slot][1], magic, ab);
+              unbias_fragments<XBF16, NA>(aa);
+              unbias_fragments<XBF16, NA>(ab);
               // Refill this slot: P steps ahead in this tile, or the next tile's first block.
               const int rs_next = rs0 + slot + P;
               if (rs_next < nsteps) {

@@ -213,6 +213,8 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
         uint32_t aa[NA], ab[NA];
         decode_unit<BITS>(wa, magic, aa);
         decode_unit<BITS>(wb, magic, ab);
+        unbias_fragments<XBF16, NA>(aa);
+        unbias_fragments<XBF16, NA>(ab);
         const uint4* bsrc = xb_lane + s * xb_step_u4;
         float d[4];
 #pragma unroll

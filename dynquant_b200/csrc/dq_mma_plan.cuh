@@ -169,6 +169,23 @@ __device__ __forceinline__ void decode_unit(const uint32_t* w, uint32_t magic, u
   }
 }
 
+// fp16 operands only: remove the magic bias in registers (exact: both numbers are integers
+// below 2048), because 1024 -- the smallest magic a 10-bit mantissa allows for fields in its
+// low bits -- is too large a bias to cancel after the contraction at full fp32 accuracy.
+// bf16 keeps the bias (128) and removes it afterwards.
+template <bool BF16, int N>
+__device__ __forceinline__ void unbias_fragments(uint32_t* a) {
+  if constexpr (!BF16) {
+    const __half2 magic = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400)));
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      __half2 v = *reinterpret_cast<__half2*>(&a[i]);
+      v = __hsub2(v, magic);
+      a[i] = *reinterpret_cast<uint32_t*>(&v);
+    }
+  }
+}
+
 // D = A * B + C, m16n8k16, fp32 accumulate; bf16 or fp16 operands.  FIRST starts a fresh
 // accumulator (C = 0 comes from the zero register, no moves).
 template <bool BF16, bool FIRST>

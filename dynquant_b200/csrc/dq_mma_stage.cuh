@@ -20,7 +20,7 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
   constexpr int LANES = QU * 4;  // lanes that build one (m, s): 16, or 32 at 8-bit
-  constexpr float kMagicValue = XBF16 ? 128.0f : 1024.0f;
+  constexpr float kMagicValue = XBF16 ? 128.0f : 0.0f;  // fp16 fragments are un-biased in registers
   const int lane = tid & (kWarp - 1);
   const int sub = lane / LANES;            // which (m, s) of this warp's batch
   const int l = lane - sub * LANES;        // lane within the builder group

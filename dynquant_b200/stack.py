@@ -67,19 +67,71 @@ class StepRunner:
         self.launches_per_step = len(stack.modules)
 
     def run(self) -> None:
-        """Enqueue the whole step on torch's current stream."""
+        """Enqueue the whole step on torch's current stream, module after module."""
         lib = _lib.load()
         with torch.cuda.device(self.device):
             _lib.check(lib.dq_gemv_sequence(self._jobs, len(self._jobs), _stream(self.device)))
 
-    def capture(self) -> None:
-        """Record the step into a CUDA graph (programmatic-dependency edges included)."""
+    def _run_jobs(self, first: int, count: int) -> None:
+        lib = _lib.load()
+        jobs = ctypes.cast(ctypes.byref(self._jobs, first * ctypes.sizeof(_lib.GemvJob)), ctypes.POINTER(_lib.GemvJob))
+        _lib.check(lib.dq_gemv_sequence(jobs, count, _stream(self.device)))
+
+    def run_dataflow(self, side_streams: list[torch.cuda.Stream]) -> None:
+        """Enqueue the step as its dependency graph: the members of a stage (q/k/v, gate/up)
+        run on separate streams, consecutive stages are ordered by events."""
+        main = torch.cuda.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            for stage in self.stack.stages():
+                if len(stage) == 1:
+                    self._run_jobs(stage[0], 1)
+                    continue
+                fork = torch.cuda.Event()
+                fork.record(main)
+                self._run_jobs(stage[0], 1)
+                for idx, side in zip(stage[1:], side_streams):
+                    side.wait_event(fork)
+                    with torch.cuda.stream(side):
+                        self._run_jobs(idx, 1)
+                    join = torch.cuda.Event()
+                    join.record(side)
+                    main.wait_event(join)
+
+    def capture(self, mode: str = "dataflow") -> None:
+        """Record the step into a CUDA graph.
+
+        ``"dataflow"``: stages in order, members of a stage concurrent (what a decoder
+        layer's dependencies allow).  ``"chain"``: every module after the previous one.
+        ``"independent"``: no edges at all -- every module's input is resident, nothing
+        waits for anything (the regime the reference's per-shape bandwidth table measures).
+        """
         self.run()  # warm: sets per-kernel attributes outside the capture
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        sides = [torch.cuda.Stream(self.device) for _ in range(8 if mode == "independent" else 2)]
         with torch.cuda.graph(graph):
-            self.run()
+            if mode == "chain":
+                self.run()
+            elif mode == "dataflow":
+                self.run_dataflow(sides)
+            elif mode == "independent":
+                main = torch.cuda.current_stream(self.device)
+                fork = torch.cuda.Event()
+                fork.record(main)
+                lanes = [main, *sides]
+                for s in sides:
+                    s.wait_event(fork)
+                for i in range(len(self._jobs)):
+                    with torch.cuda.stream(lanes[i % len(lanes)]):
+                        self._run_jobs(i, 1)
+                for s in sides:
+                    join = torch.cuda.Event()
+                    join.record(s)
+                    main.wait_event(join)
+            else:
+                raise ValueError(mode)
         self._graph = graph
+        self.mode = mode
 
     def replay(self) -> None:
         if self._graph is None:

@@ -61,6 +61,26 @@ class LinearStack:
     def weight_bytes(self) -> int:
         return sum(m.weight.nbytes for m in self.modules)
 
+    def stages(self) -> list[list[int]]:
+        """Module indices grouped by data dependency, in execution order.
+
+        Within a decoder layer q/k/v read the same hidden state, as do gate/up, so each of
+        those sets is one stage whose members are independent; o_proj, down_proj and the
+        lm_head are stages of their own.  Consecutive stages depend on each other.
+        """
+        out: list[list[int]] = []
+        last_key = None
+        for i, mod in enumerate(self.modules):
+            leaf = mod.name.rsplit(".", 1)[-1]
+            kind = {"q_proj": 0, "k_proj": 0, "v_proj": 0, "o_proj": 1, "gate_proj": 2, "up_proj": 2,
+                    "down_proj": 3}.get(leaf, 4)
+            key = (mod.name.split(".")[1] if mod.name.startswith("layers.") else mod.name, kind)
+            if key != last_key:
+                out.append([])
+                last_key = key
+            out[-1].append(i)
+        return out
+
     def algorithmic_bytes(self, m: int, act_bytes: int = 2) -> int:
         """Weights (packed + scales + offsets) once, plus activations in and results out."""
         total = 0

@@ -66,7 +66,7 @@ def bits_equal(got: torch.Tensor, want_raw: np.ndarray) -> bool:
     return bool((g == want_raw).all())
 
 
-def within_one_ulp_16(got: torch.Tensor, want32: np.ndarray, slack: float = 1e-4) -> bool:
+def within_one_ulp_16(got: torch.Tensor, want32: np.ndarray, slack: float = 2e-5) -> bool:
     """``got`` (fp16/bf16) is the fp32 oracle rounded once, give or take one unit in the last
     place -- plus ``slack * max|oracle|`` of absolute room, because an output that nearly
     cancels to zero has an ulp far below the fp32 accumulation noise of either side."""
