@@ -130,7 +130,9 @@ struct TilePtr {
   int64_t ma, mb;      // element index of (row, group 0) in scales / offsets
 };
 
-template <int BITS, bool XBF16, bool MBF16>
+// FAST: whole, aligned blocks only (the register ring runs without predicates and with
+// vector metadata loads).  !FAST: any step count.
+template <int BITS, bool XBF16, bool MBF16, bool FAST>
 __global__ void __launch_bounds__(kMaxWarps* kWarp)
     gemv_mma_kernel(const GemvArgs a, const MmaParams p) {
   using Plan = MmaPlan<BITS>;
@@ -296,13 +298,12 @@ __global__ void __launch_bounds__(kMaxWarps* kWarp)
   };
 
   if (any_work) {
-    const bool fast = p.vec_meta && (nsteps % P) == 0;
     while (true) {
       const int next_tile = tile + tile_stride;
       const bool has_next = p.kw == 1 && next_tile < p.tiles;
       const TilePtr nxt = tile_ptr(has_next ? next_tile : tile);
 
-      if (fast) {
+      if constexpr (FAST) {
         // Every block is full and block-aligned: no predicates, vector metadata loads, and the
         // refill of a slot is always a real load (of this tile's next block, the next tile's
         // first block, or -- at the very end -- a harmless re-read of this tile's first block).
@@ -471,10 +472,18 @@ int32_t launch_mma_bits(const GemvArgs& a, const MmaParams& p, int threads, size
                         const DeviceInfo& dev, cudaStream_t stream) {
   const bool xbf = a.x_dtype == DQ_BF16;
   const bool mbf = a.meta_dtype == DQ_BF16;
-  if (xbf && mbf) return launch_mma_kernel(gemv_mma_kernel<BITS, true, true>, a, p, threads, smem, dev, stream);
-  if (xbf) return launch_mma_kernel(gemv_mma_kernel<BITS, true, false>, a, p, threads, smem, dev, stream);
-  if (mbf) return launch_mma_kernel(gemv_mma_kernel<BITS, false, true>, a, p, threads, smem, dev, stream);
-  return launch_mma_kernel(gemv_mma_kernel<BITS, false, false>, a, p, threads, smem, dev, stream);
+  constexpr int P = Depth<BITS>::value;
+  const bool fast = p.vec_meta && p.steps_per_warp % P == 0 && (p.kw == 1 || p.steps % p.kw == 0);
+  if (fast) {
+    if (xbf && mbf) return launch_mma_kernel(gemv_mma_kernel<BITS, true, true, true>, a, p, threads, smem, dev, stream);
+    if (xbf) return launch_mma_kernel(gemv_mma_kernel<BITS, true, false, true>, a, p, threads, smem, dev, stream);
+    if (mbf) return launch_mma_kernel(gemv_mma_kernel<BITS, false, true, true>, a, p, threads, smem, dev, stream);
+    return launch_mma_kernel(gemv_mma_kernel<BITS, false, false, true>, a, p, threads, smem, dev, stream);
+  }
+  if (xbf && mbf) return launch_mma_kernel(gemv_mma_kernel<BITS, true, true, false>, a, p, threads, smem, dev, stream);
+  if (xbf) return launch_mma_kernel(gemv_mma_kernel<BITS, true, false, false>, a, p, threads, smem, dev, stream);
+  if (mbf) return launch_mma_kernel(gemv_mma_kernel<BITS, false, true, false>, a, p, threads, smem, dev, stream);
+  return launch_mma_kernel(gemv_mma_kernel<BITS, false, false, false>, a, p, threads, smem, dev, stream);
 }
 
 // ---- streaming kernel (dq_gemv_mma_stream.cuh) ----
@@ -487,6 +496,10 @@ bool stream_ok(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps) {
     return v != nullptr && v[0] != '\0' && v[0] != '0';
   }();
   if (off) return false;
+  // Measured on B200 (profiles/): the cp.async ring wins where a lane's unit is 32 bytes
+  // (8-bit); at 2/3/4-bit its extra shared-memory traffic costs more than the occupancy
+  // it buys and the register ring of gemv_mma_kernel<FAST> is faster.
+  if (BITS != 8) return false;
   if (a.group_values != kStepValues || steps % C::P != 0 || a.num_groups % C::P != 0) return false;
   if (tiles < dev.sm_count * stream::kWarps) return false;
   const auto align = static_cast<uintptr_t>(C::META_BYTES);
@@ -592,13 +605,41 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
     }
     if (taken || rc != DQ_OK) return rc;
   }
-  // Few rows: slice the reduction axis over the warps of a CTA until every SM has ~16
-  // warps.  Many rows: several row tiles per CTA, warps persistent over the tiles.
-  const int want = static_cast<int>(ceil_div(static_cast<int64_t>(dev->sm_count) * 16, p.tiles));
-  int kw = 1;
-  while (kw < want && kw < kMaxWarps) kw *= 2;
-  p.kw = std::min(kw, floor_pow2(p.steps));
-  p.rw = p.kw == 1 ? 8 : std::max(1, std::min(8 / p.kw, p.tiles / (2 * dev->sm_count)));
+  // Shape of a CTA: rw row tiles x kw slices of the reduction axis, 8 or 16 warps.  A short
+  // matrix is over in one dependent chain of latencies (launch, activation staging, a few
+  // steps, reduction), so what matters is that EVERY CTA is resident at once -- a second
+  // wave doubles the chain -- and, within that, that as many warps as possible share the
+  // work.  Long matrices take kw = 1 and let the warps persist over the tiles.
+  {
+    const int kw_max = std::min(kMaxWarps, floor_pow2(p.steps));
+    // CTAs of 8 warps fit twice on an SM at this kernel's register count, 16 warps once.
+    const int cap8 = 2 * dev->sm_count, cap16 = dev->sm_count;
+    int best_rw = 8, best_kw = 1;
+    int64_t best_warps = -1;
+    for (int warps = 8; warps <= kMaxWarps; warps *= 2) {
+      for (int kw = 1; kw <= std::min(warps, kw_max); kw *= 2) {
+        const int rw = warps / kw;
+        const int grid = static_cast<int>(ceil_div(p.tiles, rw));
+        if (grid > (warps == 8 ? cap8 : cap16)) continue;  // would need a second wave
+        const int64_t busy = static_cast<int64_t>(std::min(p.tiles, grid * rw)) * kw;
+        // more busy warps first; then smaller CTAs (they spread over more SMs)
+        if (busy > best_warps || (busy == best_warps && warps < best_rw * best_kw)) {
+          best_warps = busy;
+          best_rw = rw;
+          best_kw = kw;
+        }
+      }
+    }
+    p.rw = best_rw;  // nothing fits in one wave: 8 persistent warps per CTA, kw = 1
+    p.kw = best_kw;
+  }
+  {
+    // tuning overrides (measurement only)
+    static const int force_kw = [] { const char* v = std::getenv("DQ_B200_MMA_KW"); return v ? std::atoi(v) : 0; }();
+    static const int force_rw = [] { const char* v = std::getenv("DQ_B200_MMA_RW"); return v ? std::atoi(v) : 0; }();
+    if (force_kw > 0) p.kw = std::min(force_kw, floor_pow2(p.steps));
+    if (force_rw > 0) p.rw = std::min(force_rw, kMaxWarps / p.kw);
+  }
   p.steps_per_warp = static_cast<int>(ceil_div(p.steps, p.kw));
   const int depth = bits == 8 ? 2 : 4;
   const auto meta_align = static_cast<uintptr_t>(2 * depth);
