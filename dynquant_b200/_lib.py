@@ -67,12 +67,6 @@ class GemvJob(ctypes.Structure):
     ]
 
 
-class MoeBank(ctypes.Structure):
-    """``dq_moe_bank``: a stacked expert tensor folded to rows."""
-
-    _fields_ = [("weight", Weight), ("rows_per_expert", ctypes.c_int64)]
-
-
 _P = ctypes.c_void_p
 _I32 = ctypes.c_int32
 _I64 = ctypes.c_int64
@@ -91,6 +85,8 @@ SIGNATURES = {
     "dq_gemv": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P]),
     "dq_gemv_shards": (_I32, [_P, _I32, _I64, _WP, _I32, _P, _P, _I64, _I32, _P]),
     "dq_gemv_sequence": (_I32, [ctypes.POINTER(GemvJob), _I32, _P]),
+    "dq_moe_scratch_bytes": (_I32, [_I64, _I64, _I64, _I64, _I64, _I32, ctypes.POINTER(ctypes.c_int64)]),
+    "dq_moe_gemv": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _WP, _WP, _I64, _I64, _P, _I32, _P, _I64, _P]),
     "dq_gemv_host": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P, _P, _P]),
 }
 

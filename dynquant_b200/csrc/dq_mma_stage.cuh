@@ -15,7 +15,8 @@ namespace dq {
 
 template <int BITS, bool XBF16>
 __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, int m_stride_u4, uint4* xb,
-                                                 float* xsum, float* xneg, int tid, int nthreads) {
+                                                 float* xsum, float* xneg, int tid, int nthreads,
+                                                 const int* row_map = nullptr) {
   using Plan = MmaPlan<BITS>;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
@@ -32,6 +33,7 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
     const bool live = idx < nitems;
     const int m = live ? idx / steps : 0;
     const int s = live ? idx - m * steps : 0;
+    const int64_t src_row = row_map != nullptr ? row_map[m] : m;  // gathered activation rows (MoE)
     const int kbase = s * 128 + 32 * tt;
     float sx = 0.0f, sb = 0.0f;
     uint32_t regs[4];
@@ -41,8 +43,8 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
       const int k_lo = kbase + sl.v_lo;
       const int k_hi = kbase + sl.v_hi;
       float lo = 0.0f, hi = 0.0f;
-      if (live && k_lo < a.in_features) lo = load_f32(a.x, static_cast<int64_t>(m) * a.in_features + k_lo, a.x_dtype);
-      if (live && k_hi < a.in_features) hi = load_f32(a.x, static_cast<int64_t>(m) * a.in_features + k_hi, a.x_dtype);
+      if (live && k_lo < a.in_features) lo = load_f32(a.x, src_row * a.in_features + k_lo, a.x_dtype);
+      if (live && k_hi < a.in_features) hi = load_f32(a.x, src_row * a.in_features + k_hi, a.x_dtype);
       // every value of the unit appears in exactly one slot, except at 8-bit where the high
       // nibble's slot (e = 4) repeats it: count x once
       if (BITS != 8 || sl.e_lo == 0) sx += lo + hi;

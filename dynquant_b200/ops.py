@@ -245,6 +245,63 @@ def gemv_host(
     return out_host
 
 
+def moe_scratch_bytes(tokens: int, topk: int, hidden: int, inter: int, num_experts: int, act_dtype: torch.dtype) -> int:
+    n = ctypes.c_int64(0)
+    _lib.check(_lib.load().dq_moe_scratch_bytes(tokens, topk, hidden, inter, num_experts, _tag(act_dtype, "moe"), ctypes.byref(n)))
+    return int(n.value)
+
+
+def moe_gemv(
+    x: torch.Tensor,
+    topk_ids: torch.Tensor,
+    topk_weights: torch.Tensor,
+    gate_up: QuantTensor,
+    down: QuantTensor,
+    *,
+    num_experts: int,
+    out_dtype: torch.dtype | None = None,
+    scratch: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Expert layer over packed banks: ``sum_k w[t,k] * down_e(silu(gate_e(x_t)) * up_e(x_t))``.
+
+    ``gate_up`` is the bank ``[E, 2*inter, hidden]`` folded to rows (gate rows of an expert
+    first), ``down`` is ``[E, hidden, inter]`` folded to rows; ``topk_ids`` int32
+    ``[tokens, topk]`` with ids outside ``[0, num_experts)`` skipped; ``topk_weights`` fp32.
+    ``scratch`` (uint8, CUDA) may be passed to avoid an allocation per call.
+    """
+    lib = _lib.load()
+    if x.dim() != 2 or not x.is_contiguous():
+        raise RuntimeError(f"moe_gemv: x must be a contiguous 2-D [tokens, hidden] tensor, got {tuple(x.shape)}")
+    _require_cuda(x, "moe_gemv: x")
+    tokens, hidden = x.shape
+    inter = down.in_features
+    if topk_ids.dtype != torch.int32 or topk_ids.dim() != 2 or topk_ids.shape[0] != tokens or not topk_ids.is_contiguous():
+        raise RuntimeError("moe_gemv: topk_ids must be a contiguous int32 [tokens, topk] tensor")
+    if topk_weights.dtype != torch.float32 or topk_weights.shape != topk_ids.shape or not topk_weights.is_contiguous():
+        raise RuntimeError("moe_gemv: topk_weights must be a contiguous float32 tensor shaped like topk_ids")
+    topk = topk_ids.shape[1]
+    wgu = weight_descriptor("moe_gemv", gate_up.packed, gate_up.scales, gate_up.offsets, gate_up.bits,
+                            gate_up.geometry.effective_group, gate_up.in_features)
+    wdn = weight_descriptor("moe_gemv", down.packed, down.scales, down.offsets, down.bits,
+                            down.geometry.effective_group, down.in_features)
+    out_dtype = out_dtype or x.dtype
+    need = moe_scratch_bytes(tokens, topk, hidden, inter, num_experts, x.dtype)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+    elif scratch.numel() < need or scratch.dtype != torch.uint8 or scratch.device != x.device:
+        raise RuntimeError(f"moe_gemv: scratch must be a uint8 tensor of at least {need} bytes on {x.device}")
+    y = torch.empty((tokens, hidden), dtype=out_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(
+            lib.dq_moe_gemv(
+                x.data_ptr(), _tag(x.dtype, "moe_gemv: x"), tokens, topk_ids.data_ptr(), topk_weights.data_ptr(),
+                topk, num_experts, ctypes.byref(wgu), ctypes.byref(wdn), hidden, inter, y.data_ptr(),
+                _tag(out_dtype, "moe_gemv: out"), scratch.data_ptr(), scratch.numel(), _stream(x.device),
+            )
+        )
+    return y
+
+
 def gemv_max_rows() -> int:
     return int(_lib.load().dq_gemv_max_rows())
 

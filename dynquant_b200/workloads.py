@@ -157,3 +157,40 @@ def qwen14b_linear_set(device="cuda", seed: int = 14014, layers: int = 40, shard
             raise ValueError(f"{name}: {r} rows do not split over {world} ranks")
         modules.append(Module(name, random_quant_tensor(r // world, k, bit_map[name], device=device, generator=gen), src))
     return LinearStack(f"qwen3-14b-linear-set[{rank}/{world}]", 5120, 17408, modules, bit_map)
+
+
+@dataclass
+class MoeLayer:
+    """One expert layer: the two packed banks plus seeded routing for ``tokens`` tokens."""
+
+    hidden: int
+    inter: int
+    num_experts: int
+    topk: int
+    gate_up: QuantTensor  # [E * 2 * inter, hidden]
+    down: QuantTensor  # [E * hidden, inter]
+
+    def bytes_for(self, topk_ids: torch.Tensor, tokens: int, act_bytes: int = 2) -> int:
+        """Algorithmic bytes of one step: every DISTINCT activated expert's packed rows once,
+        plus token activations in and out and the routing table."""
+        active = int(torch.unique(topk_ids[(topk_ids >= 0) & (topk_ids < self.num_experts)]).numel())
+        per_expert = (self.gate_up.nbytes + self.down.nbytes) // self.num_experts
+        return active * per_expert + tokens * self.hidden * act_bytes * 2 + tokens * self.topk * 8
+
+
+def qwen3_moe_layer(device="cuda", seed: int = 3030, bits_gate_up: int = 3, bits_down: int = 4,
+                    num_experts: int = 128, hidden: int = 2048, inter: int = 768, topk: int = 8) -> MoeLayer:
+    """Qwen3-30B-A3B-shaped expert layer: 128 experts, top-8, hidden 2048, expert intermediate 768."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    gate_up = random_quant_tensor(num_experts * 2 * inter, hidden, bits_gate_up, device=device, generator=gen)
+    down = random_quant_tensor(num_experts * hidden, inter, bits_down, device=device, generator=gen)
+    return MoeLayer(hidden, inter, num_experts, topk, gate_up, down)
+
+
+def seeded_routing(tokens: int, num_experts: int, topk: int, seed: int = 99, device="cpu"):
+    """top-k of softmax(N(0,1) logits), weights renormalised over the selected experts."""
+    gen = torch.Generator().manual_seed(seed)
+    probs = torch.softmax(torch.randn(tokens, num_experts, generator=gen), dim=-1)
+    w, ids = torch.topk(probs, topk, dim=-1)
+    w = (w / w.sum(-1, keepdim=True)).to(torch.float32)
+    return ids.to(torch.int32).to(device).contiguous(), w.to(device).contiguous()

@@ -150,6 +150,31 @@ DQ_API int32_t dq_gemv_host(const void* x_host, int32_t x_dtype, int64_t m, cons
                             void* out_host, int32_t out_dtype, void* x_dev, void* out_dev,
                             void* stream);
 
+/* ---- MoE grouped GEMV -------------------------------------------------------
+ * No reference kernel or operator exists for this (the reference refuses fused-MoE
+ * layers: integration/vllm_plugin/config.py:107-112, runtime/linear.py:442-456).  The
+ * weight layout is the reference's: a stacked bank [E, out, in] folded to rows
+ * (quant/tensor.py:253-255), expert e owning rows [e*out, (e+1)*out); gate_up is
+ * [E, 2*inter, hidden] with an expert's gate rows before its up rows and down is
+ * [E, hidden, inter] (graph/experts.py:35-43).
+ *
+ *   y[t] = sum_k topk_w[t,k] * W_down[e] ( silu(W_gate[e] x[t]) * (W_up[e] x[t]) ),  e = topk_ids[t,k]
+ *
+ * x [tokens, hidden] in x_dtype (fp16 or bf16), tokens <= DQ_MOE_MAX_TOKENS;
+ * topk_ids [tokens, topk] int32, ids outside [0, num_experts) are skipped (an
+ * expert-parallel rank passes its local expert numbers and -1 for the rest);
+ * topk_w [tokens, topk] fp32; y [tokens, hidden] in y_dtype.  The intermediate
+ * silu(g)*u is rounded once to x_dtype.  fp32 accumulation, no atomics: bit-identical
+ * run to run.  `scratch` is caller-owned device memory of at least
+ * dq_moe_scratch_bytes() bytes, 256-byte aligned; its contents are overwritten. */
+DQ_API int32_t dq_moe_scratch_bytes(int64_t tokens, int64_t topk, int64_t hidden, int64_t inter,
+                                    int64_t num_experts, int32_t act_dtype, int64_t* bytes);
+DQ_API int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_t* topk_ids,
+                           const float* topk_w, int64_t topk, int64_t num_experts,
+                           const dq_weight* gate_up, const dq_weight* down, int64_t hidden,
+                           int64_t inter, void* y, int32_t y_dtype, void* scratch,
+                           int64_t scratch_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

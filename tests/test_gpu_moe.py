@@ -1,0 +1,97 @@
+"""MoE grouped GEMV against the composition oracle (the reference has no MoE kernel; the
+oracle is its per-expert dequantize + matmul definition, ``oracle/dq_oracle.c::dqo_moe``)."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import TAG, raw
+
+pytestmark = pytest.mark.gpu
+
+
+def bank_for_oracle(qt):
+    from oracle import oracle as O
+
+    return (raw(qt.packed), raw(qt.scales), raw(qt.offsets), TAG[qt.scales.dtype],
+            O.geometry(qt.bits, qt.group_size, qt.in_features))
+
+
+def run_case(tokens, experts, hidden, inter, topk, bits_gu, bits_dn, act=torch.bfloat16, seed=1, local=None):
+    from dynquant_b200 import ops
+    from dynquant_b200.workloads import qwen3_moe_layer, seeded_routing
+    from oracle import oracle as O
+
+    layer = qwen3_moe_layer("cuda", seed=seed, bits_gate_up=bits_gu, bits_down=bits_dn, num_experts=experts,
+                            hidden=hidden, inter=inter, topk=topk)
+    ids, w = seeded_routing(tokens, experts, topk, seed=seed + 7)
+    if local is not None:  # an expert-parallel rank: experts outside [lo, hi) are not held here
+        lo, hi = local
+        ids = torch.where((ids >= lo) & (ids < hi), ids, torch.full_like(ids, -1))
+    x = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(seed)).to(act)
+    got = ops.moe_gemv(x.cuda(), ids.cuda(), w.cuda(), layer.gate_up, layer.down, num_experts=experts,
+                       out_dtype=torch.float32)
+    want = O.c_moe(raw(x), TAG[act], ids.numpy(), w.numpy(), bank_for_oracle(layer.gate_up),
+                   bank_for_oracle(layer.down), inter=inter, num_experts=experts, h_round=TAG[act])
+    return got.cpu().numpy(), want, layer, ids, w, x
+
+
+@pytest.mark.parametrize("tokens", [1, 2, 5, 8, 33, 64])
+@pytest.mark.parametrize(("bits_gu", "bits_dn"), [(2, 4), (3, 3), (4, 2), (8, 8)])
+def test_moe_matches_the_composition_oracle(tokens, bits_gu, bits_dn):
+    got, want, *_ = run_case(tokens, 16, 512, 256, 4, bits_gu, bits_dn)
+    scale = np.abs(want).max() + 1e-30
+    # the intermediate is rounded to bf16 on both sides; one-ulp flips of it are the noise floor
+    assert np.abs(got - want).max() / scale <= 4e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3
+
+
+def test_moe_qwen3_shape_fp16_and_determinism():
+    from dynquant_b200 import ops
+
+    got, want, layer, ids, w, x = run_case(4, 128, 2048, 768, 8, 3, 4, act=torch.float16, seed=3)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3
+    first = ops.moe_gemv(x.cuda(), ids.cuda(), w.cuda(), layer.gate_up, layer.down, num_experts=128)
+    for _ in range(4):
+        again = ops.moe_gemv(x.cuda(), ids.cuda(), w.cuda(), layer.gate_up, layer.down, num_experts=128)
+        assert torch.equal(first, again)
+    assert first.dtype == torch.float16
+
+
+def test_moe_skips_experts_that_are_not_local():
+    got, want, *_ = run_case(8, 16, 512, 256, 4, 4, 4, local=(4, 8))
+    assert np.linalg.norm(got - want) / (np.linalg.norm(want) + 1e-30) <= 2e-3
+
+
+def test_moe_many_tokens_on_one_expert():
+    """More than eight tokens on one expert: the expert's rows are streamed once per 8 tokens."""
+    from dynquant_b200 import ops
+    from dynquant_b200.workloads import qwen3_moe_layer
+    from oracle import oracle as O
+
+    layer = qwen3_moe_layer("cuda", seed=5, bits_gate_up=4, bits_down=3, num_experts=4, hidden=256, inter=128, topk=2)
+    tokens = 21
+    ids = torch.tensor([[0, 1 + (t % 3)] for t in range(tokens)], dtype=torch.int32)
+    w = torch.full((tokens, 2), 0.5)
+    x = torch.randn(tokens, 256, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    got = ops.moe_gemv(x.cuda(), ids.cuda(), w.cuda(), layer.gate_up, layer.down, num_experts=4,
+                       out_dtype=torch.float32).cpu().numpy()
+    want = O.c_moe(raw(x), "bf16", ids.numpy(), w.numpy(), bank_for_oracle(layer.gate_up),
+                   bank_for_oracle(layer.down), inter=128, num_experts=4, h_round="bf16")
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3
+
+
+def test_moe_rejects_bad_arguments():
+    from dynquant_b200 import ops
+    from dynquant_b200.workloads import qwen3_moe_layer, seeded_routing
+
+    layer = qwen3_moe_layer("cuda", num_experts=4, hidden=256, inter=128, topk=2)
+    ids, w = seeded_routing(65, 4, 2)
+    x = torch.randn(65, 256, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="exceeds the limit"):
+        ops.moe_gemv(x, ids.cuda(), w.cuda(), layer.gate_up, layer.down, num_experts=4)
+    ids, w = seeded_routing(2, 4, 2)
+    with pytest.raises(RuntimeError, match="folded to rows"):
+        ops.moe_gemv(x[:2].contiguous(), ids.cuda(), w.cuda(), layer.down, layer.gate_up, num_experts=4)
