@@ -322,6 +322,29 @@ ScratchLayout scratch_layout(int64_t tokens, int64_t topk, int64_t hidden, int64
   return l;
 }
 
+// Scratch for dq_moe_gemv_static: lives in the library image, one copy per GPU that loads
+// it, for as long as the process runs.  Host code must never pass this NAME to a kernel --
+// on the host it is only a stand-in for the symbol; the device address comes from
+// cudaGetSymbolAddress (see static_scratch_address below).
+static __device__ __align__(256) unsigned char g_moe_static_scratch[DQ_MOE_STATIC_SCRATCH_BYTES];
+
+// Device address of g_moe_static_scratch on the CURRENT device, looked up once per device.
+int32_t static_scratch_address(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* address[kMaxDevices] = {nullptr};
+  int device = 0;
+  DQ_CUDA(cudaGetDevice(&device));
+  DQ_REQUIRE(device >= 0 && device < kMaxDevices, "moe_gemv_static: device ordinal %d out of range", device);
+  if (address[device] == nullptr) {
+    void* ptr = nullptr;
+    DQ_CUDA(cudaGetSymbolAddress(&ptr, g_moe_static_scratch));
+    DQ_REQUIRE(ptr != nullptr, "moe_gemv_static: cudaGetSymbolAddress returned a null address");
+    address[device] = ptr;  // same value from every thread that races here
+  }
+  *out = address[device];
+  return DQ_OK;
+}
+
 template <typename Kernel>
 int32_t launch_pdl(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t stream, const MoeArgs& args,
                    const char* what) {
@@ -497,6 +520,24 @@ int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_
     DQ_CHECK_LAUNCH("moe_gemv(combine)");
   }
   return DQ_OK;
+}
+
+int32_t dq_moe_gemv_static(const void* x, int32_t x_dtype, int64_t tokens, const int32_t* topk_ids,
+                           const float* topk_w, int64_t topk, int64_t num_experts, const dq_weight* gate_up,
+                           const dq_weight* down, int64_t hidden, int64_t inter, void* y, int32_t y_dtype,
+                           void* stream) {
+  int64_t need = 0;
+  if (const int32_t rc = dq_moe_scratch_bytes(tokens, topk, hidden, inter, num_experts, x_dtype, &need)) return rc;
+  DQ_REQUIRE(need <= DQ_MOE_STATIC_SCRATCH_BYTES,
+             "moe_gemv_static: this problem needs %lld bytes of scratch but the built-in buffer holds %d "
+             "(tokens=%lld topk=%lld hidden=%lld inter=%lld experts=%lld); use dq_moe_gemv with your own scratch",
+             static_cast<long long>(need), DQ_MOE_STATIC_SCRATCH_BYTES, static_cast<long long>(tokens),
+             static_cast<long long>(topk), static_cast<long long>(hidden), static_cast<long long>(inter),
+             static_cast<long long>(num_experts));
+  void* scratch = nullptr;
+  if (const int32_t rc = dq::static_scratch_address(&scratch)) return rc;
+  return dq_moe_gemv(x, x_dtype, tokens, topk_ids, topk_w, topk, num_experts, gate_up, down, hidden, inter, y,
+                     y_dtype, scratch, DQ_MOE_STATIC_SCRATCH_BYTES, stream);
 }
 
 }  // extern "C"

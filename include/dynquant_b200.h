@@ -36,6 +36,8 @@ extern "C" {
 #define DQ_GEMV_MAX_ROWS 8
 /* Most tokens one expert may receive in a single dq_moe_* call. */
 #define DQ_MOE_MAX_TOKENS 64
+/* Size of the scratch buffer built into the library for dq_moe_gemv_static (2 MiB). */
+#define DQ_MOE_STATIC_SCRATCH_BYTES (2 * 1024 * 1024)
 
 typedef enum dq_status {
   DQ_OK = 0,
@@ -174,6 +176,34 @@ DQ_API int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const
                            const dq_weight* gate_up, const dq_weight* down, int64_t hidden,
                            int64_t inter, void* y, int32_t y_dtype, void* scratch,
                            int64_t scratch_bytes, void* stream);
+
+/* dq_moe_gemv without a scratch argument and without any allocation.  This entry point has
+ * no counterpart in the reference.
+ *
+ * Who needs it: host code that must not, or cannot, obtain device memory at call time --
+ * for example a serving worker written against this C ABI (no torch allocator in reach)
+ * that has already handed all free HBM to its KV-cache pool, where a cudaMalloc would
+ * fail or stall the device, or a caller bound to a fixed memory plan that forbids new
+ * allocations once serving has started.  Inputs and outputs are still the caller's.
+ *
+ * The scratch lives inside the library: DQ_MOE_STATIC_SCRATCH_BYTES (2 MiB) of device
+ * memory per GPU that loads the library, held until the process exits.  A problem whose
+ * dq_moe_scratch_bytes() exceeds that is rejected with DQ_ERR_INVALID and a message
+ * naming both numbers (8 tokens x top-8 of a 2048/768 expert layer needs ~0.6 MiB).
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * The first call on each device looks up the buffer's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call before any
+ * stream capture begins.  Every call on a device shares the one buffer: it still holds the
+ * previous call's routing tables and intermediates when the next call starts (each call
+ * rewrites everything it reads, nothing has to start at zero), so two calls that may
+ * overlap on the GPU -- different streams, no ordering between them -- race on it.
+ * Order them, or give the overlapping one its own scratch through dq_moe_gemv. */
+DQ_API int32_t dq_moe_gemv_static(const void* x, int32_t x_dtype, int64_t tokens,
+                                  const int32_t* topk_ids, const float* topk_w, int64_t topk,
+                                  int64_t num_experts, const dq_weight* gate_up,
+                                  const dq_weight* down, int64_t hidden, int64_t inter, void* y,
+                                  int32_t y_dtype, void* stream);
 
 #ifdef __cplusplus
 }
