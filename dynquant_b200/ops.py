@@ -302,6 +302,10 @@ def moe_gemv(
     return y
 
 
+def moe_max_tokens() -> int:
+    return int(_lib.load().dq_moe_max_tokens())
+
+
 def gemv_max_rows() -> int:
     return int(_lib.load().dq_gemv_max_rows())
 
