@@ -226,10 +226,11 @@ def run_ours(args) -> None:
     if world > 1:
         from dynquant_b200.sharded import ShardedStepRunner
 
-        runner = ShardedStepRunner(full, m, rank=rank, world=world, device=device)
+        use_graph = not args.no_graph
+        runner = ShardedStepRunner(full, m, rank=rank, world=world, device=device,
+                                   graph_mode=args.graph_mode if use_graph else None)
         step_fn = runner.run
         launches_per_step = runner.launches_per_step
-        use_graph = False
     else:
         runner = StepRunner(full, m, device=device)
         use_graph = not args.no_graph
@@ -262,7 +263,7 @@ def run_ours(args) -> None:
     # ---- end to end: activations in from pinned host memory, logits back ----
     host_in = {k: v.cpu().pin_memory() for k, v in runner.inputs.items()}
     last_name = full.modules[-1].name
-    logits_dev = runner.outputs[last_name]
+    logits_dev = runner.outputs[last_name]  # sharded runs: the gathered pieces, same bytes
     host_out = torch.empty_like(logits_dev, device="cpu").pin_memory()
     h2d = sum(v.numel() * v.element_size() for v in host_in.values())
     d2h = host_out.numel() * host_out.element_size()
@@ -315,7 +316,9 @@ def run_ours(args) -> None:
             "l2": "working set (1.1 GB of weights per step) is larger than L2; no flush needed",
             "launch": (f"cuda graph of one step, {args.graph_mode} edges, programmatic dependent launch"
                        if use_graph else "dq_gemv_sequence per step"),
-            "parallelism": "single gpu" if world == 1 else f"column-sharded x{world}, NCCL all-gather",
+            "parallelism": ("single gpu" if world == 1 else
+                            f"large layers ({', '.join(runner.sharded)}) column-sharded x{world} with an NCCL "
+                            f"all-gather, small layers computed on every rank"),
             "peak": f"{peak} GB/s ({peak_kind})",
         },
         "roofline": {

@@ -152,51 +152,56 @@ class ExpertParallelMoE:
 
 
 class ShardedStepRunner:
-    """One decode step of a :class:`~dynquant_b200.workloads.LinearStack` with every module
-    column-sharded: local GEMVs from one ``dq_gemv_sequence`` call per stage, then one
-    all-gather per stage whose outputs the next stage consumes (o_proj, gate/up, down_proj and
-    the lm_head; q/k/v feed attention head-locally and are not gathered)."""
+    """One decode step of a :class:`~dynquant_b200.workloads.LinearStack` on ``world`` GPUs.
 
-    def __init__(self, stack, m: int, *, rank: int, world: int, device, act_dtype=torch.bfloat16) -> None:
-        from . import _lib
-        from .ops import _tag, weight_descriptor
+    Large modules -- those whose per-rank slab of packed rows is still at least
+    ``shard_min_bytes`` -- are column-sharded (row slabs) and their ``[M, N/world]`` outputs
+    all-gathered over NCCL; everything smaller is computed by every rank, because a gather
+    costs more than the whole small GEMV.  The local kernels of a step replay from one CUDA
+    graph (:class:`~dynquant_b200.stack.StepRunner`); the gathers follow on the same stream.
+    """
 
-        self._lib = _lib
-        self.stack, self.m, self.rank, self.world, self.device = stack, m, rank, world, torch.device(device)
-        self.local = [column_shard(mod.weight, rank, world) for mod in stack.modules]
-        widths = {}
+    def __init__(self, stack, m: int, *, rank: int, world: int, device, act_dtype=torch.bfloat16,
+                 shard_min_bytes: int = 32 << 20, graph_mode: str | None = "dataflow") -> None:
+        from .stack import StepRunner
+        from .workloads import LinearStack, Module
+
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        modules, self.sharded = [], []
         for mod in stack.modules:
-            widths.setdefault(mod.input, mod.weight.in_features)
-        gen = torch.Generator(device=self.device).manual_seed(1234)
-        self.inputs = {n: torch.randn(m, k, device=self.device, generator=gen).to(act_dtype) for n, k in widths.items()}
-        self.pieces = [torch.empty(m, qt.num_rows, dtype=act_dtype, device=self.device) for qt in self.local]
-        self.outputs = {mod.name: torch.empty(world * m, qt.num_rows, dtype=act_dtype, device=self.device)
-                        for mod, qt in zip(stack.modules, self.local)}
-        self._jobs = (_lib.GemvJob * len(self.local))()
-        for i, (mod, qt) in enumerate(zip(stack.modules, self.local)):
-            job = self._jobs[i]
-            job.x = self.inputs[mod.input].data_ptr()
-            job.out = self.pieces[i].data_ptr()
-            job.bias = None
-            job.m, job.out_stride, job.out_col0 = m, qt.num_rows, 0
-            job.x_dtype = job.out_dtype = _tag(act_dtype, "x")
-            job.weight = weight_descriptor("gemv_sequence", qt.packed, qt.scales, qt.offsets, qt.bits,
-                                           qt.geometry.effective_group, qt.in_features)
-        self.stages = stack.stages()
-        self.launches_per_step = len(self.local)
-        self.gathers_per_step = sum(1 for st in self.stages if self._gathered(st))
-
-    def _gathered(self, stage: list[int]) -> bool:
-        leaf = self.stack.modules[stage[0]].name.rsplit(".", 1)[-1]
-        return leaf not in ("q_proj", "k_proj", "v_proj")
+            qt = mod.weight
+            if world > 1 and qt.num_rows % world == 0 and qt.nbytes // world >= shard_min_bytes:
+                modules.append(Module(mod.name, column_shard(qt, rank, world), mod.input))
+                self.sharded.append(mod.name)
+            else:
+                modules.append(mod)
+        self.local_stack = LinearStack(stack.name + f"[{rank}/{world}]", stack.hidden, stack.intermediate, modules,
+                                       stack.bit_map)
+        self.runner = StepRunner(self.local_stack, m, act_dtype=act_dtype, device=self.device)
+        self.inputs = self.runner.inputs
+        self.outputs = dict(self.runner.outputs)
+        self._gathers = []
+        for name in self.sharded:
+            piece = self.runner.outputs[name]
+            full = torch.empty(world * m, piece.shape[1], dtype=piece.dtype, device=self.device)
+            self._gathers.append((piece, full))
+            self.outputs[name] = full  # [world*m, N/world]: rank-major pieces of the [m, N] result
+        self.launches_per_step = self.runner.launches_per_step
+        self.gathers_per_step = len(self._gathers)
+        self.graph_mode = graph_mode
+        if graph_mode is not None:
+            self.runner.capture(graph_mode)
 
     def run(self) -> None:
-        lib = self._lib.load()
-        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        size = ctypes.sizeof(self._lib.GemvJob)
-        for stage in self.stages:
-            jobs = ctypes.cast(ctypes.byref(self._jobs, stage[0] * size), ctypes.POINTER(self._lib.GemvJob))
-            self._lib.check(lib.dq_gemv_sequence(jobs, len(stage), stream))
-            if self._gathered(stage):
-                for idx in stage:
-                    dist.all_gather_into_tensor(self.outputs[self.stack.modules[idx].name], self.pieces[idx])
+        if self.graph_mode is not None:
+            self.runner.replay()
+        else:
+            self.runner.run()
+        for piece, full in self._gathers:
+            dist.all_gather_into_tensor(full, piece)
+
+    def gathered(self, name: str) -> torch.Tensor:
+        """The full ``[m, N]`` output of a sharded module, reassembled from the rank-major pieces."""
+        full = self.outputs[name]
+        m = full.shape[0] // self.world
+        return full.view(self.world, m, -1).permute(1, 0, 2).reshape(m, -1)

@@ -38,7 +38,8 @@ def test_linear_module_equals_dense_reconstruction(bits):
         x = torch.randn(*shape, dtype=torch.float16, device="cuda")
         got = mod(x)
         assert got.shape == (*shape[:-1], 96) and got.dtype == torch.float16
-        torch.testing.assert_close(got.float().cpu(), dense_ref(x, qt, bias), rtol=2e-2, atol=2e-2)
+        want = dense_ref(x, qt, bias)
+        torch.testing.assert_close(got.float().cpu(), want, rtol=2e-2, atol=5e-3 * float(want.abs().max()))
 
 
 def test_embedding_lookup_and_tied_table():
@@ -76,7 +77,10 @@ def test_fused_layer_with_mixed_widths_and_bias_in_one_call():
         got = method.apply(layer, x, bias)
         want = torch.cat([dense_ref(x, qt) for qt in parts], dim=-1) + bias.float().cpu()
         assert got.shape == (m, 384) and got.dtype == torch.bfloat16
-        torch.testing.assert_close(got.float().cpu(), want, rtol=2e-2, atol=3e-2)
+        # bf16 output: half an ulp of the largest value; the > 8-row path also rounds the
+        # dequantized weight to bf16 before the dense matmul, like the reference's torch path
+        atol = (2e-2 if m > 8 else 5e-3) * float(want.abs().max())
+        torch.testing.assert_close(got.float().cpu(), want, rtol=2e-2, atol=atol)
 
 
 def test_moe_method_matches_the_oracle():
