@@ -34,6 +34,7 @@
 #include <cstdlib>
 
 #include "dq_gemv.cuh"
+#include "dq_gemv_mma_short.cuh"
 #include "dq_gemv_mma_stream.cuh"
 #include "dq_mma_plan.cuh"
 #include "dq_mma_stage.cuh"
@@ -561,6 +562,68 @@ int32_t try_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int step
   return rc;
 }
 
+// ---- short-matrix kernel (dq_gemv_mma_short.cuh) ----
+
+template <int BITS>
+int32_t try_short(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps, cudaStream_t stream_h,
+                  bool* taken) {
+  *taken = false;
+  static const bool off = [] {
+    const char* v = std::getenv("DQ_B200_NO_SHORT");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  if (off || a.group_values != kStepValues) return DQ_OK;
+  if (reinterpret_cast<uintptr_t>(a.scales) % 4 != 0 || reinterpret_cast<uintptr_t>(a.offsets) % 4 != 0) return DQ_OK;
+  const int max_steps = BITS == 8 ? 4 : shortk::kMaxSteps;
+  shortk::Params p = {};
+  p.steps = steps;
+  p.tiles = tiles;
+  p.kw = 0;
+  for (int kw = shortk::kWarps; kw >= 1; kw /= 2) {  // slice as finely as the step count allows
+    if (steps % (2 * kw) == 0 && steps / kw <= max_steps) {
+      p.kw = kw;
+      break;
+    }
+  }
+  if (p.kw == 0) return DQ_OK;
+  p.rw = shortk::kWarps / p.kw;
+  p.steps_per_warp = steps / p.kw;
+  p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
+  p.m_stride_u4 = p.steps_per_warp * (BITS == 8 ? 32 : 16) + 4;
+  const size_t smem = shortk::smem_bytes<BITS>(a.m, p);
+  if (smem > static_cast<size_t>(dev.max_smem_optin)) return DQ_OK;
+  const int grid = static_cast<int>(ceil_div(tiles, p.rw));
+  int32_t rc = DQ_OK;
+  auto run = [&](auto kernel) -> int32_t {
+    if (smem > 48 * 1024) {
+      DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    }
+    int per_sm = 0;
+    DQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, shortk::kThreads, smem));
+    if (grid > per_sm * dev.sm_count) return DQ_OK;  // more than one wave: not a short matrix
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(shortk::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream_h;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
+    DQ_CHECK_LAUNCH("gemv");
+    *taken = true;
+    return DQ_OK;
+  };
+  const bool xbf = a.x_dtype == DQ_BF16, mbf = a.meta_dtype == DQ_BF16;
+  if (xbf && mbf) rc = run(shortk::gemv_mma_short_kernel<BITS, true, true>);
+  else if (xbf) rc = run(shortk::gemv_mma_short_kernel<BITS, true, false>);
+  else if (mbf) rc = run(shortk::gemv_mma_short_kernel<BITS, false, true>);
+  else rc = run(shortk::gemv_mma_short_kernel<BITS, false, false>);
+  return rc;
+}
+
 }  // namespace
 
 bool mma_path_supports(const GemvArgs& a, int bits) {
@@ -601,6 +664,21 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
         break;
       default:
         rc = try_stream<8>(a, *dev, p.tiles, p.steps, stream, &taken);
+        break;
+    }
+    if (taken || rc != DQ_OK) return rc;
+    switch (bits) {
+      case 2:
+        rc = try_short<2>(a, *dev, p.tiles, p.steps, stream, &taken);
+        break;
+      case 3:
+        rc = try_short<3>(a, *dev, p.tiles, p.steps, stream, &taken);
+        break;
+      case 4:
+        rc = try_short<4>(a, *dev, p.tiles, p.steps, stream, &taken);
+        break;
+      default:
+        rc = try_short<8>(a, *dev, p.tiles, p.steps, stream, &taken);
         break;
     }
     if (taken || rc != DQ_OK) return rc;
@@ -663,3 +741,4 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
 }
 
 }  // namespace dq
+

@@ -13,10 +13,35 @@
 
 namespace dq {
 
+// `raw` (optional): shared-memory scratch of at least m * in_features 16-bit elements.  When
+// given, and the activation is 16-bit and 16-byte aligned, the activation is first copied
+// there with 128-bit loads -- one round trip to L2 for the whole CTA -- and the fragments are
+// built from shared memory; otherwise every lane gathers its values from global memory.
 template <int BITS, bool XBF16>
 __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, int m_stride_u4, uint4* xb,
                                                  float* xsum, float* xneg, int tid, int nthreads,
-                                                 const int* row_map = nullptr) {
+                                                 const int* row_map = nullptr, unsigned short* raw = nullptr) {
+  const bool use_raw = raw != nullptr && a.x_dtype != DQ_F32 && (a.in_features & 7) == 0 &&
+                       (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
+  if (use_raw) {
+    const int vec_per_row = a.in_features >> 3;
+    for (int i = tid; i < a.m * vec_per_row; i += nthreads) {
+      const int m = i / vec_per_row;
+      const int v = i - m * vec_per_row;
+      const int64_t src_row = row_map != nullptr ? row_map[m] : m;
+      reinterpret_cast<uint4*>(raw)[i] =
+          __ldg(reinterpret_cast<const uint4*>(a.x) + src_row * vec_per_row + v);
+    }
+    __syncthreads();
+  }
+  auto fetch = [&](int m, int64_t src_row, int k) -> float {
+    if (use_raw) {
+      const unsigned short h = raw[m * a.in_features + k];
+      return a.x_dtype == DQ_BF16 ? __uint_as_float(static_cast<uint32_t>(h) << 16)
+                                  : __half2float(__ushort_as_half(h));
+    }
+    return load_f32(a.x, src_row * a.in_features + k, a.x_dtype);
+  };
   using Plan = MmaPlan<BITS>;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
@@ -28,28 +53,84 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
   const int per_warp = kWarp / LANES;      // (m, s) items per warp iteration
   const int nitems = a.m * steps;
   const int q = l >> 2, tt = l & 3;
+  // this lane always builds the same four slots: resolve them once, not once per item
+  int off_lo[4], off_hi[4];
+  float mul_lo[4], mul_hi[4];
+  bool count_x[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const Slot sl = Plan::slot(4 * q + r);
+    off_lo[r] = 32 * tt + sl.v_lo;
+    off_hi[r] = 32 * tt + sl.v_hi;
+    mul_lo[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_lo) << 23);  // exact powers of two
+    mul_hi[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_hi) << 23);
+    // every value of the unit appears in exactly one slot, except at 8-bit where the high
+    // nibble's slot (e = 4) repeats it: count x once
+    count_x[r] = BITS != 8 || sl.e_lo == 0;
+  }
+  if constexpr (XBF16) {
+    if (use_raw && a.x_dtype == DQ_BF16) {
+      // bf16 from the raw copy.  Widening is a shift, the power-of-two scaling an exact fp32
+      // multiply, and narrowing back takes the high half (nothing to round).
+      const bool whole = (a.in_features & 127) == 0;  // no pad tail: no bounds checks
+      for (int base = (tid >> 5) * per_warp; base < nitems; base += (nthreads >> 5) * per_warp) {
+        const int idx = min(base + sub, nitems - 1);
+        const bool live = base + sub < nitems;
+        const int m = idx / steps;
+        const int s = idx - m * steps;
+        const unsigned short* row = raw + m * a.in_features + s * 128;
+        const int left = a.in_features - s * 128;
+        float sx = 0.0f, sb = 0.0f;
+        uint32_t regs[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          uint32_t lo = row[whole || off_lo[r] < left ? off_lo[r] : 0];
+          uint32_t hi = row[whole || off_hi[r] < left ? off_hi[r] : 0];
+          if (!whole) {
+            lo = off_lo[r] < left ? lo : 0u;
+            hi = off_hi[r] < left ? hi : 0u;
+          }
+          const float flo = __uint_as_float(lo << 16), fhi = __uint_as_float(hi << 16);
+          if (count_x[r]) sx += flo + fhi;
+          const float slo = flo * mul_lo[r], shi = fhi * mul_hi[r];
+          sb += slo + shi;
+          regs[r] = __byte_perm(__float_as_uint(slo), __float_as_uint(shi), 0x7632);  // high halves
+        }
+        if (live) {
+          xb[m * m_stride_u4 + (s * QU + q) * 4 + tt] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
+        }
+#pragma unroll
+        for (int d = LANES / 2; d > 0; d >>= 1) {
+          sx += __shfl_xor_sync(0xffffffffu, sx, d);
+          sb += __shfl_xor_sync(0xffffffffu, sb, d);
+        }
+        if (live && l == 0) {
+          xsum[s * 8 + m] = sx;
+          xneg[s * 8 + m] = -kMagicValue * sb;
+        }
+      }
+      goto fill_zeros;
+    }
+  }
   for (int base = (tid >> 5) * per_warp; base < nitems; base += (nthreads >> 5) * per_warp) {
     const int idx = base + sub;
     const bool live = idx < nitems;
     const int m = live ? idx / steps : 0;
     const int s = live ? idx - m * steps : 0;
     const int64_t src_row = row_map != nullptr ? row_map[m] : m;  // gathered activation rows (MoE)
-    const int kbase = s * 128 + 32 * tt;
+    const int kbase = s * 128;
     float sx = 0.0f, sb = 0.0f;
     uint32_t regs[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const Slot sl = Plan::slot(4 * q + r);
-      const int k_lo = kbase + sl.v_lo;
-      const int k_hi = kbase + sl.v_hi;
+      const int k_lo = kbase + off_lo[r];
+      const int k_hi = kbase + off_hi[r];
       float lo = 0.0f, hi = 0.0f;
-      if (live && k_lo < a.in_features) lo = load_f32(a.x, src_row * a.in_features + k_lo, a.x_dtype);
-      if (live && k_hi < a.in_features) hi = load_f32(a.x, src_row * a.in_features + k_hi, a.x_dtype);
-      // every value of the unit appears in exactly one slot, except at 8-bit where the high
-      // nibble's slot (e = 4) repeats it: count x once
-      if (BITS != 8 || sl.e_lo == 0) sx += lo + hi;
-      lo *= __uint_as_float(static_cast<uint32_t>(127 + sl.e_lo) << 23);  // exact: a power of two
-      hi *= __uint_as_float(static_cast<uint32_t>(127 + sl.e_hi) << 23);
+      if (live && k_lo < a.in_features) lo = fetch(m, src_row, k_lo);
+      if (live && k_hi < a.in_features) hi = fetch(m, src_row, k_hi);
+      if (count_x[r]) sx += lo + hi;
+      lo *= mul_lo[r];
+      hi *= mul_hi[r];
       uint32_t lo16, hi16;
       if constexpr (XBF16) {
         const __nv_bfloat16 l16 = __float2bfloat16_rn(lo), h16 = __float2bfloat16_rn(hi);
@@ -75,6 +156,7 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
       xneg[s * 8 + m] = -kMagicValue * sb;
     }
   }
+fill_zeros:
   // what lanes of absent activation rows read: a block of zero fragments, zero sums
   for (int idx = tid; idx < QU * 4; idx += nthreads) {
     xb[a.m * m_stride_u4 + idx] = make_uint4(0u, 0u, 0u, 0u);
@@ -87,6 +169,113 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
       }
     }
   }
+}
+
+// Warp-local variant for the short-matrix kernel: a warp stages only the steps of its own
+// slice of the reduction axis, into shared memory only it reads, with __syncwarp as the
+// only synchronisation -- no CTA-wide barrier sits between the arrival of the activation and
+// the first mma.  Layouts (all warp-private):
+//   raw   [nsteps * 128] 16-bit scratch (one activation row at a time)
+//   xb    [m][nsteps * QU*4 (+4 pad)] uint4, then a zero block of QU*4
+//   xsum / xneg  [nsteps][8]
+template <int BITS, bool XBF16>
+__device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin, int nsteps, int m_stride_u4,
+                                                 unsigned short* raw, uint4* xb, float* xsum, float* xneg,
+                                                 int lane) {
+  using Plan = MmaPlan<BITS>;
+  constexpr int NA = Plan::kARegs;
+  constexpr int QU = NA / 4;
+  constexpr int LANES = QU * 4;
+  constexpr int PER = kWarp / LANES;  // steps built per round
+  constexpr float kMagicValue = XBF16 ? 128.0f : 0.0f;
+  const int sub = lane / LANES;
+  const int l = lane - sub * LANES;
+  const int q = l >> 2, tt = l & 3;
+  int off_lo[4], off_hi[4];
+  float mul_lo[4], mul_hi[4];
+  bool count_x[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const Slot sl = Plan::slot(4 * q + r);
+    off_lo[r] = 32 * tt + sl.v_lo;
+    off_hi[r] = 32 * tt + sl.v_hi;
+    mul_lo[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_lo) << 23);
+    mul_hi[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_hi) << 23);
+    count_x[r] = BITS != 8 || sl.e_lo == 0;
+  }
+  const int k0 = s_begin * 128;
+  const bool vec_ok = a.x_dtype != DQ_F32 && (a.in_features & 7) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
+  for (int m = 0; m < a.m; ++m) {
+    // ---- this row's slice into the warp's scratch, as 16-bit values ----
+    if (vec_ok) {
+      const uint4* src = reinterpret_cast<const uint4*>(a.x) + (static_cast<int64_t>(m) * a.in_features + k0) / 8;
+      for (int v = lane; v < nsteps * 16; v += kWarp) {
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (k0 + v * 8 < a.in_features) val = __ldg(src + v);
+        reinterpret_cast<uint4*>(raw)[v] = val;
+      }
+    } else {
+      for (int v = lane; v < nsteps * 128; v += kWarp) {
+        const int k = k0 + v;
+        const float f = k < a.in_features ? load_f32(a.x, static_cast<int64_t>(m) * a.in_features + k, a.x_dtype) : 0.0f;
+        raw[v] = XBF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f)) : __half_as_ushort(__float2half_rn(f));
+      }
+    }
+    __syncwarp();
+    // ---- fragments and sums, PER steps per round ----
+    for (int base = 0; base < nsteps; base += PER) {
+      const int j = min(base + sub, nsteps - 1);
+      const bool live = base + sub < nsteps;
+      const unsigned short* row = raw + j * 128;
+      float sx = 0.0f, sb = 0.0f;
+      uint32_t regs[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const uint32_t lo = row[off_lo[r]], hi = row[off_hi[r]];
+        float flo, fhi;
+        if constexpr (XBF16) {
+          flo = __uint_as_float(lo << 16), fhi = __uint_as_float(hi << 16);
+        } else {
+          flo = __half2float(__ushort_as_half(static_cast<unsigned short>(lo)));
+          fhi = __half2float(__ushort_as_half(static_cast<unsigned short>(hi)));
+        }
+        if (count_x[r]) sx += flo + fhi;
+        const float slo = flo * mul_lo[r], shi = fhi * mul_hi[r];  // exact: powers of two
+        if constexpr (XBF16) {
+          sb += slo + shi;
+          regs[r] = __byte_perm(__float_as_uint(slo), __float_as_uint(shi), 0x7632);  // the high halves
+        } else {
+          regs[r] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(slo))) |
+                    (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(shi))) << 16);
+        }
+      }
+      if (live) {
+        xb[m * m_stride_u4 + (j * QU + q) * 4 + tt] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
+      }
+#pragma unroll
+      for (int d = LANES / 2; d > 0; d >>= 1) {
+        sx += __shfl_xor_sync(0xffffffffu, sx, d);
+        sb += __shfl_xor_sync(0xffffffffu, sb, d);
+      }
+      if (live && l == 0) {
+        xsum[j * 8 + m] = sx;
+        xneg[j * 8 + m] = -kMagicValue * sb;
+      }
+    }
+    __syncwarp();  // everyone is done with raw before the next row overwrites it
+  }
+  for (int idx = lane; idx < QU * 4; idx += kWarp) {
+    xb[a.m * m_stride_u4 + idx] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (a.m < 8) {
+    for (int idx = lane; idx < nsteps * 8; idx += kWarp) {
+      if ((idx & 7) >= a.m) {
+        xsum[idx] = 0.0f;
+        xneg[idx] = 0.0f;
+      }
+    }
+  }
+  __syncwarp();
 }
 
 }  // namespace dq
