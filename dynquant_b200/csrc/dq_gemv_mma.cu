@@ -575,48 +575,58 @@ int32_t try_short(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps
   if (off || a.group_values != kStepValues) return DQ_OK;
   if (reinterpret_cast<uintptr_t>(a.scales) % 4 != 0 || reinterpret_cast<uintptr_t>(a.offsets) % 4 != 0) return DQ_OK;
   const int max_steps = BITS == 8 ? 4 : shortk::kMaxSteps;
+  if (a.num_groups % 2 != 0) return DQ_OK;  // rows of scales must start on 4-byte words
+  // 16-byte copies of whole steps: rows and the tensor itself must be 16-byte aligned
+  if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) {
+    return DQ_OK;
+  }
+  static const int force_warps = [] { const char* v = std::getenv("DQ_B200_SHORT_WARPS"); return v ? std::atoi(v) : 0; }();
   shortk::Params p = {};
   p.steps = steps;
   p.tiles = tiles;
-  p.kw = 0;
-  for (int kw = shortk::kWarps; kw >= 1; kw /= 2) {  // slice as finely as the step count allows
-    if (steps % (2 * kw) == 0 && steps / kw <= max_steps) {
-      p.kw = kw;
-      break;
-    }
-  }
-  if (p.kw == 0) return DQ_OK;
-  p.rw = shortk::kWarps / p.kw;
-  p.steps_per_warp = steps / p.kw;
   p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
-  p.m_stride_u4 = p.steps_per_warp * (BITS == 8 ? 32 : 16) + 4;
-  const size_t smem = shortk::smem_bytes<BITS>(a.m, p);
-  if (smem > static_cast<size_t>(dev.max_smem_optin)) return DQ_OK;
-  const int grid = static_cast<int>(ceil_div(tiles, p.rw));
+  const bool xbf = a.x_dtype == DQ_BF16, mbf = a.meta_dtype == DQ_BF16;
   int32_t rc = DQ_OK;
   auto run = [&](auto kernel) -> int32_t {
-    if (smem > 48 * 1024) {
-      DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    // Candidate CTA shapes, finest slicing of the reduction axis first: the whole grid must
+    // be resident at once and every slice must fit the per-warp step limit.
+    for (int warps = (force_warps ? force_warps : 8); warps >= 8; warps /= 2) {
+      for (int kw = warps; kw >= 1; kw /= 2) {
+        if (steps % kw != 0 || steps / kw > max_steps) continue;
+        p.kw = kw;
+        p.rw = warps / kw;
+        p.steps_per_warp = steps / kw;
+        p.meta_words = (p.steps_per_warp + 2) / 2;
+        p.m_stride_u4 = p.steps_per_warp * (BITS == 8 ? 32 : 16) + 4;
+        const size_t smem = shortk::smem_bytes<BITS>(a.m, p);
+        if (smem > static_cast<size_t>(dev.max_smem_optin)) continue;
+        const int threads = warps * kWarp;
+        const int grid = static_cast<int>(ceil_div(tiles, p.rw));
+        if (smem > 48 * 1024) {
+          DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        }
+        int per_sm = 0;
+        DQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem));
+        if (grid > per_sm * dev.sm_count) continue;  // more than one wave
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(grid));
+        cfg.blockDim = dim3(static_cast<unsigned>(threads));
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream_h;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 1 : 0;
+        DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
+        DQ_CHECK_LAUNCH("gemv");
+        *taken = true;
+        return DQ_OK;
+      }
+      if (force_warps) break;
     }
-    int per_sm = 0;
-    DQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, shortk::kThreads, smem));
-    if (grid > per_sm * dev.sm_count) return DQ_OK;  // more than one wave: not a short matrix
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(grid));
-    cfg.blockDim = dim3(shortk::kThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream_h;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
-    DQ_CHECK_LAUNCH("gemv");
-    *taken = true;
-    return DQ_OK;
+    return DQ_OK;  // not a short matrix
   };
-  const bool xbf = a.x_dtype == DQ_BF16, mbf = a.meta_dtype == DQ_BF16;
   if (xbf && mbf) rc = run(shortk::gemv_mma_short_kernel<BITS, true, true>);
   else if (xbf) rc = run(shortk::gemv_mma_short_kernel<BITS, true, false>);
   else if (mbf) rc = run(shortk::gemv_mma_short_kernel<BITS, false, true>);

@@ -27,15 +27,16 @@
 namespace dq {
 namespace shortk {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * kWarp;
+constexpr int kMaxWarps = 16;  // a CTA is 8 or 16 warps (blockDim.x)
+constexpr int kMaxThreads = kMaxWarps * kWarp;
 constexpr int kMaxSteps = 8;  // per warp
 
 struct Params {
   int steps;           // padded K / 128
   int tiles;           // ceil(rows / 16)
-  int rw, kw;          // rw * kw == kWarps
-  int steps_per_warp;  // even, <= kMaxSteps
+  int rw, kw;          // rw * kw == warps of the CTA
+  int steps_per_warp;  // <= kMaxSteps
+  int meta_words;      // 4-byte words of scales (= of offsets) a warp copies per row
   int m_stride_u4;     // uint4 per activation row of a WARP's staged fragments
   uint32_t magic;
 };
@@ -52,19 +53,45 @@ __host__ __device__ inline int warp_stage_bytes(int m, int steps_per_warp, int m
   return steps_per_warp * 256 + (m * m_stride_u4 + aregs) * 16 + steps_per_warp * 8 * 4 * 2;
 }
 
-// Shared memory: [weights: steps_per_warp][2 rows][threads][UNIT] [meta: steps_per_warp/2][threads][4 B]
+// Shared memory: [weights: steps_per_warp][2 rows][threads][UNIT] [meta: meta_words][threads][4 B]
 //                [red] [per-warp staging areas]
 template <int BITS>
 inline size_t smem_bytes(int m, const Params& p) {
-  size_t bytes = static_cast<size_t>(p.steps_per_warp) * 2 * kThreads * unit_bytes<BITS>();
-  bytes += static_cast<size_t>(p.steps_per_warp / 2) * kThreads * 4;
+  const int threads = p.rw * p.kw * kWarp;
+  size_t bytes = static_cast<size_t>(p.steps_per_warp) * 2 * threads * unit_bytes<BITS>();
+  bytes += static_cast<size_t>(p.meta_words) * threads * 4;
   bytes += static_cast<size_t>(p.kw) * p.rw * 16 * 8 * 4;
-  bytes += static_cast<size_t>(kWarps) * warp_stage_bytes<BITS>(m, p.steps_per_warp, p.m_stride_u4);
+  bytes += static_cast<size_t>(p.rw * p.kw) * warp_stage_bytes<BITS>(m, p.steps_per_warp, p.m_stride_u4);
   return bytes;
 }
 
+// One step of eight rows (8 rows x 4 units) global -> shared, as 16-byte pieces.
+//
+// In shared memory a warp's block for (step, row half) is 32 consecutive units, lane l's
+// unit at l * UNIT -- which is also the order of the bytes in global memory row by row:
+// row g holds units 4g..4g+3.  So the block is copied as 2*UNIT pieces of 16 bytes, piece p
+// coming from row p / (UNIT/4), regardless of the unit size: at 3-bit one 16-byte copy per
+// lane (24 lanes) replaces three 4-byte ones, at 2-bit 16 lanes replace 32.
+template <int BITS>
+__device__ __forceinline__ void copy_block(uint32_t dst_block, const uint32_t* __restrict__ packed,
+                                           int64_t words_per_row, int row0, int last_row, int word0, int lane) {
+  constexpr int UNIT = unit_bytes<BITS>();
+  constexpr int PIECES = 2 * UNIT;       // 16-byte pieces in the block
+  constexpr int PER_ROW = UNIT / 4;      // pieces per row
+#pragma unroll
+  for (int p0 = 0; p0 < PIECES; p0 += kWarp) {
+    const int p = p0 + lane;
+    if (PIECES % kWarp == 0 || p < PIECES) {
+      const int g = p / PER_ROW;
+      const int part = p - g * PER_ROW;
+      const int row = min(row0 + g, last_row);
+      stream::cp_async_n<16>(dst_block + p * 16, packed + row * words_per_row + word0 + part * 4);
+    }
+  }
+}
+
 template <int BITS, bool XBF16, bool MBF16>
-__global__ void __launch_bounds__(kThreads, 4) gemv_mma_short_kernel(const GemvArgs a, const Params p) {
+__global__ void __launch_bounds__(kMaxThreads, 2) gemv_mma_short_kernel(const GemvArgs a, const Params p) {
   using Plan = MmaPlan<BITS>;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
@@ -72,9 +99,10 @@ __global__ void __launch_bounds__(kThreads, 4) gemv_mma_short_kernel(const GemvA
   constexpr int STEP_WORDS = 4 * BITS;
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int kThreads = blockDim.x;
   unsigned char* wbuf = smem_raw;
   unsigned char* mbuf = wbuf + p.steps_per_warp * 2 * kThreads * UNIT;
-  float* red = reinterpret_cast<float*>(mbuf + (p.steps_per_warp / 2) * kThreads * 4);
+  float* red = reinterpret_cast<float*>(mbuf + p.meta_words * kThreads * 4);
   const int tid = threadIdx.x;
   const int lane = tid & (kWarp - 1);
   const int warp = tid >> 5;
@@ -100,22 +128,26 @@ __global__ void __launch_bounds__(kThreads, 4) gemv_mma_short_kernel(const GemvA
 
   // ---- every byte this warp will decode, requested now ----
   if (tile_live && nsteps > 0) {
-    const uint32_t wdst = static_cast<uint32_t>(__cvta_generic_to_shared(wbuf)) + tid * UNIT;
-    const uint32_t* wa = a.packed + static_cast<int64_t>(ld_a) * a.words_per_row + s_begin * STEP_WORDS + t * BITS;
-    const uint32_t* wb = a.packed + static_cast<int64_t>(ld_b) * a.words_per_row + s_begin * STEP_WORDS + t * BITS;
+    const uint32_t wdst = static_cast<uint32_t>(__cvta_generic_to_shared(wbuf)) + (tid - lane) * UNIT;
 #pragma unroll 1
     for (int j = 0; j < nsteps; ++j) {
-      stream::copy_unit<BITS>(wdst + (j * 2 + 0) * (kThreads * UNIT), wa + j * STEP_WORDS);
-      stream::copy_unit<BITS>(wdst + (j * 2 + 1) * (kThreads * UNIT), wb + j * STEP_WORDS);
+      const int word0 = (s_begin + j) * STEP_WORDS;
+      copy_block<BITS>(wdst + (j * 2 + 0) * (kThreads * UNIT), a.packed, a.words_per_row, tile * 16, a.rows - 1,
+                       word0, lane);
+      copy_block<BITS>(wdst + (j * 2 + 1) * (kThreads * UNIT), a.packed, a.words_per_row, tile * 16 + 8,
+                       a.rows - 1, word0, lane);
     }
     // lane t of a quad fetches array t: scale(row a), offset(row a), scale(row b), offset(row b)
     if (has_off || (t & 1) == 0) {
       const unsigned short* arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
-      const unsigned short* src = arr + static_cast<int64_t>((t & 2) ? ld_b : ld_a) * a.num_groups + s_begin;
+      // whole 4-byte words covering steps [s_begin, s_begin + nsteps): start at the even step below
+      const int s_even = s_begin & ~1;
+      const unsigned short* src = arr + static_cast<int64_t>((t & 2) ? ld_b : ld_a) * a.num_groups + s_even;
       const uint32_t mdst = static_cast<uint32_t>(__cvta_generic_to_shared(mbuf)) + tid * 4;
+      const int words = (s_begin + nsteps - s_even + 1) >> 1;
 #pragma unroll 1
-      for (int j = 0; j < nsteps; j += 2) {
-        stream::cp_async_n<4>(mdst + (j / 2) * (kThreads * 4), src + j);
+      for (int w = 0; w < words; ++w) {
+        stream::cp_async_n<4>(mdst + w * (kThreads * 4), src + 2 * w);
       }
     }
   }
@@ -164,8 +196,10 @@ __global__ void __launch_bounds__(kThreads, 4) gemv_mma_short_kernel(const GemvA
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) d[i] += e[i];
-      // metadata of step j: halfword (j & 1) of word j/2 of each of the quad's four arrays
-      const unsigned short* mrow = msrc + (j / 2) * (kThreads * 2) + (j & 1);
+      // metadata of step j: halfword jj & 1 of word jj / 2 of each of the quad's four arrays,
+      // jj counted from the even step at or below s_begin
+      const int jj = j + (s_begin & 1);
+      const unsigned short* mrow = msrc + (jj / 2) * (kThreads * 2) + (jj & 1);
       auto meta = [&](int i) -> float {
         const unsigned short raw = mrow[i * 2];
         if constexpr (MBF16) {
