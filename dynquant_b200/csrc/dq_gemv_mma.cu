@@ -497,10 +497,17 @@ bool stream_ok(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps) {
     return v != nullptr && v[0] != '\0' && v[0] != '0';
   }();
   if (off) return false;
-  // Measured on B200 (profiles/): the cp.async ring wins where a lane's unit is 32 bytes
-  // (8-bit); at 2/3/4-bit its extra shared-memory traffic costs more than the occupancy
-  // it buys and the register ring of gemv_mma_kernel<FAST> is faster.
-  if (BITS != 8) return false;
+  // Measured on B200 (profiles/): with 16-byte block copies the cp.async ring is as fast or
+  // faster than the register ring of gemv_mma_kernel<FAST> at 3, 4 and 8 bits (it fits three
+  // CTAs per SM); at 2 bits the two are within noise and the register ring is kept.
+  static const bool all_widths = [] {
+    const char* v = std::getenv("DQ_B200_STREAM_ALL");
+    return v != nullptr && v[0] == '1';
+  }();
+  if (BITS == 2 && !all_widths) return false;
+  if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) {
+    return false;  // whole steps are copied in 16-byte pieces
+  }
   if (a.group_values != kStepValues || steps % C::P != 0 || a.num_groups % C::P != 0) return false;
   if (tiles < dev.sm_count * stream::kWarps) return false;
   const auto align = static_cast<uintptr_t>(C::META_BYTES);

@@ -65,31 +65,6 @@ inline size_t smem_bytes(int m, const Params& p) {
   return bytes;
 }
 
-// One step of eight rows (8 rows x 4 units) global -> shared, as 16-byte pieces.
-//
-// In shared memory a warp's block for (step, row half) is 32 consecutive units, lane l's
-// unit at l * UNIT -- which is also the order of the bytes in global memory row by row:
-// row g holds units 4g..4g+3.  So the block is copied as 2*UNIT pieces of 16 bytes, piece p
-// coming from row p / (UNIT/4), regardless of the unit size: at 3-bit one 16-byte copy per
-// lane (24 lanes) replaces three 4-byte ones, at 2-bit 16 lanes replace 32.
-template <int BITS>
-__device__ __forceinline__ void copy_block(uint32_t dst_block, const uint32_t* __restrict__ packed,
-                                           int64_t words_per_row, int row0, int last_row, int word0, int lane) {
-  constexpr int UNIT = unit_bytes<BITS>();
-  constexpr int PIECES = 2 * UNIT;       // 16-byte pieces in the block
-  constexpr int PER_ROW = UNIT / 4;      // pieces per row
-#pragma unroll
-  for (int p0 = 0; p0 < PIECES; p0 += kWarp) {
-    const int p = p0 + lane;
-    if (PIECES % kWarp == 0 || p < PIECES) {
-      const int g = p / PER_ROW;
-      const int part = p - g * PER_ROW;
-      const int row = min(row0 + g, last_row);
-      stream::cp_async_n<16>(dst_block + p * 16, packed + row * words_per_row + word0 + part * 4);
-    }
-  }
-}
-
 template <int BITS, bool XBF16, bool MBF16>
 __global__ void __launch_bounds__(kMaxThreads, 2) gemv_mma_short_kernel(const GemvArgs a, const Params p) {
   using Plan = MmaPlan<BITS>;
@@ -132,9 +107,9 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_mma_short_kernel(const Ge
 #pragma unroll 1
     for (int j = 0; j < nsteps; ++j) {
       const int word0 = (s_begin + j) * STEP_WORDS;
-      copy_block<BITS>(wdst + (j * 2 + 0) * (kThreads * UNIT), a.packed, a.words_per_row, tile * 16, a.rows - 1,
+      stream::copy_block<BITS>(wdst + (j * 2 + 0) * (kThreads * UNIT), a.packed, a.words_per_row, tile * 16, a.rows - 1,
                        word0, lane);
-      copy_block<BITS>(wdst + (j * 2 + 1) * (kThreads * UNIT), a.packed, a.words_per_row, tile * 16 + 8,
+      stream::copy_block<BITS>(wdst + (j * 2 + 1) * (kThreads * UNIT), a.packed, a.words_per_row, tile * 16 + 8,
                        a.rows - 1, word0, lane);
     }
     // lane t of a quad fetches array t: scale(row a), offset(row a), scale(row b), offset(row b)

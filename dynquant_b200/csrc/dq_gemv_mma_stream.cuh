@@ -66,6 +66,32 @@ __device__ __forceinline__ void copy_unit(uint32_t dst, const uint32_t* src) {
   }
 }
 
+// One step of eight rows (8 rows x 4 units of `4*BITS` bytes) global -> shared, as 16-byte pieces.
+//
+// In shared memory a warp's block for (step, row half) is 32 consecutive units, lane l's
+// unit at l * UNIT -- which is also the order of the bytes in global memory row by row:
+// row g holds units 4g..4g+3.  So the block is copied as 2*UNIT pieces of 16 bytes, piece p
+// coming from row p / (UNIT/4), whatever the unit size: at 3-bit one 16-byte copy per lane
+// (24 lanes) replaces three 4-byte ones, at 2-bit 16 lanes replace 32.  A lane later reads a
+// unit another lane copied, so a __syncwarp must follow the cp.async wait.
+template <int BITS>
+__device__ __forceinline__ void copy_block(uint32_t dst_block, const uint32_t* __restrict__ packed,
+                                           int64_t words_per_row, int row0, int last_row, int word0, int lane) {
+  constexpr int UNIT = 4 * BITS;
+  constexpr int PIECES = 2 * UNIT;   // 16-byte pieces in the block
+  constexpr int PER_ROW = UNIT / 4;  // pieces per row
+#pragma unroll
+  for (int p0 = 0; p0 < PIECES; p0 += kWarp) {
+    const int p = p0 + lane;
+    if (PIECES % kWarp == 0 || p < PIECES) {
+      const int g = p / PER_ROW;
+      const int part = p - g * PER_ROW;
+      const int row = min(row0 + g, last_row);
+      cp_async_n<16>(dst_block + p * 16, packed + row * words_per_row + word0 + part * 4);
+    }
+  }
+}
+
 template <int BITS>
 __device__ __forceinline__ void read_unit(const unsigned char* src, uint32_t* w) {
   if constexpr (BITS == 2) {
@@ -121,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
   const int tile_stride = gridDim.x * kWarps;
   const int first_tile = blockIdx.x * kWarps + warp;
 
-  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + tid * C::UNIT;
+  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * C::UNIT;
   const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * C::META_BYTES;
   const unsigned char* ring_w_mine = ring_w + tid * C::UNIT;
   // metadata of this lane's quad: arrays 0..3 = scale(row g), offset(row g), scale(row g+8), offset(row g+8)
@@ -132,14 +158,10 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
   // ---- prefetch cursor: walks (tile, block) ahead of the compute loop ----
   int pf_tile = first_tile;
   int pf_blk = 0;
-  const uint32_t* pf_wa = nullptr;
-  const uint32_t* pf_wb = nullptr;
   const unsigned short* pf_meta = nullptr;  // this lane's array (scales or offsets) at its row, group 0
   auto pf_point = [&]() {
     const int ra = min(pf_tile * kTileRows + g, a.rows - 1);
     const int rb = min(pf_tile * kTileRows + g + 8, a.rows - 1);
-    pf_wa = a.packed + static_cast<int64_t>(ra) * a.words_per_row + t * BITS;
-    pf_wb = a.packed + static_cast<int64_t>(rb) * a.words_per_row + t * BITS;
     const unsigned short* arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
     pf_meta = arr + static_cast<int64_t>((t & 2) ? rb : ra) * a.num_groups;
   };
@@ -152,8 +174,11 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
       const uint32_t dst = ring_w_s + slot * (C::BLOCK_BYTES * kThreads);
 #pragma unroll
       for (int j = 0; j < P; ++j) {
-        copy_unit<BITS>(dst + (j * 2 + 0) * (C::UNIT * kThreads), pf_wa + (pf_blk * P + j) * STEP_WORDS);
-        copy_unit<BITS>(dst + (j * 2 + 1) * (C::UNIT * kThreads), pf_wb + (pf_blk * P + j) * STEP_WORDS);
+        const int word0 = (pf_blk * P + j) * STEP_WORDS;
+        copy_block<BITS>(dst + (j * 2 + 0) * (C::UNIT * kThreads), a.packed, a.words_per_row, pf_tile * kTileRows,
+                         a.rows - 1, word0, lane);
+        copy_block<BITS>(dst + (j * 2 + 1) * (C::UNIT * kThreads), a.packed, a.words_per_row,
+                         pf_tile * kTileRows + 8, a.rows - 1, word0, lane);
       }
       if (meta_lane) {
         cp_async_n<C::META_BYTES>(ring_m_s + slot * (C::META_BYTES * kThreads), pf_meta + pf_blk * P);
