@@ -40,6 +40,7 @@ METRIC = "packed_gemv_hbm_gbps_m1"
 UNIT = "GB/s"
 WORKLOAD = "qwen2b-stack-3.25bit-m1 (BASELINE config 2: 28 layers + 8-bit lm_head, 197 GEMVs/step)"
 FALLBACK_HBM_GBS = 6650.0
+TRAFFIC_PER_STEP = 1_158_139_360  # dram bytes read + written by one step; see profiles/stack_qwen2b_m1_launch_list.md
 
 
 def measured_peak() -> tuple[float, str]:
@@ -239,6 +240,7 @@ def run_ours(args) -> None:
             step_fn = runner.replay
         else:
             step_fn = runner.run
+            runner.count_launches()
         launches_per_step = runner.launches_per_step
     step_bytes = full.algorithmic_bytes(m)
 
@@ -298,13 +300,10 @@ def run_ours(args) -> None:
     avg_launch_s = seconds / launches
     bytes_per_launch = step_bytes / launches_per_step
     achieved = bytes_per_launch / avg_launch_s / 1e9 * (world if world > 1 else 1) / max(world, 1)
-    traffic_path = ROOT / "profiles" / "traffic.json"
-    traffic = None
-    if traffic_path.exists():
-        try:
-            traffic = json.loads(traffic_path.read_text()).get("dram_bytes_per_launch")
-        except ValueError:
-            traffic = None
+    # dram__bytes_read.sum + dram__bytes_write.sum of one step, from the ncu launch list of this
+    # very command (profiles/stack_qwen2b_m1_launch_list.md), spread over the step's launches.
+    traffic = (round(TRAFFIC_PER_STEP / launches_per_step)
+               if (args.layers == 28 and m == 1 and world == 1) else None)
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(per_step * 1e3, 4), "higher_is_better": True,
@@ -324,7 +323,8 @@ def run_ours(args) -> None:
         "roofline": {
             "bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
             "frac": round(achieved / peak, 4), "traffic": traffic,
-            "kernel": "gemv_fast_kernel (all widths; per-launch average over the step)",
+            "kernel": "gemv_mma_tile_kernel (decoder-block layers, fused shards) / gemv_mma_stream_kernel "
+                      f"(lm_head); per-launch average over the {launches_per_step} launches of a step",
             "bytes_per_launch": round(bytes_per_launch), "avg_launch_us": round(avg_launch_s * 1e6, 3),
         },
         "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

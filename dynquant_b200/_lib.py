@@ -78,6 +78,7 @@ SIGNATURES = {
     "dq_built_with_cuda": (_I32, []),
     "dq_compiled_architectures": (ctypes.c_char_p, []),
     "dq_gemv_max_rows": (_I32, []),
+    "dq_launch_count": (_I64, []),
     "dq_moe_max_tokens": (_I32, []),
     "dq_last_error": (ctypes.c_char_p, []),
     "dq_resolve_geometry": (_I32, [ctypes.c_char_p, _WP, ctypes.POINTER(Geometry)]),

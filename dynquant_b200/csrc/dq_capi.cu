@@ -5,6 +5,7 @@
 // resolve_geometry (packages/dynquant-kernels/csrc/include/dynquant/geometry.h:63-132):
 // nothing is derived by guesswork, everything is either passed in or implied
 // by a shape, and every implication is checked.
+#include <atomic>
 #include <mutex>
 
 #include "dq_common.cuh"
@@ -15,6 +16,12 @@ char* error_buffer() {
   static thread_local char buffer[kErrorBufferSize] = {0};
   return buffer;
 }
+
+namespace {
+std::atomic<int64_t> g_launches{0};
+}
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+int64_t launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
 
 const DeviceInfo* device_info() {
   constexpr int kMaxDevices = 64;
@@ -49,6 +56,9 @@ const DeviceInfo* device_info() {
 }  // namespace dq
 
 extern "C" {
+
+int64_t dq_launch_count(void) { return dq::launches_so_far(); }
+
 
 int32_t dq_abi_version(void) { return DQ_ABI_VERSION; }
 int32_t dq_built_with_cuda(void) { return 1; }

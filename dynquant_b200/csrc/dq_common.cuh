@@ -50,6 +50,7 @@ inline int32_t fail(dq_status status, const char* fmt, ...) {
 // not at some later synchronisation.
 #define DQ_CHECK_LAUNCH(what)                                                             \
   do {                                                                                    \
+    ::dq::count_launch();                                                                 \
     const cudaError_t dq_err__ = cudaGetLastError();                                      \
     if (dq_err__ != cudaSuccess) {                                                        \
       return ::dq::fail(DQ_ERR_CUDA, "%s: kernel launch failed: %s", what,                \
@@ -101,6 +102,9 @@ struct DeviceInfo {
 };
 // Cached per device; returns nullptr and sets the error on failure.
 const DeviceInfo* device_info();
+
+// Process-wide count of the kernels this library has launched (dq_launch_count).
+void count_launch();
 
 // ---- device-side dtype helpers ---------------------------------------------
 

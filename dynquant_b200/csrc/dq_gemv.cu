@@ -375,6 +375,9 @@ int32_t launch(Kernel kernel, const GemvArgs& args, int grid, size_t smem, cudaS
   return DQ_OK;
 }
 
+template <int BITS>
+int32_t launch_general(const GemvArgs& args, cudaStream_t stream);
+
 template <int BITS, int CW, int MT, int R>
 int32_t launch_fast(const GemvArgs& args, cudaStream_t stream) {
   using Cfg = ChunkCfg<BITS, CW>;
@@ -383,7 +386,7 @@ int32_t launch_fast(const GemvArgs& args, cudaStream_t stream) {
   const size_t smem =
       sizeof(float) * static_cast<size_t>(MT) * (static_cast<size_t>(args.chunks_per_row) * Cfg::kStride + args.chunks_per_row);
   if (smem > static_cast<size_t>(dev->max_smem_optin)) {
-    return fail(DQ_ERR_UNSUPPORTED, "gemv: activation tile of %zu bytes exceeds shared memory", smem);
+    return launch_general<BITS>(args, stream);  // M x K too large to stage: slower, still correct
   }
   auto kernel = gemv_fast_kernel<BITS, CW, MT, R>;
   const int tiles = static_cast<int>(ceil_div(args.rows, R));
@@ -436,9 +439,8 @@ int pick_rows_per_warp(int rows, const DeviceInfo& dev) {
   return 1;
 }
 
-int32_t gemv_one(const void* x, int32_t x_dtype, int64_t m, const dq_weight& w, const dq_geometry& g,
-                 const void* bias, void* out, int64_t out_stride, int64_t out_col0,
-                 int32_t out_dtype, cudaStream_t stream) {
+GemvArgs make_args(const void* x, int32_t x_dtype, int64_t m, const dq_weight& w, const dq_geometry& g,
+                   const void* bias, void* out, int64_t out_stride, int64_t out_col0, int32_t out_dtype) {
   GemvArgs a = {};
   a.x = x;
   a.packed = static_cast<const uint32_t*>(w.packed);
@@ -458,11 +460,31 @@ int32_t gemv_one(const void* x, int32_t x_dtype, int64_t m, const dq_weight& w, 
   a.words_per_group = g.words_per_group;
   a.group_values = g.group_values;
   a.in_features = g.in_features;
+  return a;
+}
 
-  if (!force_general() && mma_path_supports(a, w.bits)) {
-    return launch_gemv_mma(a, w.bits, stream);
+// The first `count` activation rows from row `first` on: same weight, shifted x and out.
+GemvArgs activation_rows(const GemvArgs& a, int first, int count) {
+  GemvArgs b = a;
+  b.x = static_cast<const char*>(a.x) + static_cast<int64_t>(first) * a.in_features * dtype_size(a.x_dtype);
+  b.out = static_cast<char*>(a.out) + static_cast<int64_t>(first) * a.out_stride * dtype_size(a.out_dtype);
+  b.m = count;
+  return b;
+}
+
+int32_t gemv_args(GemvArgs a, const dq_weight& w, const dq_geometry& g, cudaStream_t stream) {
+  if (!force_general()) {
+    if (mma_path_supports(a, w.bits)) return launch_gemv_mma(a, w.bits, stream);
+    // The staged activation of all rows may be what does not fit: two passes over half the
+    // rows each read the weights twice (the second time mostly from L2) but stay on the
+    // tensor-core path.
+    if (a.m > 1 && mma_path_supports(activation_rows(a, 0, (a.m + 1) / 2), w.bits)) {
+      const int half = (a.m + 1) / 2;
+      if (const int32_t rc = gemv_args(activation_rows(a, 0, half), w, g, stream)) return rc;
+      return gemv_args(activation_rows(a, half, a.m - half), w, g, stream);
+    }
   }
-  const int cw = fast_chunk_words(w, g, x, x_dtype);
+  const int cw = fast_chunk_words(w, g, a.x, a.x_dtype);
   if (cw == 0) {
     switch (w.bits) {
       case 2:
@@ -490,6 +512,12 @@ int32_t gemv_one(const void* x, int32_t x_dtype, int64_t m, const dq_weight& w, 
     default:
       return launch_fast_m<8, 4>(a, rpw, stream);
   }
+}
+
+int32_t gemv_one(const void* x, int32_t x_dtype, int64_t m, const dq_weight& w, const dq_geometry& g,
+                 const void* bias, void* out, int64_t out_stride, int64_t out_col0,
+                 int32_t out_dtype, cudaStream_t stream) {
+  return gemv_args(make_args(x, x_dtype, m, w, g, bias, out, out_stride, out_col0, out_dtype), w, g, stream);
 }
 
 int32_t check_activation(const void* x, int32_t x_dtype, int64_t m, void* out, int32_t out_dtype) {
@@ -538,16 +566,38 @@ int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const dq_weigh
              static_cast<long long>(out_stride), static_cast<long long>(total));
   if (const int32_t rc = dq::check_activation(x, x_dtype, m, out, out_dtype)) return rc;
   if (m == 0) return DQ_OK;
+  // Shards share the activation: up to four at a time go out as ONE launch when the tiled
+  // tensor-core kernel takes them, one launch each otherwise.
+  constexpr int kBatch = 4;
   int64_t col0 = 0;
-  for (int i = 0; i < num_shards; ++i) {
-    dq_geometry g;
-    dq_resolve_geometry("gemv_shards", &shards[i], &g);
-    if (shards[i].rows > 0) {
-      const int32_t rc = dq::gemv_one(x, x_dtype, m, shards[i], g, bias, out, out_stride, col0,
-                                      out_dtype, static_cast<cudaStream_t>(stream));
+  for (int first = 0; first < num_shards; first += kBatch) {
+    const int count = std::min(kBatch, num_shards - first);
+    dq::GemvArgs args[kBatch];
+    dq_geometry geo[kBatch];
+    int bits[kBatch];
+    int64_t cols[kBatch];
+    int live = 0;
+    for (int i = first; i < first + count; ++i) {
+      if (shards[i].rows > 0) {
+        dq_resolve_geometry("gemv_shards", &shards[i], &geo[live]);
+        args[live] = dq::make_args(x, x_dtype, m, shards[i], geo[live], bias, out, out_stride, col0, out_dtype);
+        bits[live] = shards[i].bits;
+        cols[live] = i;
+        ++live;
+      }
+      col0 += shards[i].rows;
+    }
+    bool taken = false;
+    if (live > 1 && !dq::force_general()) {
+      const int32_t rc = dq::launch_gemv_mma_fused(args, bits, live, static_cast<cudaStream_t>(stream), &taken);
       if (rc) return rc;
     }
-    col0 += shards[i].rows;
+    if (!taken) {
+      for (int k = 0; k < live; ++k) {
+        const int32_t rc = dq::gemv_args(args[k], shards[cols[k]], geo[k], static_cast<cudaStream_t>(stream));
+        if (rc) return rc;
+      }
+    }
   }
   return DQ_OK;
 }
@@ -564,14 +614,43 @@ int32_t dq_gemv_sequence(const dq_gemv_job* jobs, int32_t num_jobs, void* stream
                static_cast<long long>(j.out_col0), static_cast<long long>(j.out_col0 + j.weight.rows),
                static_cast<long long>(j.out_stride));
   }
-  for (int i = 0; i < num_jobs; ++i) {
-    const dq_gemv_job& j = jobs[i];
-    if (j.m == 0 || j.weight.rows == 0) continue;
-    dq_geometry g;
-    dq_resolve_geometry("gemv_sequence", &j.weight, &g);
-    const int32_t rc = dq::gemv_one(j.x, j.x_dtype, j.m, j.weight, g, j.bias, j.out, j.out_stride,
-                                    j.out_col0, j.out_dtype, static_cast<cudaStream_t>(stream));
-    if (rc) return rc;
+  // Consecutive jobs that read the SAME activation (q/k/v, gate/up) cannot depend on one
+  // another, so up to four of them go out as one launch when the tiled kernel takes them.
+  constexpr int kBatch = 4;
+  auto s = static_cast<cudaStream_t>(stream);
+  int i = 0;
+  while (i < num_jobs) {
+    const dq_gemv_job& head = jobs[i];
+    if (head.m == 0 || head.weight.rows == 0) {
+      ++i;
+      continue;
+    }
+    int end = i + 1;
+    while (end < num_jobs && end - i < kBatch && jobs[end].x == head.x && jobs[end].m == head.m &&
+           jobs[end].x_dtype == head.x_dtype && jobs[end].out_dtype == head.out_dtype &&
+           jobs[end].weight.rows > 0 && jobs[end].weight.in_features == head.weight.in_features) {
+      ++end;
+    }
+    dq::GemvArgs args[kBatch];
+    dq_geometry geo[kBatch];
+    int bits[kBatch];
+    for (int k = i; k < end; ++k) {
+      const dq_gemv_job& j = jobs[k];
+      dq_resolve_geometry("gemv_sequence", &j.weight, &geo[k - i]);
+      args[k - i] = dq::make_args(j.x, j.x_dtype, j.m, j.weight, geo[k - i], j.bias, j.out, j.out_stride,
+                                  j.out_col0, j.out_dtype);
+      bits[k - i] = j.weight.bits;
+    }
+    bool taken = false;
+    if (end - i > 1 && !dq::force_general()) {
+      if (const int32_t rc = dq::launch_gemv_mma_fused(args, bits, end - i, s, &taken)) return rc;
+    }
+    if (!taken) {
+      for (int k = i; k < end; ++k) {
+        if (const int32_t rc = dq::gemv_args(args[k - i], jobs[k].weight, geo[k - i], s)) return rc;
+      }
+    }
+    i = end;
   }
   return DQ_OK;
 }

@@ -26,6 +26,9 @@ struct GemvArgs {
 // caller can fall through to the SIMT kernels.
 bool mma_path_supports(const GemvArgs& a, int bits);
 int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream);
+// Up to four matrices that share one activation, in ONE launch.  *taken is false (and nothing
+// was launched) when the jobs do not qualify; the caller then launches them one by one.
+int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void store_out(const GemvArgs& a, int m, int row, float v) {

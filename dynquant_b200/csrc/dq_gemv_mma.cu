@@ -34,7 +34,7 @@
 #include <cstdlib>
 
 #include "dq_gemv.cuh"
-#include "dq_gemv_mma_short.cuh"
+#include "dq_gemv_mma_tile.cuh"
 #include "dq_gemv_mma_stream.cuh"
 #include "dq_mma_plan.cuh"
 #include "dq_mma_stage.cuh"
@@ -569,76 +569,161 @@ int32_t try_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int step
   return rc;
 }
 
-// ---- short-matrix kernel (dq_gemv_mma_short.cuh) ----
+// ---- tiled kernel (dq_gemv_mma_tile.cuh): short and middle-sized matrices, fused shards ----
 
-template <int BITS>
-int32_t try_short(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps, cudaStream_t stream_h,
-                  bool* taken) {
+int env_int(const char* name) {
+  const char* v = std::getenv(name);
+  return v != nullptr ? std::atoi(v) : 0;
+}
+
+// One launch for `n` matrices sharing the activation.  *taken stays false (and nothing is
+// launched) when the jobs do not meet the kernel's requirements.
+int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo& dev, cudaStream_t stream_h,
+                 bool* taken) {
   *taken = false;
-  static const bool off = [] {
-    const char* v = std::getenv("DQ_B200_NO_SHORT");
-    return v != nullptr && v[0] != '\0' && v[0] != '0';
-  }();
-  if (off || a.group_values != kStepValues) return DQ_OK;
-  if (reinterpret_cast<uintptr_t>(a.scales) % 4 != 0 || reinterpret_cast<uintptr_t>(a.offsets) % 4 != 0) return DQ_OK;
-  const int max_steps = BITS == 8 ? 4 : shortk::kMaxSteps;
-  if (a.num_groups % 2 != 0) return DQ_OK;  // rows of scales must start on 4-byte words
-  // 16-byte copies of whole steps: rows and the tensor itself must be 16-byte aligned
-  if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) {
-    return DQ_OK;
-  }
-  static const int force_warps = [] { const char* v = std::getenv("DQ_B200_SHORT_WARPS"); return v ? std::atoi(v) : 0; }();
-  shortk::Params p = {};
-  p.steps = steps;
-  p.tiles = tiles;
-  p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
-  const bool xbf = a.x_dtype == DQ_BF16, mbf = a.meta_dtype == DQ_BF16;
-  int32_t rc = DQ_OK;
-  auto run = [&](auto kernel) -> int32_t {
-    // Candidate CTA shapes, finest slicing of the reduction axis first: the whole grid must
-    // be resident at once and every slice must fit the per-warp step limit.
-    for (int warps = (force_warps ? force_warps : 8); warps >= 8; warps /= 2) {
-      for (int kw = warps; kw >= 1; kw /= 2) {
-        if (steps % kw != 0 || steps / kw > max_steps) continue;
-        p.kw = kw;
-        p.rw = warps / kw;
-        p.steps_per_warp = steps / kw;
-        p.meta_words = (p.steps_per_warp + 2) / 2;
-        p.m_stride_u4 = p.steps_per_warp * (BITS == 8 ? 32 : 16) + 4;
-        const size_t smem = shortk::smem_bytes<BITS>(a.m, p);
-        if (smem > static_cast<size_t>(dev.max_smem_optin)) continue;
-        const int threads = warps * kWarp;
-        const int grid = static_cast<int>(ceil_div(tiles, p.rw));
-        if (smem > 48 * 1024) {
-          DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        }
-        int per_sm = 0;
-        DQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem));
-        if (grid > per_sm * dev.sm_count) continue;  // more than one wave
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(static_cast<unsigned>(grid));
-        cfg.blockDim = dim3(static_cast<unsigned>(threads));
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = stream_h;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = pdl_enabled() ? 1 : 0;
-        DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
-        DQ_CHECK_LAUNCH("gemv");
-        *taken = true;
-        return DQ_OK;
-      }
-      if (force_warps) break;
+  static const bool off = env_int("DQ_B200_NO_TILE") != 0;
+  static const int force_kw = env_int("DQ_B200_TILE_KW");
+  static const int force_nb = env_int("DQ_B200_TILE_NB");
+  static const int force_per_sm = env_int("DQ_B200_TILE_PER_SM");
+  if (off || n < 1 || n > tilek::kMaxJobs) return DQ_OK;
+  const GemvArgs& a0 = jobs[0];
+  const int steps = a0.words_per_row / (4 * bits[0]);
+  int max_bits = 0, max_tiles_total = 0;
+  for (int i = 0; i < n; ++i) {
+    const GemvArgs& a = jobs[i];
+    if (a.x != a0.x || a.m != a0.m || a.x_dtype != a0.x_dtype || a.meta_dtype != a0.meta_dtype ||
+        a.in_features != a0.in_features || a.out_dtype != a0.out_dtype) {
+      return DQ_OK;
     }
-    return DQ_OK;  // not a short matrix
+    if (a.group_values != kStepValues || a.words_per_row / (4 * bits[i]) != steps || a.num_groups != steps) return DQ_OK;
+    if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) {
+      return DQ_OK;
+    }
+    max_bits = std::max(max_bits, bits[i]);
+    max_tiles_total += static_cast<int>(ceil_div(a.rows, kTileRows));
+  }
+  // Shape of the CTAs.  First choice: ONE wave in which every warp's whole share of the
+  // weights is in flight before the activation arrives -- the finest slicing of the reduction
+  // axis whose grid is resident at once.  Otherwise CTAs persist over several items with a
+  // ring of a few stages, sliced as finely as leaves four steps between two reductions.
+  constexpr size_t kSmemPerSm = 228 * 1024, kCtaReserve = 1024;
+  constexpr int kCtasByRegisters = 3;  // __launch_bounds__(256, 3)
+  struct Shape {
+    int kw = 0, ch = 0, nb = 0, per_sm = 0, ipc = 0;
+    size_t smem = 0;
   };
-  if (xbf && mbf) rc = run(shortk::gemv_mma_short_kernel<BITS, true, true>);
-  else if (xbf) rc = run(shortk::gemv_mma_short_kernel<BITS, true, false>);
-  else if (mbf) rc = run(shortk::gemv_mma_short_kernel<BITS, false, true>);
-  else rc = run(shortk::gemv_mma_short_kernel<BITS, false, false>);
-  return rc;
+  auto meta_aligned = [&](int c) {
+    for (int i = 0; i < n; ++i) {
+      const auto al = static_cast<uintptr_t>(2 * c);
+      if (jobs[i].num_groups % c != 0 || reinterpret_cast<uintptr_t>(jobs[i].scales) % al != 0 ||
+          reinterpret_cast<uintptr_t>(jobs[i].offsets) % al != 0) {
+        return false;
+      }
+    }
+    return true;
+  };
+  auto items_at = [&](int kw) {
+    const int rw = tilek::kWarps / kw;
+    int64_t items = 0;
+    for (int i = 0; i < n; ++i) items += ceil_div(ceil_div(jobs[i].rows, kTileRows), rw);
+    return items;
+  };
+  auto shape_at = [&](int kw, bool one_shot) {
+    Shape sh;
+    if (steps % kw != 0) return sh;
+    const int spw = steps / kw;
+    const int ch = (spw % 4 == 0 && meta_aligned(4)) ? 4 : ((spw % 2 == 0 && meta_aligned(2)) ? 2 : 0);
+    if (ch == 0) return sh;
+    const bool wide = kw < tilek::kWarps;
+    const size_t stage = static_cast<size_t>(ch) * 2 * (4 * max_bits) * tilek::kThreads + ch * 2 * tilek::kThreads;
+    const size_t fixed = tilek::kRedFloats * 4 +
+                         (max_bits == 8 ? tilek::stage_bytes<8>(a0.m, steps, spw, kw, wide, a0.in_features)
+                                        : tilek::stage_bytes<4>(a0.m, steps, spw, kw, wide, a0.in_features));
+    const int stages = spw / ch;
+    int nb = one_shot ? stages : std::min(stages * 2, ch == 4 ? 2 : 4);
+    if (force_nb > 0 && !one_shot) nb = force_nb;
+    nb = std::min(nb, tilek::kMaxRing);
+    if (one_shot && nb < stages) return sh;
+    const size_t smem = nb * stage + fixed;
+    if (smem > static_cast<size_t>(dev.max_smem_optin)) return sh;
+    sh.kw = kw;
+    sh.ch = ch;
+    sh.nb = nb;
+    sh.smem = smem;
+    sh.per_sm = std::min<int>(kCtasByRegisters, static_cast<int>(kSmemPerSm / (smem + kCtaReserve)));
+    if (force_per_sm > 0) sh.per_sm = std::min(sh.per_sm, force_per_sm);
+    const int64_t cap = static_cast<int64_t>(sh.per_sm) * dev.sm_count;
+    sh.ipc = static_cast<int>(ceil_div(items_at(kw), cap));
+    return sh;
+  };
+  Shape pick;
+  for (int kw = tilek::kWarps; kw >= 1 && pick.kw == 0; kw /= 2) {
+    if (force_kw > 0 && kw != force_kw) continue;
+    const Shape sh = shape_at(kw, true);
+    if (sh.kw != 0 && sh.per_sm >= 1 && sh.ipc == 1) pick = sh;
+  }
+  for (int kw = tilek::kWarps; kw >= 1 && pick.kw == 0; kw /= 2) {
+    if (force_kw > 0 && kw != force_kw) continue;
+    if (force_kw == 0 && kw > 1 && (steps % kw != 0 || steps / kw < 4)) continue;
+    const Shape sh = shape_at(kw, false);
+    if (sh.kw != 0 && sh.per_sm >= 1) pick = sh;
+  }
+  if (pick.kw == 0) return DQ_OK;
+  const int kw = pick.kw, rw = tilek::kWarps / kw, spw = steps / kw, ch = pick.ch;
+  const bool wide = kw < tilek::kWarps;
+  const size_t smem = pick.smem;
+
+  tilek::Launch L = {};
+  L.njobs = n;
+  L.steps = steps;
+  L.rw = rw;
+  L.kw = kw;
+  L.spw = spw;
+  L.nb = pick.nb;
+  L.wide_stage = wide ? 1 : 0;
+  L.meta_bf16 = a0.meta_dtype == DQ_BF16 ? 1 : 0;
+  L.magic = a0.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
+  for (int i = 0; i < n; ++i) {
+    L.job[i].a = jobs[i];
+    L.job[i].bits = bits[i];
+    L.job[i].tiles = static_cast<int>(ceil_div(jobs[i].rows, kTileRows));
+    L.job[i].items = static_cast<int>(ceil_div(L.job[i].tiles, rw));
+  }
+  // every CTA of a job takes the same number of items (ipc), the jobs' CTAs side by side
+  const int64_t cap = static_cast<int64_t>(pick.per_sm) * dev.sm_count;
+  int grid = 0;
+  for (int ipc = pick.ipc;; ++ipc) {
+    grid = 0;
+    for (int i = 0; i < n; ++i) {
+      L.job[i].cta_begin = grid;
+      L.job[i].cta_count = static_cast<int>(ceil_div(L.job[i].items, ipc));
+      grid += L.job[i].cta_count;
+    }
+    if (grid <= cap || ipc > pick.ipc + 4) break;
+  }
+
+  auto run = [&](auto kernel) -> int32_t {
+    if (smem > 48 * 1024) {
+      DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(tilek::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream_h;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, L));
+    DQ_CHECK_LAUNCH("gemv");
+    *taken = true;
+    return DQ_OK;
+  };
+  const bool xbf = a0.x_dtype == DQ_BF16;
+  if (ch == 4) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 4>) : run(tilek::gemv_mma_tile_kernel<false, 4>);
+  return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2>) : run(tilek::gemv_mma_tile_kernel<false, 2>);
 }
 
 }  // namespace
@@ -657,6 +742,16 @@ bool mma_path_supports(const GemvArgs& a, int bits) {
   const int steps = a.words_per_row / (4 * bits);
   const size_t smem = mma_smem_bytes(a.m, steps, bits == 8 ? 32 : 16, 1, kMaxWarps, &stride);
   return smem <= static_cast<size_t>(dev->max_smem_optin);
+}
+
+int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken) {
+  *taken = false;
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr) return DQ_ERR_CUDA;
+  for (int i = 0; i < n; ++i) {
+    if (!mma_path_supports(jobs[i], bits[i])) return DQ_OK;
+  }
+  return try_tile(jobs, bits, n, *dev, stream, taken);
 }
 
 int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
@@ -684,20 +779,7 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
         break;
     }
     if (taken || rc != DQ_OK) return rc;
-    switch (bits) {
-      case 2:
-        rc = try_short<2>(a, *dev, p.tiles, p.steps, stream, &taken);
-        break;
-      case 3:
-        rc = try_short<3>(a, *dev, p.tiles, p.steps, stream, &taken);
-        break;
-      case 4:
-        rc = try_short<4>(a, *dev, p.tiles, p.steps, stream, &taken);
-        break;
-      default:
-        rc = try_short<8>(a, *dev, p.tiles, p.steps, stream, &taken);
-        break;
-    }
+    rc = try_tile(&a, &bits, 1, *dev, stream, &taken);
     if (taken || rc != DQ_OK) return rc;
   }
   // Shape of a CTA: rw row tiles x kw slices of the reduction axis, 8 or 16 warps.  A short

@@ -1,0 +1,343 @@
+// Tiled tensor-core GEMV: one launch for up to four packed matrices that share an activation.
+//
+// The decoder-block layers of a model at decode time are short (a 2048 x 2048 projection at
+// 3 bits is 1.7 MB) or of middle size (a 14336 x 4096 one at 4 bits is 29 MB): too small to
+// stream, large enough that more than one wave of one-shot CTAs costs as much as the bytes.
+// This kernel covers both, and fuses the shards of a fused layer (q/k/v, gate/up), whatever
+// their widths, into ONE launch -- at this size a launch costs more than the bytes do.
+//
+//   * A CTA is 8 warps laid out as rw row tiles x kw slices of the reduction axis.  A warp
+//     keeps its slice for the whole kernel and walks over row tiles (items), CTAs striding
+//     over the items of their matrix; partial sums of the kw slices meet in shared memory
+//     once per item and are added in a fixed order (results are bit-identical run to run).
+//   * Weights travel global -> shared with 16-byte cp.async into a per-warp ring of `nb`
+//     stages of CH steps; all nb stages are requested BEFORE griddepcontrol.wait, so under
+//     programmatic dependent launch they fly while the previous layer computes, and a slot
+//     is refilled as soon as it has been consumed.  When a warp's whole share fits the ring
+//     everything is requested up front (the one-shot regime of short matrices).
+//   * The activation is staged once per CTA: warp-private slices when rw == 1 (no CTA
+//     barrier between the arrival of x and the first mma), CTA-wide otherwise.
+//   * Each CTA belongs to one matrix (a "job") and runs the body compiled for its width.
+//
+// Arithmetic is that of gemv_mma_kernel (dq_gemv_mma.cu).  Requirements, checked by the
+// host: one group per 128-value step, 16-byte aligned rows, steps divisible by kw * CH,
+// scales/offsets rows aligned to 2 * CH bytes.
+#pragma once
+
+#include "dq_gemv.cuh"
+#include "dq_gemv_mma_stream.cuh"
+#include "dq_mma_plan.cuh"
+#include "dq_mma_stage.cuh"
+
+namespace dq {
+namespace tilek {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * kWarp;
+constexpr int kMaxJobs = 4;
+constexpr int kMaxRing = 8;
+constexpr int kRedFloats = 2 * kWarps * 16 * 8;  // two buffers of one 16 x 8 partial per warp
+
+struct Job {
+  GemvArgs a;
+  int bits;
+  int tiles;      // ceil(rows / 16)
+  int items;      // ceil(tiles / rw)
+  int cta_begin;  // CTAs [cta_begin, cta_begin + cta_count) of the grid work on this job
+  int cta_count;
+};
+
+struct Launch {
+  Job job[kMaxJobs];
+  int njobs;
+  int steps;       // padded K / 128 (the jobs share the activation, hence K)
+  int rw, kw;      // rw * kw == kWarps
+  int spw;         // steps per slice = steps / kw, a multiple of CH
+  int nb;          // ring stages, 1..kMaxRing
+  int wide_stage;  // 1: the CTA stages the whole activation; 0: every warp its own slice
+  int meta_bf16;
+  uint32_t magic;
+};
+
+template <int BITS, int CH>
+struct Ring {
+  static constexpr int UNIT = 4 * BITS;
+  static constexpr int STAGE_W = CH * 2 * UNIT * kThreads;  // weights of one stage, whole CTA
+  static constexpr int STAGE_M = CH * 2 * kThreads;         // one metadata array per lane, CH groups
+};
+
+// Bytes of the staging area (after ring and reduction buffers).
+template <int BITS>
+__host__ __device__ inline size_t stage_bytes(int m, int steps, int spw, int kw, bool wide, int in_features) {
+  const int na = BITS == 8 ? 32 : 16;
+  if (wide) {
+    const size_t stride = static_cast<size_t>(steps) * na + 4;
+    return (m * stride + na) * 16 + static_cast<size_t>(steps) * 64 + static_cast<size_t>(m) * in_features * 2 + 16;
+  }
+  const size_t stride = static_cast<size_t>(spw) * na + 4;
+  return static_cast<size_t>(kw) * (spw * 256 + (m * stride + na) * 16 + spw * 64);
+}
+
+template <int BITS, int CH>
+inline size_t smem_bytes(int m, int steps, int spw, int kw, int nb, bool wide, int in_features) {
+  using R = Ring<BITS, CH>;
+  return static_cast<size_t>(nb) * (R::STAGE_W + R::STAGE_M) + kRedFloats * 4 +
+         stage_bytes<BITS>(m, steps, spw, kw, wide, in_features);
+}
+
+__device__ __forceinline__ void wait_pending(int n) {
+  switch (n) {
+    case 0: stream::cp_async_wait<0>(); break;
+    case 1: stream::cp_async_wait<1>(); break;
+    case 2: stream::cp_async_wait<2>(); break;
+    case 3: stream::cp_async_wait<3>(); break;
+    case 4: stream::cp_async_wait<4>(); break;
+    case 5: stream::cp_async_wait<5>(); break;
+    case 6: stream::cp_async_wait<6>(); break;
+    default: stream::cp_async_wait<7>(); break;
+  }
+}
+
+template <int BITS, bool XBF16, int CH>
+__device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigned char* smem) {
+  using Plan = MmaPlan<BITS>;
+  using R = Ring<BITS, CH>;
+  constexpr int NA = Plan::kARegs;
+  constexpr int QU = NA / 4;
+  constexpr int UNIT = R::UNIT;
+  constexpr int STEP_WORDS = 4 * BITS;
+  const GemvArgs& a = J.a;
+
+  const int tid = threadIdx.x;
+  const int lane = tid & (kWarp - 1);
+  const int warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int kw = L.kw, rw = L.rw, spw = L.spw, nb = L.nb;
+  const int rwi = warp / kw;
+  const int kwi = warp - rwi * kw;
+  const int s_begin = kwi * spw;
+  const int nchunks = spw / CH;
+  const bool has_off = a.offsets != nullptr;
+  const bool wide = L.wide_stage != 0;
+  const int cta = blockIdx.x - J.cta_begin;
+
+  unsigned char* ring_w = smem;
+  unsigned char* ring_m = ring_w + nb * R::STAGE_W;
+  float* red = reinterpret_cast<float*>(ring_m + nb * R::STAGE_M);
+  unsigned char* area = reinterpret_cast<unsigned char*>(red + kRedFloats);
+
+  // staging area: CTA-wide (indexed by global step) or this warp's own (indexed within its slice)
+  const int span = wide ? L.steps : spw;
+  const int m_stride_u4 = span * NA + 4;
+  unsigned short* raw;
+  uint4* xb;
+  float *xsum, *xneg;
+  if (wide) {
+    xb = reinterpret_cast<uint4*>(area);
+    xsum = reinterpret_cast<float*>(xb + a.m * m_stride_u4 + NA);
+    xneg = xsum + span * 8;
+    raw = reinterpret_cast<unsigned short*>(xneg + span * 8);
+  } else {
+    unsigned char* mine = area + kwi * (spw * 256 + (a.m * m_stride_u4 + NA) * 16 + spw * 64);
+    raw = reinterpret_cast<unsigned short*>(mine);
+    xb = reinterpret_cast<uint4*>(mine + spw * 256);
+    xsum = reinterpret_cast<float*>(xb + a.m * m_stride_u4 + NA);
+    xneg = xsum + span * 8;
+  }
+
+  pdl_launch_dependents();
+
+  // ---- prefetch cursor: walks (item, chunk) ahead of the compute loop ----
+  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * UNIT;
+  const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * (CH * 2);
+  const bool meta_lane = has_off || (t & 1) == 0;
+  const unsigned short* meta_arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
+  int pf_item = cta, pf_chunk = 0, pf_slot = 0;
+  auto prefetch_stage = [&]() {
+    if (pf_item < J.items) {
+      const int tile = pf_item * rw + rwi;
+      if (tile < J.tiles) {
+        const uint32_t dst = ring_w_s + pf_slot * R::STAGE_W;
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int word0 = (s_begin + pf_chunk * CH + j) * STEP_WORDS;
+          stream::copy_block<BITS>(dst + (j * 2 + 0) * (UNIT * kThreads), a.packed, a.words_per_row, tile * 16,
+                                   a.rows - 1, word0, lane);
+          stream::copy_block<BITS>(dst + (j * 2 + 1) * (UNIT * kThreads), a.packed, a.words_per_row, tile * 16 + 8,
+                                   a.rows - 1, word0, lane);
+        }
+        if (meta_lane) {
+          const int row = min(tile * 16 + g + ((t & 2) ? 8 : 0), a.rows - 1);
+          stream::cp_async_n<CH * 2>(ring_m_s + pf_slot * R::STAGE_M,
+                                     meta_arr + static_cast<int64_t>(row) * a.num_groups + s_begin + pf_chunk * CH);
+        }
+      }
+      if (++pf_chunk == nchunks) {
+        pf_chunk = 0;
+        pf_item += J.cta_count;
+      }
+    }
+    if (++pf_slot == nb) pf_slot = 0;
+    stream::cp_async_commit();  // an empty group keeps the wait arithmetic uniform
+  };
+  for (int i = 0; i < nb; ++i) prefetch_stage();  // the whole ring is in flight before the wait
+
+  const bool b_live = g < a.m;
+  const int sl0 = wide ? s_begin : 0;  // first step of this warp's slice in the staged arrays
+  const uint4* xb_lane = (b_live ? xb + g * m_stride_u4 + t : xb + a.m * m_stride_u4) + (b_live ? sl0 * QU * 4 : 0);
+  const int xb_step_u4 = b_live ? QU * 4 : 0;
+  const float* xsum_w = xsum + sl0 * 8 + 2 * t;
+  const float* xneg_w = xneg + sl0 * 8 + 2 * t;
+  const unsigned char* ring_w_mine = ring_w + tid * UNIT;
+  const unsigned char* ring_m_quad = ring_m + (tid & ~3) * (CH * 2);
+  const uint32_t magic = L.magic;
+  const bool mbf = L.meta_bf16 != 0;
+
+  // ---- the part that depends on the previous kernel: the activation ----
+  int slot = 0, parity = 0;
+  pdl_wait_prior_grid();
+  if (wide) {
+    const bool raw_ok = a.x_dtype != DQ_F32;
+    stage_activation<BITS, XBF16>(a, L.steps, m_stride_u4, xb, xsum, xneg, tid, kThreads, nullptr,
+                                  raw_ok ? raw : nullptr);
+    __syncthreads();
+  } else {
+    stage_warp_slice<BITS, XBF16>(a, s_begin, spw, m_stride_u4, raw, xb, xsum, xneg, lane);
+  }
+
+  for (int item = cta; item < J.items; item += J.cta_count, parity ^= 1) {
+    const int tile = item * rw + rwi;
+    const bool live = tile < J.tiles;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+      wait_pending(nb - 1);  // groups are consumed in issue order: all but the nb-1 youngest are done
+      __syncwarp();          // copies of other lanes (units, the quad's metadata) are visible
+      if (live) {
+        const unsigned char* wsrc = ring_w_mine + slot * R::STAGE_W;
+        const unsigned char* msrc = ring_m_quad + slot * R::STAGE_M;
+        uint32_t mc[4][CH / 2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (has_off || (i & 1) == 0) {
+            if constexpr (CH == 4) {
+              const uint2 v = *reinterpret_cast<const uint2*>(msrc + i * (CH * 2));
+              mc[i][0] = v.x, mc[i][1] = v.y;
+            } else {
+              mc[i][0] = *reinterpret_cast<const uint32_t*>(msrc + i * (CH * 2));
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int sl = chunk * CH + j;
+          uint32_t wa[BITS], wb[BITS];
+          stream::read_unit<BITS>(wsrc + (j * 2 + 0) * (UNIT * kThreads), wa);
+          stream::read_unit<BITS>(wsrc + (j * 2 + 1) * (UNIT * kThreads), wb);
+          uint32_t aa[NA], ab[NA];
+          decode_unit<BITS>(wa, magic, aa);
+          decode_unit<BITS>(wb, magic, ab);
+          unbias_fragments<XBF16, NA>(aa);
+          unbias_fragments<XBF16, NA>(ab);
+          const uint4* bsrc = xb_lane + sl * xb_step_u4;
+          float d[4], e[4];  // two chains: the latency of dependent mma is what a step costs here
+#pragma unroll
+          for (int q = 0; q < QU; ++q) {
+            const uint4 b = bsrc[q * 4];
+            if (q == 0) {
+              mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
+              mma_16816<XBF16, true>(e, aa[2], ab[2], aa[3], ab[3], b.z, b.w);
+            } else {
+              mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
+              mma_16816<XBF16, false>(e, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) d[i] += e[i];
+          auto meta_f32 = [&](int i) -> float {
+            const uint32_t reg = mc[i][j / 2];
+            if (mbf) return __uint_as_float((j & 1) ? (reg & 0xFFFF0000u) : (reg << 16));
+            const __half2 h = *reinterpret_cast<const __half2*>(&reg);
+            return (j & 1) ? __high2float(h) : __low2float(h);
+          };
+          const float2 xs2 = *reinterpret_cast<const float2*>(xsum_w + sl * 8);
+          const float2 xn2 = *reinterpret_cast<const float2*>(xneg_w + sl * 8);
+          const float sc_a = meta_f32(0), sc_b = meta_f32(2);
+          acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
+          acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
+          acc[2] = fmaf(sc_b, d[2] + xn2.x, acc[2]);
+          acc[3] = fmaf(sc_b, d[3] + xn2.y, acc[3]);
+          if (has_off) {
+            const float of_a = meta_f32(1), of_b = meta_f32(3);
+            acc[0] = fmaf(of_a, xs2.x, acc[0]);
+            acc[1] = fmaf(of_a, xs2.y, acc[1]);
+            acc[2] = fmaf(of_b, xs2.x, acc[2]);
+            acc[3] = fmaf(of_b, xs2.y, acc[3]);
+          }
+        }
+      }
+      if (++slot == nb) slot = 0;
+      __syncwarp();      // every lane is done with the slot just consumed:
+      prefetch_stage();  // refill it
+    }
+
+    // ---- sum the slices of the reduction axis in a fixed order, store ----
+    if (kw > 1) {
+      float* buf = red + parity * (kWarps * 128);
+      float* mine = buf + (kwi * rw + rwi) * 128;
+      *reinterpret_cast<float2*>(mine + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
+      *reinterpret_cast<float2*>(mine + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
+      __syncthreads();  // the other buffer is free again once every warp has passed this point
+      if (kwi == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = 0.0f;
+        for (int k = 0; k < kw; ++k) {
+          const float* part = buf + (k * rw + rwi) * 128;
+          const float2 pa = *reinterpret_cast<const float2*>(part + g * 8 + 2 * t);
+          const float2 pb = *reinterpret_cast<const float2*>(part + (g + 8) * 8 + 2 * t);
+          acc[0] += pa.x, acc[1] += pa.y, acc[2] += pb.x, acc[3] += pb.y;
+        }
+      }
+    }
+    if (kwi == 0 && live) {
+      const int row_a = tile * 16 + g, row_b = row_a + 8;
+      const int m0 = 2 * t;
+      if (m0 < a.m) {
+        if (row_a < a.rows) store_out(a, m0, row_a, acc[0]);
+        if (row_b < a.rows) store_out(a, m0, row_b, acc[2]);
+      }
+      if (m0 + 1 < a.m) {
+        if (row_a < a.rows) store_out(a, m0 + 1, row_a, acc[1]);
+        if (row_b < a.rows) store_out(a, m0 + 1, row_b, acc[3]);
+      }
+    }
+  }
+  stream::cp_async_wait<0>();
+}
+
+template <bool XBF16, int CH>
+__global__ void __launch_bounds__(kThreads, 3) gemv_mma_tile_kernel(const __grid_constant__ Launch L) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int j = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxJobs; ++i) {
+    if (i < L.njobs && static_cast<int>(blockIdx.x) >= L.job[i].cta_begin) j = i;
+  }
+  const Job& J = L.job[j];
+  switch (J.bits) {
+    case 2:
+      tile_body<2, XBF16, CH>(L, J, smem_raw);
+      break;
+    case 3:
+      tile_body<3, XBF16, CH>(L, J, smem_raw);
+      break;
+    case 4:
+      tile_body<4, XBF16, CH>(L, J, smem_raw);
+      break;
+    default:
+      tile_body<8, XBF16, CH>(L, J, smem_raw);
+      break;
+  }
+}
+
+}  // namespace tilek
+}  // namespace dq

@@ -13,6 +13,10 @@
 
 namespace dq {
 
+// The activation is read with L2-coherent loads (ld.global.cg): it was written by the previous
+// kernel moments ago, is read once per CTA, and must not be served from a line this SM cached
+// before the previous kernel finished.
+//
 // `raw` (optional): shared-memory scratch of at least m * in_features 16-bit elements.  When
 // given, and the activation is 16-bit and 16-byte aligned, the activation is first copied
 // there with 128-bit loads -- one round trip to L2 for the whole CTA -- and the fragments are
@@ -30,7 +34,7 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
       const int v = i - m * vec_per_row;
       const int64_t src_row = row_map != nullptr ? row_map[m] : m;
       reinterpret_cast<uint4*>(raw)[i] =
-          __ldg(reinterpret_cast<const uint4*>(a.x) + src_row * vec_per_row + v);
+          __ldcg(reinterpret_cast<const uint4*>(a.x) + src_row * vec_per_row + v);
     }
     __syncthreads();
   }
@@ -211,7 +215,7 @@ __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin,
       const uint4* src = reinterpret_cast<const uint4*>(a.x) + (static_cast<int64_t>(m) * a.in_features + k0) / 8;
       for (int v = lane; v < nsteps * 16; v += kWarp) {
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (k0 + v * 8 < a.in_features) val = __ldg(src + v);
+        if (k0 + v * 8 < a.in_features) val = __ldcg(src + v);
         reinterpret_cast<uint4*>(raw)[v] = val;
       }
     } else {

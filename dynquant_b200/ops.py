@@ -310,6 +310,11 @@ def gemv_max_rows() -> int:
     return int(_lib.load().dq_gemv_max_rows())
 
 
+def launch_count() -> int:
+    """Kernels the library has launched in this process so far (``dq_launch_count``)."""
+    return int(_lib.load().dq_launch_count())
+
+
 # --------------------------------------------------------------------------
 # runtime dispatch (reference: runtime/ops.py)
 # --------------------------------------------------------------------------

@@ -186,11 +186,13 @@ class ShardedStepRunner:
             full = torch.empty(world * m, piece.shape[1], dtype=piece.dtype, device=self.device)
             self._gathers.append((piece, full))
             self.outputs[name] = full  # [world*m, N/world]: rank-major pieces of the [m, N] result
-        self.launches_per_step = self.runner.launches_per_step
         self.gathers_per_step = len(self._gathers)
         self.graph_mode = graph_mode
         if graph_mode is not None:
             self.runner.capture(graph_mode)
+        else:
+            self.runner.count_launches()
+        self.launches_per_step = self.runner.launches_per_step
 
     def run(self) -> None:
         if self.graph_mode is not None:

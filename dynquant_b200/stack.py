@@ -64,7 +64,7 @@ class StepRunner:
                 "gemv_sequence", qt.packed, qt.scales, qt.offsets, qt.bits, qt.geometry.effective_group, qt.in_features
             )
         self._graph: torch.cuda.CUDAGraph | None = None
-        self.launches_per_step = len(stack.modules)
+        self.launches_per_step = len(stack.modules)  # replaced by the measured count in capture()
 
     def run(self) -> None:
         """Enqueue the whole step on torch's current stream, module after module."""
@@ -72,24 +72,34 @@ class StepRunner:
         with torch.cuda.device(self.device):
             _lib.check(lib.dq_gemv_sequence(self._jobs, len(self._jobs), _stream(self.device)))
 
+    def count_launches(self) -> int:
+        """Run the step once eagerly and record how many kernels it launched."""
+        lib = _lib.load()
+        before = int(lib.dq_launch_count())
+        self.run()
+        self.launches_per_step = int(lib.dq_launch_count()) - before
+        return self.launches_per_step
+
     def _run_jobs(self, first: int, count: int) -> None:
         lib = _lib.load()
         jobs = ctypes.cast(ctypes.byref(self._jobs, first * ctypes.sizeof(_lib.GemvJob)), ctypes.POINTER(_lib.GemvJob))
         _lib.check(lib.dq_gemv_sequence(jobs, count, _stream(self.device)))
 
-    def run_dataflow(self, side_streams: list[torch.cuda.Stream]) -> None:
-        """Enqueue the step as its dependency graph: the members of a stage (q/k/v, gate/up)
-        run on separate streams, consecutive stages are ordered by events."""
+    def run_dataflow(self, side_streams: list[torch.cuda.Stream] | None = None) -> None:
+        """Enqueue the step as its dependency graph: stage after stage, the members of a stage
+        (q/k/v, gate/up: contiguous jobs reading one activation) in ONE library call, which
+        issues them as one fused launch.  Stages whose members are not contiguous fork onto
+        ``side_streams``."""
         main = torch.cuda.current_stream(self.device)
         with torch.cuda.device(self.device):
             for stage in self.stack.stages():
-                if len(stage) == 1:
-                    self._run_jobs(stage[0], 1)
+                if list(stage) == list(range(stage[0], stage[0] + len(stage))):
+                    self._run_jobs(stage[0], len(stage))
                     continue
                 fork = torch.cuda.Event()
                 fork.record(main)
                 self._run_jobs(stage[0], 1)
-                for idx, side in zip(stage[1:], side_streams):
+                for idx, side in zip(stage[1:], side_streams or []):
                     side.wait_event(fork)
                     with torch.cuda.stream(side):
                         self._run_jobs(idx, 1)
@@ -100,13 +110,17 @@ class StepRunner:
     def capture(self, mode: str = "dataflow") -> None:
         """Record the step into a CUDA graph.
 
-        ``"dataflow"``: stages in order, members of a stage concurrent (what a decoder
-        layer's dependencies allow).  ``"chain"``: every module after the previous one.
+        ``"dataflow"``: stages in order, the members of a stage in one fused launch (what a
+        decoder layer's dependencies allow).  ``"chain"``: the whole job list in stream order through
+        one ``dq_gemv_sequence`` call -- consecutive modules that read the same activation
+        (q/k/v, gate/up) leave as one fused launch, the rest one after the other.
         ``"independent"``: no edges at all -- every module's input is resident, nothing
         waits for anything (the regime the reference's per-shape bandwidth table measures).
         """
         self.run()  # warm: sets per-kernel attributes outside the capture
         torch.cuda.synchronize(self.device)
+        lib = _lib.load()
+        before = int(lib.dq_launch_count())
         graph = torch.cuda.CUDAGraph()
         sides = [torch.cuda.Stream(self.device) for _ in range(8 if mode == "independent" else 2)]
         with torch.cuda.graph(graph):
@@ -132,6 +146,7 @@ class StepRunner:
                 raise ValueError(mode)
         self._graph = graph
         self.mode = mode
+        self.launches_per_step = int(lib.dq_launch_count()) - before  # kernels recorded in the graph
 
     def replay(self) -> None:
         if self._graph is None:

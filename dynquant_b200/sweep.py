@@ -1,0 +1,101 @@
+"""Width / shape sweep of the packed GEMV: achieved HBM GB/s and % of the roofline per point.
+
+The counterpart of the reference's ``benchmarks/gemv_bandwidth.py`` for this library, and
+BASELINE config 5: widths {2,3,4,8} x group {64,128} x Mistral-7B shapes x M {1,4,16} plus
+odd-N tails.  Every point runs over a ring of distinct weight tensors whose total size
+exceeds twice the L2 (so the bytes really come from HBM) and is timed with CUDA events;
+M above the operator's row limit goes through the dequant + dense path, as in the reference.
+
+    python -m dynquant_b200.sweep                      # the full config-5 grid
+    python -m dynquant_b200.sweep --shape 131072x2048 --bits 8 --m 1 --launches 4 --ring 1
+                                                       # one point, few launches (for ncu)
+
+Prints one JSON object per point.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from . import ops
+from .workloads import random_quant_tensor
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def hbm_peak_gbs() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except (KeyError, ValueError):
+            pass
+    return 6650.0, "fallback"
+
+
+def run_point(rows: int, k: int, bits: int, group: int, m: int, *, launches: int, ring: int | None,
+              device="cuda") -> dict:
+    probe = random_quant_tensor(rows, k, bits, group_size=group, device=device)
+    l2 = torch.cuda.get_device_properties(device).L2_cache_size
+    if ring is None:
+        ring = max(1, min(64, -(-2 * l2 // probe.nbytes)))
+    weights = [probe] + [random_quant_tensor(rows, k, bits, group_size=group, device=device) for _ in range(ring - 1)]
+    x = torch.randn(m, k, device=device).to(torch.bfloat16)
+
+    def step(qt):
+        return ops.quantized_matmul(x, qt)
+
+    for qt in weights[: min(3, ring)]:
+        step(qt)
+    torch.cuda.synchronize()
+    # one CUDA graph of `launches` back-to-back calls over the ring: device time only, no Python
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(launches):
+            step(weights[i % ring])
+    graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(stop) / 1e3 / launches
+    nbytes = probe.nbytes + m * k * 2 + m * rows * 2
+    peak, kind = hbm_peak_gbs()
+    gbs = nbytes / seconds / 1e9
+    return {
+        "rows": rows, "in_features": k, "bits": bits, "group_size": group, "m": m,
+        "path": "gemv" if m <= ops.gemv_max_rows() else "dequant+dense",
+        "us_per_call": round(seconds * 1e6, 2), "gbps": round(gbs, 1),
+        "pct_of_hbm_peak": round(100 * gbs / peak, 1), "peak": f"{peak} GB/s ({kind})",
+        "ring": ring, "ring_bytes": probe.nbytes * ring, "launches": launches,
+    }
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", action="append", help="ROWSxK; repeatable (default: the config-5 shapes)")
+    ap.add_argument("--bits", default="2,3,4,8")
+    ap.add_argument("--group", default="64,128")
+    ap.add_argument("--m", default="1,4,16")
+    ap.add_argument("--launches", type=int, default=50)
+    ap.add_argument("--ring", type=int, default=None, help="distinct weight tensors (default: > 2x L2)")
+    ns = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("the sweep needs a CUDA device: this library has no CPU path")
+    shapes = ns.shape or ["14336x4096", "4096x14336", "4096x4096", "4097x4096"]
+    for shape in shapes:
+        rows, k = (int(v) for v in shape.lower().split("x"))
+        for bits in (int(b) for b in ns.bits.split(",")):
+            for group in (int(g) for g in ns.group.split(",")):
+                for m in (int(v) for v in ns.m.split(",")):
+                    print(json.dumps(run_point(rows, k, bits, group, m, launches=ns.launches, ring=ns.ring)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -92,6 +92,13 @@ DQ_API int32_t dq_abi_version(void);
 DQ_API int32_t dq_built_with_cuda(void);
 DQ_API const char* dq_compiled_architectures(void);
 DQ_API int32_t dq_gemv_max_rows(void);
+
+/* Kernels this library has launched in this process so far, over all entry
+ * points (monotonic; counted at launch, also during stream capture).  No
+ * reference counterpart: the reference launches one kernel per operator call
+ * (csrc/cuda/gemv.cu:231-275), here one call may be one launch for several
+ * matrices or several launches for one, and benchmarks report the real number. */
+DQ_API int64_t dq_launch_count(void);
 DQ_API int32_t dq_moe_max_tokens(void);
 DQ_API const char* dq_last_error(void);
 
@@ -117,7 +124,8 @@ DQ_API int32_t dq_gemv(const void* x, int32_t x_dtype, int64_t m, const dq_weigh
  * plus concat of integration/vllm_plugin/linear.py:172-186 and
  * integration/serving_common/fuse.py:41-53).  Shard i writes columns
  * [sum(rows[0..i)), +rows[i]) of out [m, out_stride]; every shard shares x and
- * in_features.  bias [sum rows] in out_dtype or NULL. */
+ * in_features.  bias [sum rows] in out_dtype or NULL.  Up to four shards at a
+ * time, of any mix of widths, run as ONE kernel launch. */
 DQ_API int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const dq_weight* shards,
                               int32_t num_shards, const void* bias, void* out, int64_t out_stride,
                               int32_t out_dtype, void* stream);
@@ -141,8 +149,11 @@ typedef struct dq_gemv_job {
  * (packages/dynquant-core/src/dynquant/runtime/ops.py:184-231), without a
  * host round trip per module.  Every launch carries the programmatic
  * dependent-launch attribute, so job i+1 streams its first weights while job
- * i drains and reads its activation only after job i has completed.  All jobs
- * are validated before the first launch. */
+ * i drains and reads its activation only after job i has completed.
+ * Consecutive jobs that read the SAME activation (same x pointer, m and dtypes:
+ * the q/k/v or gate/up shards of a layer) cannot depend on one another; up to
+ * four of them are issued as one launch, so their outputs must not overlap.
+ * All jobs are validated before the first launch. */
 DQ_API int32_t dq_gemv_sequence(const dq_gemv_job* jobs, int32_t num_jobs, void* stream);
 
 /* Same as dq_gemv with x and out in HOST memory: copies x to the device,

@@ -118,9 +118,13 @@ def test_gemv_sequence_and_step_runner_match_individual_calls():
     runner.run()
     torch.cuda.synchronize()
     eager = {k: v.clone() for k, v in runner.outputs.items()}
+    # a fused launch may slice the reduction axis differently from the single call: the two
+    # agree to the rounding of the fp32 partial sums, i.e. within one bf16 ulp of the output
     for mod in stack.modules:
         want = ops.quantized_matmul(runner.inputs[mod.input], mod.weight)
-        assert torch.equal(eager[mod.name], want), mod.name
+        diff = (eager[mod.name].float() - want.float()).abs()
+        bound = want.float().abs() * 2.0**-7 + 1e-4 * want.float().abs().max()
+        assert bool((diff <= bound).all()), (mod.name, float(diff.max()))
     for mode in ("dataflow", "chain", "independent"):
         for v in runner.outputs.values():
             v.zero_()
@@ -128,7 +132,11 @@ def test_gemv_sequence_and_step_runner_match_individual_calls():
         runner.replay()
         torch.cuda.synchronize()
         for name, want in eager.items():
-            assert torch.equal(runner.outputs[name], want), (mode, name)
+            if mode == "independent":  # single launches: may slice the reduction differently
+                diff = (runner.outputs[name].float() - want.float()).abs()
+                assert bool((diff <= want.float().abs() * 2.0**-7 + 1e-4 * want.float().abs().max()).all()), name
+            else:
+                assert torch.equal(runner.outputs[name], want), (mode, name)
 
 
 def test_gemv_host_entry_point_round_trips_through_pinned_memory():
