@@ -7,25 +7,33 @@
 // (quant/tensor.py:253-255; shapes from graph/experts.py:35-43: gate_up [E, 2I, H] with
 // the gate rows first, down [E, H, I]) -- and this file computes on exactly that.
 //
-// Four launches, all on the caller's stream, no host round trip:
-//   1. route    one CTA: per-expert token counts, offsets, and the (token, slot)
-//               assignments sorted by expert (stable: ascending assignment id).
-//   2. gate_up  grid (row-tile pairs, experts).  An expert's packed rows are streamed ONCE
-//               per step for up to 8 of its tokens at a time -- the tokens are the 8
-//               columns of the m16n8k16 accumulator, exactly like the activation rows of
-//               the dense GEMV (dq_gemv_mma.cu), gathered by index while staging.  A warp
-//               computes 16 gate rows and the matching 16 up rows and writes
-//               h = silu(g) * u, rounded to the activation dtype, to scratch.
-//   3. down     same machinery over the down bank with h as the activation; the fp32
-//               result of every assignment goes to scratch.
-//   4. combine  y[t] = sum_k p[t,k] * d[t,k] in slot order -- a fixed order, so the layer is
-//               bit-identical run to run (no atomics anywhere).
-// Experts with no token exit at once; ids outside [0, num_experts) are skipped, which is how
-// an expert-parallel rank passes "not mine".
+// Three launches, all on the caller's stream, no host round trip:
+//   1. gate_up  grid (row-tile pairs, slots), one slot per expert that COULD be active
+//               (min(E, tokens * topk)).  Every CTA first works out the routing itself from
+//               topk_ids -- which expert is the slot-th one with a token, and which
+//               assignments are its (in ascending order) -- a few hundred cycles of shared-
+//               memory work instead of a launch and a round trip through global memory.
+//               CTAs of empty slots exit.  The expert's packed rows for the CTA's tile travel
+//               to shared memory ONCE (16-byte cp.async) and are reused for all of its tokens,
+//               eight at a time: the tokens are the 8 columns of the m16n8k16 accumulator,
+//               exactly like the activation rows of the dense GEMV (dq_gemv_mma.cu), gathered
+//               by index while staging.  A warp computes its slice of 16 gate rows and the
+//               matching 16 up rows; h = silu(g) * u, rounded to the activation dtype, goes
+//               to scratch.
+//   2. down     same machinery over the down bank with h as the activation; the fp32
+//               result of every assignment goes to scratch.  Routing and the down weights
+//               depend on topk_ids only, so this kernel computes the one and requests the
+//               other BEFORE griddepcontrol.wait, while gate_up is still running.
+//   3. combine  y[t] = sum_k p[t,k] * d[t,k] in slot order -- a fixed order, so the layer is
+//               bit-identical run to run (no atomics on floats anywhere).
+// ids outside [0, num_experts) are skipped, which is how an expert-parallel rank passes
+// "not mine".
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 
 #include "dq_gemv.cuh"
+#include "dq_gemv_mma_stream.cuh"
 #include "dq_mma_plan.cuh"
 #include "dq_mma_stage.cuh"
 
@@ -36,249 +44,378 @@ constexpr int kMoeWarps = 8;
 constexpr int kMoeThreads = kMoeWarps * kWarp;
 constexpr int kMaxAssign = DQ_MOE_MAX_TOKENS * 16;
 
-struct Routing {
-  int* counts;   // [E]
-  int* offsets;  // [E + 1]
-  int* sorted;   // [A] assignment ids (t * topk + k), grouped by expert
-};
-
-__global__ void __launch_bounds__(512) moe_route_kernel(const int32_t* __restrict__ ids, int assignments,
-                                                        int num_experts, Routing r) {
-  extern __shared__ int sm[];  // [E] counts, [E + 1] offsets
-  int* cnt = sm;
-  int* off = sm + num_experts;
-  pdl_launch_dependents();
-  pdl_wait_prior_grid();
-  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) cnt[e] = 0;
-  __syncthreads();
-  for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
-    const int e = ids[a];
-    if (e >= 0 && e < num_experts) atomicAdd(&cnt[e], 1);  // integer count: order-independent
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < num_experts; ++e) {
-      off[e] = run;
-      run += cnt[e];
-    }
-    off[num_experts] = run;
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
-    r.counts[e] = cnt[e];
-    r.offsets[e] = off[e];
-  }
-  if (threadIdx.x == 0) r.offsets[num_experts] = off[num_experts];
-  // stable placement: rank of a among the assignments of the same expert with a smaller id
-  for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
-    const int e = ids[a];
-    if (e < 0 || e >= num_experts) continue;
-    int rank = 0;
-    for (int b = 0; b < a; ++b) rank += (ids[b] == e);
-    r.sorted[off[e] + rank] = a;
-  }
-}
-
 struct MoeArgs {
   const void* act;          // gate_up: x [tokens, K]; down: h [assignments, K]
   const uint32_t* packed;   // the bank, [E * rows_per_expert(*2), words_per_row]
   const void* scales;
   const void* offsets;      // may be null
   void* out;                // gate_up: h [assignments, inter] act dtype; down: d [assignments, hidden] fp32
-  Routing route;
+  const int32_t* ids;       // [assignments] expert of every (token, slot)
+  int assignments, num_experts;
   int act_dtype, meta_dtype;
   int topk;
   int rows;                 // output rows per expert of this launch (inter, or hidden)
   int words_per_row, num_groups, in_features;
   int steps;                // padded K / 128
   int kw, rw;               // warps: rw row tiles x kw slices of the reduction axis
-  int steps_per_warp;
+  int spw;                  // steps per slice, a multiple of CH
+  int nb;                   // ring stages (of CH steps per warp)
+  int m_cap;                // activation rows staged at once (<= 8)
   int m_stride_u4;
   uint32_t magic;
 };
 
-template <bool BF16>
-__device__ __forceinline__ float meta_to_f32(uint32_t raw) {
-  if constexpr (BF16) {
-    return __uint_as_float(raw << 16);
-  } else {
-    return __half2float(__ushort_as_half(static_cast<unsigned short>(raw)));
+// Shared memory of moe_grouped_kernel, in order.
+struct MoeSmem {
+  size_t ring_w, ring_m, red, ids, counts, list, misc, stage, total;
+};
+
+template <int BITS, int CH>
+__host__ __device__ inline MoeSmem moe_smem(const MoeArgs& a, bool gate_up) {
+  const int halves = gate_up ? 2 : 1;
+  const int na = BITS == 8 ? 32 : 16;
+  auto up16 = [](size_t v) { return (v + 15) / 16 * 16; };
+  MoeSmem m = {};
+  size_t at = 0;
+  m.ring_w = at, at += static_cast<size_t>(a.nb) * CH * 2 * kMoeThreads * (4 * BITS);
+  m.ring_m = at, at += static_cast<size_t>(a.nb) * CH * 2 * kMoeThreads;
+  m.red = at, at += 2 * static_cast<size_t>(halves) * kMoeWarps * 128 * 4;  // two buffers, alternating per item
+  m.ids = at, at = up16(at + static_cast<size_t>(a.assignments) * 4);
+  m.counts = at, at = up16(at + static_cast<size_t>(a.num_experts) * 4);
+  m.list = at, at = up16(at + static_cast<size_t>(DQ_MOE_MAX_TOKENS) * 4);
+  m.misc = at, at += 64 * 4;  // [0] expert, [1] count, [8..15] row map, [16..47] ballot counts
+  m.stage = at;
+  at += (static_cast<size_t>(a.m_cap) * a.m_stride_u4 + na) * 16 + static_cast<size_t>(a.steps) * 64 +
+        static_cast<size_t>(a.m_cap) * a.in_features * 2 + 16;
+  m.total = at;
+  return m;
+}
+
+__device__ __forceinline__ void moe_wait_pending(int n) {
+  switch (n) {
+    case 0: stream::cp_async_wait<0>(); break;
+    case 1: stream::cp_async_wait<1>(); break;
+    case 2: stream::cp_async_wait<2>(); break;
+    case 3: stream::cp_async_wait<3>(); break;
+    case 4: stream::cp_async_wait<4>(); break;
+    case 5: stream::cp_async_wait<5>(); break;
+    case 6: stream::cp_async_wait<6>(); break;
+    default: stream::cp_async_wait<7>(); break;
   }
 }
 
-// One 16-row tile over this warp's slice of the reduction axis: acc[4] as in the dense kernel.
-template <int BITS, bool XBF16, bool MBF16>
-__device__ __forceinline__ void moe_tile(const MoeArgs& a, int64_t row_a, int64_t row_b, int s_begin, int s_end,
-                                         const uint4* xb_lane, int xb_step_u4, const float* xsum,
-                                         const float* xneg, int t, float* acc) {
+// One CTA: one active expert (grid.y = slot), a strided share of its row tiles (grid.x).
+// The plumbing is that of the tiled dense kernel (dq_gemv_mma_tile.cuh): 8 warps as rw row
+// tiles x kw slices of the reduction axis, every warp streaming ITS slice of ITS tiles
+// through a private cp.async ring of `nb` stages of CH steps, partial sums of the slices
+// added in a fixed order.  GATE_UP: an item is 16 gate rows plus the matching 16 up rows per
+// row tile, and the output is silu(g) * u.
+template <int BITS, bool XBF16, int CH, bool GATE_UP>
+__global__ void __launch_bounds__(kMoeThreads, 2) moe_grouped_kernel(const __grid_constant__ MoeArgs a) {
   using Plan = MmaPlan<BITS>;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
+  constexpr int UNIT = 4 * BITS;
   constexpr int STEP_WORDS = 4 * BITS;
-  const uint32_t* wa = a.packed + row_a * a.words_per_row + t * BITS;
-  const uint32_t* wb = a.packed + row_b * a.words_per_row + t * BITS;
-  const unsigned short* sc = reinterpret_cast<const unsigned short*>(a.scales);
-  const unsigned short* of = reinterpret_cast<const unsigned short*>(a.offsets);
-#pragma unroll 1
-  for (int s0 = s_begin; s0 < s_end; s0 += 4) {
-    // a block of up to four steps: all loads first, then the math
-    uint32_t raw[4][2][BITS];
-    uint32_t meta[4][4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (s0 + j < s_end) {
-#pragma unroll
-        for (int i = 0; i < BITS; ++i) {
-          raw[j][0][i] = __ldg(wa + (s0 + j) * STEP_WORDS + i);
-          raw[j][1][i] = __ldg(wb + (s0 + j) * STEP_WORDS + i);
-        }
-        const int64_t ia = row_a * a.num_groups + (s0 + j), ib = row_b * a.num_groups + (s0 + j);
-        meta[j][0] = __ldg(sc + ia);
-        meta[j][2] = __ldg(sc + ib);
-        meta[j][1] = of != nullptr ? __ldg(of + ia) : 0u;
-        meta[j][3] = of != nullptr ? __ldg(of + ib) : 0u;
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (s0 + j < s_end) {
-        const int s = s0 + j;
-        uint32_t aa[NA], ab[NA];
-        decode_unit<BITS>(raw[j][0], a.magic, aa);
-        decode_unit<BITS>(raw[j][1], a.magic, ab);
-        unbias_fragments<XBF16, NA>(aa);
-        unbias_fragments<XBF16, NA>(ab);
-        const uint4* bsrc = xb_lane + s * xb_step_u4;
-        float d[4];
-#pragma unroll
-        for (int q = 0; q < QU; ++q) {
-          const uint4 b = bsrc[q * 4];
-          if (q == 0) {
-            mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
-          } else {
-            mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
-          }
-          mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
-        }
-        const float2 xs2 = *reinterpret_cast<const float2*>(xsum + s * 8 + 2 * t);
-        const float2 xn2 = *reinterpret_cast<const float2*>(xneg + s * 8 + 2 * t);
-        const float sc_a = meta_to_f32<MBF16>(meta[j][0]), of_a = meta_to_f32<MBF16>(meta[j][1]);
-        const float sc_b = meta_to_f32<MBF16>(meta[j][2]), of_b = meta_to_f32<MBF16>(meta[j][3]);
-        acc[0] = fmaf(sc_a, d[0] + xn2.x, fmaf(of_a, xs2.x, acc[0]));
-        acc[1] = fmaf(sc_a, d[1] + xn2.y, fmaf(of_a, xs2.y, acc[1]));
-        acc[2] = fmaf(sc_b, d[2] + xn2.x, fmaf(of_b, xs2.x, acc[2]));
-        acc[3] = fmaf(sc_b, d[3] + xn2.y, fmaf(of_b, xs2.y, acc[3]));
-      }
-    }
-  }
-}
-
-// GATE_UP: a tile is 16 gate rows plus the matching 16 up rows, output silu(g)*u.
-template <int BITS, bool XBF16, bool MBF16, bool GATE_UP>
-__global__ void __launch_bounds__(kMoeThreads) moe_grouped_kernel(const MoeArgs a) {
-  using Plan = MmaPlan<BITS>;
-  constexpr int QU = Plan::kARegs / 4;
+  constexpr int H = GATE_UP ? 2 : 1;
+  constexpr int STAGE_W = CH * 2 * UNIT * kMoeThreads;
+  constexpr int STAGE_M = CH * 2 * kMoeThreads;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint4* xb = reinterpret_cast<uint4*>(smem_raw);
-  float* xsum = reinterpret_cast<float*>(xb + 8 * a.m_stride_u4 + QU * 4);
+  const MoeSmem lay = moe_smem<BITS, CH>(a, GATE_UP);
+  unsigned char* ring_w = smem_raw + lay.ring_w;
+  unsigned char* ring_m = smem_raw + lay.ring_m;
+  float* red = reinterpret_cast<float*>(smem_raw + lay.red);
+  int* ids_s = reinterpret_cast<int*>(smem_raw + lay.ids);
+  int* cnt = reinterpret_cast<int*>(smem_raw + lay.counts);
+  int* list = reinterpret_cast<int*>(smem_raw + lay.list);
+  int* misc = reinterpret_cast<int*>(smem_raw + lay.misc);
+  int* row_map = misc + 8;
+  int* ballots = misc + 16;
+  uint4* xb = reinterpret_cast<uint4*>(smem_raw + lay.stage);
+  float* xsum = reinterpret_cast<float*>(xb + a.m_cap * a.m_stride_u4 + NA);
   float* xneg = xsum + a.steps * 8;
-  float* red = xneg + a.steps * 8;                       // [halves][kw][rw][16][8]
-  int* row_map = reinterpret_cast<int*>(red + (GATE_UP ? 2 : 1) * a.kw * a.rw * 16 * 8);  // [8]
-
-  const int e = blockIdx.y;
-  pdl_launch_dependents();
-  pdl_wait_prior_grid();  // routing (and for the down pass, h) come from the previous kernels
-  const int count = a.route.counts[e];
-  if (count == 0) return;
-  const int first = a.route.offsets[e];
+  unsigned short* raw = reinterpret_cast<unsigned short*>(xneg + a.steps * 8);
 
   const int tid = threadIdx.x;
   const int lane = tid & (kWarp - 1);
   const int warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int rwi = warp / a.kw;
-  const int kwi = warp - rwi * a.kw;
-  const int tile = blockIdx.x * a.rw + rwi;
+  const int slot = blockIdx.y;
+
+  // gate_up: topk_ids come from the previous kernel; and only once every CTA of this grid
+  // is past that wait may the down kernel start (its routing and weight requests run ahead
+  // of ITS wait).  down: nothing it needs before the wait is written by gate_up.
+  if (GATE_UP) {
+    pdl_wait_prior_grid();
+  }
+  pdl_launch_dependents();
+
+  // ---- routing, by every CTA for itself ----
+  for (int i = tid; i < a.num_experts; i += kMoeThreads) cnt[i] = 0;
+  for (int i = tid; i < a.assignments; i += kMoeThreads) ids_s[i] = __ldcg(a.ids + i);
+  if (tid == 0) misc[0] = -1;
+  __syncthreads();
+  for (int i = tid; i < a.assignments; i += kMoeThreads) {
+    const int e = ids_s[i];
+    if (e >= 0 && e < a.num_experts) atomicAdd(&cnt[e], 1);  // integer count: order-independent
+  }
+  __syncthreads();
+  if (warp == 0) {  // the slot-th expert (ascending id) that has a token
+    int seen = 0;
+    for (int base = 0; base < a.num_experts; base += kWarp) {
+      const int e = base + lane;
+      const bool active = e < a.num_experts && cnt[e] > 0;
+      const unsigned mask = __ballot_sync(0xffffffffu, active);
+      const int before = __popc(mask & ((1u << lane) - 1u));
+      if (active && seen + before == slot) {
+        misc[0] = e;
+        misc[1] = min(cnt[e], DQ_MOE_MAX_TOKENS);
+      }
+      seen += __popc(mask);
+      if (seen > slot) break;
+    }
+  }
+  __syncthreads();
+  const int e = misc[0];
+  if (e < 0) return;  // fewer active experts than slots
+  const int count = misc[1];
+
+  // ---- this warp's sequence of ring stages: (token chunk, item, half, chunk of CH steps) ----
+  const int kw = a.kw, rw = a.rw, spw = a.spw, nb = a.nb;
+  const int rwi = warp / kw;
+  const int kwi = warp - rwi * kw;
+  const int s_begin = kwi * spw;
+  const int nchunks = spw / CH;
   const int tiles = (a.rows + 15) / 16;
-  const bool tile_live = tile < tiles;
-  const int s_begin = kwi * a.steps_per_warp;
-  const int s_end = min(a.steps, s_begin + a.steps_per_warp);
-  const int64_t expert_row0 = static_cast<int64_t>(e) * a.rows * (GATE_UP ? 2 : 1);
-  const int r_a = min(tile * 16 + g, a.rows - 1), r_b = min(tile * 16 + g + 8, a.rows - 1);
+  const int items = (tiles + rw - 1) / rw;
+  const int ntc = (count + a.m_cap - 1) / a.m_cap;  // token chunks
+  const int64_t expert_row0 = static_cast<int64_t>(e) * a.rows * H;
+  const bool has_off = a.offsets != nullptr;
+  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * UNIT;
+  const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * (CH * 2);
+  const bool meta_lane = has_off || (t & 1) == 0;
+  const unsigned short* meta_arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
+  int pf_tc = 0, pf_item = blockIdx.x, pf_half = 0, pf_chunk = 0, pf_slot = 0;
+  auto prefetch_stage = [&]() {
+    if (pf_tc < ntc && pf_item < items) {
+      const int tile = pf_item * rw + rwi;
+      if (tile < tiles) {
+        const int row0 = static_cast<int>(expert_row0) + pf_half * a.rows + tile * 16;
+        const int last = static_cast<int>(expert_row0) + (pf_half + 1) * a.rows - 1;
+        const uint32_t dst = ring_w_s + pf_slot * STAGE_W;
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int word0 = (s_begin + pf_chunk * CH + j) * STEP_WORDS;
+          stream::copy_block<BITS>(dst + (j * 2 + 0) * (UNIT * kMoeThreads), a.packed, a.words_per_row, row0, last,
+                                   word0, lane);
+          stream::copy_block<BITS>(dst + (j * 2 + 1) * (UNIT * kMoeThreads), a.packed, a.words_per_row, row0 + 8, last,
+                                   word0, lane);
+        }
+        if constexpr (CH >= 2) {  // (a single step's metadata is 2 bytes: read in the loop instead)
+          if (meta_lane) {
+            const int row = min(row0 + g + ((t & 2) ? 8 : 0), last);
+            stream::cp_async_n<CH * 2>(ring_m_s + pf_slot * STAGE_M,
+                                       meta_arr + static_cast<int64_t>(row) * a.num_groups + s_begin + pf_chunk * CH);
+          }
+        }
+      }
+      if (++pf_chunk == nchunks) {
+        pf_chunk = 0;
+        if (++pf_half == H) {
+          pf_half = 0;
+          pf_item += gridDim.x;
+          if (pf_item >= items) {
+            pf_item = blockIdx.x;
+            ++pf_tc;
+          }
+        }
+      }
+    }
+    if (++pf_slot == nb) pf_slot = 0;
+    stream::cp_async_commit();  // an empty group keeps the wait arithmetic uniform
+  };
+  for (int i = 0; i < nb; ++i) prefetch_stage();
+
+  // ---- the expert's assignments in ascending order (so results do not depend on timing) ----
+  for (int base = 0; base < a.assignments; base += kMoeThreads) {
+    const int i = base + tid;
+    const bool mine = i < a.assignments && ids_s[i] == e;
+    const unsigned mask = __ballot_sync(0xffffffffu, mine);
+    if (lane == 0) ballots[(base / kMoeThreads) * kMoeWarps + warp] = __popc(mask);
+  }
+  __syncthreads();
+  for (int base = 0; base < a.assignments; base += kMoeThreads) {
+    const int i = base + tid;
+    const bool mine = i < a.assignments && ids_s[i] == e;
+    const unsigned mask = __ballot_sync(0xffffffffu, mine);
+    if (mine) {
+      int rank = __popc(mask & ((1u << lane) - 1u));
+      const int upto = (base / kMoeThreads) * kMoeWarps + warp;
+      for (int k = 0; k < upto; ++k) rank += ballots[k];
+      if (rank < DQ_MOE_MAX_TOKENS) list[rank] = i;
+    }
+  }
+
+  if (!GATE_UP) {
+    pdl_wait_prior_grid();  // h
+  }
 
   GemvArgs stage = {};
   stage.x = a.act;
   stage.x_dtype = a.act_dtype;
   stage.in_features = a.in_features;
+  const bool mbf = a.meta_dtype == DQ_BF16;
+  const uint32_t magic = a.magic;
+  const unsigned char* ring_w_mine = ring_w + tid * UNIT;
+  const unsigned char* ring_m_quad = ring_m + (tid & ~3) * (CH * 2);
+  const float* xsum_w = xsum + s_begin * 8 + 2 * t;
+  const float* xneg_w = xneg + s_begin * 8 + 2 * t;
 
-  for (int c0 = 0; c0 < count; c0 += 8) {  // up to 8 of this expert's tokens per pass
-    const int m = min(8, count - c0);
-    __syncthreads();  // the previous pass is done with row_map / xb / red
+  int slot_r = 0, parity = 0;
+  for (int tc = 0; tc < ntc; ++tc) {
+    const int c0 = tc * a.m_cap;
+    const int m = min(a.m_cap, count - c0);
+    __syncthreads();  // list is complete; the previous chunk is done with row_map / xb
     if (tid < 8) {
-      const int aid = a.route.sorted[first + min(c0 + tid, count - 1)];
+      const int aid = list[min(c0 + tid, count - 1)];
       row_map[tid] = GATE_UP ? aid / a.topk : aid;  // x is per token, h per assignment
     }
     __syncthreads();
     stage.m = m;
-    stage_activation<BITS, XBF16>(stage, a.steps, a.m_stride_u4, xb, xsum, xneg, tid, kMoeThreads, row_map);
+    stage_activation<BITS, XBF16>(stage, a.steps, a.m_stride_u4, xb, xsum, xneg, tid, kMoeThreads, row_map, raw);
     __syncthreads();
-
     const bool b_live = g < m;
-    const uint4* xb_lane = b_live ? xb + g * a.m_stride_u4 + t : xb + m * a.m_stride_u4;
+    const uint4* xb_lane = (b_live ? xb + g * a.m_stride_u4 + t : xb + m * a.m_stride_u4) + (b_live ? s_begin * QU * 4 : 0);
     const int xb_step_u4 = b_live ? QU * 4 : 0;
-    float acc[GATE_UP ? 2 : 1][4];
+
+    for (int item = blockIdx.x; item < items; item += gridDim.x, parity ^= 1) {
+      const int tile = item * rw + rwi;
+      const bool live = tile < tiles;
+      float acc[H][4];
 #pragma unroll
-    for (int h = 0; h < (GATE_UP ? 2 : 1); ++h) {
+      for (int h = 0; h < H; ++h) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[h][i] = 0.0f;
-      if (tile_live) {
-        const int64_t base = expert_row0 + static_cast<int64_t>(h) * a.rows;  // gate rows, then up rows
-        moe_tile<BITS, XBF16, MBF16>(a, base + r_a, base + r_b, s_begin, s_end, xb_lane, xb_step_u4, xsum, xneg,
-                                     t, acc[h]);
+        for (int i = 0; i < 4; ++i) acc[h][i] = 0.0f;
+        for (int chunk = 0; chunk < nchunks; ++chunk) {
+          moe_wait_pending(nb - 1);  // groups complete in issue order: all but the nb-1 youngest are done
+          __syncwarp();              // copies of other lanes (units, the quad's metadata) are visible
+          if (live) {
+            const unsigned char* wsrc = ring_w_mine + slot_r * STAGE_W;
+            const unsigned char* msrc = ring_m_quad + slot_r * STAGE_M;
+            uint32_t mc[4][CH >= 2 ? CH / 2 : 1];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (has_off || (i & 1) == 0) {
+                if constexpr (CH == 1) {
+                  const int row0 = static_cast<int>(expert_row0) + h * a.rows;
+                  const int row = min(row0 + tile * 16 + g + ((i & 2) ? 8 : 0), row0 + a.rows - 1);
+                  const unsigned short* arr = reinterpret_cast<const unsigned short*>((i & 1) ? a.offsets : a.scales);
+                  mc[i][0] = __ldg(arr + static_cast<int64_t>(row) * a.num_groups + s_begin + chunk);
+                } else if constexpr (CH == 4) {
+                  const uint2 v = *reinterpret_cast<const uint2*>(msrc + i * (CH * 2));
+                  mc[i][0] = v.x, mc[i][1] = v.y;
+                } else {
+                  mc[i][0] = *reinterpret_cast<const uint32_t*>(msrc + i * (CH * 2));
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int sl = chunk * CH + j;
+              uint32_t wa[BITS], wb[BITS];
+              stream::read_unit<BITS>(wsrc + (j * 2 + 0) * (UNIT * kMoeThreads), wa);
+              stream::read_unit<BITS>(wsrc + (j * 2 + 1) * (UNIT * kMoeThreads), wb);
+              uint32_t aa[NA], ab[NA];
+              decode_unit<BITS>(wa, magic, aa);
+              decode_unit<BITS>(wb, magic, ab);
+              unbias_fragments<XBF16, NA>(aa);
+              unbias_fragments<XBF16, NA>(ab);
+              const uint4* bsrc = xb_lane + sl * xb_step_u4;
+              float d[4], f[4];
+#pragma unroll
+              for (int q = 0; q < QU; ++q) {
+                const uint4 b = bsrc[q * 4];
+                if (q == 0) {
+                  mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
+                  mma_16816<XBF16, true>(f, aa[2], ab[2], aa[3], ab[3], b.z, b.w);
+                } else {
+                  mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
+                  mma_16816<XBF16, false>(f, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) d[i] += f[i];
+              auto meta_f32 = [&](int i) -> float {
+                const uint32_t reg = mc[i][j / 2];
+                if (mbf) return __uint_as_float((j & 1) ? (reg & 0xFFFF0000u) : (reg << 16));
+                const __half2 hh = *reinterpret_cast<const __half2*>(&reg);
+                return (j & 1) ? __high2float(hh) : __low2float(hh);
+              };
+              const float2 xs2 = *reinterpret_cast<const float2*>(xsum_w + sl * 8);
+              const float2 xn2 = *reinterpret_cast<const float2*>(xneg_w + sl * 8);
+              const float sc_a = meta_f32(0), sc_b = meta_f32(2);
+              acc[h][0] = fmaf(sc_a, d[0] + xn2.x, acc[h][0]);
+              acc[h][1] = fmaf(sc_a, d[1] + xn2.y, acc[h][1]);
+              acc[h][2] = fmaf(sc_b, d[2] + xn2.x, acc[h][2]);
+              acc[h][3] = fmaf(sc_b, d[3] + xn2.y, acc[h][3]);
+              if (has_off) {
+                const float of_a = meta_f32(1), of_b = meta_f32(3);
+                acc[h][0] = fmaf(of_a, xs2.x, acc[h][0]);
+                acc[h][1] = fmaf(of_a, xs2.y, acc[h][1]);
+                acc[h][2] = fmaf(of_b, xs2.x, acc[h][2]);
+                acc[h][3] = fmaf(of_b, xs2.y, acc[h][3]);
+              }
+            }
+          }
+          if (++slot_r == nb) slot_r = 0;
+          __syncwarp();      // every lane is done with the slot just consumed:
+          prefetch_stage();  // refill it
+        }
       }
-    }
-    // sum the slices of the reduction axis in a fixed order
-    if (a.kw > 1) {
+      // sum the slices of the reduction axis in a fixed order (buffers alternate: one barrier per item)
+      if (kw > 1) {
+        float* rbuf = red + parity * (H * kMoeWarps * 128);
 #pragma unroll
-      for (int h = 0; h < (GATE_UP ? 2 : 1); ++h) {
-        float* mine = red + (((h * a.kw + kwi) * a.rw + rwi) * 16) * 8;
-        *reinterpret_cast<float2*>(mine + g * 8 + 2 * t) = make_float2(acc[h][0], acc[h][1]);
-        *reinterpret_cast<float2*>(mine + (g + 8) * 8 + 2 * t) = make_float2(acc[h][2], acc[h][3]);
-      }
-      __syncthreads();
-      if (kwi == 0) {
+        for (int h = 0; h < H; ++h) {
+          float* mine = rbuf + ((h * kw + kwi) * rw + rwi) * 128;
+          *reinterpret_cast<float2*>(mine + g * 8 + 2 * t) = make_float2(acc[h][0], acc[h][1]);
+          *reinterpret_cast<float2*>(mine + (g + 8) * 8 + 2 * t) = make_float2(acc[h][2], acc[h][3]);
+        }
+        __syncthreads();
+        if (kwi == 0) {
 #pragma unroll
-        for (int h = 0; h < (GATE_UP ? 2 : 1); ++h) {
+          for (int h = 0; h < H; ++h) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) acc[h][i] = 0.0f;
-          for (int k = 0; k < a.kw; ++k) {
-            const float* part = red + (((h * a.kw + k) * a.rw + rwi) * 16) * 8;
-            const float2 pa = *reinterpret_cast<const float2*>(part + g * 8 + 2 * t);
-            const float2 pb = *reinterpret_cast<const float2*>(part + (g + 8) * 8 + 2 * t);
-            acc[h][0] += pa.x, acc[h][1] += pa.y, acc[h][2] += pb.x, acc[h][3] += pb.y;
+            for (int i = 0; i < 4; ++i) acc[h][i] = 0.0f;
+            for (int k = 0; k < kw; ++k) {
+              const float* part = rbuf + ((h * kw + k) * rw + rwi) * 128;
+              const float2 pa = *reinterpret_cast<const float2*>(part + g * 8 + 2 * t);
+              const float2 pb = *reinterpret_cast<const float2*>(part + (g + 8) * 8 + 2 * t);
+              acc[h][0] += pa.x, acc[h][1] += pa.y, acc[h][2] += pb.x, acc[h][3] += pb.y;
+            }
           }
         }
       }
-    }
-    if (kwi == 0 && tile_live) {
+      if (kwi == 0 && live) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int mm = 2 * t + (i & 1);
-        const int row = tile * 16 + g + ((i & 2) ? 8 : 0);
-        if (mm < m && row < a.rows) {
-          const int aid = a.route.sorted[first + c0 + mm];
-          if constexpr (GATE_UP) {
-            const float gate = acc[0][i], up = acc[1][i];
-            const float h = (gate / (1.0f + __expf(-gate))) * up;
-            store_f32(a.out, static_cast<int64_t>(aid) * a.rows + row, a.act_dtype, h);
-          } else {
-            reinterpret_cast<float*>(a.out)[static_cast<int64_t>(aid) * a.rows + row] = acc[0][i];
+        for (int i = 0; i < 4; ++i) {
+          const int mm = 2 * t + (i & 1);
+          const int row = tile * 16 + g + ((i & 2) ? 8 : 0);
+          if (mm < m && row < a.rows) {
+            const int aid = list[c0 + mm];
+            if constexpr (GATE_UP) {
+              const float gate = acc[0][i], up = acc[H - 1][i];
+              const float hval = (gate / (1.0f + __expf(-gate))) * up;
+              store_f32(a.out, static_cast<int64_t>(aid) * a.rows + row, a.act_dtype, hval);
+            } else {
+              reinterpret_cast<float*>(a.out)[static_cast<int64_t>(aid) * a.rows + row] = acc[0][i];
+            }
           }
         }
       }
     }
   }
+  stream::cp_async_wait<0>();
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ d, const float* __restrict__ w,
@@ -304,18 +441,14 @@ __global__ void moe_combine_kernel(const float* __restrict__ d, const float* __r
 }
 
 struct ScratchLayout {
-  size_t counts, offsets, sorted, h, d, total;
+  size_t h, d, total;
 };
 
-ScratchLayout scratch_layout(int64_t tokens, int64_t topk, int64_t hidden, int64_t inter, int64_t experts,
-                             int act_bytes) {
+ScratchLayout scratch_layout(int64_t tokens, int64_t topk, int64_t hidden, int64_t inter, int act_bytes) {
   auto up = [](size_t v) { return (v + 255) / 256 * 256; };
   ScratchLayout l = {};
   const size_t assignments = static_cast<size_t>(tokens * topk);
   size_t at = 0;
-  l.counts = at, at = up(at + static_cast<size_t>(experts) * 4);
-  l.offsets = at, at = up(at + static_cast<size_t>(experts + 1) * 4);
-  l.sorted = at, at = up(at + assignments * 4);
   l.h = at, at = up(at + assignments * static_cast<size_t>(inter) * act_bytes);
   l.d = at, at = up(at + assignments * static_cast<size_t>(hidden) * 4);
   l.total = at;
@@ -366,20 +499,48 @@ int32_t launch_pdl(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStrea
   return DQ_OK;
 }
 
-template <int BITS, bool GATE_UP>
-int32_t launch_grouped(const MoeArgs& a, int experts, size_t smem, cudaStream_t stream) {
+template <int BITS, int CH, bool GATE_UP>
+int32_t launch_grouped(MoeArgs a, int slots, cudaStream_t stream) {
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr) return DQ_ERR_CUDA;
+  static const int force_nb = [] { const char* v = std::getenv("DQ_B200_MOE_NB"); return v ? std::atoi(v) : 0; }();
+  static const int force_x = [] { const char* v = std::getenv("DQ_B200_MOE_GRID_X"); return v ? std::atoi(v) : 0; }();
+  // ring: as deep as keeps two CTAs on an SM (one, if a single stage is that large)
+  a.nb = 1;
+  const size_t one = moe_smem<BITS, CH>(a, GATE_UP).total;
+  const size_t stage = static_cast<size_t>(CH) * 2 * kMoeThreads * (4 * BITS) + static_cast<size_t>(CH) * 2 * kMoeThreads;
+  const size_t fixed = one - stage;
+  const size_t per_sm = 228 * 1024, reserve = 1024;
+  size_t budget = per_sm / 2 - reserve;
+  if (fixed + 2 * stage > budget) budget = static_cast<size_t>(dev->max_smem_optin);
+  if (fixed + stage > budget) {
+    return fail(DQ_ERR_UNSUPPORTED, "moe_gemv: in_features=%d needs %zu bytes of shared memory", a.in_features,
+                fixed + stage);
+  }
+  a.nb = static_cast<int>(std::max<size_t>(1, std::min<size_t>(8, (budget - fixed) / stage)));
+  if (force_nb > 0) a.nb = static_cast<int>(std::min<size_t>(force_nb, (static_cast<size_t>(dev->max_smem_optin) - fixed) / stage));
+  const size_t smem = moe_smem<BITS, CH>(a, GATE_UP).total;
+  // CTAs per expert: every CTA pays for routing and for staging the activation, so with many
+  // active experts the CTAs are made fatter -- but the grid stays about six CTAs per SM deep,
+  // because experts differ in token count and small CTAs even that out (measured: 18 % faster
+  // at 64 tokens than two CTAs per SM).
+  // Experts expected to have a token under uniform routing: E * (1 - (1 - 1/E)^A).
   const int tiles = (a.rows + 15) / 16;
-  const dim3 grid(static_cast<unsigned>(ceil_div(tiles, a.rw)), static_cast<unsigned>(experts));
-  const bool xbf = a.act_dtype == DQ_BF16, mbf = a.meta_dtype == DQ_BF16;
+  const int items = static_cast<int>(ceil_div(tiles, a.rw));
+  const double e_count = a.num_experts;
+  const double active = std::max(1.0, e_count * (1.0 - std::pow(1.0 - 1.0 / e_count, a.assignments)));
+  int grid_x = static_cast<int>(std::min<int64_t>(items, std::max<int64_t>(1, static_cast<int64_t>(6.0 * dev->sm_count / active + 0.5))));
+  if (force_x > 0) grid_x = std::min(force_x, items);
+  const dim3 grid(static_cast<unsigned>(grid_x), static_cast<unsigned>(slots));
   const char* what = GATE_UP ? "moe_gemv(gate_up)" : "moe_gemv(down)";
-  if (xbf && mbf) return launch_pdl(moe_grouped_kernel<BITS, true, true, GATE_UP>, grid, kMoeThreads, smem, stream, a, what);
-  if (xbf) return launch_pdl(moe_grouped_kernel<BITS, true, false, GATE_UP>, grid, kMoeThreads, smem, stream, a, what);
-  if (mbf) return launch_pdl(moe_grouped_kernel<BITS, false, true, GATE_UP>, grid, kMoeThreads, smem, stream, a, what);
-  return launch_pdl(moe_grouped_kernel<BITS, false, false, GATE_UP>, grid, kMoeThreads, smem, stream, a, what);
+  if (a.act_dtype == DQ_BF16) {
+    return launch_pdl(moe_grouped_kernel<BITS, true, CH, GATE_UP>, grid, kMoeThreads, smem, stream, a, what);
+  }
+  return launch_pdl(moe_grouped_kernel<BITS, false, CH, GATE_UP>, grid, kMoeThreads, smem, stream, a, what);
 }
 
 template <bool GATE_UP>
-int32_t launch_bank(const dq_weight& w, const dq_geometry& g, MoeArgs a, int experts, cudaStream_t stream) {
+int32_t launch_bank(const dq_weight& w, const dq_geometry& g, MoeArgs a, int slots, cudaStream_t stream) {
   a.packed = static_cast<const uint32_t*>(w.packed);
   a.scales = w.scales;
   a.offsets = w.offsets;
@@ -388,32 +549,31 @@ int32_t launch_bank(const dq_weight& w, const dq_geometry& g, MoeArgs a, int exp
   a.num_groups = g.num_groups;
   a.in_features = g.in_features;
   a.steps = g.words_per_row / (4 * w.bits);
-  // 8 warps: slice the reduction axis as far as the steps allow (at most 4 ways), the rest
-  // of the warps take neighbouring row tiles
+  // 8 warps.  The reduction axis is sliced while a slice keeps at least eight steps (a warp
+  // then works through 16+ steps between two CTA-wide reductions); the other warps take
+  // neighbouring row tiles.
+  static const int force_kw = [] { const char* v = std::getenv("DQ_B200_MOE_KW"); return v ? std::atoi(v) : 0; }();
   int kw = 1;
-  while (kw < 4 && a.steps / (kw * 2) >= 2) kw *= 2;
+  while (kw < kMoeWarps && a.steps % (kw * 2) == 0 && a.steps / (kw * 2) >= 8) kw *= 2;
+  if (force_kw > 0 && a.steps % force_kw == 0) kw = force_kw;
   a.kw = kw;
   a.rw = kMoeWarps / kw;
-  a.steps_per_warp = static_cast<int>(ceil_div(a.steps, a.kw));
+  a.spw = a.steps / kw;
+  const bool meta_words = a.num_groups % 2 == 0 && reinterpret_cast<uintptr_t>(a.scales) % 4 == 0 &&
+                          reinterpret_cast<uintptr_t>(a.offsets) % 4 == 0;
+  const bool pairs = a.spw % 2 == 0 && meta_words;  // stages of two steps; else single steps
   const int aregs = w.bits == 8 ? 32 : 16;
   a.m_stride_u4 = a.steps * aregs + 4;
   a.magic = a.act_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
-  const size_t smem = (static_cast<size_t>(8) * a.m_stride_u4 + aregs) * 16 + static_cast<size_t>(a.steps) * 8 * 4 * 2 +
-                      static_cast<size_t>(GATE_UP ? 2 : 1) * a.kw * a.rw * 16 * 8 * 4 + 8 * 4;
-  const DeviceInfo* dev = device_info();
-  if (dev == nullptr) return DQ_ERR_CUDA;
-  if (smem > static_cast<size_t>(dev->max_smem_optin)) {
-    return fail(DQ_ERR_UNSUPPORTED, "moe_gemv: in_features=%d needs %zu bytes of shared memory", a.in_features, smem);
-  }
   switch (w.bits) {
     case 2:
-      return launch_grouped<2, GATE_UP>(a, experts, smem, stream);
+      return pairs ? launch_grouped<2, 2, GATE_UP>(a, slots, stream) : launch_grouped<2, 1, GATE_UP>(a, slots, stream);
     case 3:
-      return launch_grouped<3, GATE_UP>(a, experts, smem, stream);
+      return pairs ? launch_grouped<3, 2, GATE_UP>(a, slots, stream) : launch_grouped<3, 1, GATE_UP>(a, slots, stream);
     case 4:
-      return launch_grouped<4, GATE_UP>(a, experts, smem, stream);
+      return pairs ? launch_grouped<4, 2, GATE_UP>(a, slots, stream) : launch_grouped<4, 1, GATE_UP>(a, slots, stream);
     default:
-      return launch_grouped<8, GATE_UP>(a, experts, smem, stream);
+      return pairs ? launch_grouped<8, 2, GATE_UP>(a, slots, stream) : launch_grouped<8, 1, GATE_UP>(a, slots, stream);
   }
 }
 
@@ -431,7 +591,7 @@ int32_t dq_moe_scratch_bytes(int64_t tokens, int64_t topk, int64_t hidden, int64
              "moe_gemv: bad sizes (topk=%lld hidden=%lld inter=%lld experts=%lld)", static_cast<long long>(topk),
              static_cast<long long>(hidden), static_cast<long long>(inter), static_cast<long long>(num_experts));
   *bytes = static_cast<int64_t>(
-      dq::scratch_layout(tokens, topk, hidden, inter, num_experts, dq::dtype_size(act_dtype)).total);
+      dq::scratch_layout(tokens, topk, hidden, inter, dq::dtype_size(act_dtype)).total);
   return DQ_OK;
 }
 
@@ -462,45 +622,38 @@ int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_
   const bool act16 = x_dtype == DQ_BF16 || x_dtype == DQ_F16;
   const auto meta16 = [](const dq_weight* w) { return w->meta_dtype == DQ_BF16 || w->meta_dtype == DQ_F16; };
   if (!act16 || !meta16(gate_up) || !meta16(down) || gate_up->group_values != 128 || down->group_values != 128 ||
-      reinterpret_cast<uintptr_t>(gate_up->packed) % 4 != 0) {
+      reinterpret_cast<uintptr_t>(gate_up->packed) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(down->packed) % 16 != 0 || (g_gu.words_per_row * 4) % 16 != 0 ||
+      (g_dn.words_per_row * 4) % 16 != 0) {
     return dq::fail(DQ_ERR_UNSUPPORTED,
-                    "moe_gemv: this build handles fp16/bf16 activations and metadata with 128-value groups");
+                    "moe_gemv: this build handles fp16/bf16 activations and metadata, 128-value groups and "
+                    "16-byte aligned packed rows");
   }
 
   auto s = static_cast<cudaStream_t>(stream);
-  const dq::ScratchLayout lay = dq::scratch_layout(tokens, topk, hidden, inter, num_experts, dq::dtype_size(x_dtype));
+  const dq::ScratchLayout lay = dq::scratch_layout(tokens, topk, hidden, inter, dq::dtype_size(x_dtype));
   auto* base = static_cast<unsigned char*>(scratch);
-  dq::Routing route = {reinterpret_cast<int*>(base + lay.counts), reinterpret_cast<int*>(base + lay.offsets),
-                       reinterpret_cast<int*>(base + lay.sorted)};
   const int assignments = static_cast<int>(tokens * topk);
-  {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1);
-    cfg.blockDim = dim3(512);
-    cfg.dynamicSmemBytes = static_cast<size_t>(2 * num_experts + 1) * 4;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    DQ_CUDA(cudaLaunchKernelEx(&cfg, dq::moe_route_kernel, topk_ids, assignments, static_cast<int>(num_experts), route));
-    DQ_CHECK_LAUNCH("moe_gemv(route)");
-  }
+  const int slots = static_cast<int>(std::min<int64_t>(num_experts, assignments));
   dq::MoeArgs a = {};
-  a.route = route;
+  a.ids = topk_ids;
+  a.assignments = assignments;
+  a.num_experts = static_cast<int>(num_experts);
+  // Activation rows staged at once: experts rarely see more than four tokens of a batch of
+  // 32; the few that do take a second pass over their (L2-resident) rows.
+  a.m_cap = static_cast<int>(std::min<int64_t>(tokens > 32 ? 8 : 4, tokens));
   a.topk = static_cast<int>(topk);
   a.act_dtype = x_dtype;
   // gate_up: x -> h
   a.act = x;
   a.out = base + lay.h;
   a.rows = static_cast<int>(inter);
-  if (const int32_t rc = dq::launch_bank<true>(*gate_up, g_gu, a, static_cast<int>(num_experts), s)) return rc;
+  if (const int32_t rc = dq::launch_bank<true>(*gate_up, g_gu, a, slots, s)) return rc;
   // down: h -> d
   a.act = base + lay.h;
   a.out = base + lay.d;
   a.rows = static_cast<int>(hidden);
-  if (const int32_t rc = dq::launch_bank<false>(*down, g_dn, a, static_cast<int>(num_experts), s)) return rc;
+  if (const int32_t rc = dq::launch_bank<false>(*down, g_dn, a, slots, s)) return rc;
   {
     const int64_t total = tokens * hidden;
     const int threads = 256;
