@@ -474,7 +474,10 @@ GemvArgs activation_rows(const GemvArgs& a, int first, int count) {
 
 int32_t gemv_args(GemvArgs a, const dq_weight& w, const dq_geometry& g, cudaStream_t stream) {
   if (!force_general()) {
-    if (mma_path_supports(a, w.bits)) return launch_gemv_mma(a, w.bits, stream);
+    if (mma_path_supports(a, w.bits)) {
+      const int32_t rc = launch_gemv_mma(a, w.bits, stream);
+      if (rc != DQ_ERR_UNSUPPORTED) return rc;  // (unsupported: silently on to the SIMT kernels)
+    }
     // The staged activation of all rows may be what does not fit: two passes over half the
     // rows each read the weights twice (the second time mostly from L2) but stay on the
     // tensor-core path.

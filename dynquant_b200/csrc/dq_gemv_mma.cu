@@ -595,7 +595,12 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
         a.in_features != a0.in_features || a.out_dtype != a0.out_dtype) {
       return DQ_OK;
     }
-    if (a.group_values != kStepValues || a.words_per_row / (4 * bits[i]) != steps || a.num_groups != steps) return DQ_OK;
+    if (a.group_values != a0.group_values || a.words_per_row / (4 * bits[i]) != steps) return DQ_OK;
+    if (a.group_values == kStepValues / 2) {
+      if (bits[i] == 3 || a.num_groups != 2 * steps) return DQ_OK;  // 3-bit half units straddle words
+    } else if (a.group_values != kStepValues || a.num_groups != steps) {
+      return DQ_OK;
+    }
     if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) {
       return DQ_OK;
     }
@@ -612,10 +617,12 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     int kw = 0, ch = 0, nb = 0, per_sm = 0, ipc = 0;
     size_t smem = 0;
   };
+  const bool g64 = a0.group_values == kStepValues / 2;
+  const int gps = g64 ? 2 : 1;  // groups per step
   auto meta_aligned = [&](int c) {
     for (int i = 0; i < n; ++i) {
-      const auto al = static_cast<uintptr_t>(2 * c);
-      if (jobs[i].num_groups % c != 0 || reinterpret_cast<uintptr_t>(jobs[i].scales) % al != 0 ||
+      const auto al = static_cast<uintptr_t>(2 * c * gps);  // a stage's metadata of one row, copied whole
+      if (jobs[i].num_groups % (c * gps) != 0 || reinterpret_cast<uintptr_t>(jobs[i].scales) % al != 0 ||
           reinterpret_cast<uintptr_t>(jobs[i].offsets) % al != 0) {
         return false;
       }
@@ -635,15 +642,18 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     const int ch = (spw % 4 == 0 && meta_aligned(4)) ? 4 : ((spw % 2 == 0 && meta_aligned(2)) ? 2 : 0);
     if (ch == 0) return sh;
     const bool wide = kw < tilek::kWarps;
-    const size_t stage = static_cast<size_t>(ch) * 2 * (4 * max_bits) * tilek::kThreads + ch * 2 * tilek::kThreads;
+    const size_t stage = static_cast<size_t>(ch) * 2 * (4 * max_bits) * tilek::kThreads + ch * gps * 2 * tilek::kThreads;
     const size_t fixed = tilek::kRedFloats * 4 +
-                         (max_bits == 8 ? tilek::stage_bytes<8>(a0.m, steps, spw, kw, wide, a0.in_features)
-                                        : tilek::stage_bytes<4>(a0.m, steps, spw, kw, wide, a0.in_features));
+                         (max_bits == 8 ? tilek::stage_bytes<8>(a0.m, steps, spw, kw, wide, a0.in_features, gps)
+                                        : tilek::stage_bytes<4>(a0.m, steps, spw, kw, wide, a0.in_features, gps));
     const int stages = spw / ch;
     int nb = one_shot ? stages : std::min(stages * 2, ch == 4 ? 2 : 4);
     if (force_nb > 0 && !one_shot) nb = force_nb;
     nb = std::min(nb, tilek::kMaxRing);
     if (one_shot && nb < stages) return sh;
+    if (!one_shot) {  // a persistent CTA takes whatever ring still fits, two stages at least
+      while (nb > 2 && nb * stage + fixed > static_cast<size_t>(dev.max_smem_optin)) --nb;
+    }
     const size_t smem = nb * stage + fixed;
     if (smem > static_cast<size_t>(dev.max_smem_optin)) return sh;
     sh.kw = kw;
@@ -722,8 +732,12 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     return DQ_OK;
   };
   const bool xbf = a0.x_dtype == DQ_BF16;
-  if (ch == 4) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 4>) : run(tilek::gemv_mma_tile_kernel<false, 4>);
-  return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2>) : run(tilek::gemv_mma_tile_kernel<false, 2>);
+  if (g64) {
+    if (ch == 4) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 4, true>) : run(tilek::gemv_mma_tile_kernel<false, 4, true>);
+    return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2, true>) : run(tilek::gemv_mma_tile_kernel<false, 2, true>);
+  }
+  if (ch == 4) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 4, false>) : run(tilek::gemv_mma_tile_kernel<false, 4, false>);
+  return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2, false>) : run(tilek::gemv_mma_tile_kernel<false, 2, false>);
 }
 
 }  // namespace
@@ -732,7 +746,11 @@ bool mma_path_supports(const GemvArgs& a, int bits) {
   if (!mma_enabled()) return false;
   if (a.x_dtype != DQ_BF16 && a.x_dtype != DQ_F16) return false;
   if (a.meta_dtype != DQ_BF16 && a.meta_dtype != DQ_F16) return false;
-  if (a.group_values % kStepValues != 0) return false;
+  if (a.group_values == kStepValues / 2) {
+    if (bits == 3) return false;  // 64-value groups: the tiled kernel only, and not at 3 bits
+  } else if (a.group_values % kStepValues != 0) {
+    return false;
+  }
   const auto addr = reinterpret_cast<uintptr_t>(a.packed);
   const int align = bits == 2 ? 8 : (bits == 3 ? 4 : 16);
   if (addr % align != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % align != 0) return false;
@@ -757,6 +775,11 @@ int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cuda
 int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
   const DeviceInfo* dev = device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
+  if (a.group_values == kStepValues / 2) {  // two groups per step: only the tiled kernel does that
+    bool taken = false;
+    const int32_t rc = try_tile(&a, &bits, 1, *dev, stream, &taken);
+    return (rc == DQ_OK && !taken) ? DQ_ERR_UNSUPPORTED : rc;
+  }
   MmaParams p = {};
   p.steps = a.words_per_row / (4 * bits);  // a step is 4 units of `bits` words
   p.steps_per_group = a.group_values / kStepValues;

@@ -20,8 +20,10 @@
 //   * Each CTA belongs to one matrix (a "job") and runs the body compiled for its width.
 //
 // Arithmetic is that of gemv_mma_kernel (dq_gemv_mma.cu).  Requirements, checked by the
-// host: one group per 128-value step, 16-byte aligned rows, steps divisible by kw * CH,
-// scales/offsets rows aligned to 2 * CH bytes.
+// host: one group per 128-value step -- or two (64-value groups) at 2, 4 and 8 bits, where
+// a lane decodes 16 values of each group and the two halves of a step are accumulated and
+// scaled separately --, 16-byte aligned rows, steps divisible by kw * CH, and scales/offsets
+// rows aligned to a stage's worth of metadata.
 #pragma once
 
 #include "dq_gemv.cuh"
@@ -59,30 +61,27 @@ struct Launch {
   uint32_t magic;
 };
 
-template <int BITS, int CH>
+template <int BITS, int CH, bool G64 = false>
 struct Ring {
   static constexpr int UNIT = 4 * BITS;
+  static constexpr int GPS = G64 ? 2 : 1;                    // groups per 128-value step
+  static constexpr int META = CH * GPS * 2;                  // bytes of one metadata array of one stage
   static constexpr int STAGE_W = CH * 2 * UNIT * kThreads;  // weights of one stage, whole CTA
-  static constexpr int STAGE_M = CH * 2 * kThreads;         // one metadata array per lane, CH groups
+  static constexpr int STAGE_M = META * kThreads;            // one metadata array per lane
 };
 
 // Bytes of the staging area (after ring and reduction buffers).
+// `gps`: groups per 128-value step (1, or 2 with 64-value groups): the sums are per group.
 template <int BITS>
-__host__ __device__ inline size_t stage_bytes(int m, int steps, int spw, int kw, bool wide, int in_features) {
+__host__ __device__ inline size_t stage_bytes(int m, int steps, int spw, int kw, bool wide, int in_features,
+                                              int gps = 1) {
   const int na = BITS == 8 ? 32 : 16;
   if (wide) {
     const size_t stride = static_cast<size_t>(steps) * na + 4;
-    return (m * stride + na) * 16 + static_cast<size_t>(steps) * 64 + static_cast<size_t>(m) * in_features * 2 + 16;
+    return (m * stride + na) * 16 + static_cast<size_t>(steps) * 64 * gps + static_cast<size_t>(m) * in_features * 2 + 16;
   }
   const size_t stride = static_cast<size_t>(spw) * na + 4;
-  return static_cast<size_t>(kw) * (spw * 256 + (m * stride + na) * 16 + spw * 64);
-}
-
-template <int BITS, int CH>
-inline size_t smem_bytes(int m, int steps, int spw, int kw, int nb, bool wide, int in_features) {
-  using R = Ring<BITS, CH>;
-  return static_cast<size_t>(nb) * (R::STAGE_W + R::STAGE_M) + kRedFloats * 4 +
-         stage_bytes<BITS>(m, steps, spw, kw, wide, in_features);
+  return static_cast<size_t>(kw) * (spw * 256 + (m * stride + na) * 16 + spw * 64 * gps);
 }
 
 __device__ __forceinline__ void wait_pending(int n) {
@@ -98,10 +97,36 @@ __device__ __forceinline__ void wait_pending(int n) {
   }
 }
 
-template <int BITS, bool XBF16, int CH>
+// One lane's fragment source of one row of one step.  Normally its 32-value unit; with
+// 64-value groups the two half units (16 values of each group), 2 * UNIT bytes apart.
+template <int BITS, bool G64>
+__device__ __forceinline__ void read_lane_words(const unsigned char* src, uint32_t* w) {
+  if constexpr (!G64) {
+    stream::read_unit<BITS>(src, w);
+  } else {
+    constexpr int UNIT = 4 * BITS;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const unsigned char* p = src + half * 2 * UNIT;
+      if constexpr (BITS == 2) {
+        w[half] = *reinterpret_cast<const uint32_t*>(p);
+      } else if constexpr (BITS == 4) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        w[2 * half] = v.x, w[2 * half + 1] = v.y;
+      } else {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        w[4 * half] = v.x, w[4 * half + 1] = v.y, w[4 * half + 2] = v.z, w[4 * half + 3] = v.w;
+      }
+    }
+  }
+}
+
+template <int BITS, bool XBF16, int CH, bool G64>
 __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigned char* smem) {
+  static_assert(!(G64 && BITS == 3), "3-bit units do not split into two 16-value halves on word boundaries");
   using Plan = MmaPlan<BITS>;
-  using R = Ring<BITS, CH>;
+  using R = Ring<BITS, CH, G64>;
+  constexpr int GPS = R::GPS;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
   constexpr int UNIT = R::UNIT;
@@ -135,21 +160,21 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   if (wide) {
     xb = reinterpret_cast<uint4*>(area);
     xsum = reinterpret_cast<float*>(xb + a.m * m_stride_u4 + NA);
-    xneg = xsum + span * 8;
-    raw = reinterpret_cast<unsigned short*>(xneg + span * 8);
+    xneg = xsum + span * 8 * GPS;
+    raw = reinterpret_cast<unsigned short*>(xneg + span * 8 * GPS);
   } else {
-    unsigned char* mine = area + kwi * (spw * 256 + (a.m * m_stride_u4 + NA) * 16 + spw * 64);
+    unsigned char* mine = area + kwi * (spw * 256 + (a.m * m_stride_u4 + NA) * 16 + spw * 64 * GPS);
     raw = reinterpret_cast<unsigned short*>(mine);
     xb = reinterpret_cast<uint4*>(mine + spw * 256);
     xsum = reinterpret_cast<float*>(xb + a.m * m_stride_u4 + NA);
-    xneg = xsum + span * 8;
+    xneg = xsum + span * 8 * GPS;
   }
 
   pdl_launch_dependents();
 
   // ---- prefetch cursor: walks (item, chunk) ahead of the compute loop ----
   const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * UNIT;
-  const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * (CH * 2);
+  const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * R::META;
   const bool meta_lane = has_off || (t & 1) == 0;
   const unsigned short* meta_arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
   int pf_item = cta, pf_chunk = 0, pf_slot = 0;
@@ -168,8 +193,9 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
         }
         if (meta_lane) {
           const int row = min(tile * 16 + g + ((t & 2) ? 8 : 0), a.rows - 1);
-          stream::cp_async_n<CH * 2>(ring_m_s + pf_slot * R::STAGE_M,
-                                     meta_arr + static_cast<int64_t>(row) * a.num_groups + s_begin + pf_chunk * CH);
+          stream::cp_async_n<R::META>(ring_m_s + pf_slot * R::STAGE_M,
+                                      meta_arr + static_cast<int64_t>(row) * a.num_groups +
+                                          (s_begin + pf_chunk * CH) * GPS);
         }
       }
       if (++pf_chunk == nchunks) {
@@ -186,10 +212,10 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   const int sl0 = wide ? s_begin : 0;  // first step of this warp's slice in the staged arrays
   const uint4* xb_lane = (b_live ? xb + g * m_stride_u4 + t : xb + a.m * m_stride_u4) + (b_live ? sl0 * QU * 4 : 0);
   const int xb_step_u4 = b_live ? QU * 4 : 0;
-  const float* xsum_w = xsum + sl0 * 8 + 2 * t;
-  const float* xneg_w = xneg + sl0 * 8 + 2 * t;
-  const unsigned char* ring_w_mine = ring_w + tid * UNIT;
-  const unsigned char* ring_m_quad = ring_m + (tid & ~3) * (CH * 2);
+  const float* xsum_w = xsum + sl0 * 8 * GPS + 2 * t;
+  const float* xneg_w = xneg + sl0 * 8 * GPS + 2 * t;
+  const unsigned char* ring_w_mine = G64 ? ring_w + (tid & ~3) * UNIT + t * (UNIT / 2) : ring_w + tid * UNIT;
+  const unsigned char* ring_m_quad = ring_m + (tid & ~3) * R::META;
   const uint32_t magic = L.magic;
   const bool mbf = L.meta_bf16 != 0;
 
@@ -198,11 +224,11 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   pdl_wait_prior_grid();
   if (wide) {
     const bool raw_ok = a.x_dtype != DQ_F32;
-    stage_activation<BITS, XBF16>(a, L.steps, m_stride_u4, xb, xsum, xneg, tid, kThreads, nullptr,
-                                  raw_ok ? raw : nullptr);
+    stage_activation<BITS, XBF16, G64>(a, L.steps, m_stride_u4, xb, xsum, xneg, tid, kThreads, nullptr,
+                                       raw_ok ? raw : nullptr);
     __syncthreads();
   } else {
-    stage_warp_slice<BITS, XBF16>(a, s_begin, spw, m_stride_u4, raw, xb, xsum, xneg, lane);
+    stage_warp_slice<BITS, XBF16, G64>(a, s_begin, spw, m_stride_u4, raw, xb, xsum, xneg, lane);
   }
 
   for (int item = cta; item < J.items; item += J.cta_count, parity ^= 1) {
@@ -215,15 +241,19 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
       if (live) {
         const unsigned char* wsrc = ring_w_mine + slot * R::STAGE_W;
         const unsigned char* msrc = ring_m_quad + slot * R::STAGE_M;
-        uint32_t mc[4][CH / 2];
+        constexpr int MW = R::META / 4;  // 32-bit words of one metadata array of this stage
+        uint32_t mc[4][MW];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           if (has_off || (i & 1) == 0) {
-            if constexpr (CH == 4) {
-              const uint2 v = *reinterpret_cast<const uint2*>(msrc + i * (CH * 2));
+            if constexpr (MW == 4) {
+              const uint4 v = *reinterpret_cast<const uint4*>(msrc + i * R::META);
+              mc[i][0] = v.x, mc[i][1] = v.y, mc[i][2] = v.z, mc[i][3] = v.w;
+            } else if constexpr (MW == 2) {
+              const uint2 v = *reinterpret_cast<const uint2*>(msrc + i * R::META);
               mc[i][0] = v.x, mc[i][1] = v.y;
             } else {
-              mc[i][0] = *reinterpret_cast<const uint32_t*>(msrc + i * (CH * 2));
+              mc[i][0] = *reinterpret_cast<const uint32_t*>(msrc + i * R::META);
             }
           }
         }
@@ -231,47 +261,76 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
         for (int j = 0; j < CH; ++j) {
           const int sl = chunk * CH + j;
           uint32_t wa[BITS], wb[BITS];
-          stream::read_unit<BITS>(wsrc + (j * 2 + 0) * (UNIT * kThreads), wa);
-          stream::read_unit<BITS>(wsrc + (j * 2 + 1) * (UNIT * kThreads), wb);
+          read_lane_words<BITS, G64>(wsrc + (j * 2 + 0) * (UNIT * kThreads), wa);
+          read_lane_words<BITS, G64>(wsrc + (j * 2 + 1) * (UNIT * kThreads), wb);
           uint32_t aa[NA], ab[NA];
           decode_unit<BITS>(wa, magic, aa);
           decode_unit<BITS>(wb, magic, ab);
           unbias_fragments<XBF16, NA>(aa);
           unbias_fragments<XBF16, NA>(ab);
           const uint4* bsrc = xb_lane + sl * xb_step_u4;
-          float d[4], e[4];  // two chains: the latency of dependent mma is what a step costs here
+          // two accumulators: the first half of the registers (d) and the second (e).  They
+          // halve the chain of dependent mma; with 64-value groups they ARE the two groups.
+          float d[4], e[4];
 #pragma unroll
-          for (int q = 0; q < QU; ++q) {
-            const uint4 b = bsrc[q * 4];
+          for (int q = 0; q < QU / 2; ++q) {
+            const uint4 b0 = bsrc[q * 4];
+            const uint4 b1 = bsrc[(q + QU / 2) * 4];
             if (q == 0) {
-              mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
-              mma_16816<XBF16, true>(e, aa[2], ab[2], aa[3], ab[3], b.z, b.w);
+              mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b0.x, b0.y);
+              mma_16816<XBF16, true>(e, aa[NA / 2], ab[NA / 2], aa[NA / 2 + 1], ab[NA / 2 + 1], b1.x, b1.y);
             } else {
-              mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
-              mma_16816<XBF16, false>(e, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
+              mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b0.x, b0.y);
+              mma_16816<XBF16, false>(e, aa[NA / 2 + 4 * q], ab[NA / 2 + 4 * q], aa[NA / 2 + 4 * q + 1],
+                                      ab[NA / 2 + 4 * q + 1], b1.x, b1.y);
             }
+            mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b0.z, b0.w);
+            mma_16816<XBF16, false>(e, aa[NA / 2 + 4 * q + 2], ab[NA / 2 + 4 * q + 2], aa[NA / 2 + 4 * q + 3],
+                                    ab[NA / 2 + 4 * q + 3], b1.z, b1.w);
           }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) d[i] += e[i];
-          auto meta_f32 = [&](int i) -> float {
-            const uint32_t reg = mc[i][j / 2];
-            if (mbf) return __uint_as_float((j & 1) ? (reg & 0xFFFF0000u) : (reg << 16));
+          // halfword `hw` of metadata array i of this stage
+          auto meta_f32 = [&](int i, int hw) -> float {
+            const uint32_t reg = mc[i][hw / 2];
+            if (mbf) return __uint_as_float((hw & 1) ? (reg & 0xFFFF0000u) : (reg << 16));
             const __half2 h = *reinterpret_cast<const __half2*>(&reg);
-            return (j & 1) ? __high2float(h) : __low2float(h);
+            return (hw & 1) ? __high2float(h) : __low2float(h);
           };
-          const float2 xs2 = *reinterpret_cast<const float2*>(xsum_w + sl * 8);
-          const float2 xn2 = *reinterpret_cast<const float2*>(xneg_w + sl * 8);
-          const float sc_a = meta_f32(0), sc_b = meta_f32(2);
-          acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
-          acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
-          acc[2] = fmaf(sc_b, d[2] + xn2.x, acc[2]);
-          acc[3] = fmaf(sc_b, d[3] + xn2.y, acc[3]);
-          if (has_off) {
-            const float of_a = meta_f32(1), of_b = meta_f32(3);
-            acc[0] = fmaf(of_a, xs2.x, acc[0]);
-            acc[1] = fmaf(of_a, xs2.y, acc[1]);
-            acc[2] = fmaf(of_b, xs2.x, acc[2]);
-            acc[3] = fmaf(of_b, xs2.y, acc[3]);
+          if constexpr (!G64) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d[i] += e[i];
+            const float2 xs2 = *reinterpret_cast<const float2*>(xsum_w + sl * 8);
+            const float2 xn2 = *reinterpret_cast<const float2*>(xneg_w + sl * 8);
+            const float sc_a = meta_f32(0, j), sc_b = meta_f32(2, j);
+            acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
+            acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
+            acc[2] = fmaf(sc_b, d[2] + xn2.x, acc[2]);
+            acc[3] = fmaf(sc_b, d[3] + xn2.y, acc[3]);
+            if (has_off) {
+              const float of_a = meta_f32(1, j), of_b = meta_f32(3, j);
+              acc[0] = fmaf(of_a, xs2.x, acc[0]);
+              acc[1] = fmaf(of_a, xs2.y, acc[1]);
+              acc[2] = fmaf(of_b, xs2.x, acc[2]);
+              acc[3] = fmaf(of_b, xs2.y, acc[3]);
+            }
+          } else {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const float* dd = half == 0 ? d : e;
+              const float2 xs2 = *reinterpret_cast<const float2*>(xsum_w + (sl * 2 + half) * 8);
+              const float2 xn2 = *reinterpret_cast<const float2*>(xneg_w + (sl * 2 + half) * 8);
+              const float sc_a = meta_f32(0, 2 * j + half), sc_b = meta_f32(2, 2 * j + half);
+              acc[0] = fmaf(sc_a, dd[0] + xn2.x, acc[0]);
+              acc[1] = fmaf(sc_a, dd[1] + xn2.y, acc[1]);
+              acc[2] = fmaf(sc_b, dd[2] + xn2.x, acc[2]);
+              acc[3] = fmaf(sc_b, dd[3] + xn2.y, acc[3]);
+              if (has_off) {
+                const float of_a = meta_f32(1, 2 * j + half), of_b = meta_f32(3, 2 * j + half);
+                acc[0] = fmaf(of_a, xs2.x, acc[0]);
+                acc[1] = fmaf(of_a, xs2.y, acc[1]);
+                acc[2] = fmaf(of_b, xs2.x, acc[2]);
+                acc[3] = fmaf(of_b, xs2.y, acc[3]);
+              }
+            }
           }
         }
       }
@@ -314,7 +373,7 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   stream::cp_async_wait<0>();
 }
 
-template <bool XBF16, int CH>
+template <bool XBF16, int CH, bool G64>
 __global__ void __launch_bounds__(kThreads, 3) gemv_mma_tile_kernel(const __grid_constant__ Launch L) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int j = 0;
@@ -325,16 +384,16 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_tile_kernel(const __grid
   const Job& J = L.job[j];
   switch (J.bits) {
     case 2:
-      tile_body<2, XBF16, CH>(L, J, smem_raw);
+      tile_body<2, XBF16, CH, G64>(L, J, smem_raw);
       break;
     case 3:
-      tile_body<3, XBF16, CH>(L, J, smem_raw);
+      if constexpr (!G64) tile_body<3, XBF16, CH, false>(L, J, smem_raw);  // (the host never sends 3-bit here)
       break;
     case 4:
-      tile_body<4, XBF16, CH>(L, J, smem_raw);
+      tile_body<4, XBF16, CH, G64>(L, J, smem_raw);
       break;
     default:
-      tile_body<8, XBF16, CH>(L, J, smem_raw);
+      tile_body<8, XBF16, CH, G64>(L, J, smem_raw);
       break;
   }
 }

@@ -13,6 +13,17 @@
 
 namespace dq {
 
+// Position inside a 128-value step of value `v` (0..31) of quad lane `tt`'s unit.  Normally a
+// unit is 32 consecutive values.  With 64-value groups (G64) a lane instead owns 16 values of
+// EACH of the step's two groups -- [16 tt, 16 tt + 16) and [64 + 16 tt, 64 + 16 tt + 16) -- so
+// that the first half of its fragment registers belongs to one group and the second half to
+// the other, and the two halves can be accumulated (and scaled) separately.
+template <bool G64>
+__host__ __device__ constexpr int step_position(int tt, int v) {
+  if (G64) return v < 16 ? 16 * tt + v : 64 + 16 * tt + (v - 16);
+  return 32 * tt + v;
+}
+
 // The activation is read with L2-coherent loads (ld.global.cg): it was written by the previous
 // kernel moments ago, is read once per CTA, and must not be served from a line this SM cached
 // before the previous kernel finished.
@@ -21,7 +32,8 @@ namespace dq {
 // given, and the activation is 16-bit and 16-byte aligned, the activation is first copied
 // there with 128-bit loads -- one round trip to L2 for the whole CTA -- and the fragments are
 // built from shared memory; otherwise every lane gathers its values from global memory.
-template <int BITS, bool XBF16>
+// With G64 the sums are per (step, group): xsum / xneg are [steps][2][8].
+template <int BITS, bool XBF16, bool G64 = false>
 __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, int m_stride_u4, uint4* xb,
                                                  float* xsum, float* xneg, int tid, int nthreads,
                                                  const int* row_map = nullptr, unsigned short* raw = nullptr) {
@@ -64,8 +76,8 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     const Slot sl = Plan::slot(4 * q + r);
-    off_lo[r] = 32 * tt + sl.v_lo;
-    off_hi[r] = 32 * tt + sl.v_hi;
+    off_lo[r] = step_position<G64>(tt, sl.v_lo);
+    off_hi[r] = step_position<G64>(tt, sl.v_hi);
     mul_lo[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_lo) << 23);  // exact powers of two
     mul_hi[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_hi) << 23);
     // every value of the unit appears in exactly one slot, except at 8-bit where the high
@@ -104,11 +116,16 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
           xb[m * m_stride_u4 + (s * QU + q) * 4 + tt] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
         }
 #pragma unroll
-        for (int d = LANES / 2; d > 0; d >>= 1) {
+        for (int d = (G64 ? LANES / 4 : LANES / 2); d > 0; d >>= 1) {
           sx += __shfl_xor_sync(0xffffffffu, sx, d);
           sb += __shfl_xor_sync(0xffffffffu, sb, d);
         }
-        if (live && l == 0) {
+        if (G64) {  // lanes 0 and LANES/2 of the builder group hold the sums of the two groups
+          if (live && (l == 0 || l == LANES / 2)) {
+            xsum[(s * 2 + (l != 0)) * 8 + m] = sx;
+            xneg[(s * 2 + (l != 0)) * 8 + m] = -kMagicValue * sb;
+          }
+        } else if (live && l == 0) {
           xsum[s * 8 + m] = sx;
           xneg[s * 8 + m] = -kMagicValue * sb;
         }
@@ -151,11 +168,16 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
       xb[m * m_stride_u4 + (s * QU + q) * 4 + tt] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
     }
 #pragma unroll
-    for (int d = LANES / 2; d > 0; d >>= 1) {
+    for (int d = (G64 ? LANES / 4 : LANES / 2); d > 0; d >>= 1) {
       sx += __shfl_xor_sync(0xffffffffu, sx, d);
       sb += __shfl_xor_sync(0xffffffffu, sb, d);
     }
-    if (live && l == 0) {
+    if (G64) {
+      if (live && (l == 0 || l == LANES / 2)) {
+        xsum[(s * 2 + (l != 0)) * 8 + m] = sx;
+        xneg[(s * 2 + (l != 0)) * 8 + m] = -kMagicValue * sb;
+      }
+    } else if (live && l == 0) {
       xsum[s * 8 + m] = sx;
       xneg[s * 8 + m] = -kMagicValue * sb;
     }
@@ -166,7 +188,7 @@ fill_zeros:
     xb[a.m * m_stride_u4 + idx] = make_uint4(0u, 0u, 0u, 0u);
   }
   if (a.m < 8) {
-    for (int idx = tid; idx < steps * 8; idx += nthreads) {
+    for (int idx = tid; idx < steps * (G64 ? 16 : 8); idx += nthreads) {
       if ((idx & 7) >= a.m) {
         xsum[idx] = 0.0f;
         xneg[idx] = 0.0f;
@@ -181,8 +203,8 @@ fill_zeros:
 // the first mma.  Layouts (all warp-private):
 //   raw   [nsteps * 128] 16-bit scratch (one activation row at a time)
 //   xb    [m][nsteps * QU*4 (+4 pad)] uint4, then a zero block of QU*4
-//   xsum / xneg  [nsteps][8]
-template <int BITS, bool XBF16>
+//   xsum / xneg  [nsteps][8]   ([nsteps][2][8] with 64-value groups)
+template <int BITS, bool XBF16, bool G64 = false>
 __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin, int nsteps, int m_stride_u4,
                                                  unsigned short* raw, uint4* xb, float* xsum, float* xneg,
                                                  int lane) {
@@ -201,8 +223,8 @@ __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin,
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     const Slot sl = Plan::slot(4 * q + r);
-    off_lo[r] = 32 * tt + sl.v_lo;
-    off_hi[r] = 32 * tt + sl.v_hi;
+    off_lo[r] = step_position<G64>(tt, sl.v_lo);
+    off_hi[r] = step_position<G64>(tt, sl.v_hi);
     mul_lo[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_lo) << 23);
     mul_hi[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_hi) << 23);
     count_x[r] = BITS != 8 || sl.e_lo == 0;
@@ -257,11 +279,16 @@ __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin,
         xb[m * m_stride_u4 + (j * QU + q) * 4 + tt] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
       }
 #pragma unroll
-      for (int d = LANES / 2; d > 0; d >>= 1) {
+      for (int d = (G64 ? LANES / 4 : LANES / 2); d > 0; d >>= 1) {
         sx += __shfl_xor_sync(0xffffffffu, sx, d);
         sb += __shfl_xor_sync(0xffffffffu, sb, d);
       }
-      if (live && l == 0) {
+      if (G64) {
+        if (live && (l == 0 || l == LANES / 2)) {
+          xsum[(j * 2 + (l != 0)) * 8 + m] = sx;
+          xneg[(j * 2 + (l != 0)) * 8 + m] = -kMagicValue * sb;
+        }
+      } else if (live && l == 0) {
         xsum[j * 8 + m] = sx;
         xneg[j * 8 + m] = -kMagicValue * sb;
       }
@@ -272,7 +299,7 @@ __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin,
     xb[a.m * m_stride_u4 + idx] = make_uint4(0u, 0u, 0u, 0u);
   }
   if (a.m < 8) {
-    for (int idx = lane; idx < nsteps * 8; idx += kWarp) {
+    for (int idx = lane; idx < nsteps * (G64 ? 16 : 8); idx += kWarp) {
       if ((idx & 7) >= a.m) {
         xsum[idx] = 0.0f;
         xneg[idx] = 0.0f;

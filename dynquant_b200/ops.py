@@ -185,6 +185,31 @@ def gemv(
     return out
 
 
+# Up to this many activation rows a packed matmul is issued as GEMV launches of
+# ``gemv_max_rows()`` rows each: re-reading the packed weights (mostly from L2) a few times
+# is cheaper than writing the dense weight out and reading it back, which is what the
+# dequantize + dense path costs.  Measured on B200 for a 14336 x 4096 layer at 16 rows:
+# two GEMV launches ~45 us against ~215-275 us for dequantize + matmul.
+GEMV_CHUNKED_MAX_ROWS = 64
+
+
+def gemv_row_chunks(
+    x: torch.Tensor,
+    shards: list[QuantTensor],
+    bias: torch.Tensor | None = None,
+    *,
+    out_dtype: torch.dtype | None = None,
+) -> torch.Tensor:
+    """``gemv_shards`` for more rows than one launch takes: ``gemv_max_rows()`` rows per launch."""
+    step = gemv_max_rows()
+    out_dtype = out_dtype or x.dtype
+    total = sum(qt.num_rows for qt in shards)
+    out = torch.empty((x.shape[0], total), dtype=out_dtype, device=x.device)
+    for start in range(0, x.shape[0], step):
+        out[start : start + step] = gemv_shards(x[start : start + step], shards, bias, out_dtype=out_dtype)
+    return out
+
+
 def gemv_shards(
     x: torch.Tensor,
     shards: list[QuantTensor],
@@ -354,6 +379,8 @@ def quantized_matmul(x: torch.Tensor, qt: QuantTensor, bias: torch.Tensor | None
             out = gemv(flat.contiguous(), *args)
         else:
             out = gemv_shards(flat.contiguous(), [qt], bias.contiguous())
+    elif flat.shape[0] <= GEMV_CHUNKED_MAX_ROWS and flat.is_cuda:
+        out = gemv_row_chunks(flat.contiguous(), [qt], None if bias is None else bias.contiguous())
     else:
         weight = dequant(*args)
         out = torch.nn.functional.linear(flat, weight.to(x.dtype), bias)

@@ -183,6 +183,10 @@ class DynQuantLinearMethod:
             if bias is not None and bias.dtype != flat.dtype:
                 bias = bias.to(flat.dtype)
             out = ops.gemv_shards(flat.contiguous(), shards, None if bias is None else bias.contiguous())
+        elif flat.shape[0] <= ops.GEMV_CHUNKED_MAX_ROWS:
+            if bias is not None and bias.dtype != flat.dtype:
+                bias = bias.to(flat.dtype)
+            out = ops.gemv_row_chunks(flat.contiguous(), shards, None if bias is None else bias.contiguous())
         else:
             parts = [
                 torch.nn.functional.linear(flat, ops.dequant(*ops._kernel_args(qt)).to(flat.dtype)) for qt in shards

@@ -4,7 +4,8 @@ The counterpart of the reference's ``benchmarks/gemv_bandwidth.py`` for this lib
 BASELINE config 5: widths {2,3,4,8} x group {64,128} x Mistral-7B shapes x M {1,4,16} plus
 odd-N tails.  Every point runs over a ring of distinct weight tensors whose total size
 exceeds twice the L2 (so the bytes really come from HBM) and is timed with CUDA events;
-M above the operator's row limit goes through the dequant + dense path, as in the reference.
+M above the operator's row limit of 8 is issued as several GEMV launches up to 64 rows, and
+through the dequant + dense path beyond, as in the reference.
 
     python -m dynquant_b200.sweep                      # the full config-5 grid
     python -m dynquant_b200.sweep --shape 131072x2048 --bits 8 --m 1 --launches 4 --ring 1
@@ -70,7 +71,8 @@ def run_point(rows: int, k: int, bits: int, group: int, m: int, *, launches: int
     gbs = nbytes / seconds / 1e9
     return {
         "rows": rows, "in_features": k, "bits": bits, "group_size": group, "m": m,
-        "path": "gemv" if m <= ops.gemv_max_rows() else "dequant+dense",
+        "path": ("gemv" if m <= ops.gemv_max_rows() else
+                 "gemv x%d" % -(-m // ops.gemv_max_rows()) if m <= ops.GEMV_CHUNKED_MAX_ROWS else "dequant+dense"),
         "us_per_call": round(seconds * 1e6, 2), "gbps": round(gbs, 1),
         "pct_of_hbm_peak": round(100 * gbs / peak, 1), "peak": f"{peak} GB/s ({kind})",
         "ring": ring, "ring_bytes": probe.nbytes * ring, "launches": launches,
