@@ -478,10 +478,10 @@ int32_t gemv_args(GemvArgs a, const dq_weight& w, const dq_geometry& g, cudaStre
       const int32_t rc = launch_gemv_mma(a, w.bits, stream);
       if (rc != DQ_ERR_UNSUPPORTED) return rc;  // (unsupported: silently on to the SIMT kernels)
     }
-    // The staged activation of all rows may be what does not fit: two passes over half the
-    // rows each read the weights twice (the second time mostly from L2) but stay on the
+    // The staged activation of all rows may be what does not fit: passes over half the rows
+    // each (halved again if need be) re-read the weights, mostly from L2, but stay on the
     // tensor-core path.
-    if (a.m > 1 && mma_path_supports(activation_rows(a, 0, (a.m + 1) / 2), w.bits)) {
+    if (a.m > 1 && mma_path_supports(activation_rows(a, 0, 1), w.bits)) {
       const int half = (a.m + 1) / 2;
       if (const int32_t rc = gemv_args(activation_rows(a, 0, half), w, g, stream)) return rc;
       return gemv_args(activation_rows(a, half, a.m - half), w, g, stream);

@@ -597,7 +597,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     }
     if (a.group_values != a0.group_values || a.words_per_row / (4 * bits[i]) != steps) return DQ_OK;
     if (a.group_values == kStepValues / 2) {
-      if (bits[i] == 3 || a.num_groups != 2 * steps) return DQ_OK;  // 3-bit half units straddle words
+      if (a.num_groups != 2 * steps) return DQ_OK;
     } else if (a.group_values != kStepValues || a.num_groups != steps) {
       return DQ_OK;
     }
@@ -635,12 +635,9 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     for (int i = 0; i < n; ++i) items += ceil_div(ceil_div(jobs[i].rows, kTileRows), rw);
     return items;
   };
-  auto shape_at = [&](int kw, bool one_shot) {
+  auto shape_with = [&](int kw, bool one_shot, int ch) {
     Shape sh;
-    if (steps % kw != 0) return sh;
     const int spw = steps / kw;
-    const int ch = (spw % 4 == 0 && meta_aligned(4)) ? 4 : ((spw % 2 == 0 && meta_aligned(2)) ? 2 : 0);
-    if (ch == 0) return sh;
     const bool wide = kw < tilek::kWarps;
     const size_t stage = static_cast<size_t>(ch) * 2 * (4 * max_bits) * tilek::kThreads + ch * gps * 2 * tilek::kThreads;
     const size_t fixed = tilek::kRedFloats * 4 +
@@ -664,6 +661,16 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     if (force_per_sm > 0) sh.per_sm = std::min(sh.per_sm, force_per_sm);
     const int64_t cap = static_cast<int64_t>(sh.per_sm) * dev.sm_count;
     sh.ipc = static_cast<int>(ceil_div(items_at(kw), cap));
+    return sh;
+  };
+  // stages of four steps where they fit, of two otherwise (long rows x many activation rows
+  // leave little shared memory beside the staged activation)
+  auto shape_at = [&](int kw, bool one_shot) {
+    Shape sh;
+    if (steps % kw != 0) return sh;
+    const int spw = steps / kw;
+    if (spw % 4 == 0 && meta_aligned(4)) sh = shape_with(kw, one_shot, 4);
+    if (sh.kw == 0 && spw % 2 == 0 && meta_aligned(2)) sh = shape_with(kw, one_shot, 2);
     return sh;
   };
   Shape pick;
@@ -746,10 +753,8 @@ bool mma_path_supports(const GemvArgs& a, int bits) {
   if (!mma_enabled()) return false;
   if (a.x_dtype != DQ_BF16 && a.x_dtype != DQ_F16) return false;
   if (a.meta_dtype != DQ_BF16 && a.meta_dtype != DQ_F16) return false;
-  if (a.group_values == kStepValues / 2) {
-    if (bits == 3) return false;  // 64-value groups: the tiled kernel only, and not at 3 bits
-  } else if (a.group_values % kStepValues != 0) {
-    return false;
+  if (a.group_values != kStepValues / 2 && a.group_values % kStepValues != 0) {
+    return false;  // (64-value groups: the tiled kernel only)
   }
   const auto addr = reinterpret_cast<uintptr_t>(a.packed);
   const int align = bits == 2 ? 8 : (bits == 3 ? 4 : 16);

@@ -20,10 +20,9 @@
 //   * Each CTA belongs to one matrix (a "job") and runs the body compiled for its width.
 //
 // Arithmetic is that of gemv_mma_kernel (dq_gemv_mma.cu).  Requirements, checked by the
-// host: one group per 128-value step -- or two (64-value groups) at 2, 4 and 8 bits, where
-// a lane decodes 16 values of each group and the two halves of a step are accumulated and
-// scaled separately --, 16-byte aligned rows, steps divisible by kw * CH, and scales/offsets
-// rows aligned to a stage's worth of metadata.
+// host: one group per 128-value step, or two (64-value groups), whose halves of a step are
+// accumulated and scaled separately (see tile_body); 16-byte aligned rows, steps divisible
+// by kw * CH, and scales/offsets rows aligned to a stage's worth of metadata.
 #pragma once
 
 #include "dq_gemv.cuh"
@@ -123,7 +122,13 @@ __device__ __forceinline__ void read_lane_words(const unsigned char* src, uint32
 
 template <int BITS, bool XBF16, int CH, bool G64>
 __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigned char* smem) {
-  static_assert(!(G64 && BITS == 3), "3-bit units do not split into two 16-value halves on word boundaries");
+  // 64-value groups: at 2, 4 and 8 bits a lane owns 16 values of each group (HALVES: the two
+  // halves of its registers are the two groups).  3-bit half units do not start on words, so
+  // there a lane keeps its whole unit -- quad lanes 0,1 are the first group, 2,3 the second --
+  // and every step runs its mma twice, once per group, the lanes of the other group feeding
+  // a zero B fragment (QUADS).
+  constexpr bool HALVES = G64 && BITS != 3;
+  constexpr bool QUADS = G64 && BITS == 3;
   using Plan = MmaPlan<BITS>;
   using R = Ring<BITS, CH, G64>;
   constexpr int GPS = R::GPS;
@@ -214,7 +219,7 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   const int xb_step_u4 = b_live ? QU * 4 : 0;
   const float* xsum_w = xsum + sl0 * 8 * GPS + 2 * t;
   const float* xneg_w = xneg + sl0 * 8 * GPS + 2 * t;
-  const unsigned char* ring_w_mine = G64 ? ring_w + (tid & ~3) * UNIT + t * (UNIT / 2) : ring_w + tid * UNIT;
+  const unsigned char* ring_w_mine = HALVES ? ring_w + (tid & ~3) * UNIT + t * (UNIT / 2) : ring_w + tid * UNIT;
   const unsigned char* ring_m_quad = ring_m + (tid & ~3) * R::META;
   const uint32_t magic = L.magic;
   const bool mbf = L.meta_bf16 != 0;
@@ -261,8 +266,8 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
         for (int j = 0; j < CH; ++j) {
           const int sl = chunk * CH + j;
           uint32_t wa[BITS], wb[BITS];
-          read_lane_words<BITS, G64>(wsrc + (j * 2 + 0) * (UNIT * kThreads), wa);
-          read_lane_words<BITS, G64>(wsrc + (j * 2 + 1) * (UNIT * kThreads), wb);
+          read_lane_words<BITS, HALVES>(wsrc + (j * 2 + 0) * (UNIT * kThreads), wa);
+          read_lane_words<BITS, HALVES>(wsrc + (j * 2 + 1) * (UNIT * kThreads), wb);
           uint32_t aa[NA], ab[NA];
           decode_unit<BITS>(wa, magic, aa);
           decode_unit<BITS>(wb, magic, ab);
@@ -272,21 +277,43 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
           // two accumulators: the first half of the registers (d) and the second (e).  They
           // halve the chain of dependent mma; with 64-value groups they ARE the two groups.
           float d[4], e[4];
+          if constexpr (QUADS) {
+            // d: the first group (this lane's B is zero unless t < 2); e: the second
+            const uint4* zsrc = xb + a.m * m_stride_u4;
+            const uint4* bsrc_d = (t < 2) ? bsrc : zsrc;
+            const uint4* bsrc_e = (t < 2) ? zsrc : bsrc;
+            const int step_d = (t < 2) ? 4 : 0, step_e = (t < 2) ? 0 : 4;
 #pragma unroll
-          for (int q = 0; q < QU / 2; ++q) {
-            const uint4 b0 = bsrc[q * 4];
-            const uint4 b1 = bsrc[(q + QU / 2) * 4];
-            if (q == 0) {
-              mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b0.x, b0.y);
-              mma_16816<XBF16, true>(e, aa[NA / 2], ab[NA / 2], aa[NA / 2 + 1], ab[NA / 2 + 1], b1.x, b1.y);
-            } else {
-              mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b0.x, b0.y);
-              mma_16816<XBF16, false>(e, aa[NA / 2 + 4 * q], ab[NA / 2 + 4 * q], aa[NA / 2 + 4 * q + 1],
-                                      ab[NA / 2 + 4 * q + 1], b1.x, b1.y);
+            for (int q = 0; q < QU; ++q) {
+              const uint4 b0 = bsrc_d[q * step_d];
+              const uint4 b1 = bsrc_e[q * step_e];
+              if (q == 0) {
+                mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b0.x, b0.y);
+                mma_16816<XBF16, true>(e, aa[0], ab[0], aa[1], ab[1], b1.x, b1.y);
+              } else {
+                mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b0.x, b0.y);
+                mma_16816<XBF16, false>(e, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b1.x, b1.y);
+              }
+              mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b0.z, b0.w);
+              mma_16816<XBF16, false>(e, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b1.z, b1.w);
             }
-            mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b0.z, b0.w);
-            mma_16816<XBF16, false>(e, aa[NA / 2 + 4 * q + 2], ab[NA / 2 + 4 * q + 2], aa[NA / 2 + 4 * q + 3],
-                                    ab[NA / 2 + 4 * q + 3], b1.z, b1.w);
+          } else {
+#pragma unroll
+            for (int q = 0; q < QU / 2; ++q) {
+              const uint4 b0 = bsrc[q * 4];
+              const uint4 b1 = bsrc[(q + QU / 2) * 4];
+              if (q == 0) {
+                mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b0.x, b0.y);
+                mma_16816<XBF16, true>(e, aa[NA / 2], ab[NA / 2], aa[NA / 2 + 1], ab[NA / 2 + 1], b1.x, b1.y);
+              } else {
+                mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b0.x, b0.y);
+                mma_16816<XBF16, false>(e, aa[NA / 2 + 4 * q], ab[NA / 2 + 4 * q], aa[NA / 2 + 4 * q + 1],
+                                        ab[NA / 2 + 4 * q + 1], b1.x, b1.y);
+              }
+              mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b0.z, b0.w);
+              mma_16816<XBF16, false>(e, aa[NA / 2 + 4 * q + 2], ab[NA / 2 + 4 * q + 2], aa[NA / 2 + 4 * q + 3],
+                                      ab[NA / 2 + 4 * q + 3], b1.z, b1.w);
+            }
           }
           // halfword `hw` of metadata array i of this stage
           auto meta_f32 = [&](int i, int hw) -> float {
@@ -387,7 +414,7 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_tile_kernel(const __grid
       tile_body<2, XBF16, CH, G64>(L, J, smem_raw);
       break;
     case 3:
-      if constexpr (!G64) tile_body<3, XBF16, CH, false>(L, J, smem_raw);  // (the host never sends 3-bit here)
+      tile_body<3, XBF16, CH, G64>(L, J, smem_raw);
       break;
     case 4:
       tile_body<4, XBF16, CH, G64>(L, J, smem_raw);

@@ -18,10 +18,30 @@ namespace dq {
 // EACH of the step's two groups -- [16 tt, 16 tt + 16) and [64 + 16 tt, 64 + 16 tt + 16) -- so
 // that the first half of its fragment registers belongs to one group and the second half to
 // the other, and the two halves can be accumulated (and scaled) separately.
-template <bool G64>
+//
+// At 3 bits a 16-value half unit is 48 bits and does not start on a word, so there a lane keeps
+// its whole 32-value unit: quad lanes 0,1 hold values of the first group, 2,3 of the second
+// (SPLIT_QUAD), and the kernel separates the groups by giving the other pair of lanes a zero
+// B fragment.
+template <bool G64, int BITS>
 __host__ __device__ constexpr int step_position(int tt, int v) {
-  if (G64) return v < 16 ? 16 * tt + v : 64 + 16 * tt + (v - 16);
+  if (G64 && BITS != 3) return v < 16 ? 16 * tt + v : 64 + 16 * tt + (v - 16);
   return 32 * tt + v;
+}
+
+// Fixed-order reduction of a per-lane partial over the LANES lanes (lane index l = 4 q + tt)
+// that build one (activation row, step).  MODE 0: one sum, in lane 0.  MODE 1 (groups are
+// the two halves of the registers, i.e. of q): sums in lanes 0 and LANES/2.  MODE 2 (groups
+// are the quad-lane pairs, bit 1 of l): sums in lanes 0 and 2.
+template <int LANES, int MODE>
+__device__ __forceinline__ void reduce_builder_group(float& sx, float& sb) {
+#pragma unroll
+  for (int d = LANES / 2; d > 0; d >>= 1) {
+    if (MODE == 1 && d == LANES / 2) continue;
+    if (MODE == 2 && d == 2) continue;
+    sx += __shfl_xor_sync(0xffffffffu, sx, d);
+    sb += __shfl_xor_sync(0xffffffffu, sb, d);
+  }
 }
 
 // The activation is read with L2-coherent loads (ld.global.cg): it was written by the previous
@@ -62,6 +82,8 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
   constexpr int LANES = QU * 4;  // lanes that build one (m, s): 16, or 32 at 8-bit
+  constexpr int kSplit = !G64 ? 0 : (BITS == 3 ? 2 : 1);       // how the two groups of a step map to lanes
+  constexpr int kSecond = BITS == 3 ? 2 : LANES / 2;           // lane holding the second group's sums
   constexpr float kMagicValue = XBF16 ? 128.0f : 0.0f;  // fp16 fragments are un-biased in registers
   const int lane = tid & (kWarp - 1);
   const int sub = lane / LANES;            // which (m, s) of this warp's batch
@@ -76,8 +98,8 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     const Slot sl = Plan::slot(4 * q + r);
-    off_lo[r] = step_position<G64>(tt, sl.v_lo);
-    off_hi[r] = step_position<G64>(tt, sl.v_hi);
+    off_lo[r] = step_position<G64, BITS>(tt, sl.v_lo);
+    off_hi[r] = step_position<G64, BITS>(tt, sl.v_hi);
     mul_lo[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_lo) << 23);  // exact powers of two
     mul_hi[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_hi) << 23);
     // every value of the unit appears in exactly one slot, except at 8-bit where the high
@@ -115,13 +137,9 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
         if (live) {
           xb[m * m_stride_u4 + (s * QU + q) * 4 + tt] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
         }
-#pragma unroll
-        for (int d = (G64 ? LANES / 4 : LANES / 2); d > 0; d >>= 1) {
-          sx += __shfl_xor_sync(0xffffffffu, sx, d);
-          sb += __shfl_xor_sync(0xffffffffu, sb, d);
-        }
-        if (G64) {  // lanes 0 and LANES/2 of the builder group hold the sums of the two groups
-          if (live && (l == 0 || l == LANES / 2)) {
+        reduce_builder_group<LANES, kSplit>(sx, sb);
+        if (G64) {  // two lanes of the builder group hold the sums of the two groups
+          if (live && (l == 0 || l == kSecond)) {
             xsum[(s * 2 + (l != 0)) * 8 + m] = sx;
             xneg[(s * 2 + (l != 0)) * 8 + m] = -kMagicValue * sb;
           }
@@ -167,13 +185,9 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
     if (live) {
       xb[m * m_stride_u4 + (s * QU + q) * 4 + tt] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
     }
-#pragma unroll
-    for (int d = (G64 ? LANES / 4 : LANES / 2); d > 0; d >>= 1) {
-      sx += __shfl_xor_sync(0xffffffffu, sx, d);
-      sb += __shfl_xor_sync(0xffffffffu, sb, d);
-    }
+    reduce_builder_group<LANES, kSplit>(sx, sb);
     if (G64) {
-      if (live && (l == 0 || l == LANES / 2)) {
+      if (live && (l == 0 || l == kSecond)) {
         xsum[(s * 2 + (l != 0)) * 8 + m] = sx;
         xneg[(s * 2 + (l != 0)) * 8 + m] = -kMagicValue * sb;
       }
@@ -212,6 +226,8 @@ __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin,
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
   constexpr int LANES = QU * 4;
+  constexpr int kSplit = !G64 ? 0 : (BITS == 3 ? 2 : 1);
+  constexpr int kSecond = BITS == 3 ? 2 : LANES / 2;
   constexpr int PER = kWarp / LANES;  // steps built per round
   constexpr float kMagicValue = XBF16 ? 128.0f : 0.0f;
   const int sub = lane / LANES;
@@ -223,8 +239,8 @@ __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin,
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     const Slot sl = Plan::slot(4 * q + r);
-    off_lo[r] = step_position<G64>(tt, sl.v_lo);
-    off_hi[r] = step_position<G64>(tt, sl.v_hi);
+    off_lo[r] = step_position<G64, BITS>(tt, sl.v_lo);
+    off_hi[r] = step_position<G64, BITS>(tt, sl.v_hi);
     mul_lo[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_lo) << 23);
     mul_hi[r] = __uint_as_float(static_cast<uint32_t>(127 + sl.e_hi) << 23);
     count_x[r] = BITS != 8 || sl.e_lo == 0;
@@ -278,13 +294,9 @@ __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin,
       if (live) {
         xb[m * m_stride_u4 + (j * QU + q) * 4 + tt] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
       }
-#pragma unroll
-      for (int d = (G64 ? LANES / 4 : LANES / 2); d > 0; d >>= 1) {
-        sx += __shfl_xor_sync(0xffffffffu, sx, d);
-        sb += __shfl_xor_sync(0xffffffffu, sb, d);
-      }
+      reduce_builder_group<LANES, kSplit>(sx, sb);
       if (G64) {
-        if (live && (l == 0 || l == LANES / 2)) {
+        if (live && (l == 0 || l == kSecond)) {
           xsum[(j * 2 + (l != 0)) * 8 + m] = sx;
           xneg[(j * 2 + (l != 0)) * 8 + m] = -kMagicValue * sb;
         }
