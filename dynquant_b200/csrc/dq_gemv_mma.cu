@@ -589,6 +589,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
   const GemvArgs& a0 = jobs[0];
   const int steps = a0.words_per_row / (4 * bits[0]);
   int max_bits = 0, max_tiles_total = 0;
+  const bool g64_jobs = a0.group_values == kStepValues / 2;
   for (int i = 0; i < n; ++i) {
     const GemvArgs& a = jobs[i];
     if (a.x != a0.x || a.m != a0.m || a.x_dtype != a0.x_dtype || a.meta_dtype != a0.meta_dtype ||
@@ -607,6 +608,11 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     max_bits = std::max(max_bits, bits[i]);
     max_tiles_total += static_cast<int>(ceil_div(a.rows, kTileRows));
   }
+  // Long matrices with one group per step have leaner kernels of their own (the streaming
+  // kernel, or the register ring at 2 bits): this one is for what does not fill the machine
+  // eight tiles per SM deep, for fused shards and for 64-value groups.
+  static const bool tile_all = env_int("DQ_B200_TILE_ALL") != 0;
+  if (n == 1 && !g64_jobs && !tile_all && max_tiles_total >= dev.sm_count * tilek::kWarps) return DQ_OK;
   // Shape of the CTAs.  First choice: ONE wave in which every warp's whole share of the
   // weights is in flight before the activation arrives -- the finest slicing of the reduction
   // axis whose grid is resident at once.  Otherwise CTAs persist over several items with a
