@@ -215,7 +215,9 @@ def run_ours(args) -> None:
         import torch.distributed as dist_mod
 
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=120))
 
     from dynquant_b200 import _lib
     from dynquant_b200.stack import StepRunner

@@ -43,7 +43,10 @@ def main() -> None:
         import torch.distributed as dist_mod
 
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        # a short timeout: a rank that fails must end the others' next collective, not hang them
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=60))
     peak, kind = hbm_peak_gbs()
     widths = [(3, 4), (2, 3), (4, 2), (3, 3), (4, 4), (2, 4)]
     layers = [qwen3_moe_layer("cpu" if ns.ep else dev, seed=3030 + i, bits_gate_up=widths[i % 6][0],
@@ -75,14 +78,17 @@ def main() -> None:
         for _ in range(3):
             step()
         torch.cuda.synchronize()
-        run = step
-        if not ns.ep:  # single GPU: replay a CUDA graph of the step, so the time is the device's
+        # Single GPU: replay a CUDA graph of the step, so that the time is the device's.  With
+        # --ep the step runs eagerly: its NCCL exchanges are issued from Python, rank by rank,
+        # and the time includes that host work.
+        run, launch = step, "eager"
+        if not ns.ep:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 step()
-            run = graph.replay
-            run()
+            graph.replay()
             torch.cuda.synchronize()
+            run, launch = graph.replay, "cuda graph"
         if dist is not None:
             dist.barrier()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -100,7 +106,7 @@ def main() -> None:
         if rank == 0:
             print(json.dumps({
                 "workload": "qwen3-30b-a3b expert layer", "tokens": tokens, "n_gpus": world,
-                "exchange": ns.mode if ns.ep else None,
+                "exchange": ns.mode if ns.ep else None, "launch": launch,
                 "us_per_layer": round(seconds * 1e6, 2), "tokens_per_s_per_layer": round(tokens / seconds, 1),
                 "activated_experts": int(torch.unique(ids_all).numel()),
                 "algorithmic_mb_per_layer": round(nbytes / 1e6, 2), "gbps": round(nbytes / seconds / 1e9, 1),
