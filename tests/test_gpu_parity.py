@@ -211,3 +211,63 @@ def test_empty_shapes_return_empty():
     assert ops.gemv(x, qt.packed, qt.scales, qt.offsets, 4, 128, 256).shape == (0, 64)
     empty = qt.rows(0, 0)
     assert ops.dequant(empty.packed, empty.scales, empty.offsets, 4, 128, 256).shape == (0, 256)
+
+
+# ---- regimes of the tiled tensor-core kernel (persistent CTAs, 64-value groups, fused shards,
+# ---- activation-row split): same oracle, same bar
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("group", [64, 128])
+def test_gemv_many_short_rows_take_the_persistent_regime(bits, group):
+    """64,000 rows of 256 values: more row tiles than one wave of CTAs holds, so CTAs walk over
+    several items through their ring; with 64-value groups this is the only tensor-core kernel."""
+    from dynquant_b200 import ops
+
+    rows, k = 64000, 256
+    qt = make_quant(rows, k, group, bits, torch.float16).to("cuda")
+    for m in (1, 8):
+        x = torch.randn(m, k, generator=torch.Generator().manual_seed(bits + m)).to(torch.bfloat16).cuda()
+        want = oracle_gemv(x, qt)
+        acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, qt.geometry.effective_group, k,
+                       out_dtype=torch.float32).cpu().numpy()
+        assert np.abs(acc - want).max() / (np.abs(want).max() + 1e-30) <= 1e-3
+        assert np.linalg.norm(acc - want) / (np.linalg.norm(want) + 1e-30) <= 1e-3
+
+
+@pytest.mark.parametrize("group", [64, 128])
+def test_fused_shards_of_every_width_in_one_launch(group):
+    """Four shards (2, 3, 4, 8 bits) against one activation: one launch, each CTA the body of
+    its shard's width, bias folded into the store."""
+    from dynquant_b200 import ops
+
+    k = 1024
+    sizes = [(2, 96), (3, 160), (4, 33), (8, 64)]
+    shards = [make_quant(rows, k, group, bits, torch.float16, seed=40 + bits).to("cuda") for bits, rows in sizes]
+    total = sum(rows for _, rows in sizes)
+    bias = torch.randn(total, generator=torch.Generator().manual_seed(7)).to(torch.float32).cuda()
+    for m in (1, 5):
+        x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16).cuda()
+        before = ops.launch_count()
+        got = ops.gemv_shards(x, shards, bias, out_dtype=torch.float32)
+        assert ops.launch_count() - before == 1
+        want = np.concatenate([oracle_gemv(x, qt) for qt in shards], axis=1) + bias.cpu().numpy()
+        assert got.shape == (m, total)
+        assert np.abs(got.cpu().numpy() - want).max() / np.abs(want).max() <= 1e-3
+
+
+@pytest.mark.parametrize("bits", [3, 8])
+def test_gemv_splits_activation_rows_when_their_fragments_do_not_fit(bits):
+    """8 rows x 14336 values of staged fragments exceed shared memory (at 8 bits even 4 do): the
+    rows are processed in halves, on the tensor-core path, with the same results."""
+    from dynquant_b200 import ops
+
+    rows, k, m = 64, 14336, 8
+    qt = make_quant(rows, k, 128, bits, torch.float16).to("cuda")
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+    want = oracle_gemv(x, qt)
+    acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, 128, k, out_dtype=torch.float32).cpu().numpy()
+    assert np.abs(acc - want).max() / np.abs(want).max() <= 1e-3
+    single = torch.cat([ops.gemv(x[i : i + 1], qt.packed, qt.scales, qt.offsets, bits, 128, k, out_dtype=torch.float32)
+                        for i in range(m)])
+    assert np.abs(acc - single.cpu().numpy()).max() / np.abs(want).max() <= 1e-5
