@@ -44,6 +44,126 @@ __device__ __forceinline__ void reduce_builder_group(float& sx, float& sb) {
   }
 }
 
+// Unit-per-lane staging, the fast path of both variants below when the activation is 16-bit,
+// 16-byte aligned and in_features is a multiple of 8.  A task is (activation row m, step j,
+// quad lane tt): the lane loads the 32 values whose fragments quad lane tt of the compute
+// warps will want -- four 128-bit L2-coherent loads straight from global memory, no bounce
+// through shared memory -- builds ALL of that unit's fragment registers with compile-time
+// slot positions, stores them, and reduces the two sums over the four lanes of its quad
+// (two shuffle levels, fixed order).  Tasks tid, tid + nthreads, ... ; consecutive tasks of
+// a quad are the four tt of one (m, j).  Steps are [s_first, s_first + nsteps) of the row and
+// are indexed from 0 in xb / xsum / xneg.  The caller synchronises afterwards.
+template <int BITS, bool XBF16, bool G64>
+__device__ __forceinline__ void stage_units(const GemvArgs& a, int s_first, int nsteps, int m_stride_u4, uint4* xb,
+                                            float* xsum, float* xneg, int tid, int nthreads,
+                                            const int* row_map) {
+  using Plan = MmaPlan<BITS>;
+  constexpr int NA = Plan::kARegs;
+  constexpr int QU = NA / 4;
+  constexpr float kMagicValue = XBF16 ? 128.0f : 0.0f;
+  constexpr bool HALVES = G64 && BITS != 3;  // groups = halves of the registers
+  constexpr bool QUADS = G64 && BITS == 3;   // groups = quad-lane pairs
+  const int total = a.m * nsteps * 4;
+  const int rounds = (total + nthreads - 1) / nthreads;
+  for (int r = 0; r < rounds; ++r) {
+    const int id = tid + r * nthreads;
+    const bool live = id < total;
+    const int tt = id & 3;
+    const int mj = live ? (id >> 2) : 0;
+    const int m = mj / nsteps;
+    const int j = mj - m * nsteps;
+    const int64_t src_row = row_map != nullptr ? row_map[m] : m;
+    const int k_step = (s_first + j) * 128;
+    // the unit as 16 words of two 16-bit values: value v sits in word v / 2
+    uint32_t w[16];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int k = k_step + step_position<G64, BITS>(tt, 8 * c);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (live && k < a.in_features) {
+        v = __ldcg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(a.x) + src_row * a.in_features + k));
+      }
+      w[4 * c] = v.x, w[4 * c + 1] = v.y, w[4 * c + 2] = v.z, w[4 * c + 3] = v.w;
+    }
+    auto value = [&](int v) -> float {
+      const uint32_t word = w[v >> 1];
+      if constexpr (XBF16) {
+        return __uint_as_float((v & 1) ? (word & 0xFFFF0000u) : (word << 16));
+      } else {
+        const __half2 h = *reinterpret_cast<const __half2*>(&word);
+        return (v & 1) ? __high2float(h) : __low2float(h);
+      }
+    };
+    float sx[2] = {0.0f, 0.0f}, sb[2] = {0.0f, 0.0f};  // per group of the step (one group: [0] only)
+    uint32_t regs[NA];
+#pragma unroll
+    for (int n = 0; n < NA; ++n) {
+      constexpr int kHalf = NA / 2;
+      const Slot sl = Plan::slot(n);
+      const int grp = HALVES ? (n >= kHalf) : 0;
+      const float flo = value(sl.v_lo), fhi = value(sl.v_hi);
+      // every value of the unit appears in exactly one slot, except at 8-bit where the high
+      // nibble's slot (e = 4) repeats it: count x once
+      if (BITS != 8 || sl.e_lo == 0) sx[grp] += flo + fhi;
+      const float slo = flo * __uint_as_float(static_cast<uint32_t>(127 + sl.e_lo) << 23);  // exact powers of two
+      const float shi = fhi * __uint_as_float(static_cast<uint32_t>(127 + sl.e_hi) << 23);
+      if constexpr (XBF16) {
+        sb[grp] += slo + shi;
+        regs[n] = __byte_perm(__float_as_uint(slo), __float_as_uint(shi), 0x7632);  // high halves: nothing to round
+      } else {
+        const __half2 h2 = __floats2half2_rn(slo, shi);
+        regs[n] = *reinterpret_cast<const uint32_t*>(&h2);
+      }
+    }
+    if (live) {
+#pragma unroll
+      for (int q = 0; q < QU; ++q) {
+        xb[m * m_stride_u4 + (j * QU + q) * 4 + tt] = make_uint4(regs[4 * q], regs[4 * q + 1], regs[4 * q + 2], regs[4 * q + 3]);
+      }
+    }
+    // sums over the quad (QUADS: over the lane pair -- the pairs are the two groups)
+#pragma unroll
+    for (int g2 = 0; g2 < (HALVES ? 2 : 1); ++g2) {
+      sx[g2] += __shfl_xor_sync(0xffffffffu, sx[g2], 1);
+      sb[g2] += __shfl_xor_sync(0xffffffffu, sb[g2], 1);
+      if (!QUADS) {
+        sx[g2] += __shfl_xor_sync(0xffffffffu, sx[g2], 2);
+        sb[g2] += __shfl_xor_sync(0xffffffffu, sb[g2], 2);
+      }
+    }
+    if (live) {
+      if (HALVES) {
+        if (tt == 0) {
+          xsum[(j * 2 + 0) * 8 + m] = sx[0], xneg[(j * 2 + 0) * 8 + m] = -kMagicValue * sb[0];
+          xsum[(j * 2 + 1) * 8 + m] = sx[1], xneg[(j * 2 + 1) * 8 + m] = -kMagicValue * sb[1];
+        }
+      } else if (QUADS) {
+        if ((tt & 1) == 0) {
+          xsum[(j * 2 + (tt >> 1)) * 8 + m] = sx[0], xneg[(j * 2 + (tt >> 1)) * 8 + m] = -kMagicValue * sb[0];
+        }
+      } else if (tt == 0) {
+        xsum[j * 8 + m] = sx[0], xneg[j * 8 + m] = -kMagicValue * sb[0];
+      }
+    }
+  }
+  // what lanes of absent activation rows read: a block of zero fragments, zero sums
+  for (int idx = tid; idx < NA; idx += nthreads) {
+    xb[a.m * m_stride_u4 + idx] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (a.m < 8) {
+    for (int idx = tid; idx < nsteps * (G64 ? 16 : 8); idx += nthreads) {
+      if ((idx & 7) >= a.m) {
+        xsum[idx] = 0.0f;
+        xneg[idx] = 0.0f;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ bool stage_units_ok(const GemvArgs& a) {
+  return a.x_dtype != DQ_F32 && (a.in_features & 7) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
+}
+
 // The activation is read with L2-coherent loads (ld.global.cg): it was written by the previous
 // kernel moments ago, is read once per CTA, and must not be served from a line this SM cached
 // before the previous kernel finished.
@@ -57,6 +177,10 @@ template <int BITS, bool XBF16, bool G64 = false>
 __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, int m_stride_u4, uint4* xb,
                                                  float* xsum, float* xneg, int tid, int nthreads,
                                                  const int* row_map = nullptr, unsigned short* raw = nullptr) {
+  if (stage_units_ok(a)) {  // (uniform over the CTA)
+    stage_units<BITS, XBF16, G64>(a, 0, steps, m_stride_u4, xb, xsum, xneg, tid, nthreads, row_map);
+    return;
+  }
   const bool use_raw = raw != nullptr && a.x_dtype != DQ_F32 && (a.in_features & 7) == 0 &&
                        (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
   if (use_raw) {
@@ -230,6 +354,11 @@ __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin,
   constexpr int kSecond = BITS == 3 ? 2 : LANES / 2;
   constexpr int PER = kWarp / LANES;  // steps built per round
   constexpr float kMagicValue = XBF16 ? 128.0f : 0.0f;
+  if (stage_units_ok(a)) {
+    stage_units<BITS, XBF16, G64>(a, s_begin, nsteps, m_stride_u4, xb, xsum, xneg, lane, kWarp, nullptr);
+    __syncwarp();
+    return;
+  }
   const int sub = lane / LANES;
   const int l = lane - sub * LANES;
   const int q = l >> 2, tt = l & 3;
