@@ -60,6 +60,7 @@ struct MoeArgs {
   int kw, rw;               // warps: rw row tiles x kw slices of the reduction axis
   int spw;                  // steps per slice, a multiple of CH
   int nb;                   // ring stages (of CH steps per warp)
+  int tokens;               // of the whole call
   int m_cap;                // activation rows staged at once (<= 8)
   int m_stride_u4;
   uint32_t magic;
@@ -549,12 +550,15 @@ int32_t launch_bank(const dq_weight& w, const dq_geometry& g, MoeArgs a, int slo
   a.num_groups = g.num_groups;
   a.in_features = g.in_features;
   a.steps = g.words_per_row / (4 * w.bits);
-  // 8 warps.  The reduction axis is sliced while a slice keeps at least eight steps (a warp
-  // then works through 16+ steps between two CTA-wide reductions); the other warps take
-  // neighbouring row tiles.
+  // 8 warps: kw slices of the reduction axis (each an even number of steps), the other
+  // warps take neighbouring row tiles.
   static const int force_kw = [] { const char* v = std::getenv("DQ_B200_MOE_KW"); return v ? std::atoi(v) : 0; }();
+  // Measured on B200 (Qwen3-30B-A3B shape): with one token a layer is a chain of latencies
+  // and four slices are fastest (19.2 us against 23.8 with two); up to 32 tokens two
+  // slices; beyond, whole rows per warp (no reduction at all: 130 us against 137 at 64).
+  const int want_kw = a.tokens <= 1 ? 4 : (a.tokens <= 32 ? 2 : 1);
   int kw = 1;
-  while (kw < kMoeWarps && a.steps % (kw * 2) == 0 && a.steps / (kw * 2) >= 8) kw *= 2;
+  while (kw < want_kw && a.steps % (kw * 2) == 0 && (a.steps / (kw * 2)) % 2 == 0) kw *= 2;
   if (force_kw > 0 && a.steps % force_kw == 0) kw = force_kw;
   a.kw = kw;
   a.rw = kMoeWarps / kw;
@@ -643,6 +647,7 @@ int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_
   // 32; the few that do take a second pass over their (L2-resident) rows.
   a.m_cap = static_cast<int>(std::min<int64_t>(tokens > 32 ? 8 : 4, tokens));
   a.topk = static_cast<int>(topk);
+  a.tokens = static_cast<int>(tokens);
   a.act_dtype = x_dtype;
   // gate_up: x -> h
   a.act = x;

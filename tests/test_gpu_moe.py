@@ -65,6 +65,38 @@ def test_moe_skips_experts_that_are_not_local():
     assert np.linalg.norm(got - want) / (np.linalg.norm(want) + 1e-30) <= 2e-3
 
 
+def test_moe_with_no_local_expert_at_all_writes_zeros():
+    """Every id outside [0, num_experts) -- an expert-parallel rank that owns none of the experts
+    a batch was routed to: the output is zero (and is written: it starts as garbage here)."""
+    from dynquant_b200 import ops
+    from dynquant_b200.workloads import qwen3_moe_layer
+
+    layer = qwen3_moe_layer("cuda", seed=5, num_experts=4, hidden=256, inter=128, topk=2)
+    ids = torch.full((3, 2), -1, dtype=torch.int32, device="cuda")
+    w = torch.full((3, 2), 0.5, device="cuda")
+    x = torch.randn(3, 256, device="cuda").to(torch.bfloat16)
+    scratch = torch.full((ops.moe_scratch_bytes(3, 2, 256, 128, 4, torch.bfloat16),), 0xAB, dtype=torch.uint8, device="cuda")
+    for _ in range(2):  # the second call reuses the scratch the first one left behind
+        got = ops.moe_gemv(x, ids, w, layer.gate_up, layer.down, num_experts=4, scratch=scratch)
+        assert got.shape == (3, 256) and not bool(got.float().abs().max() > 0)
+
+
+def test_moe_reuses_scratch_that_starts_as_garbage():
+    """The per-group counters of the fused combine live in caller scratch: never-initialised
+    memory, and memory left behind by a previous call of another size, must both work."""
+    from dynquant_b200 import ops
+    from dynquant_b200.workloads import qwen3_moe_layer, seeded_routing
+
+    layer = qwen3_moe_layer("cuda", seed=6, bits_gate_up=3, bits_down=4, num_experts=8, hidden=512, inter=256, topk=2)
+    scratch = torch.full((ops.moe_scratch_bytes(16, 2, 512, 256, 8, torch.bfloat16),), 0xCD, dtype=torch.uint8, device="cuda")
+    for tokens in (16, 3, 9):
+        ids, w = seeded_routing(tokens, 8, 2, seed=tokens)
+        x = torch.randn(tokens, 512, generator=torch.Generator().manual_seed(tokens)).to(torch.bfloat16).cuda()
+        with_scratch = ops.moe_gemv(x, ids.cuda(), w.cuda(), layer.gate_up, layer.down, num_experts=8, scratch=scratch)
+        fresh = ops.moe_gemv(x, ids.cuda(), w.cuda(), layer.gate_up, layer.down, num_experts=8)
+        assert torch.equal(with_scratch, fresh)
+
+
 def test_moe_many_tokens_on_one_expert():
     """More than eight tokens on one expert: the expert's rows are streamed once per 8 tokens."""
     from dynquant_b200 import ops
