@@ -19,6 +19,7 @@ from .format import (
     row_geometry,
     unpack_nbit,
 )
+from .checkpoint import PackedCheckpoint, load_packed_checkpoint, save_packed_checkpoint
 from .ops import dequantize, embedding_lookup, gemv_max_rows, quantized_matmul
 
 ABI_VERSION = 2
@@ -44,6 +45,7 @@ __all__ = [
     "BIT_OPTIONS",
     "DEFAULT_GROUP_SIZE",
     "PER_ROW_GROUP_SIZE",
+    "PackedCheckpoint",
     "PackingError",
     "QuantTensor",
     "RowGeometry",
@@ -51,9 +53,11 @@ __all__ = [
     "embedding_lookup",
     "gemv_max_rows",
     "is_available",
+    "load_packed_checkpoint",
     "ops",
     "pack_nbit",
     "quantized_matmul",
     "row_geometry",
+    "save_packed_checkpoint",
     "unpack_nbit",
 ]
