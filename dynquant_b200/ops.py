@@ -205,8 +205,8 @@ def gemv_row_chunks(
     out_dtype = out_dtype or x.dtype
     total = sum(qt.num_rows for qt in shards)
     out = torch.empty((x.shape[0], total), dtype=out_dtype, device=x.device)
-    for start in range(0, x.shape[0], step):
-        out[start : start + step] = gemv_shards(x[start : start + step], shards, bias, out_dtype=out_dtype)
+    for start in range(0, x.shape[0], step):  # each launch writes its rows of `out` in place
+        gemv_shards(x[start : start + step], shards, bias, out_dtype=out_dtype, out=out[start : start + step])
     return out
 
 
@@ -216,8 +216,11 @@ def gemv_shards(
     bias: torch.Tensor | None = None,
     *,
     out_dtype: torch.dtype | None = None,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
-    """All shards of a fused layer against one activation; outputs concatenated along the last dim."""
+    """All shards of a fused layer against one activation; outputs concatenated along the last dim.
+
+    ``out`` (optional): a contiguous ``[m, total_rows]`` tensor to write into instead of a new one."""
     lib = _lib.load()
     if not shards:
         raise RuntimeError("gemv_shards: need at least one shard")
@@ -234,7 +237,10 @@ def gemv_shards(
         if bias.shape != (total,) or bias.dtype != out_dtype or not bias.is_contiguous():
             raise RuntimeError(f"gemv_shards: bias must be a contiguous [{total}] tensor of {out_dtype}")
     m = x.shape[0]
-    out = torch.empty((m, total), dtype=out_dtype, device=x.device)
+    if out is None:
+        out = torch.empty((m, total), dtype=out_dtype, device=x.device)
+    elif out.shape != (m, total) or out.dtype != out_dtype or not out.is_contiguous() or out.device != x.device:
+        raise RuntimeError(f"gemv_shards: out must be a contiguous [{m}, {total}] {out_dtype} tensor on {x.device}")
     with torch.cuda.device(x.device):
         _lib.check(
             lib.dq_gemv_shards(

@@ -126,9 +126,15 @@ class DynQuantLinearMethod:
     ) -> None:
         del output_size
         if input_size_per_partition != input_size:
-            raise NotImplementedError(
-                "row-parallel (input-split) placement is not built; column-shard the layer instead"
-            )
+            # row-parallel placement: this rank holds a slice of the input axis, legal only on
+            # group boundaries (reference serving_common/geometry.py:481-551); the framework's
+            # RowParallelLinear all-reduces the partial sums apply() returns
+            for spec in self.shards:
+                if spec.group_size <= 0 or input_size_per_partition % spec.group_size:
+                    raise ValueError(
+                        f"shard {spec.name}: an input slice of {input_size_per_partition} values is not a whole "
+                        f"number of groups of {spec.group_size}; split the input axis on group boundaries"
+                    )
         specs = match_shards_to_partitions(self.shards, output_partition_sizes)
         geometry = FusedPackedGeometry(specs, input_size_per_partition)
         device = extra_weight_attrs.get("device")

@@ -1,5 +1,5 @@
-"""Multi-GPU placement of the two paths that shard: column-sharded dense GEMV and
-expert-parallel MoE.  One process per GPU, ``torch.distributed`` for the exchange (NCCL on
+"""Multi-GPU placement of the paths that shard: column-sharded (and input-sharded) dense GEMV
+and expert-parallel MoE.  One process per GPU, ``torch.distributed`` for the exchange (NCCL on
 GPUs; the same code runs over gloo on CPU in the tests, with the oracle as the compute).
 
 The reference issues no collective itself -- tensor parallelism there is weight placement
@@ -36,6 +36,74 @@ def expert_shard(bank: QuantTensor, rows_per_expert: int, num_experts: int, rank
         raise ValueError(f"{num_experts} experts do not split evenly over {world} ranks")
     per = num_experts // world
     return bank.rows(rank * per * rows_per_expert, (rank + 1) * per * rows_per_expert)
+
+
+def input_shard(qt: QuantTensor, rank: int, world: int) -> QuantTensor:
+    """The slice ``[rank*K/world, (rank+1)*K/world)`` of the INPUT axis of a packed tensor.
+
+    Legal only on group boundaries (reference ``row_parallel_split``,
+    ``integration/serving_common/geometry.py:481-551``): a group's words, scale and offset move
+    together, so the groups must divide evenly over the ranks and ``in_features`` must be a
+    whole number of groups; per-row tensors (one group spanning the row) are refused as there
+    (``:513-520``).  The result is a copy: its rows are shorter, so no view of the parent can
+    have the parent's layout.
+    """
+    from dataclasses import replace
+
+    if qt.is_per_row:
+        raise ValueError("a per-row-grouped tensor has one group per row and cannot be split along its input axis")
+    g = qt.geometry
+    if g.num_groups % world or qt.in_features != g.num_groups * qt.group_size:
+        raise ValueError(
+            f"{g.num_groups} groups of {qt.group_size} over in_features={qt.in_features} do not split on group "
+            f"boundaries over {world} ranks"
+        )
+    per = g.num_groups // world
+    words = slice(rank * per * g.words_per_group, (rank + 1) * per * g.words_per_group)
+    groups = slice(rank * per, (rank + 1) * per)
+    k = per * qt.group_size
+    return replace(
+        qt,
+        packed=qt.packed[:, words].contiguous(),
+        scales=qt.scales[:, groups].contiguous(),
+        offsets=None if qt.offsets is None else qt.offsets[:, groups].contiguous(),
+        in_features=k,
+        logical_shape=(qt.num_rows, k),
+    )
+
+
+class InputShardedLinear:
+    """``y = x @ W.T`` with ``W``'s input axis split over the ranks (the o_proj / down_proj
+    placement of tensor parallelism): every rank holds ``x[:, its slice]``, computes fp32
+    partial sums over its slice and the partials are all-reduced.  The sum over ranks is in
+    NCCL's order, so unlike the column-sharded layer the result may differ from the
+    single-device one in the last fp32 bit."""
+
+    def __init__(self, local: QuantTensor, *, bias: torch.Tensor | None = None, group=None,
+                 compute: Callable | None = None) -> None:
+        self.local = local
+        self.bias = bias
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if compute is None:
+            from . import ops
+
+            def compute(x, qt):
+                if x.shape[0] > ops.gemv_max_rows():
+                    return ops.gemv_row_chunks(x.contiguous(), [qt], out_dtype=torch.float32)
+                return ops.gemv_shards(x.contiguous(), [qt], out_dtype=torch.float32)
+
+        self.compute = compute
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        partial = self.compute(x_local, self.local).to(torch.float32).contiguous()  # [M, N], this rank's slice of K
+        dist.all_reduce(partial, group=self.group)
+        if self.bias is not None:
+            partial = partial + self.bias.to(torch.float32)
+        return partial.to(x_local.dtype)
+
+    __call__ = forward
 
 
 class ColumnShardedLinear:

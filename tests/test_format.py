@@ -89,3 +89,19 @@ def test_constant_group_is_exact():
     qt = QuantTensor.from_dense(w, bits=2, group_size=128)
     assert float(qt.scales.abs().max()) == 0.0 and float(qt.offsets[0, 0]) == 0.375
     assert int(qt.packed.abs().max()) == 0
+
+
+def test_linear_method_accepts_an_input_slice_on_group_boundaries_only():
+    """Row-parallel placement: the layer's buffers are sized for this rank's slice of the input
+    axis; a slice that cuts a group is refused (reference serving_common/geometry.py:481-551)."""
+    import pytest
+    import torch
+
+    from dynquant_b200.plugin import DynQuantLinearMethod, ShardSpec
+
+    method = DynQuantLinearMethod(None, [ShardSpec("down_proj", 3, 128, 64)])
+    layer = torch.nn.Module()
+    method.create_weights(layer, 256, [64], 512, 64, torch.float16)  # half of a 512-wide input
+    assert layer.qweight.numel() == 64 * (256 * 3 // 32) and layer.scales.numel() == 64 * 2
+    with pytest.raises(ValueError, match="whole number of groups"):
+        method.create_weights(torch.nn.Module(), 192, [64], 384, 64, torch.float16)

@@ -59,7 +59,8 @@ def _worker(rank: int, world: int, port: int, results):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from dynquant_b200.format import QuantTensor
-        from dynquant_b200.sharded import ColumnShardedLinear, ExpertParallelMoE, column_shard, expert_shard
+        from dynquant_b200.sharded import (ColumnShardedLinear, ExpertParallelMoE, InputShardedLinear, column_shard,
+                                           expert_shard, input_shard)
         from dynquant_b200.workloads import random_quant_tensor, seeded_routing
 
         gen = torch.Generator().manual_seed(5)
@@ -70,6 +71,20 @@ def _worker(rank: int, world: int, port: int, results):
         layer = ColumnShardedLinear(column_shard(qt, rank, world), compute=_oracle_matmul)
         got = layer(x)
         ok_dense = bool(torch.equal(got, full))
+        # ---- input-sharded dense (K split on group boundaries, partial sums all-reduced) ----
+        errs_in = {}
+        for bits in (2, 3, 4, 8):
+            wide = random_quant_tensor(48, 512, bits, generator=gen)
+            xw = torch.randn(3, 512, generator=gen).to(torch.bfloat16)
+            bias = torch.randn(48, generator=gen)
+            want_in = _oracle_matmul(xw, wide) + bias
+            part = input_shard(wide, rank, world)
+            k_local = 512 // world
+            layer_in = InputShardedLinear(part, bias=bias, compute=_oracle_matmul)
+            y_in = layer_in(xw[:, rank * k_local : (rank + 1) * k_local].contiguous()).float()
+            ref_in = want_in.to(torch.bfloat16).float()
+            errs_in[bits] = float((y_in - ref_in).abs().max() / ref_in.abs().max())
+            assert part.in_features == k_local and part.packed.shape == (48, k_local * bits // 32)
         # ---- expert parallel ----
         experts, hidden, inter, topk, t_local = 4, 256, 128, 2, 3
         gate_up = random_quant_tensor(experts * 2 * inter, hidden, 4, generator=gen)
@@ -86,7 +101,7 @@ def _worker(rank: int, world: int, port: int, results):
             y = ep(x_all[mine], ids_all[mine], w_all[mine], mode=mode).float()
             ref = want[mine].to(torch.bfloat16).float()
             errs[mode] = float((y - ref).abs().max() / (ref.abs().max() + 1e-30))
-        results[rank] = (ok_dense, errs)
+        results[rank] = (ok_dense, errs, errs_in)
     finally:
         dist.destroy_process_group()
 
@@ -99,8 +114,10 @@ def test_two_rank_sharding_reassembles_to_the_single_device_result():
     mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
     assert len(results) == world
     for rank in range(world):
-        ok_dense, errs = results[rank]
+        ok_dense, errs, errs_in = results[rank]
         assert ok_dense, f"rank {rank}: gathered column shards differ from the unsharded result"
+        for bits, err in errs_in.items():
+            assert err <= 1e-2, f"rank {rank} input-sharded {bits}-bit: {err}"  # one bf16 rounding of the output
         for mode, err in errs.items():
             assert err <= 1e-2, f"rank {rank} {mode}: {err}"  # one bf16 rounding of the output
 
@@ -116,3 +133,9 @@ def test_shard_helpers_reject_uneven_splits():
         expert_shard(qt, 2, 5, 0, 2)
     part = column_shard(qt, 1, 2)
     assert part.num_rows == 5 and part.row_offset == 5
+    from dynquant_b200.sharded import input_shard
+
+    with pytest.raises(ValueError, match="group boundaries"):
+        input_shard(random_quant_tensor(4, 384, 4), 0, 2)  # three groups over two ranks
+    with pytest.raises(ValueError, match="per-row"):
+        input_shard(random_quant_tensor(4, 256, 4, group_size=-1), 0, 2)
