@@ -497,14 +497,14 @@ bool stream_ok(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps) {
     return v != nullptr && v[0] != '\0' && v[0] != '0';
   }();
   if (off) return false;
-  // Measured on B200 (profiles/): with 16-byte block copies the cp.async ring is as fast or
-  // faster than the register ring of gemv_mma_kernel<FAST> at 3, 4 and 8 bits (it fits three
-  // CTAs per SM); at 2 bits the two are within noise and the register ring is kept.
-  static const bool all_widths = [] {
-    const char* v = std::getenv("DQ_B200_STREAM_ALL");
+  // Measured on B200 (profiles/): with 16-byte block copies and running source pointers the
+  // cp.async ring is as fast or faster than the register ring of gemv_mma_kernel<FAST> at
+  // every width (it fits three CTAs per SM).
+  static const bool ring_at_2bit = [] {  // measurement switch: the register ring instead, at 2 bits
+    const char* v = std::getenv("DQ_B200_RING_2BIT");
     return v != nullptr && v[0] == '1';
   }();
-  if (BITS == 2 && !all_widths) return false;
+  if (BITS == 2 && ring_at_2bit) return false;
   if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) {
     return false;  // whole steps are copied in 16-byte pieces
   }

@@ -156,10 +156,33 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
   pdl_launch_dependents();
 
   // ---- prefetch cursor: walks (tile, block) ahead of the compute loop ----
+  // Integer instructions issue at half rate on this GPU and the decode needs that pipe, so
+  // the cursor is kept as running pointers: everything that depends on the lane or the tile
+  // is resolved once per tile, a block costs a pointer bump per source row and its copies
+  // use immediate offsets.
+  constexpr int PIECES = 2 * C::UNIT;        // 16-byte pieces of one (step, row half) block
+  constexpr int PER_ROW = C::UNIT / 4;       // pieces per row
+  constexpr int NSRC = (PIECES + kWarp - 1) / kWarp;  // pieces of a block this lane copies
+  constexpr int STEP_BYTES = STEP_WORDS * 4;
   int pf_tile = first_tile;
   int pf_blk = 0;
-  const unsigned short* pf_meta = nullptr;  // this lane's array (scales or offsets) at its row, group 0
+  const unsigned char* pf_src[2][NSRC];  // [row half][piece]: this lane's source at the block's first step
+  const unsigned short* pf_meta = nullptr;  // this lane's array (scales or offsets) at its row, at the block's first group
+  bool pf_lane[NSRC];
+#pragma unroll
+  for (int i = 0; i < NSRC; ++i) pf_lane[i] = (PIECES % kWarp == 0) || (i * kWarp + lane < PIECES);
   auto pf_point = [&]() {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int i = 0; i < NSRC; ++i) {
+        const int piece = i * kWarp + lane;
+        const int pg = piece / PER_ROW;
+        const int part = piece - pg * PER_ROW;
+        const int row = min(pf_tile * kTileRows + h * 8 + pg, a.rows - 1);
+        pf_src[h][i] = reinterpret_cast<const unsigned char*>(a.packed + static_cast<int64_t>(row) * a.words_per_row + part * 4);
+      }
+    }
     const int ra = min(pf_tile * kTileRows + g, a.rows - 1);
     const int rb = min(pf_tile * kTileRows + g + 8, a.rows - 1);
     const unsigned short* arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
@@ -167,29 +190,44 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
   };
   if (pf_tile < p.tiles) pf_point();
   const bool meta_lane = has_off || (t & 1) == 0;
-  int pf_count = 0;  // blocks issued so far (ring slot = count % NB)
+  // ring slot of the block being requested, as byte offsets into the two rings
+  uint32_t pf_w = ring_w_s + lane * 16, pf_m = ring_m_s;
+  const uint32_t ring_w_end = ring_w_s + lane * 16 + NB * (C::BLOCK_BYTES * kThreads);
+  const uint32_t ring_m_end = ring_m_s + NB * (C::META_BYTES * kThreads);
   auto prefetch_block = [&]() {
     if (pf_tile < p.tiles) {
-      const int slot = pf_count % NB;
-      const uint32_t dst = ring_w_s + slot * (C::BLOCK_BYTES * kThreads);
 #pragma unroll
       for (int j = 0; j < P; ++j) {
-        const int word0 = (pf_blk * P + j) * STEP_WORDS;
-        copy_block<BITS>(dst + (j * 2 + 0) * (C::UNIT * kThreads), a.packed, a.words_per_row, pf_tile * kTileRows,
-                         a.rows - 1, word0, lane);
-        copy_block<BITS>(dst + (j * 2 + 1) * (C::UNIT * kThreads), a.packed, a.words_per_row,
-                         pf_tile * kTileRows + 8, a.rows - 1, word0, lane);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < NSRC; ++i) {
+            if (pf_lane[i]) {
+              cp_async_n<16>(pf_w + (j * 2 + h) * (C::UNIT * kThreads) + i * (kWarp * 16), pf_src[h][i] + j * STEP_BYTES);
+            }
+          }
+        }
       }
-      if (meta_lane) {
-        cp_async_n<C::META_BYTES>(ring_m_s + slot * (C::META_BYTES * kThreads), pf_meta + pf_blk * P);
-      }
+      if (meta_lane) cp_async_n<C::META_BYTES>(pf_m, pf_meta);
       if (++pf_blk == nblocks) {
         pf_blk = 0;
         pf_tile += tile_stride;
         if (pf_tile < p.tiles) pf_point();
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < NSRC; ++i) pf_src[h][i] += P * STEP_BYTES;
+        }
+        pf_meta += P;
       }
     }
-    ++pf_count;
+    pf_w += C::BLOCK_BYTES * kThreads;
+    pf_m += C::META_BYTES * kThreads;
+    if (pf_w == ring_w_end) {
+      pf_w -= NB * (C::BLOCK_BYTES * kThreads);
+      pf_m = ring_m_end - NB * (C::META_BYTES * kThreads);
+    }
     cp_async_commit();  // an empty group keeps the wait arithmetic uniform
   };
 #pragma unroll
@@ -205,18 +243,26 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
   // ---- compute loop: one block of P steps per iteration ----
   const bool b_live = g < a.m;
   const uint4* xb_lane = b_live ? xb + g * p.m_stride_u4 + t : xb + a.m * p.m_stride_u4;
+  const int xb_blk_u4 = b_live ? QU * 4 * P : 0;  // uint4 per block of steps (0: the zero block, re-read)
   const int xb_step_u4 = b_live ? QU * 4 : 0;
+  const float* xsum_t = xsum + 2 * t;
+  const float* xneg_t = xneg + 2 * t;
   float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  int count = 0;
+  // ring slot being consumed
+  const unsigned char* wslot = ring_w_mine;
+  const unsigned char* mslot = ring_m_quad;
+  const unsigned char* const wslot_end = ring_w_mine + NB * (C::BLOCK_BYTES * kThreads);
   for (int tile = first_tile; tile < p.tiles; tile += tile_stride) {
-    for (int blk = 0; blk < nblocks; ++blk, ++count) {
+    const uint4* bblk = xb_lane;
+    const float* xs_blk = xsum_t;
+    const float* xn_blk = xneg_t;
+    for (int blk = 0; blk < nblocks; ++blk) {
       __syncwarp();      // every lane is done with the slot about to be refilled
-      prefetch_block();  // refills slot (count + NB - 1) % NB
+      prefetch_block();  // refills the slot consumed one iteration ago
       cp_async_wait<NB - 1>();
       __syncwarp();      // the quad's metadata copies are visible to each other
-      const int slot = count % NB;
-      const unsigned char* wsrc = ring_w_mine + slot * (C::BLOCK_BYTES * kThreads);
-      const unsigned char* msrc = ring_m_quad + slot * (C::META_BYTES * kThreads);
+      const unsigned char* wsrc = wslot;
+      const unsigned char* msrc = mslot;
       uint32_t mc[4][P / 2];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -231,7 +277,6 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
       }
 #pragma unroll
       for (int j = 0; j < P; ++j) {
-        const int s = blk * P + j;
         uint32_t wa[BITS], wb[BITS];
         read_unit<BITS>(wsrc + (j * 2 + 0) * (C::UNIT * kThreads), wa);
         read_unit<BITS>(wsrc + (j * 2 + 1) * (C::UNIT * kThreads), wb);
@@ -240,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
         decode_unit<BITS>(wb, magic, ab);
         unbias_fragments<XBF16, NA>(aa);
         unbias_fragments<XBF16, NA>(ab);
-        const uint4* bsrc = xb_lane + s * xb_step_u4;
+        const uint4* bsrc = bblk + j * xb_step_u4;
         float d[4];
 #pragma unroll
         for (int q = 0; q < QU; ++q) {
@@ -261,8 +306,8 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
             return (j & 1) ? __high2float(h) : __low2float(h);
           }
         };
-        const float2 xs2 = *reinterpret_cast<const float2*>(xsum + s * 8 + 2 * t);
-        const float2 xn2 = *reinterpret_cast<const float2*>(xneg + s * 8 + 2 * t);
+        const float2 xs2 = *reinterpret_cast<const float2*>(xs_blk + j * 8);
+        const float2 xn2 = *reinterpret_cast<const float2*>(xn_blk + j * 8);
         const float sc_a = meta_f32(0), sc_b = meta_f32(2);
         acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
         acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
@@ -275,6 +320,15 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
           acc[2] = fmaf(of_b, xs2.x, acc[2]);
           acc[3] = fmaf(of_b, xs2.y, acc[3]);
         }
+      }
+      bblk += xb_blk_u4;
+      xs_blk += P * 8;
+      xn_blk += P * 8;
+      wslot += C::BLOCK_BYTES * kThreads;
+      mslot += C::META_BYTES * kThreads;
+      if (wslot == wslot_end) {
+        wslot = ring_w_mine;
+        mslot = ring_m_quad;
       }
     }
     const int row_a = tile * kTileRows + g, row_b = row_a + 8;
