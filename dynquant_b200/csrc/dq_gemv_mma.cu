@@ -618,7 +618,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
   // axis whose grid is resident at once.  Otherwise CTAs persist over several items with a
   // ring of a few stages, sliced as finely as leaves four steps between two reductions.
   constexpr size_t kSmemPerSm = 228 * 1024, kCtaReserve = 1024;
-  constexpr int kCtasByRegisters = 3;  // __launch_bounds__(256, 3)
+  constexpr int kCtasByRegisters = 2;  // __launch_bounds__(256, 2)
   struct Shape {
     int kw = 0, ch = 0, nb = 0, per_sm = 0, ipc = 0;
     size_t smem = 0;

@@ -178,37 +178,83 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   pdl_launch_dependents();
 
   // ---- prefetch cursor: walks (item, chunk) ahead of the compute loop ----
-  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * UNIT;
-  const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * R::META;
+  // Kept as running pointers (integer instructions issue at half rate and the decode needs
+  // that pipe): what depends on the lane or the row tile is resolved once per item, a stage
+  // costs one pointer bump per source row and its copies use immediate offsets.
+  constexpr int PIECES = 2 * UNIT;       // 16-byte pieces of one (step, row half) block
+  constexpr int PER_ROW = UNIT / 4;      // pieces per row
+  constexpr int NSRC = (PIECES + kWarp - 1) / kWarp;  // pieces of a block this lane copies
+  constexpr int STEP_BYTES = STEP_WORDS * 4;
   const bool meta_lane = has_off || (t & 1) == 0;
   const unsigned short* meta_arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
-  int pf_item = cta, pf_chunk = 0, pf_slot = 0;
+  bool pf_lane[NSRC];
+#pragma unroll
+  for (int i = 0; i < NSRC; ++i) pf_lane[i] = (PIECES % kWarp == 0) || (i * kWarp + lane < PIECES);
+  const unsigned char* pf_src[2][NSRC];  // [row half][piece]: this lane's source at the stage's first step
+  const unsigned short* pf_meta = nullptr;
+  int pf_item = cta, pf_chunk = 0;
+  bool pf_live = false;
+  auto pf_point = [&]() {  // start of an item
+    const int tile = pf_item * rw + rwi;
+    pf_live = pf_item < J.items && tile < J.tiles;
+    if (pf_live) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int i = 0; i < NSRC; ++i) {
+          const int piece = i * kWarp + lane;
+          const int pg = piece / PER_ROW;
+          const int part = piece - pg * PER_ROW;
+          const int row = min(tile * 16 + h * 8 + pg, a.rows - 1);
+          pf_src[h][i] = reinterpret_cast<const unsigned char*>(a.packed + static_cast<int64_t>(row) * a.words_per_row +
+                                                                 part * 4) + s_begin * STEP_BYTES;
+        }
+      }
+      const int row = min(tile * 16 + g + ((t & 2) ? 8 : 0), a.rows - 1);
+      pf_meta = meta_arr + static_cast<int64_t>(row) * a.num_groups + s_begin * GPS;
+    }
+  };
+  pf_point();
+  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * UNIT + lane * 16;
+  const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * R::META;
+  uint32_t pf_w = ring_w_s, pf_m = ring_m_s;
+  const uint32_t pf_w_end = ring_w_s + nb * R::STAGE_W;
   auto prefetch_stage = [&]() {
     if (pf_item < J.items) {
-      const int tile = pf_item * rw + rwi;
-      if (tile < J.tiles) {
-        const uint32_t dst = ring_w_s + pf_slot * R::STAGE_W;
+      if (pf_live) {
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
-          const int word0 = (s_begin + pf_chunk * CH + j) * STEP_WORDS;
-          stream::copy_block<BITS>(dst + (j * 2 + 0) * (UNIT * kThreads), a.packed, a.words_per_row, tile * 16,
-                                   a.rows - 1, word0, lane);
-          stream::copy_block<BITS>(dst + (j * 2 + 1) * (UNIT * kThreads), a.packed, a.words_per_row, tile * 16 + 8,
-                                   a.rows - 1, word0, lane);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int i = 0; i < NSRC; ++i) {
+              if (pf_lane[i]) {
+                stream::cp_async_n<16>(pf_w + (j * 2 + h) * (UNIT * kThreads) + i * (kWarp * 16), pf_src[h][i] + j * STEP_BYTES);
+              }
+            }
+          }
         }
-        if (meta_lane) {
-          const int row = min(tile * 16 + g + ((t & 2) ? 8 : 0), a.rows - 1);
-          stream::cp_async_n<R::META>(ring_m_s + pf_slot * R::STAGE_M,
-                                      meta_arr + static_cast<int64_t>(row) * a.num_groups +
-                                          (s_begin + pf_chunk * CH) * GPS);
-        }
+        if (meta_lane) stream::cp_async_n<R::META>(pf_m, pf_meta);
       }
       if (++pf_chunk == nchunks) {
         pf_chunk = 0;
         pf_item += J.cta_count;
+        pf_point();
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < NSRC; ++i) pf_src[h][i] += CH * STEP_BYTES;
+        }
+        pf_meta += CH * GPS;
       }
     }
-    if (++pf_slot == nb) pf_slot = 0;
+    pf_w += R::STAGE_W;
+    pf_m += R::STAGE_M;
+    if (pf_w == pf_w_end) {
+      pf_w = ring_w_s;
+      pf_m = ring_m_s;
+    }
     stream::cp_async_commit();  // an empty group keeps the wait arithmetic uniform
   };
   for (int i = 0; i < nb; ++i) prefetch_stage();  // the whole ring is in flight before the wait
@@ -225,7 +271,7 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   const bool mbf = L.meta_bf16 != 0;
 
   // ---- the part that depends on the previous kernel: the activation ----
-  int slot = 0, parity = 0;
+  int parity = 0;
   pdl_wait_prior_grid();
   if (wide) {
     const bool raw_ok = a.x_dtype != DQ_F32;
@@ -236,16 +282,23 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
     stage_warp_slice<BITS, XBF16, G64>(a, s_begin, spw, m_stride_u4, raw, xb, xsum, xneg, lane);
   }
 
+  const unsigned char* wslot = ring_w_mine;  // ring slot being consumed
+  const unsigned char* mslot = ring_m_quad;
+  const unsigned char* const wslot_end = ring_w_mine + nb * R::STAGE_W;
+  const int xb_chunk_u4 = xb_step_u4 * CH;
   for (int item = cta; item < J.items; item += J.cta_count, parity ^= 1) {
     const int tile = item * rw + rwi;
     const bool live = tile < J.tiles;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint4* bchunk = xb_lane;
+    const float* xs_chunk = xsum_w;
+    const float* xn_chunk = xneg_w;
     for (int chunk = 0; chunk < nchunks; ++chunk) {
       wait_pending(nb - 1);  // groups are consumed in issue order: all but the nb-1 youngest are done
       __syncwarp();          // copies of other lanes (units, the quad's metadata) are visible
       if (live) {
-        const unsigned char* wsrc = ring_w_mine + slot * R::STAGE_W;
-        const unsigned char* msrc = ring_m_quad + slot * R::STAGE_M;
+        const unsigned char* wsrc = wslot;
+        const unsigned char* msrc = mslot;
         constexpr int MW = R::META / 4;  // 32-bit words of one metadata array of this stage
         uint32_t mc[4][MW];
 #pragma unroll
@@ -264,7 +317,6 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
         }
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
-          const int sl = chunk * CH + j;
           uint32_t wa[BITS], wb[BITS];
           read_lane_words<BITS, HALVES>(wsrc + (j * 2 + 0) * (UNIT * kThreads), wa);
           read_lane_words<BITS, HALVES>(wsrc + (j * 2 + 1) * (UNIT * kThreads), wb);
@@ -273,7 +325,7 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
           decode_unit<BITS>(wb, magic, ab);
           unbias_fragments<XBF16, NA>(aa);
           unbias_fragments<XBF16, NA>(ab);
-          const uint4* bsrc = xb_lane + sl * xb_step_u4;
+          const uint4* bsrc = bchunk + j * xb_step_u4;
           // two accumulators: the first half of the registers (d) and the second (e).  They
           // halve the chain of dependent mma; with 64-value groups they ARE the two groups.
           float d[4], e[4];
@@ -325,8 +377,8 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
           if constexpr (!G64) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) d[i] += e[i];
-            const float2 xs2 = *reinterpret_cast<const float2*>(xsum_w + sl * 8);
-            const float2 xn2 = *reinterpret_cast<const float2*>(xneg_w + sl * 8);
+            const float2 xs2 = *reinterpret_cast<const float2*>(xs_chunk + j * 8);
+            const float2 xn2 = *reinterpret_cast<const float2*>(xn_chunk + j * 8);
             const float sc_a = meta_f32(0, j), sc_b = meta_f32(2, j);
             acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
             acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
@@ -343,8 +395,8 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               const float* dd = half == 0 ? d : e;
-              const float2 xs2 = *reinterpret_cast<const float2*>(xsum_w + (sl * 2 + half) * 8);
-              const float2 xn2 = *reinterpret_cast<const float2*>(xneg_w + (sl * 2 + half) * 8);
+              const float2 xs2 = *reinterpret_cast<const float2*>(xs_chunk + (j * 2 + half) * 8);
+              const float2 xn2 = *reinterpret_cast<const float2*>(xn_chunk + (j * 2 + half) * 8);
               const float sc_a = meta_f32(0, 2 * j + half), sc_b = meta_f32(2, 2 * j + half);
               acc[0] = fmaf(sc_a, dd[0] + xn2.x, acc[0]);
               acc[1] = fmaf(sc_a, dd[1] + xn2.y, acc[1]);
@@ -361,7 +413,15 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
           }
         }
       }
-      if (++slot == nb) slot = 0;
+      bchunk += xb_chunk_u4;
+      xs_chunk += CH * 8 * GPS;
+      xn_chunk += CH * 8 * GPS;
+      wslot += R::STAGE_W;
+      mslot += R::STAGE_M;
+      if (wslot == wslot_end) {
+        wslot = ring_w_mine;
+        mslot = ring_m_quad;
+      }
       __syncwarp();      // every lane is done with the slot just consumed:
       prefetch_stage();  // refill it
     }
@@ -401,7 +461,7 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
 }
 
 template <bool XBF16, int CH, bool G64>
-__global__ void __launch_bounds__(kThreads, 3) gemv_mma_tile_kernel(const __grid_constant__ Launch L) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_mma_tile_kernel(const __grid_constant__ Launch L) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int j = 0;
 #pragma unroll
