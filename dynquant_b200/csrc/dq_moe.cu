@@ -192,32 +192,66 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_grouped_kernel(const __gri
   const int ntc = (count + a.m_cap - 1) / a.m_cap;  // token chunks
   const int64_t expert_row0 = static_cast<int64_t>(e) * a.rows * H;
   const bool has_off = a.offsets != nullptr;
-  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * UNIT;
+  // The cursor is kept as running pointers (integer instructions issue at half rate and the
+  // decode needs that pipe): what depends on the lane, the row tile or the half is resolved
+  // once per (item, half), a stage costs a pointer bump per source row, copies use immediates.
+  constexpr int PIECES = 2 * UNIT;       // 16-byte pieces of one (step, row half) block
+  constexpr int PER_ROW = UNIT / 4;      // pieces per row
+  constexpr int NSRC = (PIECES + kWarp - 1) / kWarp;
+  constexpr int STEP_BYTES = STEP_WORDS * 4;
+  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * UNIT + lane * 16;
   const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * (CH * 2);
   const bool meta_lane = has_off || (t & 1) == 0;
   const unsigned short* meta_arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
-  int pf_tc = 0, pf_item = blockIdx.x, pf_half = 0, pf_chunk = 0, pf_slot = 0;
+  bool pf_lane[NSRC];
+#pragma unroll
+  for (int i = 0; i < NSRC; ++i) pf_lane[i] = (PIECES % kWarp == 0) || (i * kWarp + lane < PIECES);
+  const unsigned char* pf_src[2][NSRC];
+  const unsigned short* pf_meta = nullptr;
+  int pf_tc = 0, pf_item = blockIdx.x, pf_half = 0, pf_chunk = 0;
+  bool pf_live = false;
+  auto pf_point = [&]() {  // start of an (item, half)
+    const int tile = pf_item * rw + rwi;
+    pf_live = pf_tc < ntc && pf_item < items && tile < tiles;
+    if (pf_live) {
+      const int row0 = static_cast<int>(expert_row0) + pf_half * a.rows + tile * 16;
+      const int last = static_cast<int>(expert_row0) + (pf_half + 1) * a.rows - 1;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int i = 0; i < NSRC; ++i) {
+          const int piece = i * kWarp + lane;
+          const int pg = piece / PER_ROW;
+          const int part = piece - pg * PER_ROW;
+          const int row = min(row0 + h * 8 + pg, last);
+          pf_src[h][i] = reinterpret_cast<const unsigned char*>(a.packed + static_cast<int64_t>(row) * a.words_per_row +
+                                                                 part * 4) + s_begin * STEP_BYTES;
+        }
+      }
+      const int row = min(row0 + g + ((t & 2) ? 8 : 0), last);
+      pf_meta = meta_arr + static_cast<int64_t>(row) * a.num_groups + s_begin;
+    }
+  };
+  pf_point();
+  uint32_t pf_w = ring_w_s, pf_m = ring_m_s;
+  const uint32_t pf_w_end = ring_w_s + nb * STAGE_W;
   auto prefetch_stage = [&]() {
     if (pf_tc < ntc && pf_item < items) {
-      const int tile = pf_item * rw + rwi;
-      if (tile < tiles) {
-        const int row0 = static_cast<int>(expert_row0) + pf_half * a.rows + tile * 16;
-        const int last = static_cast<int>(expert_row0) + (pf_half + 1) * a.rows - 1;
-        const uint32_t dst = ring_w_s + pf_slot * STAGE_W;
+      if (pf_live) {
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
-          const int word0 = (s_begin + pf_chunk * CH + j) * STEP_WORDS;
-          stream::copy_block<BITS>(dst + (j * 2 + 0) * (UNIT * kMoeThreads), a.packed, a.words_per_row, row0, last,
-                                   word0, lane);
-          stream::copy_block<BITS>(dst + (j * 2 + 1) * (UNIT * kMoeThreads), a.packed, a.words_per_row, row0 + 8, last,
-                                   word0, lane);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int i = 0; i < NSRC; ++i) {
+              if (pf_lane[i]) {
+                stream::cp_async_n<16>(pf_w + (j * 2 + h) * (UNIT * kMoeThreads) + i * (kWarp * 16), pf_src[h][i] + j * STEP_BYTES);
+              }
+            }
+          }
         }
         if constexpr (CH >= 2) {  // (a single step's metadata is 2 bytes: read in the loop instead)
-          if (meta_lane) {
-            const int row = min(row0 + g + ((t & 2) ? 8 : 0), last);
-            stream::cp_async_n<CH * 2>(ring_m_s + pf_slot * STAGE_M,
-                                       meta_arr + static_cast<int64_t>(row) * a.num_groups + s_begin + pf_chunk * CH);
-          }
+          if (meta_lane) stream::cp_async_n<CH * 2>(pf_m, pf_meta);
         }
       }
       if (++pf_chunk == nchunks) {
@@ -230,9 +264,22 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_grouped_kernel(const __gri
             ++pf_tc;
           }
         }
+        pf_point();
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < NSRC; ++i) pf_src[h][i] += CH * STEP_BYTES;
+        }
+        pf_meta += CH;
       }
     }
-    if (++pf_slot == nb) pf_slot = 0;
+    pf_w += STAGE_W;
+    pf_m += STAGE_M;
+    if (pf_w == pf_w_end) {
+      pf_w = ring_w_s;
+      pf_m = ring_m_s;
+    }
     stream::cp_async_commit();  // an empty group keeps the wait arithmetic uniform
   };
   for (int i = 0; i < nb; ++i) prefetch_stage();
@@ -272,7 +319,10 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_grouped_kernel(const __gri
   const float* xsum_w = xsum + s_begin * 8 + 2 * t;
   const float* xneg_w = xneg + s_begin * 8 + 2 * t;
 
-  int slot_r = 0, parity = 0;
+  int parity = 0;
+  const unsigned char* wslot = ring_w_mine;  // ring slot being consumed
+  const unsigned char* mslot = ring_m_quad;
+  const unsigned char* const wslot_end = ring_w_mine + nb * STAGE_W;
   for (int tc = 0; tc < ntc; ++tc) {
     const int c0 = tc * a.m_cap;
     const int m = min(a.m_cap, count - c0);
@@ -301,8 +351,8 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_grouped_kernel(const __gri
           moe_wait_pending(nb - 1);  // groups complete in issue order: all but the nb-1 youngest are done
           __syncwarp();              // copies of other lanes (units, the quad's metadata) are visible
           if (live) {
-            const unsigned char* wsrc = ring_w_mine + slot_r * STAGE_W;
-            const unsigned char* msrc = ring_m_quad + slot_r * STAGE_M;
+            const unsigned char* wsrc = wslot;
+            const unsigned char* msrc = mslot;
             uint32_t mc[4][CH >= 2 ? CH / 2 : 1];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -368,7 +418,12 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_grouped_kernel(const __gri
               }
             }
           }
-          if (++slot_r == nb) slot_r = 0;
+          wslot += STAGE_W;
+          mslot += STAGE_M;
+          if (wslot == wslot_end) {
+            wslot = ring_w_mine;
+            mslot = ring_m_quad;
+          }
           __syncwarp();      // every lane is done with the slot just consumed:
           prefetch_stage();  // refill it
         }
