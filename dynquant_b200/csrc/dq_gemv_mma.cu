@@ -32,6 +32,7 @@
 // zero there (reference docs/format-spec.md:205-214).
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "dq_gemv.cuh"
 #include "dq_gemv_mma_tile.cuh"
@@ -618,7 +619,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
   // axis whose grid is resident at once.  Otherwise CTAs persist over several items with a
   // ring of a few stages, sliced as finely as leaves four steps between two reductions.
   constexpr size_t kSmemPerSm = 228 * 1024, kCtaReserve = 1024;
-  constexpr int kCtasByRegisters = 2;  // __launch_bounds__(256, 2)
+  int ctas_by_registers = 3;  // which build of the kernel: see gemv_mma_tile_kernel
   struct Shape {
     int kw = 0, ch = 0, nb = 0, per_sm = 0, ipc = 0;
     size_t smem = 0;
@@ -663,7 +664,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     sh.ch = ch;
     sh.nb = nb;
     sh.smem = smem;
-    sh.per_sm = std::min<int>(kCtasByRegisters, static_cast<int>(kSmemPerSm / (smem + kCtaReserve)));
+    sh.per_sm = std::min<int>(ctas_by_registers, static_cast<int>(kSmemPerSm / (smem + kCtaReserve)));
     if (force_per_sm > 0) sh.per_sm = std::min(sh.per_sm, force_per_sm);
     const int64_t cap = static_cast<int64_t>(sh.per_sm) * dev.sm_count;
     sh.ipc = static_cast<int>(ceil_div(items_at(kw), cap));
@@ -679,17 +680,30 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     if (sh.kw == 0 && spw % 2 == 0 && meta_aligned(2)) sh = shape_with(kw, one_shot, 2);
     return sh;
   };
-  Shape pick;
-  for (int kw = tilek::kWarps; kw >= 1 && pick.kw == 0; kw /= 2) {
-    if (force_kw > 0 && kw != force_kw) continue;
-    const Shape sh = shape_at(kw, true);
-    if (sh.kw != 0 && sh.per_sm >= 1 && sh.ipc == 1) pick = sh;
-  }
-  for (int kw = tilek::kWarps; kw >= 1 && pick.kw == 0; kw /= 2) {
-    if (force_kw > 0 && kw != force_kw) continue;
-    if (force_kw == 0 && kw > 1 && (steps % kw != 0 || steps / kw < 4)) continue;
-    const Shape sh = shape_at(kw, false);
-    if (sh.kw != 0 && sh.per_sm >= 1) pick = sh;
+  auto choose = [&]() {
+    Shape best;
+    for (int kw = tilek::kWarps; kw >= 1 && best.kw == 0; kw /= 2) {
+      if (force_kw > 0 && kw != force_kw) continue;
+      const Shape sh = shape_at(kw, true);
+      if (sh.kw != 0 && sh.per_sm >= 1 && sh.ipc == 1) best = sh;
+    }
+    for (int kw = tilek::kWarps; kw >= 1 && best.kw == 0; kw /= 2) {
+      if (force_kw > 0 && kw != force_kw) continue;
+      if (force_kw == 0 && kw > 1 && (steps % kw != 0 || steps / kw < 4)) continue;
+      const Shape sh = shape_at(kw, false);
+      if (sh.kw != 0 && sh.per_sm >= 1) best = sh;
+    }
+    return best;
+  };
+  // The three-CTA build only where its third CTA per SM buys a finer one-wave slicing.
+  static const int force_ctas = env_int("DQ_B200_TILE_CTAS");
+  ctas_by_registers = 3;
+  Shape pick = choose();
+  const bool needs_three = pick.kw != 0 && pick.ipc == 1 && pick.nb == (steps / pick.kw) / pick.ch &&
+                           items_at(pick.kw) > 2LL * dev.sm_count;
+  if ((!needs_three && force_ctas != 3) || force_ctas == 2) {
+    ctas_by_registers = 2;
+    pick = choose();
   }
   if (pick.kw == 0) return DQ_OK;
   const int kw = pick.kw, rw = tilek::kWarps / kw, spw = steps / kw, ch = pick.ch;
@@ -745,12 +759,17 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     return DQ_OK;
   };
   const bool xbf = a0.x_dtype == DQ_BF16;
-  if (g64) {
-    if (ch == 4) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 4, true>) : run(tilek::gemv_mma_tile_kernel<false, 4, true>);
-    return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2, true>) : run(tilek::gemv_mma_tile_kernel<false, 2, true>);
-  }
-  if (ch == 4) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 4, false>) : run(tilek::gemv_mma_tile_kernel<false, 4, false>);
-  return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2, false>) : run(tilek::gemv_mma_tile_kernel<false, 2, false>);
+  auto dispatch = [&](auto ctas) -> int32_t {
+    constexpr int N = decltype(ctas)::value;
+    if (g64) {
+      if (ch == 4) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 4, true, N>) : run(tilek::gemv_mma_tile_kernel<false, 4, true, N>);
+      return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2, true, N>) : run(tilek::gemv_mma_tile_kernel<false, 2, true, N>);
+    }
+    if (ch == 4) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 4, false, N>) : run(tilek::gemv_mma_tile_kernel<false, 4, false, N>);
+    return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2, false, N>) : run(tilek::gemv_mma_tile_kernel<false, 2, false, N>);
+  };
+  if (ctas_by_registers == 3) return dispatch(std::integral_constant<int, 3>{});
+  return dispatch(std::integral_constant<int, 2>{});
 }
 
 }  // namespace

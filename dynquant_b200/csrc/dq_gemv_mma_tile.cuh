@@ -460,8 +460,12 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   stream::cp_async_wait<0>();
 }
 
-template <bool XBF16, int CH, bool G64>
-__global__ void __launch_bounds__(kThreads, 2) gemv_mma_tile_kernel(const __grid_constant__ Launch L) {
+// CTAS: resident CTAs per SM the kernel is compiled for.  Two (128 registers, nothing spilled)
+// is the faster build; three (80 registers, a few spills) exists for launches whose single
+// wave needs the third CTA per SM -- the alternative there is a coarser slicing of the
+// reduction axis, which costs more than the spills.
+template <bool XBF16, int CH, bool G64, int CTAS>
+__global__ void __launch_bounds__(kThreads, CTAS) gemv_mma_tile_kernel(const __grid_constant__ Launch L) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int j = 0;
 #pragma unroll
