@@ -14,9 +14,13 @@
 // fmaf as well; with fp32 scales it follows the torch definition.  An absent
 // offsets tensor means "no add", not "+0".
 //
-// One thread decodes one block (16/32/8/4 values at 2/3/4/8-bit) per step of a
-// grid-stride loop, so a warp reads 32 consecutive blocks of words and writes
-// 32 * values_per_block consecutive outputs.
+// Two kernels.  dequant_octet_kernel is the one nearly every tensor takes (in_features and
+// the group size multiples of 8): a thread produces 8 consecutive values -- one 16-byte
+// store for a 16-bit output, so a warp writes 512 contiguous bytes per store instruction --
+// from the 8 * BITS bits at bit 8 * BITS * octet of its row (the packed row is one
+// contiguous LSB-first bit string: groups are whole numbers of 32-value blocks).  Rows run
+// over blockIdx.y and octets over blockIdx.x, so no thread divides anything.  dequant_kernel
+// is the general one: one thread per block of 16/32/8/4 values at 2/3/4/8-bit, any tail.
 #include <algorithm>
 
 #include "dq_decode.cuh"
@@ -36,6 +40,67 @@ struct DequantArgs {
   int words_per_row, num_groups, words_per_group, group_values, in_features;
   int blocks_per_group, blocks_per_row;
 };
+
+// 8 consecutive values of one row per thread.  `group_shift` >= 0: the group size is 2^shift.
+template <int BITS>
+__global__ void __launch_bounds__(kDequantThreads) dequant_octet_kernel(const DequantArgs a, int octets_per_row,
+                                                                        int group_shift) {
+  const bool has_offsets = a.offsets != nullptr;
+  constexpr uint32_t kMask = (1u << BITS) - 1u;
+  for (int row = blockIdx.y; row < a.rows; row += gridDim.y) {
+    const uint32_t* src = a.packed + static_cast<int64_t>(row) * a.words_per_row;
+    for (int o = blockIdx.x * kDequantThreads + threadIdx.x; o < octets_per_row; o += gridDim.x * kDequantThreads) {
+      const int bit = o * 8 * BITS;
+      const int word = bit >> 5;
+      // the octet's 8 * BITS bits (64 at 8-bit: two whole words)
+      uint32_t lo, hi = 0u;
+      if constexpr (BITS == 8) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(src) + o);
+        lo = v.x, hi = v.y;
+      } else if constexpr (BITS == 4) {
+        lo = __ldg(src + word);
+      } else if constexpr (BITS == 2) {
+        lo = __ldg(src + word) >> (bit & 31);
+      } else {
+        const uint32_t w0 = __ldg(src + word);
+        const uint32_t w1 = (bit & 31) > 8 ? __ldg(src + word + 1) : 0u;  // 24 bits from bit (bit & 31)
+        lo = __funnelshift_r(w0, w1, bit & 31);
+      }
+      const int value0 = o * 8;
+      const int g = group_shift >= 0 ? (value0 >> group_shift) : value0 / a.group_values;
+      const int64_t meta = static_cast<int64_t>(row) * a.num_groups + g;
+      const float scale = load_f32(a.scales, meta, a.meta_dtype);
+      const float offset = has_offsets ? load_f32(a.offsets, meta, a.meta_dtype) : 0.0f;
+      float vals[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint32_t q;
+        if constexpr (BITS == 8) {
+          q = ((i < 4 ? lo : hi) >> (8 * (i & 3))) & 0xFFu;
+        } else {
+          q = (lo >> (BITS * i)) & kMask;
+        }
+        float v = __fmul_rn(static_cast<float>(q), scale);
+        if (has_offsets) v = __fadd_rn(v, offset);
+        vals[i] = v;
+      }
+      const int64_t out_base = static_cast<int64_t>(row) * a.in_features + value0;
+      if (a.out_dtype == DQ_F32) {
+        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + out_base);
+        dst[0] = make_float4(vals[0], vals[1], vals[2], vals[3]);
+        dst[1] = make_float4(vals[4], vals[5], vals[6], vals[7]);
+      } else {
+        uint32_t p16[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          p16[j] = round_to_16(vals[2 * j], a.out_dtype) | (round_to_16(vals[2 * j + 1], a.out_dtype) << 16);
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.out) + out_base) =
+            make_uint4(p16[0], p16[1], p16[2], p16[3]);
+      }
+    }
+  }
+}
 
 template <int BITS>
 __global__ void __launch_bounds__(kDequantThreads) dequant_kernel(const DequantArgs a) {
@@ -166,10 +231,43 @@ extern "C" int32_t dq_dequant(const dq_weight* w, void* out, int32_t out_dtype, 
 
   const dq::DeviceInfo* dev = dq::device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
+  auto s = static_cast<cudaStream_t>(stream);
+  // The octet kernel: whole octets per row and per group, 16-byte aligned output rows, and
+  // (8-bit) 8-byte aligned packed rows.
+  const size_t out_elem = static_cast<size_t>(dq::dtype_size(out_dtype));
+  const bool octets = a.in_features % 8 == 0 && a.group_values % 8 == 0 &&
+                      reinterpret_cast<uintptr_t>(out) % 16 == 0 && (a.in_features * out_elem) % 16 == 0 &&
+                      (w->bits != 8 || (reinterpret_cast<uintptr_t>(a.packed) % 8 == 0 && a.words_per_row % 2 == 0));
+  if (octets) {
+    const int octets_per_row = a.in_features / 8;
+    int shift = -1;
+    if ((a.group_values & (a.group_values - 1)) == 0) {
+      shift = 0;
+      while ((1 << shift) < a.group_values) ++shift;
+    }
+    const int gx = static_cast<int>(std::min<int64_t>(dq::ceil_div(octets_per_row, dq::kDequantThreads), 64));
+    const int gy = static_cast<int>(std::min<int64_t>(a.rows, std::max<int64_t>(1, (static_cast<int64_t>(dev->sm_count) * 64) / gx)));
+    const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+    switch (w->bits) {
+      case 2:
+        dq::dequant_octet_kernel<2><<<grid, dq::kDequantThreads, 0, s>>>(a, octets_per_row, shift);
+        break;
+      case 3:
+        dq::dequant_octet_kernel<3><<<grid, dq::kDequantThreads, 0, s>>>(a, octets_per_row, shift);
+        break;
+      case 4:
+        dq::dequant_octet_kernel<4><<<grid, dq::kDequantThreads, 0, s>>>(a, octets_per_row, shift);
+        break;
+      default:
+        dq::dequant_octet_kernel<8><<<grid, dq::kDequantThreads, 0, s>>>(a, octets_per_row, shift);
+        break;
+    }
+    DQ_CHECK_LAUNCH("dequant");
+    return DQ_OK;
+  }
   const int64_t total = static_cast<int64_t>(a.rows) * a.blocks_per_row;
   const int64_t want = dq::ceil_div(total, dq::kDequantThreads);
   const int grid = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(dev->sm_count) * 32));
-  auto s = static_cast<cudaStream_t>(stream);
   switch (w->bits) {
     case 2:
       dq::dequant_kernel<2><<<grid, dq::kDequantThreads, 0, s>>>(a);

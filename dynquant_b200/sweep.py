@@ -10,6 +10,8 @@ through the dequant + dense path beyond, as in the reference.
     python -m dynquant_b200.sweep                      # the full config-5 grid
     python -m dynquant_b200.sweep --shape 131072x2048 --bits 8 --m 1 --launches 4 --ring 1
                                                        # one point, few launches (for ncu)
+    python -m dynquant_b200.sweep --op dequant --shape 32768x4096 --group 128
+                                                       # the dequant operator instead (write-bound)
 
 Prints one JSON object per point.
 """
@@ -79,8 +81,36 @@ def run_point(rows: int, k: int, bits: int, group: int, m: int, *, launches: int
     }
 
 
+def run_dequant_point(rows: int, k: int, bits: int, group: int, *, launches: int, device="cuda") -> dict:
+    """Dense reconstruction of one packed tensor: bytes = packed + metadata read, dense written."""
+    qt = random_quant_tensor(rows, k, bits, group_size=group, device=device)
+    out = ops.dequantize(qt)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(launches):
+            out = ops.dequantize(qt)
+    graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(stop) / 1e3 / launches
+    nbytes = qt.nbytes + out.numel() * out.element_size()
+    peak, kind = hbm_peak_gbs()
+    return {
+        "op": "dequant", "rows": rows, "in_features": k, "bits": bits, "group_size": group,
+        "us_per_call": round(seconds * 1e6, 2), "gbps": round(nbytes / seconds / 1e9, 1),
+        "pct_of_hbm_peak": round(100 * nbytes / seconds / 1e9 / peak, 1), "peak": f"{peak} GB/s ({kind})",
+        "bytes": nbytes, "launches": launches,
+    }
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="gemv", choices=["gemv", "dequant"])
     ap.add_argument("--shape", action="append", help="ROWSxK; repeatable (default: the config-5 shapes)")
     ap.add_argument("--bits", default="2,3,4,8")
     ap.add_argument("--group", default="64,128")
@@ -95,6 +125,9 @@ def main() -> None:
         rows, k = (int(v) for v in shape.lower().split("x"))
         for bits in (int(b) for b in ns.bits.split(",")):
             for group in (int(g) for g in ns.group.split(",")):
+                if ns.op == "dequant":
+                    print(json.dumps(run_dequant_point(rows, k, bits, group, launches=ns.launches)), flush=True)
+                    continue
                 for m in (int(v) for v in ns.m.split(",")):
                     print(json.dumps(run_point(rows, k, bits, group, m, launches=ns.launches, ring=ns.ring)), flush=True)
 
