@@ -40,7 +40,7 @@ METRIC = "packed_gemv_hbm_gbps_m1"
 UNIT = "GB/s"
 WORKLOAD = "qwen2b-stack-3.25bit-m1 (BASELINE config 2: 28 layers + 8-bit lm_head, 197 GEMVs/step)"
 FALLBACK_HBM_GBS = 6650.0
-TRAFFIC_PER_STEP = 1_158_139_360  # dram bytes read + written by one step; see profiles/stack_qwen2b_m1_launch_list.md
+TRAFFIC_PER_STEP = 1_165_303_296  # dram bytes read + written by one step; see profiles/stack_qwen2b_m1_launch_list.md
 
 
 def measured_peak() -> tuple[float, str]:

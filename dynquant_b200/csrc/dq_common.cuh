@@ -140,6 +140,17 @@ __device__ __forceinline__ uint32_t round_to_16(float v, int dtype) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// Two values rounded (nearest-even) to the tagged 16-bit dtype and packed, `lo` in the low half:
+// one conversion instruction for the pair.
+__device__ __forceinline__ uint32_t round_pair_to_16(float lo, float hi, int dtype) {
+  if (dtype == DQ_F16) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&b);
+}
+
 // Streaming 128-bit load: weights are read exactly once, so keep them out of L1.
 __device__ __forceinline__ uint4 ldg_stream_128(const void* p) {
   uint4 v;

@@ -80,7 +80,10 @@ __global__ void __launch_bounds__(kDequantThreads) dequant_octet_kernel(const De
         } else {
           q = (lo >> (BITS * i)) & kMask;
         }
-        float v = __fmul_rn(static_cast<float>(q), scale);
+        // float(q) without the conversion unit (a quarter-rate pipe): 2^23 + q is exactly
+        // representable, so OR-ing q into the mantissa of 2^23 and subtracting 2^23 is exact
+        const float qf = __uint_as_float(0x4B000000u | q) - 8388608.0f;
+        float v = __fmul_rn(qf, scale);
         if (has_offsets) v = __fadd_rn(v, offset);
         vals[i] = v;
       }
@@ -93,7 +96,7 @@ __global__ void __launch_bounds__(kDequantThreads) dequant_octet_kernel(const De
         uint32_t p16[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          p16[j] = round_to_16(vals[2 * j], a.out_dtype) | (round_to_16(vals[2 * j + 1], a.out_dtype) << 16);
+          p16[j] = round_pair_to_16(vals[2 * j], vals[2 * j + 1], a.out_dtype);
         }
         *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.out) + out_base) =
             make_uint4(p16[0], p16[1], p16[2], p16[3]);
