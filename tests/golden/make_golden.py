@@ -2,7 +2,7 @@
 
 Run in a container where the reference checkout is mounted::
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [--reference /root/reference]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [--reference <checkout>]
 
 It imports the reference's own Python package (``dynquant.quant.pack``,
 ``dynquant.quant.tensor``, ``dynquant.runtime.ops`` on the torch backend) and writes
