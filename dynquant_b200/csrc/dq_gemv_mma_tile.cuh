@@ -272,14 +272,24 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
 
   // ---- the part that depends on the previous kernel: the activation ----
   int parity = 0;
+  // the zero fragments and zero sums of absent activation rows do not depend on the
+  // activation: written now, they are off the chain that starts when the wait releases
+  const bool prefilled = stage_units_ok(a);
+  if (prefilled) {
+    if (wide) {
+      stage_zero_fill<BITS, G64>(a.m, L.steps, m_stride_u4, xb, xsum, xneg, tid, kThreads);
+    } else {
+      stage_zero_fill<BITS, G64>(a.m, spw, m_stride_u4, xb, xsum, xneg, lane, kWarp);
+    }
+  }
   pdl_wait_prior_grid();
   if (wide) {
     const bool raw_ok = a.x_dtype != DQ_F32;
     stage_activation<BITS, XBF16, G64>(a, L.steps, m_stride_u4, xb, xsum, xneg, tid, kThreads, nullptr,
-                                       raw_ok ? raw : nullptr);
+                                       raw_ok ? raw : nullptr, prefilled);
     __syncthreads();
   } else {
-    stage_warp_slice<BITS, XBF16, G64>(a, s_begin, spw, m_stride_u4, raw, xb, xsum, xneg, lane);
+    stage_warp_slice<BITS, XBF16, G64>(a, s_begin, spw, m_stride_u4, raw, xb, xsum, xneg, lane, prefilled);
   }
 
   const unsigned char* wslot = ring_w_mine;  // ring slot being consumed

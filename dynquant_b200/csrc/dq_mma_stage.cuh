@@ -44,6 +44,26 @@ __device__ __forceinline__ void reduce_builder_group(float& sx, float& sb) {
   }
 }
 
+// What lanes of absent activation rows read: a block of zero fragments after the last staged
+// row, and zero sums in the columns of the rows that do not exist.  Nothing here depends on
+// the activation, so a kernel may do it before its dependency wait (`prefilled` below).
+template <int BITS, bool G64>
+__device__ __forceinline__ void stage_zero_fill(int m, int nsteps, int m_stride_u4, uint4* xb, float* xsum,
+                                                float* xneg, int tid, int nthreads) {
+  constexpr int NA = MmaPlan<BITS>::kARegs;
+  for (int idx = tid; idx < NA; idx += nthreads) {
+    xb[m * m_stride_u4 + idx] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (m < 8) {
+    for (int idx = tid; idx < nsteps * (G64 ? 16 : 8); idx += nthreads) {
+      if ((idx & 7) >= m) {
+        xsum[idx] = 0.0f;
+        xneg[idx] = 0.0f;
+      }
+    }
+  }
+}
+
 // Unit-per-lane staging, the fast path of both variants below when the activation is 16-bit,
 // 16-byte aligned and in_features is a multiple of 8.  A task is (activation row m, step j,
 // quad lane tt): the lane loads the 32 values whose fragments quad lane tt of the compute
@@ -56,7 +76,7 @@ __device__ __forceinline__ void reduce_builder_group(float& sx, float& sb) {
 template <int BITS, bool XBF16, bool G64>
 __device__ __forceinline__ void stage_units(const GemvArgs& a, int s_first, int nsteps, int m_stride_u4, uint4* xb,
                                             float* xsum, float* xneg, int tid, int nthreads,
-                                            const int* row_map) {
+                                            const int* row_map, bool prefilled = false) {
   using Plan = MmaPlan<BITS>;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
@@ -146,18 +166,7 @@ __device__ __forceinline__ void stage_units(const GemvArgs& a, int s_first, int 
       }
     }
   }
-  // what lanes of absent activation rows read: a block of zero fragments, zero sums
-  for (int idx = tid; idx < NA; idx += nthreads) {
-    xb[a.m * m_stride_u4 + idx] = make_uint4(0u, 0u, 0u, 0u);
-  }
-  if (a.m < 8) {
-    for (int idx = tid; idx < nsteps * (G64 ? 16 : 8); idx += nthreads) {
-      if ((idx & 7) >= a.m) {
-        xsum[idx] = 0.0f;
-        xneg[idx] = 0.0f;
-      }
-    }
-  }
+  if (!prefilled) stage_zero_fill<BITS, G64>(a.m, nsteps, m_stride_u4, xb, xsum, xneg, tid, nthreads);
 }
 
 __device__ __forceinline__ bool stage_units_ok(const GemvArgs& a) {
@@ -176,9 +185,10 @@ __device__ __forceinline__ bool stage_units_ok(const GemvArgs& a) {
 template <int BITS, bool XBF16, bool G64 = false>
 __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, int m_stride_u4, uint4* xb,
                                                  float* xsum, float* xneg, int tid, int nthreads,
-                                                 const int* row_map = nullptr, unsigned short* raw = nullptr) {
+                                                 const int* row_map = nullptr, unsigned short* raw = nullptr,
+                                                 bool prefilled = false) {
   if (stage_units_ok(a)) {  // (uniform over the CTA)
-    stage_units<BITS, XBF16, G64>(a, 0, steps, m_stride_u4, xb, xsum, xneg, tid, nthreads, row_map);
+    stage_units<BITS, XBF16, G64>(a, 0, steps, m_stride_u4, xb, xsum, xneg, tid, nthreads, row_map, prefilled);
     return;
   }
   const bool use_raw = raw != nullptr && a.x_dtype != DQ_F32 && (a.in_features & 7) == 0 &&
@@ -345,7 +355,7 @@ fill_zeros:
 template <int BITS, bool XBF16, bool G64 = false>
 __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin, int nsteps, int m_stride_u4,
                                                  unsigned short* raw, uint4* xb, float* xsum, float* xneg,
-                                                 int lane) {
+                                                 int lane, bool prefilled = false) {
   using Plan = MmaPlan<BITS>;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
@@ -355,7 +365,7 @@ __device__ __forceinline__ void stage_warp_slice(const GemvArgs& a, int s_begin,
   constexpr int PER = kWarp / LANES;  // steps built per round
   constexpr float kMagicValue = XBF16 ? 128.0f : 0.0f;
   if (stage_units_ok(a)) {
-    stage_units<BITS, XBF16, G64>(a, s_begin, nsteps, m_stride_u4, xb, xsum, xneg, lane, kWarp, nullptr);
+    stage_units<BITS, XBF16, G64>(a, s_begin, nsteps, m_stride_u4, xb, xsum, xneg, lane, kWarp, nullptr, prefilled);
     __syncwarp();
     return;
   }
