@@ -300,6 +300,14 @@ def run_ours(args) -> None:
         return
 
     peak, peak_kind = measured_peak()
+    # The second denominator: what a read-only stream and a copy reach on this GPU, now, through
+    # this library's own launch path (the reference quotes against the same pair, measured in
+    # its own session: commands/bench.py:95-120).  Outside the timed regions.
+    probe = None
+    if not args.no_probe:
+        from dynquant_b200 import ops as _ops
+
+        probe = _ops.achievable_bandwidth(nbytes=4 << 30, iters=10, device=device)
     launches = launches_per_step * args.steps
     avg_launch_s = seconds / launches
     bytes_per_launch = step_bytes / launches_per_step
@@ -330,6 +338,10 @@ def run_ours(args) -> None:
             "kernel": "gemv_mma_tile_kernel (decoder-block layers, fused shards) / gemv_mma_stream_kernel "
                       f"(lm_head); per-launch average over the {launches_per_step} launches of a step",
             "bytes_per_launch": round(bytes_per_launch), "avg_launch_us": round(avg_launch_s * 1e6, 3),
+            "probe": (None if probe is None else {
+                "read_gbs": round(probe["read_gbs"], 1), "copy_gbs": round(probe["copy_gbs"], 1),
+                "bytes": probe["bytes"], "frac_of_read": round(achieved / probe["read_gbs"], 4),
+                "kernels": "dq_probe_read / dq_probe_copy, 10 launches each, CUDA events"}),
         },
         "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
@@ -352,6 +364,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=28, help="reduce the stack (profiling only)")
     ap.add_argument("--no-graph", action="store_true", help="launch with dq_gemv_sequence instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-probe", action="store_true", help="skip the read/copy bandwidth probe")
     ap.add_argument("--graph-mode", choices=["dataflow", "chain", "independent"], default="dataflow",
                     help="edges of the captured step: a decoder layer's data dependencies (default), "
                          "a strict chain, or none")

@@ -83,6 +83,8 @@ SIGNATURES = {
     "dq_last_error": (ctypes.c_char_p, []),
     "dq_resolve_geometry": (_I32, [ctypes.c_char_p, _WP, ctypes.POINTER(Geometry)]),
     "dq_dequant": (_I32, [_WP, _P, _I32, _P]),
+    "dq_probe_read": (_I32, [_P, _I64, _P, _P]),
+    "dq_probe_copy": (_I32, [_P, _P, _I64, _P]),
     "dq_gemv": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P]),
     "dq_gemv_shards": (_I32, [_P, _I32, _I64, _WP, _I32, _P, _P, _I64, _I32, _P]),
     "dq_gemv_sequence": (_I32, [ctypes.POINTER(GemvJob), _I32, _P]),

@@ -346,6 +346,70 @@ def launch_count() -> int:
     return int(_lib.load().dq_launch_count())
 
 
+def probe_read(buf: torch.Tensor, sink: torch.Tensor) -> None:
+    """One read-only pass over ``buf`` (``dq_probe_read``); XOR of its 32-bit words into ``sink[0]``."""
+    _require_cuda(buf, "probe_read: buffer")
+    if not buf.is_contiguous() or sink.dtype != torch.int64 or sink.device != buf.device:
+        raise RuntimeError("probe_read: expected a contiguous buffer and an int64 sink on the same device")
+    nbytes = buf.numel() * buf.element_size()
+    with torch.cuda.device(buf.device):
+        _lib.check(_lib.load().dq_probe_read(buf.data_ptr(), nbytes, sink.data_ptr(), _stream(buf.device)))
+
+
+def probe_copy(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """``dst <- src`` through the library's streaming copy kernel (``dq_probe_copy``)."""
+    _require_cuda(src, "probe_copy: source")
+    _require_cuda(dst, "probe_copy: destination")
+    nbytes = src.numel() * src.element_size()
+    if not (src.is_contiguous() and dst.is_contiguous()) or dst.numel() * dst.element_size() != nbytes:
+        raise RuntimeError("probe_copy: expected two contiguous buffers of the same size in bytes")
+    if dst.device != src.device:
+        raise RuntimeError("probe_copy: both buffers must be on one device")
+    with torch.cuda.device(src.device):
+        _lib.check(_lib.load().dq_probe_copy(dst.data_ptr(), src.data_ptr(), nbytes, _stream(src.device)))
+
+
+def achievable_bandwidth(nbytes: int = 4 << 30, iters: int = 10, device: torch.device | None = None) -> dict:
+    """Read and copy bandwidth this GPU delivers right now, in GB/s, timed with CUDA events.
+
+    The reference measures the same pair with ``src.sum()`` and ``dst.copy_(src)`` on 1 GiB
+    (commands/bench.py:95-120); the default here is 4 GiB read and 2 GiB copied to 2 GiB so
+    that a 126 MB L2 serves a negligible part.  The buffers are released before returning.
+    """
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    nbytes = max(16, nbytes // 32 * 32)
+    with torch.cuda.device(device):
+        buf = torch.empty(nbytes // 8, dtype=torch.int64, device=device)
+        buf.random_()
+        sink = torch.zeros(1, dtype=torch.int64, device=device)
+        half = buf.numel() // 2
+        src, dst = buf[:half], buf[half:]
+
+        def timed(fn) -> float:
+            for _ in range(2):
+                fn()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(device)
+            start.record()
+            for _ in range(iters):
+                fn()
+            stop.record()
+            torch.cuda.synchronize(device)
+            return start.elapsed_time(stop) * 1e-3 / iters
+
+        read_s = timed(lambda: probe_read(buf, sink))
+        copy_s = timed(lambda: probe_copy(dst, src))
+        result = {
+            "read_gbs": nbytes / read_s / 1e9,
+            "copy_gbs": 2 * (nbytes // 2) / copy_s / 1e9,
+            "bytes": nbytes,
+            "iters": iters,
+        }
+        del buf, src, dst, sink
+        torch.cuda.empty_cache()
+    return result
+
+
 # --------------------------------------------------------------------------
 # runtime dispatch (reference: runtime/ops.py)
 # --------------------------------------------------------------------------

@@ -112,6 +112,18 @@ DQ_API int32_t dq_resolve_geometry(const char* op, const dq_weight* w, dq_geomet
  * in fp32, one rounding to out_dtype. */
 DQ_API int32_t dq_dequant(const dq_weight* w, void* out, int32_t out_dtype, void* stream);
 
+/* ---- achievable-bandwidth probes (reference: achievable_bandwidth,
+ *      packages/dynquant-core/src/dynquant/commands/bench.py:95-120, which times
+ *      a large read and a large copy in the session it benchmarks in) ----------
+ * dq_probe_read streams `bytes` (a multiple of 16, 16-byte aligned buffer) from
+ * HBM once and XORs every 32-bit word read into *sink (device memory, 8-byte
+ * aligned; the low 32 bits carry the XOR of all words, so a caller can check
+ * that the whole buffer was read).  dq_probe_copy copies `bytes` between two
+ * non-overlapping 16-byte aligned device buffers.  Both enqueue one kernel on
+ * `stream`; the caller times them with events. */
+DQ_API int32_t dq_probe_read(const void* src, int64_t bytes, uint64_t* sink, void* stream);
+DQ_API int32_t dq_probe_copy(void* dst, const void* src, int64_t bytes, void* stream);
+
 /* ---- gemv (reference: gemv_cuda, csrc/gemv/gemv.cu:695-756) ----------------
  * x [m, in_features] in x_dtype, contiguous, m <= DQ_GEMV_MAX_ROWS.
  * out [m, rows] in out_dtype (the reference writes x's dtype; DQ_F32 gives the

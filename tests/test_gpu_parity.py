@@ -271,3 +271,29 @@ def test_gemv_splits_activation_rows_when_their_fragments_do_not_fit(bits):
     single = torch.cat([ops.gemv(x[i : i + 1], qt.packed, qt.scales, qt.offsets, bits, 128, k, out_dtype=torch.float32)
                         for i in range(m)])
     assert np.abs(acc - single.cpu().numpy()).max() / np.abs(want).max() <= 1e-5
+
+
+def test_bandwidth_probes_touch_every_byte():
+    """``dq_probe_read`` XORs every 32-bit word of the buffer; ``dq_probe_copy`` is a copy.
+
+    They are the denominators of a bandwidth fraction (the reference measures the same pair
+    with ``sum()`` and ``copy_``, commands/bench.py:95-120): a probe that skipped a byte would
+    overstate the achievable bandwidth.
+    """
+    from dynquant_b200 import ops
+
+    gen = torch.Generator().manual_seed(17)
+    for words in (4, 1024 + 4, 3 * 1_000_003 * 4 + 8):  # tails shorter than one unrolled round, ragged sizes
+        host = torch.randint(-(2**31), 2**31 - 1, (words,), dtype=torch.int32, generator=gen)
+        buf = host.cuda()
+        sink = torch.zeros(1, dtype=torch.int64, device="cuda")
+        ops.probe_read(buf, sink)
+        expect = int(np.bitwise_xor.reduce(host.numpy().view(np.uint32)))
+        assert int(sink.item()) & 0xFFFFFFFF == expect
+        dst = torch.zeros_like(buf)
+        ops.probe_copy(dst, buf)
+        assert torch.equal(dst.cpu(), host)
+    with pytest.raises(RuntimeError, match="multiple of 16 bytes"):
+        ops.probe_read(torch.zeros(3, dtype=torch.int32, device="cuda"), sink)
+    with pytest.raises(RuntimeError, match="overlap"):
+        ops.probe_copy(buf[4:12], buf[8:16])
