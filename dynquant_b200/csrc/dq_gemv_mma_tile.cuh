@@ -77,7 +77,7 @@ __host__ __device__ inline size_t stage_bytes(int m, int steps, int spw, int kw,
   const int na = BITS == 8 ? 32 : 16;
   if (wide) {
     const size_t stride = static_cast<size_t>(steps) * na + 4;
-    return (m * stride + na) * 16 + static_cast<size_t>(steps) * 64 * gps + static_cast<size_t>(m) * in_features * 2 + 16;
+    return (m * stride + na) * 16 + static_cast<size_t>(steps) * 64 * gps + 16;
   }
   const size_t stride = static_cast<size_t>(spw) * na + 4;
   return static_cast<size_t>(kw) * (spw * 256 + (m * stride + na) * 16 + spw * 64 * gps);
@@ -166,7 +166,7 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
     xb = reinterpret_cast<uint4*>(area);
     xsum = reinterpret_cast<float*>(xb + a.m * m_stride_u4 + NA);
     xneg = xsum + span * 8 * GPS;
-    raw = reinterpret_cast<unsigned short*>(xneg + span * 8 * GPS);
+    raw = nullptr;  // CTA-wide staging reads the activation straight from global memory
   } else {
     unsigned char* mine = area + kwi * (spw * 256 + (a.m * m_stride_u4 + NA) * 16 + spw * 64 * GPS);
     raw = reinterpret_cast<unsigned short*>(mine);
@@ -284,9 +284,7 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   }
   pdl_wait_prior_grid();
   if (wide) {
-    const bool raw_ok = a.x_dtype != DQ_F32;
-    stage_activation<BITS, XBF16, G64>(a, L.steps, m_stride_u4, xb, xsum, xneg, tid, kThreads, nullptr,
-                                       raw_ok ? raw : nullptr, prefilled);
+    stage_activation<BITS, XBF16, G64>(a, L.steps, m_stride_u4, xb, xsum, xneg, tid, kThreads, nullptr, prefilled);
     __syncthreads();
   } else {
     stage_warp_slice<BITS, XBF16, G64>(a, s_begin, spw, m_stride_u4, raw, xb, xsum, xneg, lane, prefilled);

@@ -177,41 +177,18 @@ __device__ __forceinline__ bool stage_units_ok(const GemvArgs& a) {
 // kernel moments ago, is read once per CTA, and must not be served from a line this SM cached
 // before the previous kernel finished.
 //
-// `raw` (optional): shared-memory scratch of at least m * in_features 16-bit elements.  When
-// given, and the activation is 16-bit and 16-byte aligned, the activation is first copied
-// there with 128-bit loads -- one round trip to L2 for the whole CTA -- and the fragments are
-// built from shared memory; otherwise every lane gathers its values from global memory.
+// Aligned 16-bit activations take the unit-per-lane path (stage_units); anything else (fp32, odd
+// alignment) is gathered value by value from global memory.
 // With G64 the sums are per (step, group): xsum / xneg are [steps][2][8].
 template <int BITS, bool XBF16, bool G64 = false>
 __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, int m_stride_u4, uint4* xb,
                                                  float* xsum, float* xneg, int tid, int nthreads,
-                                                 const int* row_map = nullptr, unsigned short* raw = nullptr,
-                                                 bool prefilled = false) {
+                                                 const int* row_map = nullptr, bool prefilled = false) {
   if (stage_units_ok(a)) {  // (uniform over the CTA)
     stage_units<BITS, XBF16, G64>(a, 0, steps, m_stride_u4, xb, xsum, xneg, tid, nthreads, row_map, prefilled);
     return;
   }
-  const bool use_raw = raw != nullptr && a.x_dtype != DQ_F32 && (a.in_features & 7) == 0 &&
-                       (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
-  if (use_raw) {
-    const int vec_per_row = a.in_features >> 3;
-    for (int i = tid; i < a.m * vec_per_row; i += nthreads) {
-      const int m = i / vec_per_row;
-      const int v = i - m * vec_per_row;
-      const int64_t src_row = row_map != nullptr ? row_map[m] : m;
-      reinterpret_cast<uint4*>(raw)[i] =
-          __ldcg(reinterpret_cast<const uint4*>(a.x) + src_row * vec_per_row + v);
-    }
-    __syncthreads();
-  }
-  auto fetch = [&](int m, int64_t src_row, int k) -> float {
-    if (use_raw) {
-      const unsigned short h = raw[m * a.in_features + k];
-      return a.x_dtype == DQ_BF16 ? __uint_as_float(static_cast<uint32_t>(h) << 16)
-                                  : __half2float(__ushort_as_half(h));
-    }
-    return load_f32(a.x, src_row * a.in_features + k, a.x_dtype);
-  };
+  auto fetch = [&](int64_t src_row, int k) -> float { return load_f32(a.x, src_row * a.in_features + k, a.x_dtype); };
   using Plan = MmaPlan<BITS>;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
@@ -240,51 +217,6 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
     // nibble's slot (e = 4) repeats it: count x once
     count_x[r] = BITS != 8 || sl.e_lo == 0;
   }
-  if constexpr (XBF16) {
-    if (use_raw && a.x_dtype == DQ_BF16) {
-      // bf16 from the raw copy.  Widening is a shift, the power-of-two scaling an exact fp32
-      // multiply, and narrowing back takes the high half (nothing to round).
-      const bool whole = (a.in_features & 127) == 0;  // no pad tail: no bounds checks
-      for (int base = (tid >> 5) * per_warp; base < nitems; base += (nthreads >> 5) * per_warp) {
-        const int idx = min(base + sub, nitems - 1);
-        const bool live = base + sub < nitems;
-        const int m = idx / steps;
-        const int s = idx - m * steps;
-        const unsigned short* row = raw + m * a.in_features + s * 128;
-        const int left = a.in_features - s * 128;
-        float sx = 0.0f, sb = 0.0f;
-        uint32_t regs[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          uint32_t lo = row[whole || off_lo[r] < left ? off_lo[r] : 0];
-          uint32_t hi = row[whole || off_hi[r] < left ? off_hi[r] : 0];
-          if (!whole) {
-            lo = off_lo[r] < left ? lo : 0u;
-            hi = off_hi[r] < left ? hi : 0u;
-          }
-          const float flo = __uint_as_float(lo << 16), fhi = __uint_as_float(hi << 16);
-          if (count_x[r]) sx += flo + fhi;
-          const float slo = flo * mul_lo[r], shi = fhi * mul_hi[r];
-          sb += slo + shi;
-          regs[r] = __byte_perm(__float_as_uint(slo), __float_as_uint(shi), 0x7632);  // high halves
-        }
-        if (live) {
-          xb[m * m_stride_u4 + (s * QU + q) * 4 + tt] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
-        }
-        reduce_builder_group<LANES, kSplit>(sx, sb);
-        if (G64) {  // two lanes of the builder group hold the sums of the two groups
-          if (live && (l == 0 || l == kSecond)) {
-            xsum[(s * 2 + (l != 0)) * 8 + m] = sx;
-            xneg[(s * 2 + (l != 0)) * 8 + m] = -kMagicValue * sb;
-          }
-        } else if (live && l == 0) {
-          xsum[s * 8 + m] = sx;
-          xneg[s * 8 + m] = -kMagicValue * sb;
-        }
-      }
-      goto fill_zeros;
-    }
-  }
   for (int base = (tid >> 5) * per_warp; base < nitems; base += (nthreads >> 5) * per_warp) {
     const int idx = base + sub;
     const bool live = idx < nitems;
@@ -299,8 +231,8 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
       const int k_lo = kbase + off_lo[r];
       const int k_hi = kbase + off_hi[r];
       float lo = 0.0f, hi = 0.0f;
-      if (live && k_lo < a.in_features) lo = fetch(m, src_row, k_lo);
-      if (live && k_hi < a.in_features) hi = fetch(m, src_row, k_hi);
+      if (live && k_lo < a.in_features) lo = fetch(src_row, k_lo);
+      if (live && k_hi < a.in_features) hi = fetch(src_row, k_hi);
       if (count_x[r]) sx += lo + hi;
       lo *= mul_lo[r];
       hi *= mul_hi[r];
@@ -330,7 +262,6 @@ __device__ __forceinline__ void stage_activation(const GemvArgs& a, int steps, i
       xneg[s * 8 + m] = -kMagicValue * sb;
     }
   }
-fill_zeros:
   // what lanes of absent activation rows read: a block of zero fragments, zero sums
   for (int idx = tid; idx < QU * 4; idx += nthreads) {
     xb[a.m * m_stride_u4 + idx] = make_uint4(0u, 0u, 0u, 0u);

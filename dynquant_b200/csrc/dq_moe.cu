@@ -80,14 +80,14 @@ __host__ __device__ inline MoeSmem moe_smem(const MoeArgs& a, bool gate_up) {
   size_t at = 0;
   m.ring_w = at, at += static_cast<size_t>(a.nb) * CH * 2 * kMoeThreads * (4 * BITS);
   m.ring_m = at, at += static_cast<size_t>(a.nb) * CH * 2 * kMoeThreads;
-  m.red = at, at += 2 * static_cast<size_t>(halves) * kMoeWarps * 128 * 4;  // two buffers, alternating per item
+  // partial sums of the slices of the reduction axis: two buffers, alternating per item
+  m.red = at, at += a.kw > 1 ? 2 * static_cast<size_t>(halves) * kMoeWarps * 128 * 4 : 0;
   m.ids = at, at = up16(at + static_cast<size_t>(a.assignments) * 4);
   m.counts = at, at = up16(at + static_cast<size_t>(a.num_experts) * 4);
   m.list = at, at = up16(at + static_cast<size_t>(DQ_MOE_MAX_TOKENS) * 4);
   m.misc = at, at += 64 * 4;  // [0] expert, [1] count, [8..15] row map, [16..47] ballot counts
   m.stage = at;
-  at += (static_cast<size_t>(a.m_cap) * a.m_stride_u4 + na) * 16 + static_cast<size_t>(a.steps) * 64 +
-        static_cast<size_t>(a.m_cap) * a.in_features * 2 + 16;
+  at += (static_cast<size_t>(a.m_cap) * a.m_stride_u4 + na) * 16 + static_cast<size_t>(a.steps) * 64 + 16;
   m.total = at;
   return m;
 }
@@ -111,8 +111,8 @@ __device__ __forceinline__ void moe_wait_pending(int n) {
 // through a private cp.async ring of `nb` stages of CH steps, partial sums of the slices
 // added in a fixed order.  GATE_UP: an item is 16 gate rows plus the matching 16 up rows per
 // row tile, and the output is silu(g) * u.
-template <int BITS, bool XBF16, int CH, bool GATE_UP>
-__global__ void __launch_bounds__(kMoeThreads, 2) moe_grouped_kernel(const __grid_constant__ MoeArgs a) {
+template <int BITS, bool XBF16, int CH, bool GATE_UP, int CTAS>
+__global__ void __launch_bounds__(kMoeThreads, CTAS) moe_grouped_kernel(const __grid_constant__ MoeArgs a) {
   using Plan = MmaPlan<BITS>;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
@@ -135,7 +135,6 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_grouped_kernel(const __gri
   uint4* xb = reinterpret_cast<uint4*>(smem_raw + lay.stage);
   float* xsum = reinterpret_cast<float*>(xb + a.m_cap * a.m_stride_u4 + NA);
   float* xneg = xsum + a.steps * 8;
-  unsigned short* raw = reinterpret_cast<unsigned short*>(xneg + a.steps * 8);
 
   const int tid = threadIdx.x;
   const int lane = tid & (kWarp - 1);
@@ -333,7 +332,7 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_grouped_kernel(const __gri
     }
     __syncthreads();
     stage.m = m;
-    stage_activation<BITS, XBF16>(stage, a.steps, a.m_stride_u4, xb, xsum, xneg, tid, kMoeThreads, row_map, raw);
+    stage_activation<BITS, XBF16>(stage, a.steps, a.m_stride_u4, xb, xsum, xneg, tid, kMoeThreads, row_map);
     __syncthreads();
     const bool b_live = g < m;
     const uint4* xb_lane = (b_live ? xb + g * a.m_stride_u4 + t : xb + m * a.m_stride_u4) + (b_live ? s_begin * QU * 4 : 0);
@@ -534,6 +533,23 @@ int32_t static_scratch_address(void** out) {
   return DQ_OK;
 }
 
+// Measurement switches of the MoE launcher (integers from the environment; 0 / unset = the
+// built-in choice).  Read once per process -- unless DQ_B200_MOE_LIVE_KNOBS is set, in which
+// case every launch reads them again so that one process can time several settings.
+inline int moe_knob(const char* name, int* cached, bool* have) {
+  static const bool live = std::getenv("DQ_B200_MOE_LIVE_KNOBS") != nullptr;
+  if (!live && *have) return *cached;
+  const char* v = std::getenv(name);
+  const int value = v ? std::atoi(v) : 0;
+  *cached = value;
+  *have = true;
+  return value;
+}
+#define DQ_MOE_KNOB(var, name)            \
+  static int var##_cached = 0;            \
+  static bool var##_have = false;         \
+  const int var = ::dq::moe_knob(name, &var##_cached, &var##_have)
+
 template <typename Kernel>
 int32_t launch_pdl(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t stream, const MoeArgs& args,
                    const char* what) {
@@ -559,15 +575,22 @@ template <int BITS, int CH, bool GATE_UP>
 int32_t launch_grouped(MoeArgs a, int slots, cudaStream_t stream) {
   const DeviceInfo* dev = device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
-  static const int force_nb = [] { const char* v = std::getenv("DQ_B200_MOE_NB"); return v ? std::atoi(v) : 0; }();
-  static const int force_x = [] { const char* v = std::getenv("DQ_B200_MOE_GRID_X"); return v ? std::atoi(v) : 0; }();
+  DQ_MOE_KNOB(force_nb, "DQ_B200_MOE_NB");
+  DQ_MOE_KNOB(force_x_both, "DQ_B200_MOE_GRID_X");
+  DQ_MOE_KNOB(force_x_one, GATE_UP ? "DQ_B200_MOE_GRID_X_UP" : "DQ_B200_MOE_GRID_X_DOWN");
+  const int force_x = force_x_one > 0 ? force_x_one : force_x_both;
   // ring: as deep as keeps two CTAs on an SM (one, if a single stage is that large)
   a.nb = 1;
   const size_t one = moe_smem<BITS, CH>(a, GATE_UP).total;
   const size_t stage = static_cast<size_t>(CH) * 2 * kMoeThreads * (4 * BITS) + static_cast<size_t>(CH) * 2 * kMoeThreads;
   const size_t fixed = one - stage;
+  // Two register builds, like the tiled dense kernel: three CTAs per SM (80 registers) when a
+  // ring of two stages still fits beside the staged activation, else two (128 registers).
+  DQ_MOE_KNOB(force_ctas, "DQ_B200_MOE_CTAS");
   const size_t per_sm = 228 * 1024, reserve = 1024;
-  size_t budget = per_sm / 2 - reserve;
+  int ctas = force_ctas == 2 || force_ctas == 3 ? force_ctas : (a.tokens >= 32 ? 3 : 2);
+  if (ctas == 3 && fixed + 2 * stage > per_sm / 3 - reserve) ctas = 2;
+  size_t budget = per_sm / ctas - reserve;
   if (fixed + 2 * stage > budget) budget = static_cast<size_t>(dev->max_smem_optin);
   if (fixed + stage > budget) {
     return fail(DQ_ERR_UNSUPPORTED, "moe_gemv: in_features=%d needs %zu bytes of shared memory", a.in_features,
@@ -576,23 +599,30 @@ int32_t launch_grouped(MoeArgs a, int slots, cudaStream_t stream) {
   a.nb = static_cast<int>(std::max<size_t>(1, std::min<size_t>(8, (budget - fixed) / stage)));
   if (force_nb > 0) a.nb = static_cast<int>(std::min<size_t>(force_nb, (static_cast<size_t>(dev->max_smem_optin) - fixed) / stage));
   const size_t smem = moe_smem<BITS, CH>(a, GATE_UP).total;
-  // CTAs per expert: every CTA pays for routing and for staging the activation, so with many
-  // active experts the CTAs are made fatter -- but the grid stays about six CTAs per SM deep,
-  // because experts differ in token count and small CTAs even that out (measured: 18 % faster
-  // at 64 tokens than two CTAs per SM).
-  // Experts expected to have a token under uniform routing: E * (1 - (1 - 1/E)^A).
+  // CTAs per expert (measured on B200, Qwen3-30B-A3B shape, 1..64 tokens).  Every CTA pays
+  // for routing and for staging the activation rows of its expert, so a CTA gets at least
+  // about a dozen steps per warp to do; beyond that, more and smaller CTAs even out the
+  // experts' different loads.  With so few tokens that this leaves SMs idle, the grid is
+  // widened to one full wave over the experts expected to be active
+  // (E * (1 - (1 - 1/E)^A) under uniform routing).
   const int tiles = (a.rows + 15) / 16;
   const int items = static_cast<int>(ceil_div(tiles, a.rw));
   const double e_count = a.num_experts;
   const double active = std::max(1.0, e_count * (1.0 - std::pow(1.0 - 1.0 / e_count, a.assignments)));
-  int grid_x = static_cast<int>(std::min<int64_t>(items, std::max<int64_t>(1, static_cast<int64_t>(6.0 * dev->sm_count / active + 0.5))));
+  const int steps_per_item = (GATE_UP ? 2 : 1) * a.spw;
+  const int items_per_cta = std::max(1, static_cast<int>(ceil_div(12, steps_per_item)));
+  const int one_wave = static_cast<int>(std::ceil(static_cast<double>(ctas) * dev->sm_count / active));
+  int grid_x = static_cast<int>(std::min<int64_t>(items, std::max<int64_t>(ceil_div(items, items_per_cta), one_wave)));
+  grid_x = static_cast<int>(ceil_div(items, ceil_div(items, grid_x)));  // no CTA with one item more than the others need
   if (force_x > 0) grid_x = std::min(force_x, items);
   const dim3 grid(static_cast<unsigned>(grid_x), static_cast<unsigned>(slots));
   const char* what = GATE_UP ? "moe_gemv(gate_up)" : "moe_gemv(down)";
   if (a.act_dtype == DQ_BF16) {
-    return launch_pdl(moe_grouped_kernel<BITS, true, CH, GATE_UP>, grid, kMoeThreads, smem, stream, a, what);
+    return ctas == 3 ? launch_pdl(moe_grouped_kernel<BITS, true, CH, GATE_UP, 3>, grid, kMoeThreads, smem, stream, a, what)
+                     : launch_pdl(moe_grouped_kernel<BITS, true, CH, GATE_UP, 2>, grid, kMoeThreads, smem, stream, a, what);
   }
-  return launch_pdl(moe_grouped_kernel<BITS, false, CH, GATE_UP>, grid, kMoeThreads, smem, stream, a, what);
+  return ctas == 3 ? launch_pdl(moe_grouped_kernel<BITS, false, CH, GATE_UP, 3>, grid, kMoeThreads, smem, stream, a, what)
+                   : launch_pdl(moe_grouped_kernel<BITS, false, CH, GATE_UP, 2>, grid, kMoeThreads, smem, stream, a, what);
 }
 
 template <bool GATE_UP>
@@ -607,11 +637,12 @@ int32_t launch_bank(const dq_weight& w, const dq_geometry& g, MoeArgs a, int slo
   a.steps = g.words_per_row / (4 * w.bits);
   // 8 warps: kw slices of the reduction axis (each an even number of steps), the other
   // warps take neighbouring row tiles.
-  static const int force_kw = [] { const char* v = std::getenv("DQ_B200_MOE_KW"); return v ? std::atoi(v) : 0; }();
-  // Measured on B200 (Qwen3-30B-A3B shape): with one token a layer is a chain of latencies
-  // and four slices are fastest (19.2 us against 23.8 with two); up to 32 tokens two
-  // slices; beyond, whole rows per warp (no reduction at all: 130 us against 137 at 64).
-  const int want_kw = a.tokens <= 1 ? 4 : (a.tokens <= 32 ? 2 : 1);
+  DQ_MOE_KNOB(force_kw, "DQ_B200_MOE_KW");
+  // Measured on B200 (Qwen3-30B-A3B shape): up to three tokens a layer is a chain of
+  // latencies and four slices are fastest (18.4 us against 22.2 with two at one token); from
+  // four tokens on, whole rows per warp and no cross-warp sum at all (16 tokens: 68 us
+  // against 78 with two slices; 64 tokens: 107 against 124).
+  const int want_kw = a.tokens <= 3 ? 4 : 1;
   int kw = 1;
   while (kw < want_kw && a.steps % (kw * 2) == 0 && (a.steps / (kw * 2)) % 2 == 0) kw *= 2;
   if (force_kw > 0 && a.steps % force_kw == 0) kw = force_kw;
@@ -698,9 +729,13 @@ int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_
   a.ids = topk_ids;
   a.assignments = assignments;
   a.num_experts = static_cast<int>(num_experts);
-  // Activation rows staged at once: experts rarely see more than four tokens of a batch of
-  // 32; the few that do take a second pass over their (L2-resident) rows.
-  a.m_cap = static_cast<int>(std::min<int64_t>(tokens > 32 ? 8 : 4, tokens));
+  // Activation rows staged at once: the eight columns of one mma.  An expert with more tokens
+  // than that takes another pass over its (L2-resident) rows.
+  a.m_cap = static_cast<int>(std::min<int64_t>(8, tokens));
+  {
+    DQ_MOE_KNOB(force_m_cap, "DQ_B200_MOE_M_CAP");
+    if (force_m_cap >= 1 && force_m_cap <= 8) a.m_cap = static_cast<int>(std::min<int64_t>(force_m_cap, tokens));
+  }
   a.topk = static_cast<int>(topk);
   a.tokens = static_cast<int>(tokens);
   a.act_dtype = x_dtype;
