@@ -152,3 +152,43 @@ class StepRunner:
         if self._graph is None:
             raise RuntimeError("capture() first")
         self._graph.replay()
+
+    def capture_with_io(self, host_inputs: dict[str, torch.Tensor], output: str, host_output: torch.Tensor,
+                        mode: str = "dataflow") -> None:
+        """Record host -> device copies of the activations, the step, and the device -> host
+        copy of one module's output into ONE graph: a serving loop that owns pinned staging
+        buffers then pays a single graph launch per step instead of one host call per copy.
+
+        ``host_inputs``: pinned CPU tensors, one per entry of ``inputs`` (same shapes and
+        dtypes); ``output``: the module whose result is read back into pinned ``host_output``.
+        """
+        if set(host_inputs) != set(self.inputs):
+            raise ValueError(f"host_inputs must cover exactly {sorted(self.inputs)}")
+        for name, t in host_inputs.items():
+            if not t.is_pinned() or t.shape != self.inputs[name].shape or t.dtype != self.inputs[name].dtype:
+                raise ValueError(f"host input {name!r} must be pinned and match the device tensor")
+        dev_out = self.outputs[output]
+        if not host_output.is_pinned() or host_output.shape != dev_out.shape or host_output.dtype != dev_out.dtype:
+            raise ValueError("host_output must be pinned and match the module's output")
+        self.run()
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        sides = [torch.cuda.Stream(self.device) for _ in range(2)]
+        with torch.cuda.graph(graph):
+            for name, t in host_inputs.items():
+                self.inputs[name].copy_(t, non_blocking=True)
+            if mode == "chain":
+                self.run()
+            elif mode == "dataflow":
+                self.run_dataflow(sides)
+            else:
+                raise ValueError(mode)
+            host_output.copy_(dev_out, non_blocking=True)
+        self._graph_io = graph
+
+    def replay_with_io(self) -> None:
+        """One step including its copies (``capture_with_io``); the caller synchronises the stream."""
+        graph = getattr(self, "_graph_io", None)
+        if graph is None:
+            raise RuntimeError("capture_with_io() first")
+        graph.replay()

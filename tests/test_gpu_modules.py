@@ -151,3 +151,30 @@ def test_gemv_host_entry_point_round_trips_through_pinned_memory():
     ops.gemv_host(x_host, qt, out_host, x_dev, out_dev)
     want = ops.gemv(x_host.cuda(), qt.packed, qt.scales, qt.offsets, 4, 128, 512)
     assert torch.equal(out_host, want.cpu())
+
+
+def test_step_graph_with_its_copies_matches_the_plain_step():
+    """``capture_with_io``: host -> device copies, the step and the read-back in one graph give
+    what the same step gives on resident inputs."""
+    from dynquant_b200.stack import StepRunner
+    from dynquant_b200.workloads import qwen2b_stack
+
+    stack = qwen2b_stack(device="cuda", layers=1, vocab=1024)
+    runner = StepRunner(stack, 2, device="cuda")
+    runner.run()
+    torch.cuda.synchronize()
+    last = stack.modules[-1].name
+    expect = runner.outputs[last].clone()
+    host_in = {k: v.cpu().pin_memory() for k, v in runner.inputs.items()}
+    host_out = torch.zeros_like(expect, device="cpu").pin_memory()
+    for v in runner.inputs.values():
+        v.zero_()  # the graph must bring the activations back from the host
+    runner.capture_with_io(host_in, last, host_out)
+    for v in runner.inputs.values():
+        v.zero_()
+    runner.outputs[last].zero_()
+    runner.replay_with_io()
+    torch.cuda.synchronize()
+    assert torch.equal(host_out, expect.cpu())
+    with pytest.raises(ValueError, match="pinned"):
+        runner.capture_with_io({k: v.cpu() for k, v in runner.inputs.items()}, last, host_out)
