@@ -577,15 +577,31 @@ int env_int(const char* name) {
   return v != nullptr ? std::atoi(v) : 0;
 }
 
+// A measurement switch: read once per process -- unless DQ_B200_LIVE_KNOBS is set, in which
+// case every launch reads it again so that one process can time several settings.
+struct Knob {
+  const char* name;
+  int cached = 0;
+  bool have = false;
+  int get() {
+    static const bool live = std::getenv("DQ_B200_LIVE_KNOBS") != nullptr;
+    if (live || !have) {
+      cached = env_int(name);
+      have = true;
+    }
+    return cached;
+  }
+};
+
 // One launch for `n` matrices sharing the activation.  *taken stays false (and nothing is
 // launched) when the jobs do not meet the kernel's requirements.
 int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo& dev, cudaStream_t stream_h,
                  bool* taken) {
   *taken = false;
   static const bool off = env_int("DQ_B200_NO_TILE") != 0;
-  static const int force_kw = env_int("DQ_B200_TILE_KW");
-  static const int force_nb = env_int("DQ_B200_TILE_NB");
-  static const int force_per_sm = env_int("DQ_B200_TILE_PER_SM");
+  static Knob knob_kw{"DQ_B200_TILE_KW"}, knob_nb{"DQ_B200_TILE_NB"}, knob_per_sm{"DQ_B200_TILE_PER_SM"},
+      knob_ctas{"DQ_B200_TILE_CTAS"};
+  const int force_kw = knob_kw.get(), force_nb = knob_nb.get(), force_per_sm = knob_per_sm.get();
   if (off || n < 1 || n > tilek::kMaxJobs) return DQ_OK;
   const GemvArgs& a0 = jobs[0];
   const int steps = a0.words_per_row / (4 * bits[0]);
@@ -696,7 +712,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     return best;
   };
   // The three-CTA build only where its third CTA per SM buys a finer one-wave slicing.
-  static const int force_ctas = env_int("DQ_B200_TILE_CTAS");
+  const int force_ctas = knob_ctas.get();
   ctas_by_registers = 3;
   Shape pick = choose();
   const bool needs_three = pick.kw != 0 && pick.ipc == 1 && pick.nb == (steps / pick.kw) / pick.ch &&
