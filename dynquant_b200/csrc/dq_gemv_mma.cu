@@ -698,6 +698,14 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
   };
   auto choose = [&]() {
     Shape best;
+    // Several activation rows: staging them is the larger part of a CTA's prologue, so whole
+    // rows per warp (the activation staged once per eight row tiles) win over the finest
+    // slicing as soon as that still gives every other SM a CTA (measured, 12288 x 2048 at
+    // eight rows: 8.4-8.8 us against 9.1-11.1).
+    if (a0.m >= 6 && force_kw == 0) {
+      const Shape sh = shape_at(1, true);
+      if (sh.kw != 0 && sh.per_sm >= 1 && sh.ipc == 1 && items_at(1) * 2 >= dev.sm_count) best = sh;
+    }
     for (int kw = tilek::kWarps; kw >= 1 && best.kw == 0; kw /= 2) {
       if (force_kw > 0 && kw != force_kw) continue;
       const Shape sh = shape_at(kw, true);
