@@ -38,7 +38,7 @@ def run_case(tokens, experts, hidden, inter, topk, bits_gu, bits_dn, act=torch.b
     return got.cpu().numpy(), want, layer, ids, w, x
 
 
-@pytest.mark.parametrize("tokens", [1, 2, 5, 8, 33, 64])
+@pytest.mark.parametrize("tokens", [1, 2, 3, 4, 5, 8, 16, 32, 33, 64])
 @pytest.mark.parametrize(("bits_gu", "bits_dn"), [(2, 4), (3, 3), (4, 2), (8, 8)])
 def test_moe_matches_the_composition_oracle(tokens, bits_gu, bits_dn):
     got, want, *_ = run_case(tokens, 16, 512, 256, 4, bits_gu, bits_dn)
@@ -58,6 +58,13 @@ def test_moe_qwen3_shape_fp16_and_determinism():
         again = ops.moe_gemv(x.cuda(), ids.cuda(), w.cuda(), layer.gate_up, layer.down, num_experts=128)
         assert torch.equal(first, again)
     assert first.dtype == torch.float16
+
+
+def test_moe_qwen3_shape_at_thirty_two_tokens():
+    """The real expert shape where the launcher switches to its 80-register build (three CTAs
+    per SM), whole rows per warp and eight staged rows."""
+    got, want, *_ = run_case(32, 128, 2048, 768, 8, 2, 4, seed=11)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3
 
 
 def test_moe_skips_experts_that_are_not_local():
