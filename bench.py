@@ -274,7 +274,7 @@ def run_ours(args) -> None:
     h2d = sum(v.numel() * v.element_size() for v in host_in.values())
     d2h = host_out.numel() * host_out.element_size()
 
-    io_graph = world == 1 and use_graph and args.graph_mode in ("dataflow", "chain") and not args.e2e_eager_copies
+    io_graph = world == 1 and use_graph and args.graph_mode in ("plan", "dataflow", "chain") and not args.e2e_eager_copies
     if io_graph:
         # the serving loop's form: pinned staging buffers, copies and kernels in one graph
         runner.capture_with_io(host_in, last_name, host_out, args.graph_mode)
@@ -376,7 +376,7 @@ def main() -> None:
     ap.add_argument("--no-probe", action="store_true", help="skip the read/copy bandwidth probe")
     ap.add_argument("--e2e-eager-copies", action="store_true",
                     help="end-to-end arm: issue the host<->device copies as separate calls around the step's graph")
-    ap.add_argument("--graph-mode", choices=["dataflow", "chain", "independent"], default="dataflow",
+    ap.add_argument("--graph-mode", choices=["plan", "dataflow", "chain", "independent"], default="plan",
                     help="edges of the captured step: a decoder layer's data dependencies (default), "
                          "a strict chain, or none")
     args = ap.parse_args()

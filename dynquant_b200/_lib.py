@@ -67,6 +67,20 @@ class GemvJob(ctypes.Structure):
     ]
 
 
+class PlanInfo(ctypes.Structure):
+    """``dq_plan_info``."""
+
+    _fields_ = [
+        ("num_stages", ctypes.c_int32),
+        ("num_jobs", ctypes.c_int32),
+        ("grid", ctypes.c_int32),
+        ("threads", ctypes.c_int32),
+        ("ring_slots", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("shared_bytes", ctypes.c_int64),
+    ]
+
+
 _P = ctypes.c_void_p
 _I32 = ctypes.c_int32
 _I64 = ctypes.c_int64
@@ -79,6 +93,7 @@ SIGNATURES = {
     "dq_compiled_architectures": (ctypes.c_char_p, []),
     "dq_gemv_max_rows": (_I32, []),
     "dq_launch_count": (_I64, []),
+    "dq_last_kernel": (ctypes.c_char_p, []),
     "dq_moe_max_tokens": (_I32, []),
     "dq_last_error": (ctypes.c_char_p, []),
     "dq_resolve_geometry": (_I32, [ctypes.c_char_p, _WP, ctypes.POINTER(Geometry)]),
@@ -91,6 +106,14 @@ SIGNATURES = {
     "dq_moe_scratch_bytes": (_I32, [_I64, _I64, _I64, _I64, _I64, _I32, ctypes.POINTER(ctypes.c_int64)]),
     "dq_moe_gemv": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _WP, _WP, _I64, _I64, _P, _I32, _P, _I64, _P]),
     "dq_moe_gemv_static": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _WP, _WP, _I64, _I64, _P, _I32, _P]),
+    "dq_plan_workspace_bytes": (_I32, [_I32, ctypes.POINTER(ctypes.c_int64)]),
+    "dq_plan_create": (_I32, [ctypes.POINTER(GemvJob), _I32, _P, _I64, _P, ctypes.POINTER(_P)]),
+    "dq_plan_launch": (_I32, [_P, _P]),
+    "dq_plan_status": (_I32, [_P, _P]),
+    "dq_plan_describe": (_I32, [_P, ctypes.POINTER(PlanInfo)]),
+    "dq_plan_stage_shape": (_I32, [_P, _I32, ctypes.POINTER(_I32), ctypes.POINTER(_I32), ctypes.POINTER(_I32)]),
+    "dq_plan_set_wait": (_I32, [_P, _I32, _I32, _I32, _P]),
+    "dq_plan_destroy": (None, [_P]),
     "dq_gemv_host": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P, _P, _P]),
 }
 

@@ -21,6 +21,11 @@ namespace {
 std::atomic<int64_t> g_launches{0};
 }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+namespace {
+thread_local const char* t_last_kernel = "";
+}
+void note_kernel(const char* name) { t_last_kernel = name; }
+const char* last_kernel() { return t_last_kernel; }
 int64_t launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
 
 const DeviceInfo* device_info() {
@@ -58,6 +63,7 @@ const DeviceInfo* device_info() {
 extern "C" {
 
 int64_t dq_launch_count(void) { return dq::launches_so_far(); }
+const char* dq_last_kernel(void) { return dq::last_kernel(); }
 
 
 int32_t dq_abi_version(void) { return DQ_ABI_VERSION; }

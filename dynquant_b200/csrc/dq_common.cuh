@@ -105,6 +105,9 @@ const DeviceInfo* device_info();
 
 // Process-wide count of the kernels this library has launched (dq_launch_count).
 void count_launch();
+// Name of the kernel the calling thread launched last (dq_last_kernel): lets a test prove which
+// of the kernels a shape was dispatched to.
+void note_kernel(const char* name);
 
 // ---- device-side dtype helpers ---------------------------------------------
 

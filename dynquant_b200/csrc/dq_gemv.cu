@@ -355,7 +355,7 @@ int fast_chunk_words(const dq_weight& w, const dq_geometry& g, const void* x, in
 
 template <typename Kernel>
 int32_t launch(Kernel kernel, const GemvArgs& args, int grid, size_t smem, cudaStream_t stream,
-               const char* what) {
+               const char* what /* kernel name, for dq_last_kernel */) {
   if (smem > 48 * 1024) {
     DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem)));
@@ -371,7 +371,8 @@ int32_t launch(Kernel kernel, const GemvArgs& args, int grid, size_t smem, cudaS
   cfg.attrs = attr;
   cfg.numAttrs = use_pdl() ? 1 : 0;
   DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, args));
-  DQ_CHECK_LAUNCH(what);
+  DQ_CHECK_LAUNCH("gemv");
+  note_kernel(what);
   return DQ_OK;
 }
 
@@ -396,7 +397,7 @@ int32_t launch_fast(const GemvArgs& args, cudaStream_t stream) {
   int per_sm = static_cast<int>(std::min<size_t>(2048 / kThreads, smem ? per_sm_smem / (smem + 1024) : 8));
   per_sm = std::max(per_sm, 1);
   const int grid = std::min(ctas, dev->sm_count * per_sm);
-  return launch(kernel, args, grid, smem, stream, "gemv");
+  return launch(kernel, args, grid, smem, stream, "gemv_fast_kernel");
 }
 
 template <int BITS, int CW>
@@ -425,10 +426,10 @@ int32_t launch_general(const GemvArgs& args, cudaStream_t stream) {
   const int ctas = static_cast<int>(ceil_div(args.rows, kWarpsPerCta));
   const int grid = std::min(ctas, dev->sm_count * 8);
   const int m = args.m;
-  if (m == 1) return launch(gemv_general_kernel<BITS, 1>, args, grid, 0, stream, "gemv");
-  if (m == 2) return launch(gemv_general_kernel<BITS, 2>, args, grid, 0, stream, "gemv");
-  if (m <= 4) return launch(gemv_general_kernel<BITS, 4>, args, grid, 0, stream, "gemv");
-  return launch(gemv_general_kernel<BITS, 8>, args, grid, 0, stream, "gemv");
+  if (m == 1) return launch(gemv_general_kernel<BITS, 1>, args, grid, 0, stream, "gemv_general_kernel");
+  if (m == 2) return launch(gemv_general_kernel<BITS, 2>, args, grid, 0, stream, "gemv_general_kernel");
+  if (m <= 4) return launch(gemv_general_kernel<BITS, 4>, args, grid, 0, stream, "gemv_general_kernel");
+  return launch(gemv_general_kernel<BITS, 8>, args, grid, 0, stream, "gemv_general_kernel");
 }
 
 // Rows per warp: as many as still leave every resident warp a tile.

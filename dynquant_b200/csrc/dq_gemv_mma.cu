@@ -466,6 +466,7 @@ int32_t launch_mma_kernel(Kernel kernel, const GemvArgs& a, MmaParams p, int thr
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
   DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
   DQ_CHECK_LAUNCH("gemv");
+  note_kernel("gemv_mma_kernel");
   return DQ_OK;
 }
 
@@ -549,6 +550,7 @@ int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int s
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
     DQ_CHECK_LAUNCH("gemv");
+    note_kernel("gemv_mma_stream_kernel");
     return DQ_OK;
   };
   const bool xbf = a.x_dtype == DQ_BF16;
@@ -779,6 +781,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, L));
     DQ_CHECK_LAUNCH("gemv");
+    note_kernel("gemv_mma_tile_kernel");
     *taken = true;
     return DQ_OK;
   };

@@ -346,6 +346,11 @@ def launch_count() -> int:
     return int(_lib.load().dq_launch_count())
 
 
+def last_kernel() -> str:
+    """Name of the kernel this thread's last GEMV call launched (``dq_last_kernel``)."""
+    return _lib.load().dq_last_kernel().decode()
+
+
 def probe_read(buf: torch.Tensor, sink: torch.Tensor) -> None:
     """One read-only pass over ``buf`` (``dq_probe_read``); XOR of its 32-bit words into ``sink[0]``."""
     _require_cuda(buf, "probe_read: buffer")

@@ -21,6 +21,64 @@ from .ops import _stream, _tag, weight_descriptor
 from .workloads import LinearStack
 
 
+class GemvPlan:
+    """A job list compiled into ONE persistent kernel (``dq_plan_*`` of the C ABI).
+
+    Same results as ``dq_gemv_sequence`` over the same ``dq_gemv_job`` array; the jobs' tensors
+    are referenced, not copied, and must outlive the plan.  ``launch()`` enqueues exactly one
+    kernel on torch's current stream and may be captured in a CUDA graph; ``check()``
+    synchronises and raises if a stage's bounded wait ran out.
+    """
+
+    def __init__(self, jobs, count: int, device: torch.device):
+        lib = _lib.load()
+        self.device = torch.device(device)
+        need = ctypes.c_int64()
+        _lib.check(lib.dq_plan_workspace_bytes(count, ctypes.byref(need)))
+        self.workspace = torch.zeros(need.value, dtype=torch.uint8, device=self.device)
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.dq_plan_create(jobs, count, self.workspace.data_ptr(), need.value,
+                                          _stream(self.device), ctypes.byref(handle)))
+        self._handle = handle
+        self._jobs = jobs  # keeps the ctypes array (and through the runner, the tensors) alive
+
+    def launch(self) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().dq_plan_launch(self._handle, _stream(self.device)))
+
+    def check(self) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().dq_plan_status(self._handle, _stream(self.device)))
+
+    def info(self) -> dict:
+        out = _lib.PlanInfo()
+        _lib.check(_lib.load().dq_plan_describe(self._handle, ctypes.byref(out)))
+        return {name: int(getattr(out, name)) for name, _ in out._fields_ if name != "reserved"}
+
+    def stage_shape(self, stage: int) -> dict:
+        kw, cs = ctypes.c_int32(), ctypes.c_int32()
+        ctas = (ctypes.c_int32 * 4)()
+        _lib.check(_lib.load().dq_plan_stage_shape(self._handle, stage, ctypes.byref(kw), ctypes.byref(cs), ctas))
+        return {"k_slices": kw.value, "slot_steps": cs.value, "ctas": [int(c) for c in ctas if c]}
+
+    def set_wait(self, stage: int, wait_target: int, spin_limit: int) -> None:
+        """Failure-handling hook (``dq_plan_set_wait``): make a stage wait for a count."""
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().dq_plan_set_wait(self._handle, stage, wait_target, spin_limit, _stream(self.device)))
+
+    def close(self) -> None:
+        if self._handle:
+            _lib.load().dq_plan_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):  # pragma: no cover - interpreter teardown order
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class StepRunner:
     """Pre-built launch list for one decode step over a :class:`LinearStack`.
 
@@ -64,7 +122,18 @@ class StepRunner:
                 "gemv_sequence", qt.packed, qt.scales, qt.offsets, qt.bits, qt.geometry.effective_group, qt.in_features
             )
         self._graph: torch.cuda.CUDAGraph | None = None
+        self._plan: GemvPlan | None = None
         self.launches_per_step = len(stack.modules)  # replaced by the measured count in capture()
+
+    def plan(self) -> GemvPlan:
+        """The whole step as one persistent kernel (built on first use).  Raises ``RuntimeError``
+        when a module does not meet the plan kernel's requirements."""
+        if self._plan is None:
+            self._plan = GemvPlan(self._jobs, len(self._jobs), self.device)
+        return self._plan
+
+    def run_plan(self) -> None:
+        self.plan().launch()
 
     def run(self) -> None:
         """Enqueue the whole step on torch's current stream, module after module."""
@@ -116,7 +185,12 @@ class StepRunner:
         (q/k/v, gate/up) leave as one fused launch, the rest one after the other.
         ``"independent"``: no edges at all -- every module's input is resident, nothing
         waits for anything (the regime the reference's per-shape bandwidth table measures).
+        ``"plan"``: the same chain of stages as ``"dataflow"`` as ONE persistent kernel
+        (:class:`GemvPlan`).
         """
+        if mode == "plan":
+            self.run_plan()  # builds the plan; first launch outside the capture
+            self.plan().check()
         self.run()  # warm: sets per-kernel attributes outside the capture
         torch.cuda.synchronize(self.device)
         lib = _lib.load()
@@ -126,6 +200,8 @@ class StepRunner:
         with torch.cuda.graph(graph):
             if mode == "chain":
                 self.run()
+            elif mode == "plan":
+                self.run_plan()
             elif mode == "dataflow":
                 self.run_dataflow(sides)
             elif mode == "independent":
@@ -179,6 +255,8 @@ class StepRunner:
                 self.inputs[name].copy_(t, non_blocking=True)
             if mode == "chain":
                 self.run()
+            elif mode == "plan":
+                self.run_plan()
             elif mode == "dataflow":
                 self.run_dataflow(sides)
             else:

@@ -99,6 +99,12 @@ DQ_API int32_t dq_gemv_max_rows(void);
  * (csrc/cuda/gemv.cu:231-275), here one call may be one launch for several
  * matrices or several launches for one, and benchmarks report the real number. */
 DQ_API int64_t dq_launch_count(void);
+/* Name of the kernel the calling thread's most recent GEMV entry point launched last
+ * ("gemv_mma_stream_kernel", "gemv_mma_tile_kernel", "gemv_mma_kernel", "gemv_fast_kernel",
+ * "gemv_general_kernel", "gemv_plan_kernel"; "" before the first launch).  No reference
+ * counterpart: the reference has two kernels and a documented rule between them
+ * (csrc/gemv/gemv.cu:566-598); here a test uses this to prove which kernel it exercised. */
+DQ_API const char* dq_last_kernel(void);
 DQ_API int32_t dq_moe_max_tokens(void);
 DQ_API const char* dq_last_error(void);
 
@@ -167,6 +173,59 @@ typedef struct dq_gemv_job {
  * four of them are issued as one launch, so their outputs must not overlap.
  * All jobs are validated before the first launch. */
 DQ_API int32_t dq_gemv_sequence(const dq_gemv_job* jobs, int32_t num_jobs, void* stream);
+
+/* ---- whole-step plans: a job list compiled once, run by ONE persistent kernel ------------
+ * Same semantics as dq_gemv_sequence over the same job list (reference: one
+ * quantized_matmul call per module per decode step,
+ * packages/dynquant-core/src/dynquant/runtime/ops.py:184-231; its own profile of a decode
+ * step -- experiments/four_point/RESULTS.md:884-906 -- is host and launch time around
+ * single-digit-microsecond kernels).  Consecutive jobs that read the same activation form a
+ * stage; a stage may read what the stage before it wrote.  One grid of one CTA per SM walks
+ * the stages: weights stream ahead of the arithmetic across stage boundaries, and a stage
+ * reads its activation only after the stage before it has stored every output -- a
+ * completion counter in `workspace`, polled with a BOUNDED spin.  If the bound runs out
+ * (the grid was not resident at once, or a test asked for it) the kernel sets a status word
+ * and returns; dq_plan_status reports DQ_ERR_DEVICE.
+ *
+ * Requirements, checked by dq_plan_create (DQ_ERR_UNSUPPORTED names the first job that
+ * fails them; launch such lists with dq_gemv_sequence): fp16/bf16 activations of one dtype,
+ * 1..DQ_GEMV_MAX_ROWS rows, 16-byte aligned with in_features a multiple of 8; fp16/bf16
+ * scales; 128-value groups, an even number per row; 16-byte aligned packed rows.
+ *
+ * `workspace` is caller-owned device memory (dq_plan_workspace_bytes, 256-byte aligned)
+ * that must stay alive and untouched for the life of the plan; the job list's tensors are
+ * referenced, not copied.  A plan belongs to the device that was current at creation.
+ * Launches of ONE plan must not overlap on the GPU (they share the counters); launches of
+ * different plans may.  dq_plan_launch enqueues exactly one kernel and is capturable. */
+typedef struct dq_plan dq_plan;
+typedef struct dq_plan_info {
+  int32_t num_stages;
+  int32_t num_jobs;
+  int32_t grid;       /* CTAs = SMs of the device */
+  int32_t threads;    /* per CTA */
+  int32_t ring_slots; /* weight slots each warp keeps in flight */
+  int32_t reserved;
+  int64_t shared_bytes;
+} dq_plan_info;
+DQ_API int32_t dq_plan_workspace_bytes(int32_t num_jobs, int64_t* bytes);
+DQ_API int32_t dq_plan_create(const dq_gemv_job* jobs, int32_t num_jobs, void* workspace,
+                              int64_t workspace_bytes, void* stream, dq_plan** plan);
+DQ_API int32_t dq_plan_launch(dq_plan* plan, void* stream);
+/* Synchronises `stream` and reads the plan's status word: DQ_OK, or DQ_ERR_DEVICE with the
+ * stage that gave up in dq_last_error() (the word and the counters are then cleared, so the
+ * plan can be launched again). */
+DQ_API int32_t dq_plan_status(dq_plan* plan, void* stream);
+DQ_API int32_t dq_plan_describe(const dq_plan* plan, dq_plan_info* info);
+/* Slicing chosen for one stage: warps along the reduction axis, steps per ring slot and the
+ * CTAs given to each of its (up to four) jobs.  Any out pointer may be NULL. */
+DQ_API int32_t dq_plan_stage_shape(const dq_plan* plan, int32_t stage, int32_t* k_slices,
+                                   int32_t* slot_steps, int32_t* cta_counts);
+/* Failure-handling hook: overwrite the count stage `stage` waits for (negative: keep it) and
+ * the spin bound of every wait.  A count the previous stage can never reach makes the wait
+ * run out -- the way the tests exercise the error path without faulting anything. */
+DQ_API int32_t dq_plan_set_wait(dq_plan* plan, int32_t stage, int32_t wait_target,
+                                int32_t spin_limit, void* stream);
+DQ_API void dq_plan_destroy(dq_plan* plan);
 
 /* Same as dq_gemv with x and out in HOST memory: copies x to the device,
  * launches, copies the result back and synchronises.  `x_dev` / `out_dev` are

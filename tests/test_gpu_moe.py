@@ -134,3 +134,78 @@ def test_moe_rejects_bad_arguments():
     ids, w = seeded_routing(2, 4, 2)
     with pytest.raises(RuntimeError, match="folded to rows"):
         ops.moe_gemv(x[:2].contiguous(), ids.cuda(), w.cuda(), layer.down, layer.gate_up, num_experts=4)
+
+
+def test_moe_qwen3_shape_at_sixty_four_tokens():
+    """BASELINE's MoE configuration at its largest step: 128 experts, top-8, hidden 2048,
+    intermediate 768, 64 tokens (512 assignments, nearly every expert active)."""
+    got, want, *_ = run_case(64, 128, 2048, 768, 8, 3, 2, seed=21)
+    scale = np.abs(want).max() + 1e-30
+    assert np.abs(got - want).max() / scale <= 4e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3
+
+
+@pytest.mark.parametrize("act", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize(("bits_gu", "bits_dn"), [(2, 4), (3, 3), (4, 2), (8, 8)])
+def test_moe_stage_by_stage(act, bits_gu, bits_dn):
+    """Where the end-to-end distance comes from.  The call's scratch holds both intermediates:
+    ``h = silu(g) * u`` per assignment, rounded once to the activation dtype, and the fp32 down
+    projection ``d`` per assignment.  Checked separately:
+
+    * h is the oracle's fp32 ``silu(g) * u`` rounded once, give or take one unit in the last
+      place (with fp16 activations that is inside 1e-3 normwise; bf16's unit is 2^-8);
+    * d, computed by the oracle FROM THE KERNEL'S OWN h, is within 1e-3: the down stage adds
+      nothing beyond accumulation noise;
+    * y is the weighted sum of the kernel's own d rows, in slot order, to fp32 rounding.
+
+    So all of the layer's distance from an unrounded oracle is the one rounding of h."""
+    from dynquant_b200 import ops
+    from dynquant_b200.workloads import qwen3_moe_layer, seeded_routing
+    from oracle import oracle as O
+
+    tokens, experts, hidden, inter, topk = 12, 16, 512, 256, 4
+    layer = qwen3_moe_layer("cuda", seed=31, bits_gate_up=bits_gu, bits_down=bits_dn, num_experts=experts,
+                            hidden=hidden, inter=inter, topk=topk)
+    ids, w = seeded_routing(tokens, experts, topk, seed=5)
+    x = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(4)).to(act)
+    need = ops.moe_scratch_bytes(tokens, topk, hidden, inter, experts, act)
+    scratch = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    y = ops.moe_gemv(x.cuda(), ids.cuda(), w.cuda(), layer.gate_up, layer.down, num_experts=experts,
+                     out_dtype=torch.float32, scratch=scratch)
+    torch.cuda.synchronize()
+    n_assign = tokens * topk
+    h_bytes = n_assign * inter * 2
+    h = scratch[:h_bytes].view(act).view(n_assign, inter).cpu()
+    d_off = (h_bytes + 255) // 256 * 256
+    d = scratch[d_off:d_off + n_assign * hidden * 4].view(torch.float32).view(n_assign, hidden).cpu()
+
+    def expert_rows(bank, e, rows_per_expert):
+        part = bank.rows(e * rows_per_expert, (e + 1) * rows_per_expert)
+        return (raw(part.packed), raw(part.scales), raw(part.offsets), TAG[part.scales.dtype],
+                O.geometry(part.bits, part.group_size, part.in_features))
+
+    h_err2 = h_ref2 = 0.0
+    for t in range(tokens):
+        for k in range(topk):
+            e, aid = int(ids[t, k]), t * topk + k
+            packed, scales, offsets, tag, geom = expert_rows(layer.gate_up, e, 2 * inter)
+            gu = O.c_gemv(raw(x[t:t + 1]), TAG[act], packed, scales, offsets, tag, geom)[0]
+            g, u = gu[:inter].astype(np.float64), gu[inter:].astype(np.float64)
+            h32 = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+            got_h = h[aid].float().numpy()
+            rounded = torch.from_numpy(h32).to(act)
+            # one unit in the last place of the rounded value (the kernel's fp32 g, u differ from
+            # the oracle's double sums in the last bits, which can move a value across a tie)
+            ulp = np.maximum(np.abs(rounded.float().numpy()), 1e-4) * 2.0 ** (-(10 if act == torch.float16 else 7))
+            assert (np.abs(got_h - rounded.float().numpy()) <= ulp + 1e-6).all(), (t, k)
+            h_err2 += float(((got_h - h32) ** 2).sum())
+            h_ref2 += float((h32 ** 2).sum())
+            packed, scales, offsets, tag, geom = expert_rows(layer.down, e, hidden)
+            want_d = O.c_gemv(raw(h[aid:aid + 1]), TAG[act], packed, scales, offsets, tag, geom)[0]
+            got_d = d[aid].numpy()
+            assert np.abs(got_d - want_d).max() / (np.abs(want_d).max() + 1e-30) <= 1e-3, (t, k)
+            assert np.linalg.norm(got_d - want_d) / (np.linalg.norm(want_d) + 1e-30) <= 1e-3, (t, k)
+    if act == torch.float16:
+        assert (h_err2 / h_ref2) ** 0.5 <= 1e-3  # fp16's rounding itself is inside the bar
+    combined = (w.double().reshape(n_assign, 1) * d.double()).reshape(tokens, topk, hidden).sum(1)
+    assert float((y.cpu().double() - combined).abs().max()) <= 1e-5 * float(combined.abs().max())

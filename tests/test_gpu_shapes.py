@@ -1,0 +1,277 @@
+"""Parity at the benchmark configurations' own shapes, per kernel, and with guarded buffers.
+
+Same oracle and bars as ``test_gpu_parity.py`` (fp32 accumulators within 1e-3 of
+``x.float() @ dequant(fp32).T``, normwise and max/max).  What this file adds:
+
+* every tensor-core kernel is reached on purpose, and ``dq_last_kernel`` proves which one ran;
+* BASELINE's first configuration exactly, the corner shapes of its width/shape sweep, and the
+  248,320-row head of its decode stack;
+* canary-padded output buffers on every tail geometry: a store outside ``out`` fails the test
+  (the stand-in for a memory checker, which this pool does not offer);
+* the two SIMT paths against each other, the selection made by an environment variable in a
+  child process (reference tests/test_kernels_parity.py:232-304).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+import sys
+import textwrap
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, make_quant
+from test_gpu_parity import GEOMETRIES, oracle_dequant, oracle_gemv, within_one_ulp_16
+
+pytestmark = pytest.mark.gpu
+
+BITS = [2, 3, 4, 8]
+
+
+def random_qt(rows, k, bits, group=128, meta=torch.float16, seed=0, offsets=True):
+    """Uniform random codes, U(0.005, 0.02) scales, offsets -2^(b-1) * scale: the benchmark's data."""
+    from dynquant_b200.workloads import random_quant_tensor
+
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    qt = random_quant_tensor(rows, k, bits, group_size=group, meta_dtype=meta, device="cuda", generator=gen)
+    if not offsets:
+        qt.offsets = None
+    return qt
+
+
+def check_acc(acc: torch.Tensor, want: np.ndarray, tol: float = 1e-3) -> None:
+    got = acc.float().cpu().numpy()
+    assert got.shape == want.shape
+    scale = np.abs(want).max() + 1e-30
+    assert np.abs(got - want).max() / scale <= tol
+    assert np.linalg.norm(got - want) / (np.linalg.norm(want) + 1e-30) <= tol
+
+
+# ---- (a) the streaming kernel: long matrices, every width -------------------------------------
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize(("rows", "k", "m", "xdt", "meta", "offsets"), [
+    (19001, 512, 1, torch.bfloat16, torch.float16, True),    # rows not a multiple of 16
+    (19001, 512, 8, torch.bfloat16, torch.float16, True),
+    (20480, 512, 3, torch.float16, torch.bfloat16, False),   # fp16 x, bf16 scales, no offsets
+    (24000, 2048, 1, torch.bfloat16, torch.bfloat16, True),
+    (33000, 512, 8, torch.float16, torch.float16, True),
+])
+def test_long_matrices_take_the_streaming_kernel(bits, rows, k, m, xdt, meta, offsets):
+    from dynquant_b200 import ops
+
+    qt = random_qt(rows, k, bits, meta=meta, seed=bits * 31 + rows, offsets=offsets)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(m + bits)).to(xdt).cuda()
+    args = (x, qt.packed, qt.scales, qt.offsets, bits, 128, k)
+    acc = ops.gemv(*args, out_dtype=torch.float32)
+    assert ops.last_kernel() == "gemv_mma_stream_kernel"
+    want = oracle_gemv(x, qt)
+    check_acc(acc, want)
+    got = ops.gemv(*args)
+    assert torch.equal(got.cpu(), acc.cpu().to(xdt))  # the 16-bit output is the accumulator rounded once
+    assert within_one_ulp_16(got, want)
+    assert torch.equal(ops.gemv(*args), got)  # bit-identical repeat
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_the_register_ring_kernel_takes_what_the_other_two_refuse(bits):
+    """A long matrix whose step count is odd (K = 384: three steps) fits neither the streaming
+    kernel (whole blocks of steps) nor the tiled one (long, one matrix): gemv_mma_kernel."""
+    from dynquant_b200 import ops
+
+    rows, k = 19200, 384
+    qt = random_qt(rows, k, bits, seed=bits)
+    x = torch.randn(2, k, generator=torch.Generator().manual_seed(bits)).to(torch.bfloat16).cuda()
+    acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, 128, k, out_dtype=torch.float32)
+    assert ops.last_kernel() == "gemv_mma_kernel"
+    check_acc(acc, oracle_gemv(x, qt))
+
+
+# ---- (b) BASELINE configuration 1, exactly ------------------------------------------------------
+
+
+@pytest.mark.parametrize("meta", [torch.float16, torch.bfloat16])
+def test_baseline_config_1(meta):
+    """M=1, K=2048, N=6144, 4-bit, groups of 128, codes uniform in [0, 15], scales U(0.005, 0.02),
+    zero-point 8 written out as offsets = -8 * scale, bf16 activations ~ N(0, 1)."""
+    from dynquant_b200 import ops
+
+    qt = random_qt(6144, 2048, 4, meta=meta, seed=1)
+    assert torch.equal(qt.offsets.float(), (-8.0 * qt.scales.float()).to(meta).float())
+    x = torch.randn(1, 2048, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, 4, 128, 2048, out_dtype=torch.float32)
+    assert ops.last_kernel() == "gemv_mma_tile_kernel"
+    want = oracle_gemv(x, qt)
+    check_acc(acc, want)
+    got = ops.gemv(x, qt.packed, qt.scales, qt.offsets, 4, 128, 2048)
+    assert got.dtype == torch.bfloat16 and within_one_ulp_16(got, want)
+    dense = ops.dequant(qt.packed, qt.scales, qt.offsets, 4, 128, 2048)
+    assert (dense.cpu().view(torch.int16).numpy().view(np.uint16) == oracle_dequant(qt)).all()
+
+
+# ---- (c) corners of the width / shape sweep (configuration 5) -----------------------------------
+
+SWEEP_SHAPES = [(14336, 4096), (4096, 14336), (4096, 4096), (4097, 4096)]  # (rows N, reduction K)
+
+
+@pytest.mark.parametrize("group", [64, 128])
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("shape", range(len(SWEEP_SHAPES)))
+def test_sweep_shapes(bits, group, shape):
+    """Every (width, group, shape) of the sweep; the activation-row counts 1, 4 and 16 rotate over
+    the combinations (16 rows go through quantized_matmul's chunks of 8)."""
+    from dynquant_b200 import ops
+
+    rows, k = SWEEP_SHAPES[shape]
+    m = (1, 4, 16)[(shape + bits + group // 64) % 3]
+    qt = random_qt(rows, k, bits, group=group, seed=bits * 7 + shape)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(shape)).to(torch.bfloat16).cuda()
+    want = oracle_gemv(x, qt)
+    if m <= ops.gemv_max_rows():
+        acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, group, k, out_dtype=torch.float32)
+        assert ops.last_kernel().startswith("gemv_mma")
+    else:
+        acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
+    check_acc(acc, want)
+    out = ops.quantized_matmul(x, qt)
+    assert out.dtype == torch.bfloat16 and within_one_ulp_16(out, want)
+
+
+# ---- (d) the head of the decode stack -----------------------------------------------------------
+
+
+def test_the_248320_row_head():
+    """248,320 x 2048 at 8 bits (45 % of the benchmark step's bytes): three slabs of its rows
+    against the oracle, the rest through a row-sum identity -- the sum of all outputs equals the
+    activation against the column sums of the dequantized matrix, here checked slab by slab on
+    the GPU's own dequant (bit-exact elsewhere in this suite)."""
+    from dynquant_b200 import ops
+
+    rows, k = 248320, 2048
+    qt = random_qt(rows, k, 8, seed=8)
+    x = torch.randn(1, k, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).cuda()
+    acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, 8, 128, k, out_dtype=torch.float32)
+    assert ops.last_kernel() == "gemv_mma_stream_kernel"
+    for lo, hi in ((0, 4096), (120000, 124096), (rows - 4099, rows)):
+        check_acc(acc[:, lo:hi], oracle_gemv(x, qt.rows(lo, hi)))
+    # every row, against dequant + matmul in double on the GPU
+    total = 0.0
+    worst = 0.0
+    for lo in range(0, rows, 31040):
+        part = qt.rows(lo, lo + 31040)
+        dense = ops.dequant(part.packed, part.scales, part.offsets, 8, 128, k, out_dtype=torch.float32)
+        ref = (dense.double() @ x.double().T).T
+        worst = max(worst, float((acc[:, lo:lo + 31040].double() - ref).abs().max()))
+        total = max(total, float(ref.abs().max()))
+    assert worst / total <= 1e-3
+
+
+# ---- (g) guarded output buffers -----------------------------------------------------------------
+
+PAD = 64  # elements either side: 256 bytes of fp32
+
+
+def guarded(m, rows, dtype):
+    buf = torch.full((PAD + m * rows + PAD,), -12345.0, dtype=dtype, device="cuda")
+    return buf, buf[PAD:PAD + m * rows].view(m, rows)
+
+
+def guards_intact(buf, m, rows):
+    return bool((buf[:PAD] == -12345.0).all()) and bool((buf[PAD + m * rows:] == -12345.0).all())
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize(("rows", "k", "group"), GEOMETRIES + [(4097, 512, 128), (19001, 512, 128), (1000, 384, 128)])
+def test_gemv_never_writes_outside_its_output(rows, k, group, bits, out_dtype):
+    from dynquant_b200 import ops
+
+    qt = make_quant(rows, k, group, bits, torch.float16).to("cuda") if rows < 4000 else random_qt(rows, k, bits, group)
+    for m in (1, 5, 8):
+        x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16).cuda()
+        buf, out = guarded(m, rows, out_dtype)
+        got = ops.gemv_shards(x, [qt], out_dtype=out_dtype, out=out)
+        torch.cuda.synchronize()
+        assert guards_intact(buf, m, rows), (ops.last_kernel(), m)
+        assert not bool((got == -12345.0).any())  # and every element inside was written
+        if out_dtype == torch.float32:
+            check_acc(got, oracle_gemv(x, qt))
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize(("rows", "k", "group"), GEOMETRIES)
+def test_dequant_never_writes_outside_its_output(rows, k, group, bits):
+    from dynquant_b200 import _lib
+    from dynquant_b200.ops import _stream, _tag, weight_descriptor
+
+    qt = make_quant(rows, k, group, bits, torch.float16).to("cuda")
+    buf, out = guarded(rows, k, torch.float16)
+    w = weight_descriptor("dequant", qt.packed, qt.scales, qt.offsets, bits, qt.geometry.effective_group, k)
+    _lib.check(_lib.load().dq_dequant(ctypes.byref(w), out.data_ptr(), _tag(torch.float16, "out"), _stream(out.device)))
+    torch.cuda.synchronize()
+    assert guards_intact(buf, rows, k)
+    assert (out.cpu().view(torch.int16).numpy().view(np.uint16) == oracle_dequant(qt)).all()
+
+
+def test_fused_shards_never_write_outside_their_output():
+    from dynquant_b200 import ops
+
+    k = 1024
+    shards = [make_quant(rows, k, 128, bits, torch.float16, seed=60 + bits).to("cuda")
+              for bits, rows in ((2, 96), (3, 161), (4, 33), (8, 7))]
+    total = sum(q.num_rows for q in shards)
+    for m in (1, 8):
+        x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16).cuda()
+        buf, out = guarded(m, total, torch.float32)
+        got = ops.gemv_shards(x, shards, out_dtype=torch.float32, out=out)
+        torch.cuda.synchronize()
+        assert guards_intact(buf, m, total)
+        check_acc(got, np.concatenate([oracle_gemv(x, q) for q in shards], axis=1))
+
+
+# ---- (h) the two SIMT paths against each other --------------------------------------------------
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_the_two_simt_paths_agree(tmp_path, bits):
+    """fp32 activations take the SIMT kernels: the chunked fast path here, the general
+    block-at-a-time kernel in a child process started with DYNQUANT_GEMV_SCALAR=1 (the switch is
+    read once per process, like the reference's).  Same integers, same scales, another summation
+    order: they must agree to accumulation noise (2e-3, the reference's bar)."""
+    from dynquant_b200 import ops
+
+    saved = tmp_path / "general.pt"
+    body = textwrap.dedent(
+        f"""
+        import sys
+        sys.path.insert(0, {str(ROOT)!r})
+        sys.path.insert(0, {str(ROOT / "tests")!r})
+        import torch
+        from conftest import make_quant
+        from dynquant_b200 import ops
+        qt = make_quant(260, 2048, 128, {bits}, torch.float32, seed=7).to("cuda")
+        x = torch.randn(4, 2048, generator=torch.Generator().manual_seed(11)).cuda()
+        y = ops.gemv(x, qt.packed, qt.scales, qt.offsets, {bits}, 128, 2048)
+        WHICH
+        torch.save(y.cpu(), {str(saved)!r})
+        """
+    )
+    subprocess.run([sys.executable, "-c", body.replace("WHICH", 'assert ops.last_kernel() == "gemv_general_kernel"')],
+                   check=True, env={**os.environ, "DYNQUANT_GEMV_SCALAR": "1"})
+    qt = make_quant(260, 2048, 128, bits, torch.float32, seed=7).to("cuda")
+    x = torch.randn(4, 2048, generator=torch.Generator().manual_seed(11)).cuda()
+    fast = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, 128, 2048)
+    assert ops.last_kernel() == "gemv_fast_kernel"
+    general = torch.load(saved).cuda()
+    torch.testing.assert_close(fast, general, rtol=2e-3, atol=2e-3)
+    # and the tensor-core path on the same integers, with the activation rounded to bf16 first
+    xb = x.to(torch.bfloat16)
+    qh = make_quant(260, 2048, 128, bits, torch.float16, seed=7).to("cuda")
+    mma = ops.gemv(xb, qh.packed, qh.scales, qh.offsets, bits, 128, 2048, out_dtype=torch.float32)
+    assert ops.last_kernel().startswith("gemv_mma")
+    check_acc(mma, oracle_gemv(xb, qh))
