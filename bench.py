@@ -5,20 +5,29 @@ One "step" is one pass of the hot path over every packed linear module of the
 synthetic Qwen-style 2B decode stack (28 layers, hidden 2048, intermediate 6144,
 16 q / 8 kv heads of 128, seeded width map over {2,3,4,8} with a nominal mean of
 3.25 bits, 8-bit lm_head of 248,320 rows) at M=1 with bf16 activations: 197
-GEMV launches, 1.1 GB of packed weights, larger than L2 by an order of
-magnitude, so every step re-reads its weights from HBM.
+GEMVs, 1.15 GB of packed weights -- larger than L2 by an order of magnitude, so
+every step re-reads its weights from HBM.  The step replays from a CUDA graph:
+by default one launch per stage of a decoder layer's data flow (the members of
+a stage -- q/k/v, gate/up -- fused into one launch), ``--graph-mode plan`` for
+the whole step as one persistent kernel (``dq_plan_*``).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-prints ONE JSON line.  `value` is algorithmic GB/s with inputs resident in HBM;
-`e2e` is the same metric through the public runner with the step's activations
+prints ONE JSON line.  ``value`` is algorithmic GB/s with inputs resident in HBM;
+``e2e`` is the same metric through the public runner with the step's activations
 copied in from pinned host memory and the logits copied back, inside the timed
-region; `roofline` relates the dominant kernel to the measured HBM peak;
-`cpu_baseline` times the reference's CPU path on a bounded sample of the same
-workload on this machine's host cores.
+region; ``roofline`` relates the kernel that dominates the step to the measured
+HBM peak; ``cpu_baseline`` times the reference's CPU path on a bounded sample of
+the same workload on this machine's host cores.  Two more blocks carry the rest
+of the metric, measured in the same process after the headline region: ``moe``
+(expert layer of BASELINE's fourth configuration: tokens/s, us per layer and
+fraction of the roofline at 1, 8 and 64 tokens) and ``config3`` (the Qwen3-14B-
+shaped linear set of the third configuration).
 
-Under torchrun (N > 1) every module is column-sharded over the ranks and the
-pieces the next module needs are all-gathered over NCCL; value is whole-job.
+Under torchrun (N > 1) the modules whose per-rank slab is still large (the
+lm_head) are column-sharded over the ranks and their outputs all-gathered over
+NCCL; small modules are computed by every rank; ``value`` is whole-job, and the
+line says whether the gathered output equals the unsharded result.
 """
 
 from __future__ import annotations
@@ -40,7 +49,7 @@ METRIC = "packed_gemv_hbm_gbps_m1"
 UNIT = "GB/s"
 WORKLOAD = "qwen2b-stack-3.25bit-m1 (BASELINE config 2: 28 layers + 8-bit lm_head, 197 GEMVs/step)"
 FALLBACK_HBM_GBS = 6650.0
-TRAFFIC_PER_STEP = 1_165_303_296  # dram bytes read + written by one step; see profiles/stack_qwen2b_m1_launch_list.md
+REFERENCE_THREADS = 16  # host threads of the reference arm and the cpu baseline, at every N
 
 
 def measured_peak() -> tuple[float, str]:
@@ -115,19 +124,29 @@ class ClockSampler:
         return out
 
 
+def run_cpu_sample(spec: dict) -> dict:
+    """One run of the CPU timing script in a child process, with a fixed thread count: under
+    ``torch.distributed.run`` the environment carries OMP_NUM_THREADS=1, which would make the
+    reference arm slower at N > 1 than at N = 1."""
+    threads = min(REFERENCE_THREADS, os.cpu_count() or 1)
+    env = {**os.environ, "OMP_NUM_THREADS": str(threads), "MKL_NUM_THREADS": str(threads)}
+    spec = {**spec, "threads": threads}
+    res = subprocess.run([sys.executable, str(ROOT / "oracle" / "cpu_baseline.py"), json.dumps(spec)],
+                         capture_output=True, text=True, timeout=900, env=env)
+    if res.returncode != 0:
+        raise RuntimeError(res.stderr.strip()[-300:])
+    return json.loads(res.stdout.strip().splitlines()[-1])
+
+
 def cpu_baseline_sample(stack_modules, m: int, budget_modules: int = 56, repeat: int = 8) -> dict:
     """Time the reference CPU path on the first ``budget_modules`` modules of the stack: eight
     decoder layers (184 MB of packed weights, more than the host's last-level cache), eight
     passes -- about ten seconds of CPU work at the ~0.2 GB/s the reference's operator reaches."""
     sample = [(mod.weight.num_rows, mod.weight.in_features, mod.weight.bits) for mod in stack_modules[:budget_modules]]
-    spec = {"modules": sample, "m": m, "repeat": repeat, "seed": 7}
-    res = subprocess.run(
-        [sys.executable, str(ROOT / "oracle" / "cpu_baseline.py"), json.dumps(spec)],
-        capture_output=True, text=True, timeout=900,
-    )
-    if res.returncode != 0:
-        return {"value": None, "unit": UNIT, "cores": None, "kind": "port", "sample": f"failed: {res.stderr[-200:]}"}
-    out = json.loads(res.stdout.strip().splitlines()[-1])
+    try:
+        out = run_cpu_sample({"modules": sample, "m": m, "repeat": repeat, "seed": 7})
+    except (RuntimeError, subprocess.TimeoutExpired) as exc:
+        return {"value": None, "unit": UNIT, "cores": None, "kind": "port", "sample": f"failed: {exc}"}
     return {
         "value": round(out["gbps"], 4), "unit": UNIT, "cores": out["cores"], "kind": out["kind"],
         "sample": f"{out['modules']} GEMVs (first {budget_modules} modules of the stack x{repeat}, "
@@ -157,14 +176,11 @@ def run_reference(args) -> None:
     spec = {"modules": sample, "m": 1, "repeat": 1, "seed": 7}
     times, last = [], None
     for i in range(args.warmup + args.steps):
-        res = subprocess.run(
-            [sys.executable, str(ROOT / "oracle" / "cpu_baseline.py"), json.dumps(spec)],
-            capture_output=True, text=True, timeout=900,
-        )
-        if res.returncode != 0:
-            print(json.dumps({"impl": "reference", "unavailable": res.stderr.strip()[-200:]}))
+        try:
+            last = run_cpu_sample(spec)
+        except (RuntimeError, subprocess.TimeoutExpired) as exc:
+            print(json.dumps({"impl": "reference", "unavailable": str(exc)[-200:]}))
             return
-        last = json.loads(res.stdout.strip().splitlines()[-1])
         if i >= args.warmup:
             times.append(last["seconds"])
     sec = sum(times) / len(times)
@@ -173,7 +189,7 @@ def run_reference(args) -> None:
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": {"workload": WORKLOAD, "m": 1, "sample": sample_txt},
         "cpu_baseline": {"value": round(value, 4), "unit": UNIT, "cores": last["cores"], "kind": last["kind"],
                          "sample": sample_txt},
@@ -201,6 +217,84 @@ def time_steps(fn, steps: int, warmup: int, sync, barrier):
     return start.elapsed_time(stop) / 1e3  # seconds
 
 
+def max_over_ranks(seconds: float, dist, device) -> float:
+    if dist is None:
+        return seconds
+    import torch
+
+    t = torch.tensor([seconds], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def capture_runner(runner, mode: str) -> str:
+    """Capture a StepRunner in ``mode``; a stack the plan kernel cannot take falls back to the
+    launch-per-stage graph (still this library's kernels).  Returns the mode in use."""
+    if mode == "plan":
+        try:
+            runner.capture("plan")
+            return "plan"
+        except RuntimeError as exc:
+            if "dq_gemv_sequence" not in str(exc):
+                raise
+            mode = "dataflow"
+    runner.capture(mode)
+    return mode
+
+
+def full_sharded_names(full, world: int, shard_min_bytes: int = 32 << 20) -> list[str]:
+    return [mod.name for mod in full.modules
+            if mod.weight.num_rows % world == 0 and mod.weight.nbytes // world >= shard_min_bytes]
+
+
+def config3_block(args, rank, world, device, dist, peak) -> dict:
+    """BASELINE's third configuration: the Qwen3-14B-shaped linear set (40 layers, hidden 5120,
+    intermediate 17408, seeded 3/4-bit map), every module column-sharded over the ranks (each
+    rank generates and holds only its slab of rows), M = 1.  The per-rank step is one plan
+    kernel; under N > 1 the slabs' outputs are all-gathered after it (one NCCL call per module,
+    issued after the step -- the synthetic set's activations are resident, so nothing in the
+    step waits for a gather)."""
+    import torch
+
+    from dynquant_b200.stack import StepRunner
+    from dynquant_b200.workloads import qwen14b_linear_set
+
+    local = qwen14b_linear_set(device=device, shard=(rank, world))
+    runner = StepRunner(local, 1, device=device)
+    mode = capture_runner(runner, args.graph_mode)
+    gathers = []
+    if world > 1:
+        for mod in local.modules:
+            piece = runner.outputs[mod.name]
+            gathers.append((piece, torch.empty(world, piece.shape[1], dtype=piece.dtype, device=device)))
+
+    def step():
+        runner.replay()
+        for piece, full in gathers:
+            dist.all_gather_into_tensor(full, piece)
+
+    def sync():
+        torch.cuda.synchronize(device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    steps = max(5, args.steps // 3)
+    seconds = max_over_ranks(time_steps(step, steps, 3, sync, barrier), dist, device) / steps
+    local_bytes = local.algorithmic_bytes(1)
+    total_bytes = local_bytes * world
+    return {
+        "workload": "qwen3-14b-shaped linear set (BASELINE config 3: 40 layers x 7 modules, 3/4-bit, M=1)",
+        "placement": "single gpu" if world == 1 else f"every module column-sharded x{world}, NCCL all-gather per module",
+        "launch": f"cuda graph, {mode}", "launches_per_step": runner.launches_per_step,
+        "ms_per_step": round(seconds * 1e3, 4), "weight_bytes_per_gpu": local.weight_bytes,
+        "gbps_aggregate": round(total_bytes / seconds / 1e9, 1),
+        "gbps_per_gpu": round(local_bytes / seconds / 1e9, 1),
+        "frac_of_hbm_peak_per_gpu": round(local_bytes / seconds / 1e9 / peak, 4),
+    }
+
+
 def run_ours(args) -> None:
     import torch
 
@@ -214,38 +308,41 @@ def run_ours(args) -> None:
     device = torch.device("cuda", local)
     dist = None
     if world > 1:
+        import datetime
+
         import torch.distributed as dist_mod
 
         dist = dist_mod
-        import datetime
-
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=120))
 
     from dynquant_b200 import _lib
     from dynquant_b200.stack import StepRunner
-    from dynquant_b200.workloads import qwen2b_stack
+    from dynquant_b200.workloads import LinearStack, qwen2b_stack
 
     _lib.load()
     m = args.m
-    full = qwen2b_stack(device="cpu" if False else device, layers=args.layers)  # generated on the GPU
+    full = qwen2b_stack(device=device, layers=args.layers)  # generated on the GPU, same on every rank
+    use_graph = not args.no_graph
+    sharded_matches = None
     if world > 1:
         from dynquant_b200.sharded import ShardedStepRunner
 
-        use_graph = not args.no_graph
         runner = ShardedStepRunner(full, m, rank=rank, world=world, device=device,
                                    graph_mode=args.graph_mode if use_graph else None)
         step_fn = runner.run
-        launches_per_step = runner.launches_per_step
+        mode = runner.graph_mode
+        local_bytes = runner.local_stack.algorithmic_bytes(m)
     else:
         runner = StepRunner(full, m, device=device)
-        use_graph = not args.no_graph
+        mode = None
         if use_graph:
-            runner.capture(args.graph_mode)
+            mode = capture_runner(runner, args.graph_mode)
             step_fn = runner.replay
         else:
             step_fn = runner.run
             runner.count_launches()
-        launches_per_step = runner.launches_per_step
+        local_bytes = full.algorithmic_bytes(m)
+    launches_per_step = runner.launches_per_step
     step_bytes = full.algorithmic_bytes(m)
 
     def sync():
@@ -259,12 +356,29 @@ def run_ours(args) -> None:
         seconds = time_steps(step_fn, args.steps, args.warmup, sync, barrier)
         time.sleep(0.15)
     clock_summary = clocks.summary()
-    if dist is not None:
-        t = torch.tensor([seconds], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        seconds = float(t.item())
+    seconds = max_over_ranks(seconds, dist, device)
     per_step = seconds / args.steps
     value = step_bytes / per_step / 1e9
+    if world == 1 and mode == "plan":
+        runner.plan().check()  # no stage's bounded wait ran out during the timed steps
+
+    # ---- sharded runs: the gathered output against the same module computed unsharded ----
+    if world > 1 and runner.sharded:
+        name = runner.sharded[-1]
+        mod = next(mm for mm in full.modules if mm.name == name)
+        single = StepRunner(LinearStack("check", full.hidden, full.intermediate, [mod], full.bit_map), m, device=device)
+        single.inputs[mod.input].copy_(runner.inputs[mod.input])
+        try:
+            single.run_plan()
+            single.plan().check()
+        except RuntimeError:
+            single.run()
+        sync()
+        same = torch.equal(single.outputs[name], runner.gathered(name))
+        flag = torch.tensor([1 if same else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        sharded_matches = bool(flag.item())
+        del single
 
     # ---- end to end: activations in from pinned host memory, logits back ----
     host_in = {k: v.cpu().pin_memory() for k, v in runner.inputs.items()}
@@ -274,10 +388,10 @@ def run_ours(args) -> None:
     h2d = sum(v.numel() * v.element_size() for v in host_in.values())
     d2h = host_out.numel() * host_out.element_size()
 
-    io_graph = world == 1 and use_graph and args.graph_mode in ("plan", "dataflow", "chain") and not args.e2e_eager_copies
+    io_graph = world == 1 and use_graph and mode in ("plan", "dataflow", "chain") and not args.e2e_eager_copies
     if io_graph:
         # the serving loop's form: pinned staging buffers, copies and kernels in one graph
-        runner.capture_with_io(host_in, last_name, host_out, args.graph_mode)
+        runner.capture_with_io(host_in, last_name, host_out, mode)
 
     def e2e_step():
         if io_graph:
@@ -295,57 +409,92 @@ def run_ours(args) -> None:
     t0 = time.perf_counter()
     for _ in range(args.steps):
         e2e_step()
-    e2e_seconds = time.perf_counter() - t0
-    if dist is not None:
-        t = torch.tensor([e2e_seconds], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_seconds = float(t.item())
+    e2e_seconds = max_over_ranks(time.perf_counter() - t0, dist, device)
     e2e_value = step_bytes / (e2e_seconds / args.steps) / 1e9
+
+    peak, peak_kind = measured_peak()
+
+    # ---- the dominant kernel, on its own: bytes one launch moves / that launch's duration ----
+    # One plan launch IS the step.  In the launch-per-stage modes the lm_head launch (45 % of the
+    # bytes) is timed apart and the decoder-block launches get the rest of the step.
+    launches = launches_per_step * args.steps
+    if mode == "plan":
+        kernel = "gemv_plan_kernel"
+        kernel_bytes, kernel_seconds = local_bytes, per_step
+        other = None
+    else:
+        head = full.modules[-1] if world == 1 else runner.local_stack.modules[-1]
+        head_bytes = head.weight.nbytes + m * head.weight.in_features * 2 + m * head.weight.num_rows * 2
+        hr = StepRunner(LinearStack("head", full.hidden, full.intermediate, [head], full.bit_map), m, device=device)
+        hr.capture("chain")
+        head_seconds = time_steps(hr.replay, 20, 3, sync, lambda: None) / 20
+        kernel = "gemv_mma_tile_kernel"
+        kernel_bytes = (local_bytes - head_bytes) / max(1, launches_per_step - 1)
+        kernel_seconds = max(per_step - head_seconds, 1e-9) / max(1, launches_per_step - 1)
+        other = {"kernel": "gemv_mma_stream_kernel (lm_head)", "bytes": head_bytes,
+                 "us": round(head_seconds * 1e6, 2), "frac": round(head_bytes / head_seconds / 1e9 / peak, 4)}
+        del hr
+    achieved = kernel_bytes / kernel_seconds / 1e9
+
+    # The second denominator: what a read-only stream and a copy reach on this GPU, now, through
+    # this library's own launch path (the reference quotes against the same pair, measured in
+    # its own session: commands/bench.py:95-120).  Outside the timed regions.
+    probe = None
+    if not args.no_probe and rank == 0:
+        from dynquant_b200 import ops as _ops
+
+        probe = _ops.achievable_bandwidth(nbytes=4 << 30, iters=10, device=device)
+
+    # ---- the rest of the metric: expert layer (config 4) and the 14B linear set (config 3) ----
+    extras = {}
+    parallelism = ("single gpu" if world == 1 else
+                   f"large layers ({', '.join(full_sharded_names(full, world))}) column-sharded x{world} with an NCCL "
+                   f"all-gather, small layers computed on every rank")
+    weight_bytes = full.weight_bytes
+    cpu_modules = [(mod.weight.num_rows, mod.weight.in_features, mod.weight.bits) for mod in full.modules[:56]]
+    if not args.no_extras and args.layers == 28:
+        del runner, step_fn, full, host_in, host_out, logits_dev
+        torch.cuda.empty_cache()
+        sys.path.insert(0, str(ROOT / "benchmarks"))
+        import moe_bench
+
+        tokens = [t for t in (1, 8, 64) if world == 1 or (t % world == 0)]
+        extras["moe"] = {
+            "metric": "moe_decode_tokens_per_s", "n_gpus": world,
+            "placement": "single gpu" if world == 1 else f"experts placed over {world} ranks, all-to-all exchange (NCCL)",
+            "points": moe_bench.measure(tokens, layers=6, steps=20, rank=rank, world=world, device=device, dist=dist),
+        }
+        torch.cuda.empty_cache()
+        extras["config3"] = config3_block(args, rank, world, device, dist, peak)
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    peak, peak_kind = measured_peak()
-    # The second denominator: what a read-only stream and a copy reach on this GPU, now, through
-    # this library's own launch path (the reference quotes against the same pair, measured in
-    # its own session: commands/bench.py:95-120).  Outside the timed regions.
-    probe = None
-    if not args.no_probe:
-        from dynquant_b200 import ops as _ops
-
-        probe = _ops.achievable_bandwidth(nbytes=4 << 30, iters=10, device=device)
-    launches = launches_per_step * args.steps
-    avg_launch_s = seconds / launches
-    bytes_per_launch = step_bytes / launches_per_step
-    achieved = bytes_per_launch / avg_launch_s / 1e9 * (world if world > 1 else 1) / max(world, 1)
-    # dram__bytes_read.sum + dram__bytes_write.sum of one step, from the ncu launch list of this
-    # very command (profiles/stack_qwen2b_m1_launch_list.md), spread over the step's launches.
-    traffic = (round(TRAFFIC_PER_STEP / launches_per_step)
-               if (args.layers == 28 and m == 1 and world == 1) else None)
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(per_step * 1e3, 4), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
             "workload": WORKLOAD if args.layers == 28 else f"qwen2b-stack reduced to {args.layers} layers",
             "m": m, "activations": "bf16", "scales": "fp16", "group_size": 128,
-            "weight_bytes": full.weight_bytes, "algorithmic_bytes_per_step": step_bytes,
+            "weight_bytes": weight_bytes, "algorithmic_bytes_per_step": step_bytes,
             "l2": "working set (1.1 GB of weights per step) is larger than L2; no flush needed",
-            "launch": (f"cuda graph of one step, {args.graph_mode} edges, programmatic dependent launch"
-                       if use_graph else "dq_gemv_sequence per step"),
-            "parallelism": ("single gpu" if world == 1 else
-                            f"large layers ({', '.join(runner.sharded)}) column-sharded x{world} with an NCCL "
-                            f"all-gather, small layers computed on every rank"),
+            "launch": (f"cuda graph of one step: {mode}" if use_graph else "dq_gemv_sequence per step"),
+            "parallelism": parallelism,
             "peak": f"{peak} GB/s ({peak_kind})",
         },
         "roofline": {
             "bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-            "frac": round(achieved / peak, 4), "traffic": traffic,
-            "kernel": "gemv_mma_tile_kernel (decoder-block layers, fused shards) / gemv_mma_stream_kernel "
-                      f"(lm_head); per-launch average over the {launches_per_step} launches of a step",
-            "bytes_per_launch": round(bytes_per_launch), "avg_launch_us": round(avg_launch_s * 1e6, 3),
+            "frac": round(achieved / peak, 4),
+            "kernel": kernel, "bytes_per_launch": round(kernel_bytes), "launch_us": round(kernel_seconds * 1e6, 3),
+            "per_gpu": world > 1,
+            "traffic": None, "traffic_source": "ncu capture of this command, summarised under profiles/ (not measured in this run)",
+            "step_average": {"bytes_per_launch": round(local_bytes / launches_per_step),
+                             "launch_us": round(per_step / launches_per_step * 1e6, 3),
+                             "frac": round(local_bytes / per_step / 1e9 / peak, 4)},
+            "other_kernel": other,
             "probe": (None if probe is None else {
                 "read_gbs": round(probe["read_gbs"], 1), "copy_gbs": round(probe["copy_gbs"], 1),
                 "bytes": probe["bytes"], "frac_of_read": round(achieved / probe["read_gbs"], 4),
@@ -356,8 +505,20 @@ def run_ours(args) -> None:
         "gpu_launches": launches,
         "clocks": clock_summary,
     }
+    if sharded_matches is not None:
+        line["sharded_matches"] = sharded_matches
+    line.update(extras)
     if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline_sample(full.modules, m)
+        try:
+            out = run_cpu_sample({"modules": cpu_modules, "m": m, "repeat": 8, "seed": 7})
+            line["cpu_baseline"] = {
+                "value": round(out["gbps"], 4), "unit": UNIT, "cores": out["cores"], "kind": out["kind"],
+                "sample": f"{out['modules']} GEMVs (first {len(cpu_modules)} modules of the stack x8, "
+                          f"{out['bytes'] / 1e6:.1f} MB algorithmic) in {out['seconds']:.2f} s",
+                "seconds": round(out["seconds"], 3),
+            }
+        except (RuntimeError, subprocess.TimeoutExpired) as exc:
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": None, "kind": "port", "sample": f"failed: {exc}"}
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
@@ -374,11 +535,13 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true", help="launch with dq_gemv_sequence instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-probe", action="store_true", help="skip the read/copy bandwidth probe")
+    ap.add_argument("--no-extras", action="store_true", help="skip the moe and config3 blocks")
     ap.add_argument("--e2e-eager-copies", action="store_true",
                     help="end-to-end arm: issue the host<->device copies as separate calls around the step's graph")
-    ap.add_argument("--graph-mode", choices=["plan", "dataflow", "chain", "independent"], default="plan",
-                    help="edges of the captured step: a decoder layer's data dependencies (default), "
-                         "a strict chain, or none")
+    ap.add_argument("--graph-mode", choices=["plan", "dataflow", "chain", "independent"], default="dataflow",
+                    help="the captured step: a launch per stage with a decoder layer's data dependencies (default, "
+                         "the fastest measured), one whole-step plan kernel, a strict chain of launches, or "
+                         "launches with no edges")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

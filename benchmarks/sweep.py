@@ -7,10 +7,10 @@ exceeds twice the L2 (so the bytes really come from HBM) and is timed with CUDA 
 M above the operator's row limit of 8 is issued as several GEMV launches up to 64 rows, and
 through the dequant + dense path beyond, as in the reference.
 
-    python -m dynquant_b200.sweep                      # the full config-5 grid
-    python -m dynquant_b200.sweep --shape 131072x2048 --bits 8 --m 1 --launches 4 --ring 1
+    python benchmarks/sweep.py                      # the full config-5 grid
+    python benchmarks/sweep.py --shape 131072x2048 --bits 8 --m 1 --launches 4 --ring 1
                                                        # one point, few launches (for ncu)
-    python -m dynquant_b200.sweep --op dequant --shape 32768x4096 --group 128
+    python benchmarks/sweep.py --op dequant --shape 32768x4096 --group 128
                                                        # the dequant operator instead (write-bound)
 
 Prints one JSON object per point.
@@ -20,14 +20,17 @@ from __future__ import annotations
 
 import argparse
 import json
+import sys
 from pathlib import Path
 
 import torch
 
-from . import ops
-from .workloads import random_quant_tensor
-
 ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from dynquant_b200 import ops  # noqa: E402
+from dynquant_b200.workloads import random_quant_tensor  # noqa: E402
 
 
 def hbm_peak_gbs() -> tuple[float, str]:

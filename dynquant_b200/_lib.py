@@ -76,7 +76,7 @@ class PlanInfo(ctypes.Structure):
         ("grid", ctypes.c_int32),
         ("threads", ctypes.c_int32),
         ("ring_slots", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("launches", ctypes.c_int32),
         ("shared_bytes", ctypes.c_int64),
     ]
 

@@ -92,9 +92,17 @@ struct PlanParams {
   const PJob* jobs;
   unsigned int* counters;  // [nstages] completion counters, then [nstages] = CTAs that left, [nstages + 1] = status
   int nstages;
+  int first_stage, last_stage;  // this launch runs stages [first_stage, last_stage)
+  int njobs;
+  int tables_in_smem;  // 1: every CTA keeps its own copy of the two tables in shared memory
   int nb;          // ring slots per warp
   int spin_limit;
-  uint32_t magic;  // 16-bit magic constant in both halves; a parameter so it stays a register operand
+  int area_bytes;  // bytes of the staged-activation area (the tables follow it in shared memory)
+  uint32_t magic;
+#ifdef DQ_PLAN_TRACE
+  unsigned long long* trace;  // [nstages][2 CTAs][8] device timestamps (diagnostic builds only)
+  int debug_flags;            // 1: arrive without fence/release, 2: poll with relaxed loads, 4: no waits (timing experiments only)
+#endif  // 16-bit magic constant in both halves; a parameter so it stays a register operand
 };
 
 __device__ __forceinline__ unsigned int ld_acquire(const unsigned int* p) {
@@ -111,15 +119,38 @@ __device__ __forceinline__ void red_release_add(unsigned int* p, unsigned int v)
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+#ifdef DQ_PLAN_TRACE
+__device__ int g_debug_relaxed_poll = 0;
+#endif
+
 // Bounded wait for *ctr >= target.  False when the bound ran out or another CTA already failed.
 __device__ __forceinline__ bool wait_counter(const unsigned int* ctr, unsigned int target, const unsigned int* status,
                                              int limit) {
   for (int it = 0; it < limit; ++it) {
+#ifdef DQ_PLAN_TRACE
+    if (g_debug_relaxed_poll) {
+      if (ld_relaxed(ctr) >= target) return true;
+      continue;
+    }
+#endif
     if (ld_acquire(ctr) >= target) return true;
     if ((it & 63) == 63 && ld_relaxed(status) != 0u) return false;
   }
   return false;
 }
+
+#ifdef DQ_PLAN_TRACE
+__device__ __forceinline__ void trace_point(const PlanParams& P, int stage, int point) {
+  if (P.trace != nullptr && threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    P.trace[(static_cast<size_t>(stage) * 2 + (blockIdx.x == 0 ? 0 : 1)) * 8 + point] = t;
+  }
+}
+#define DQ_TRACE(stage, point) trace_point(P, stage, point)
+#else
+#define DQ_TRACE(stage, point)
+#endif
 
 __device__ __forceinline__ void wait_pending(int n) {
   switch (n) {
@@ -239,12 +270,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
   unsigned char* const area = reinterpret_cast<unsigned char*>(red + kRedFloats);
   if (tid == 0) s_abort = 0;
 
+  // The stage and job tables are read at every stage and item boundary, by both cursors: from
+  // shared memory when they fit (a copy per CTA), so that no L2 round trip sits between two stages.
+  const PStage* stages = P.stages;
+  const PJob* jobs = P.jobs;
+  if (P.tables_in_smem) {
+    unsigned char* tables = area + P.area_bytes;
+    const int stage_words = P.nstages * static_cast<int>(sizeof(PStage) / 4);
+    const int job_words = P.njobs * static_cast<int>(sizeof(PJob) / 4);
+    uint32_t* dst_s = reinterpret_cast<uint32_t*>(tables);
+    uint32_t* dst_j = dst_s + stage_words;
+    const uint32_t* src_s = reinterpret_cast<const uint32_t*>(P.stages);
+    const uint32_t* src_j = reinterpret_cast<const uint32_t*>(P.jobs);
+    for (int i = tid; i < stage_words; i += kThreads) dst_s[i] = src_s[i];
+    for (int i = tid; i < job_words; i += kThreads) dst_j[i] = src_j[i];
+    stages = reinterpret_cast<const PStage*>(dst_s);
+    jobs = reinterpret_cast<const PJob*>(dst_j);
+    __syncthreads();
+  }
+
   // ---- prefetch cursor: this warp's sequence of (stage, item, chunk) slots, nb ahead ----
-  int pf_stage = -1, pf_item = 0, pf_items = 0, pf_stride = 1, pf_job = 0;
+  int pf_stage = P.first_stage - 1, pf_item = 0, pf_items = 0, pf_stride = 1, pf_job = 0;
   int pf_chunk = 0, pf_nchunks = 1, pf_cs = 1, pf_bits = 2, pf_step0 = 0, pf_rw = 1, pf_rwi = 0;
   bool pf_valid = false, pf_meta_live = false;
+  bool pf_seek_pending = false;  // the cursor finished an item and has not looked for the next one yet
   const unsigned char* pf_base = nullptr;  // the job's packed words
   uint32_t pf_off[4] = {0u, 0u, 0u, 0u};   // byte offset of each 16-byte piece this lane copies, at step 0 of the row
+  uint32_t pf_piece[4] = {0u, 0u, 0u, 0u}; // which (row, part) of a tile's step each of them is, at this stage's width
   int pf_pieces = 0;                       // how many of them are real
   const unsigned short* pf_meta = nullptr; // this lane's metadata array at its row
   int pf_slot = 0;
@@ -252,60 +304,64 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
 
   auto pf_seek = [&]() {
     pf_valid = false;
+#pragma unroll 1
     while (true) {
-      if (pf_stage >= 0 && pf_item < pf_items) {
-        const PJob& J = P.jobs[pf_job];
+      if (pf_stage >= P.first_stage && pf_item < pf_items) {
+        const PJob& J = jobs[pf_job];
         const int tile = pf_item * pf_rw + pf_rwi;
-        const int tiles = __ldg(&J.tiles);
+        const int tiles = J.tiles;
         if (tile < tiles) {
-          const int bits = pf_bits;
-          const int rows = __ldg(&J.rows);
-          const uint32_t row_bytes = static_cast<uint32_t>(__ldg(&J.words_per_row)) * 4u;
-          const int npieces = 16 * bits;  // 16-byte pieces of one step of 16 rows
-          pf_pieces = 0;
+          const int rows = J.rows;
+          const uint32_t row_bytes = static_cast<uint32_t>(J.words_per_row) * 4u;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const int p = lane + i * kWarp;
-            if (p < npieces) {
-              const int r = p / bits;
-              const int part = p - r * bits;
-              const int row = min(tile * kTileRows + r, rows - 1);
-              pf_off[i] = static_cast<uint32_t>(row) * row_bytes + part * 16;
-              pf_pieces = i + 1;
-            }
+            // pf_piece: (row of the tile << 8 | byte offset inside the row's step), resolved once per stage
+            const int row = min(tile * kTileRows + static_cast<int>(pf_piece[i] >> 8), rows - 1);
+            pf_off[i] = static_cast<uint32_t>(row) * row_bytes + (pf_piece[i] & 0xffu);
           }
-          pf_base = reinterpret_cast<const unsigned char*>(__ldg(reinterpret_cast<const unsigned long long*>(&J.packed)));
-          const void* arr = (t & 1) ? reinterpret_cast<const void*>(__ldg(reinterpret_cast<const unsigned long long*>(&J.offsets)))
-                                    : reinterpret_cast<const void*>(__ldg(reinterpret_cast<const unsigned long long*>(&J.scales)));
+          pf_base = reinterpret_cast<const unsigned char*>(reinterpret_cast<unsigned long long>(J.packed));
+          const void* arr = (t & 1) ? reinterpret_cast<const void*>(reinterpret_cast<unsigned long long>(J.offsets))
+                                    : reinterpret_cast<const void*>(reinterpret_cast<unsigned long long>(J.scales));
           pf_meta_live = arr != nullptr;
           const int mrow = min(tile * kTileRows + g + ((t & 2) ? 8 : 0), rows - 1);
-          pf_meta = reinterpret_cast<const unsigned short*>(arr) + static_cast<int64_t>(mrow) * __ldg(&J.num_groups);
+          pf_meta = reinterpret_cast<const unsigned short*>(arr) + static_cast<int64_t>(mrow) * J.num_groups;
           pf_chunk = 0;
           pf_valid = true;
           return;
         }
         pf_item = pf_items;  // rows beyond the last tile: nothing further in this job for this warp
       }
-      if (++pf_stage >= P.nstages) {
-        pf_stage = P.nstages;
+      if (++pf_stage >= P.last_stage) {
+        pf_stage = P.last_stage;
         pf_items = 0;
         return;
       }
-      const PStage& S = P.stages[pf_stage];
+      const PStage& S = stages[pf_stage];
       pf_items = 0;
-      const int jb = __ldg(&S.job_begin), nj = __ldg(&S.njobs);
+      const int jb = S.job_begin, nj = S.njobs;
+#pragma unroll 1
       for (int j = 0; j < nj; ++j) {
-        const PJob& J = P.jobs[jb + j];
-        const int cb = __ldg(&J.cta_begin), cc = __ldg(&J.cta_count);
+        const PJob& J = jobs[jb + j];
+        const int cb = J.cta_begin, cc = J.cta_count;
         if (cta >= cb && cta < cb + cc) {
-          const int kw = __ldg(&S.kw);
+          const int kw = S.kw;
           pf_job = jb + j;
-          pf_items = __ldg(&J.items);
+          pf_items = J.items;
           pf_item = cta - cb;
           pf_stride = cc;
-          pf_bits = __ldg(&J.bits);
-          pf_cs = __ldg(&S.cs);
-          const int spw = __ldg(&S.spw);
+          pf_bits = J.bits;
+          pf_pieces = 0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int pc = lane + i * kWarp;  // 16-byte pieces of one step of 16 rows: 16 * bits of them
+            if (pc < 16 * pf_bits) {
+              const int r = pc / pf_bits;
+              pf_piece[i] = (static_cast<uint32_t>(r) << 8) | static_cast<uint32_t>((pc - r * pf_bits) * 16);
+              pf_pieces = i + 1;
+            }
+          }
+          pf_cs = S.cs;
+          const int spw = S.spw;
           pf_nchunks = spw / pf_cs;
           pf_rw = kWarps / kw;
           pf_rwi = warp / kw;
@@ -316,13 +372,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
   };
 
   // Request the slot at the cursor (if any) into ring slot pf_slot, move the cursor on.
+  // The search for the next item reads the tables and resolves this lane's source addresses: a
+  // few hundred instructions.  It is left pending when an item ends and done at the next
+  // request -- or earlier, at a point off the chain between two stages (pf_catch_up).
+  auto pf_catch_up = [&]() {
+    if (pf_seek_pending) {
+      pf_seek_pending = false;
+      pf_seek();
+    }
+  };
   auto pf_issue = [&]() {
+    pf_catch_up();
     if (pf_valid) {
       const uint32_t dst = ring_s + pf_slot * kSlotBytes;
       const int step_bytes = 16 * pf_bits;
       const int first = pf_step0 + pf_chunk * pf_cs;  // first step of the slot
       const unsigned char* src0 = pf_base + static_cast<uint32_t>(first * step_bytes);
       const int slot_step = 16 * step_bytes;  // bytes of one step of 16 rows in the slot
+#pragma unroll 1
       for (int j = 0; j < pf_cs; ++j) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -342,14 +409,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
       }
       if (++pf_chunk == pf_nchunks) {
         pf_item += pf_stride;
-        pf_seek();
+        pf_valid = false;
+        pf_seek_pending = true;
       }
     }
     stream::cp_async_commit();  // an empty group keeps the wait arithmetic uniform
     if (++pf_slot == nb) pf_slot = 0;
   };
 
-  pf_seek();
+  pf_seek_pending = true;  // (the first request looks for the first item)
   for (int i = 0; i < nb; ++i) pf_issue();
   __syncthreads();  // s_abort is initialised
 
@@ -357,14 +425,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
   int parity = 0;
   bool aborted = false;
 
-  for (int s = 0; s < P.nstages && !aborted; ++s) {
-    const PStage& S = P.stages[s];
+#pragma unroll 1
+  for (int s = P.first_stage; s < P.last_stage && !aborted; ++s) {
+    const PStage& S = stages[s];
     // ---- which job of the stage is this CTA's ----
-    const int jb = __ldg(&S.job_begin), nj = __ldg(&S.njobs);
+    const int jb = S.job_begin, nj = S.njobs;
     int my_job = -1, cta_rel = 0, cta_count = 1;
     for (int j = 0; j < nj; ++j) {
-      const PJob& J = P.jobs[jb + j];
-      const int cb = __ldg(&J.cta_begin), cc = __ldg(&J.cta_count);
+      const PJob& J = jobs[jb + j];
+      const int cb = J.cta_begin, cc = J.cta_count;
       if (cta >= cb && cta < cb + cc) {
         my_job = jb + j;
         cta_rel = cta - cb;
@@ -372,30 +441,31 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
       }
     }
     if (my_job < 0) continue;  // nothing of this stage is ours (and the prefetch cursor skipped it too)
-    const PJob& J = P.jobs[my_job];
-    const int bits = __ldg(&J.bits);
-    const int items = __ldg(&J.items);
-    const int tiles = __ldg(&J.tiles);
-    const int kw = __ldg(&S.kw), spw = __ldg(&S.spw), cs = __ldg(&S.cs);
+    DQ_TRACE(s, 0);
+    const PJob& J = jobs[my_job];
+    const int bits = J.bits;
+    const int items = J.items;
+    const int tiles = J.tiles;
+    const int kw = S.kw, spw = S.spw, cs = S.cs;
     const int rw = kWarps / kw;
     const int rwi = warp / kw;
     const int kwi = warp - rwi * kw;
     const int nchunks = spw / cs;
-    const int steps = __ldg(&S.steps);
-    const int m = __ldg(&S.m);
-    const bool mbf = __ldg(&S.meta_bf16) != 0;
+    const int steps = S.steps;
+    const int m = S.m;
+    const bool mbf = S.meta_bf16 != 0;
     GemvArgs a = {};
-    a.x = reinterpret_cast<const void*>(__ldg(reinterpret_cast<const unsigned long long*>(&S.x)));
-    a.in_features = __ldg(&S.in_features);
+    a.x = reinterpret_cast<const void*>(reinterpret_cast<unsigned long long>(S.x));
+    a.in_features = S.in_features;
     a.m = m;
     a.x_dtype = XBF16 ? DQ_BF16 : DQ_F16;
-    a.out_dtype = __ldg(&S.out_dtype);
-    a.bias = reinterpret_cast<const void*>(__ldg(reinterpret_cast<const unsigned long long*>(&J.bias)));
-    a.out = reinterpret_cast<void*>(__ldg(reinterpret_cast<const unsigned long long*>(&J.out)));
-    a.out_stride = __ldg(reinterpret_cast<const long long*>(&J.out_stride));
-    a.out_col0 = __ldg(reinterpret_cast<const long long*>(&J.out_col0));
-    a.rows = __ldg(&J.rows);
-    const bool has_off = __ldg(reinterpret_cast<const unsigned long long*>(&J.offsets)) != 0ull;
+    a.out_dtype = S.out_dtype;
+    a.bias = reinterpret_cast<const void*>(reinterpret_cast<unsigned long long>(J.bias));
+    a.out = reinterpret_cast<void*>(reinterpret_cast<unsigned long long>(J.out));
+    a.out_stride = J.out_stride;
+    a.out_col0 = J.out_col0;
+    a.rows = J.rows;
+    const bool has_off = reinterpret_cast<unsigned long long>(J.offsets) != 0ull;
 
     // ---- staged activation of this stage, in the fragment order of this job's width ----
     const int NA = bits == 8 ? 32 : 16;
@@ -410,30 +480,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
     } else {
       stage_zero_fill<4, false>(m, steps, m_stride_u4, xb, xsum, xneg, tid, kThreads);
     }
-    const int wait_stage = __ldg(&S.wait_stage);
-    if (wait_stage >= 0 && warp * kWarp < m * steps * 4) {
-      // this warp reads the activation: it waits, bounded, for the stage that produces it
-      int ok = 1;
+    const int wait_stage = S.wait_stage;
+    const bool stager = warp * kWarp < m * steps * 4;  // this warp builds fragments (tasks go round-robin over threads)
+    int ok = 1;
+#ifdef DQ_PLAN_TRACE
+    const bool skip_wait = (P.debug_flags & 4) != 0;  // (timing experiment: arithmetic without the chain)
+#else
+    constexpr bool skip_wait = false;
+#endif
+    if (stager && wait_stage >= P.first_stage && !skip_wait) {  // (an earlier launch's stages are complete: stream order)
+      // it reads the activation: it waits, bounded, for the stage that produces it
       if (lane == 0) {
-        ok = wait_counter(P.counters + wait_stage, static_cast<unsigned int>(__ldg(&S.wait_target)), status,
-                          P.spin_limit)
-                 ? 1
-                 : 0;
+        ok = wait_counter(P.counters + wait_stage, static_cast<unsigned int>(S.wait_target), status, P.spin_limit) ? 1 : 0;
         if (!ok) {
           atomicCAS(status, 0u, 1u | (static_cast<unsigned int>(s) << 8));
           s_abort = 1;
         }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (ok) stage_for_bits<XBF16>(bits, a, steps, m_stride_u4, xb, xsum, xneg, tid);
-    } else if (wait_stage < 0) {
-      stage_for_bits<XBF16>(bits, a, steps, m_stride_u4, xb, xsum, xneg, tid);
     }
+    if (stager && ok) stage_for_bits<XBF16>(bits, a, steps, m_stride_u4, xb, xsum, xneg, tid);
+    DQ_TRACE(s, 1);
     __syncthreads();
     if (s_abort) {
       aborted = true;
       break;
     }
+    DQ_TRACE(s, 2);
 
     const bool b_live = g < m;
     const int s_begin = kwi * spw;
@@ -442,6 +515,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
     const float* xsum_w = xsum + s_begin * 8 + 2 * t;
     const float* xneg_w = xneg + s_begin * 8 + 2 * t;
 
+#pragma unroll 1
     for (int item = cta_rel; item < items; item += cta_count, parity ^= 1) {
       const int tile = item * rw + rwi;
       const bool live = tile < tiles;
@@ -450,6 +524,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
         const uint4* bchunk = xb_lane;
         const float* xs_chunk = xsum_w;
         const float* xn_chunk = xneg_w;
+#pragma unroll 1
         for (int chunk = 0; chunk < nchunks; ++chunk) {
           wait_pending(nb - 1);  // groups complete in issue order: all but the nb-1 youngest are done
           __syncwarp();          // pieces other lanes copied are visible
@@ -487,6 +562,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
         if (kwi == 0) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[i] = 0.0f;
+#pragma unroll 2
           for (int k = 0; k < kw; ++k) {
             const float* part = buf + (k * rw + rwi) * 128;
             const float2 pa = *reinterpret_cast<const float2*>(part + g * 8 + 2 * t);
@@ -509,11 +585,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
       }
     }
     // ---- this CTA's share of the stage is stored: tell the stage that waits for it ----
+    DQ_TRACE(s, 3);
     __syncthreads();  // (also: the staged activation and the partial-sum buffers are free again)
-    if (tid == 0 && __ldg(&S.signal) != 0) {
-      __threadfence();
-      red_release_add(P.counters + s, 1u);
+    DQ_TRACE(s, 4);
+    if (tid == 0 && S.signal != 0) {
+#ifdef DQ_PLAN_TRACE
+      if (P.debug_flags & 1) {
+        atomicAdd(P.counters + s, 1u);
+      } else
+#endif
+      {
+        red_release_add(P.counters + s, 1u);  // (release at GPU scope: cumulative over the CTA's stores, through the barrier)
+      }
     }
+    DQ_TRACE(s, 5);
+    pf_catch_up();  // the stage is signalled: now is the cheap moment to look for this warp's next item
+    DQ_TRACE(s, 6);
   }
 
   stream::cp_async_wait<0>();  // nothing of ours is still in flight when the CTA leaves
@@ -524,7 +611,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
     const unsigned int left = atomicAdd(P.counters + P.nstages, 1u);
     if (left == gridDim.x - 1) {
       __threadfence();
-      for (int i = 0; i <= P.nstages; ++i) P.counters[i] = 0u;
+      for (int i = P.first_stage; i < P.last_stage; ++i) P.counters[i] = 0u;
+      P.counters[P.nstages] = 0u;
     }
   }
 }
@@ -536,9 +624,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_plan_kernel(const __grid_con
 // host side
 // ---------------------------------------------------------------------------------------------
 
+// One launch of a plan: a range of stages in the persistent kernel, or one long matrix handed to
+// the streaming GEMV (a matrix that fills the machine many tiles deep gains nothing from the
+// stage machinery and runs faster on the leaner kernel: dq_gemv_mma_stream.cuh).
+struct PlanOp {
+  int first_stage, last_stage;  // persistent kernel over [first_stage, last_stage) ...
+  int job;                      // ... or, when >= 0, this job of the caller's list on its own
+};
+
 struct dq_plan {
   std::vector<dq::plank::PStage> stages;
   std::vector<dq::plank::PJob> jobs;
+  std::vector<dq_gemv_job> user_jobs;
+  std::vector<PlanOp> ops;
   dq::plank::PlanParams params;
   void* workspace;
   int64_t workspace_bytes;
@@ -595,8 +693,9 @@ Pick pick_shape(const dq_gemv_job* jobs, int n, int steps, int grid) {
     double per_item[kMaxStageJobs], weight[kMaxStageJobs], total = 0.0;
     for (int i = 0; i < n; ++i) {
       items[i] = ceil_div(ceil_div(jobs[i].weight.rows, kTileRows), rw);
-      // a slot costs a wait and a refill; a sliced item a barrier and a pass through shared memory
-      per_item[i] = spw * step_cost(jobs[i].weight.bits) + 0.25 * (spw / cs) + (kw > 1 ? 1.5 : 0.2);
+      // in units of one step of all 16 warps of an SM (issue-bound, about a microsecond): a slot
+      // costs a wait and a refill; a sliced item a barrier and a pass through shared memory
+      per_item[i] = spw * step_cost(jobs[i].weight.bits) + 0.1 * (spw / cs) + (kw > 1 ? 0.35 : 0.05);
       weight[i] = items[i] * per_item[i];
       total += weight[i];
     }
@@ -702,6 +801,8 @@ int32_t dq_plan_create(const dq_gemv_job* jobs, int32_t num_jobs, void* workspac
   plan->x_bf16 = jobs[0].x_dtype == DQ_BF16 ? 1 : 0;
 
   // ---- stages: consecutive jobs that read the same activation ----
+  plan->user_jobs.assign(jobs, jobs + num_jobs);
+  std::vector<int> own_launch;  // per stage: the job it hands to the streaming GEMV, or -1
   size_t stage_area = 0;
   int i = 0;
   while (i < num_jobs) {
@@ -760,26 +861,50 @@ int32_t dq_plan_create(const dq_gemv_job* jobs, int32_t num_jobs, void* workspac
       max_bits = std::max(max_bits, J.bits);
       plan->jobs.push_back(J);
     }
-    if (sidx > 0) {
-      plan->stages[sidx - 1].signal = 1;
-    }
     S.pad = active;  // CTAs that arrive on this stage's counter (copied into the waiter below)
     plan->stages.push_back(S);
-    const int na = max_bits == 8 ? 32 : 16;
-    const size_t area = (static_cast<size_t>(S.m) * (static_cast<size_t>(steps) * na + 4) + na) * 16 +
-                        static_cast<size_t>(steps) * 64 + 16;
-    stage_area = std::max(stage_area, area);
+    const bool long_matrix = n == 1 && ceil_div(head.weight.rows, kTileRows) >= static_cast<int64_t>(dev->sm_count) * 8;
+    own_launch.push_back(long_matrix ? i : -1);
+    if (!long_matrix) {
+      const int na = max_bits == 8 ? 32 : 16;
+      const size_t area = (static_cast<size_t>(S.m) * (static_cast<size_t>(steps) * na + 4) + na) * 16 +
+                          static_cast<size_t>(steps) * 64 + 16;
+      stage_area = std::max(stage_area, area);
+    }
     i = end;
   }
-  for (size_t s = 1; s < plan->stages.size(); ++s) plan->stages[s].wait_target = plan->stages[s - 1].pad;
-  for (auto& S : plan->stages) S.pad = 0;
+  const int total_stages = static_cast<int>(plan->stages.size());
+  for (int s = 1; s < total_stages; ++s) plan->stages[s].wait_target = plan->stages[s - 1].pad;
+  for (int s = 0; s < total_stages; ++s) {
+    PStage& S = plan->stages[s];
+    S.pad = 0;
+    // a stage signals only a successor that runs in the same launch
+    S.signal = (s + 1 < total_stages && own_launch[s] < 0 && own_launch[s + 1] < 0) ? 1 : 0;
+  }
+  for (int s = 0; s < total_stages;) {
+    if (own_launch[s] >= 0) {
+      plan->ops.push_back(PlanOp{s, s + 1, own_launch[s]});
+      ++s;
+      continue;
+    }
+    int e = s;
+    while (e < total_stages && own_launch[e] < 0) ++e;
+    plan->ops.push_back(PlanOp{s, e, -1});
+    s = e;
+  }
 
-  // ---- shared memory: the deepest ring that leaves room for the largest staged activation ----
-  const size_t fixed = kRedFloats * 4 + stage_area + 128;
-  int nb = 0;
-  for (int cand = 4; cand >= 2; --cand) {
-    if (fixed + static_cast<size_t>(cand) * kWarps * kSlotBytes <= static_cast<size_t>(dev->max_smem_optin)) {
-      nb = cand;
+  // ---- shared memory: staged activation, partial sums, the weight ring -- and, when they fit
+  // beside a ring of at least three slots, a copy of the two tables ----
+  const size_t area_bytes = align_up(stage_area, 16);
+  const size_t table_bytes = align_up(plan->stages.size() * sizeof(PStage) + plan->jobs.size() * sizeof(PJob), 16);
+  const size_t fixed = kRedFloats * 4 + area_bytes + 1024;  // (+ the kernel's static shared memory)
+  int nb = 0, tables = 0;
+  const int order[6][2] = {{1, 4}, {1, 3}, {0, 4}, {0, 3}, {1, 2}, {0, 2}};  // (tables in smem, ring slots)
+  for (const auto& cand : order) {
+    const size_t need_smem = fixed + (cand[0] ? table_bytes : 0) + static_cast<size_t>(cand[1]) * kWarps * kSlotBytes;
+    if (need_smem <= static_cast<size_t>(dev->max_smem_optin)) {
+      tables = cand[0];
+      nb = cand[1];
       break;
     }
   }
@@ -789,7 +914,7 @@ int32_t dq_plan_create(const dq_gemv_job* jobs, int32_t num_jobs, void* workspac
                 "plan_create: the staged activation (%zu bytes) leaves no room for the weight ring; launch with dq_gemv_sequence",
                 stage_area);
   }
-  plan->smem = fixed + static_cast<size_t>(nb) * kWarps * kSlotBytes;
+  plan->smem = fixed + (tables ? table_bytes : 0) + static_cast<size_t>(nb) * kWarps * kSlotBytes;
 
   auto set_attr = [&](auto kernel) -> int32_t {
     DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan->smem)));
@@ -830,6 +955,11 @@ int32_t dq_plan_create(const dq_gemv_job* jobs, int32_t num_jobs, void* workspac
   plan->params.jobs = reinterpret_cast<const PJob*>(d_jobs);
   plan->params.counters = reinterpret_cast<unsigned int*>(d_counters);
   plan->params.nstages = static_cast<int>(plan->stages.size());
+  plan->params.first_stage = 0;
+  plan->params.last_stage = plan->params.nstages;
+  plan->params.njobs = static_cast<int>(plan->jobs.size());
+  plan->params.tables_in_smem = tables;
+  plan->params.area_bytes = static_cast<int>(area_bytes);
   plan->params.nb = nb;
   plan->params.spin_limit = kDefaultSpinLimit;
   plan->params.magic = plan->x_bf16 ? 0x43004300u : 0x64006400u;
@@ -842,13 +972,22 @@ int32_t dq_plan_launch(dq_plan* plan, void* stream) {
   using namespace dq::plank;
   DQ_REQUIRE(plan != nullptr, "plan_launch: null plan");
   auto s = static_cast<cudaStream_t>(stream);
-  if (plan->x_bf16) {
-    gemv_plan_kernel<true><<<plan->grid, kThreads, plan->smem, s>>>(plan->params);
-  } else {
-    gemv_plan_kernel<false><<<plan->grid, kThreads, plan->smem, s>>>(plan->params);
+  for (const PlanOp& op : plan->ops) {
+    if (op.job >= 0) {
+      if (const int32_t rc = dq_gemv_sequence(&plan->user_jobs[op.job], 1, stream)) return rc;
+      continue;
+    }
+    PlanParams params = plan->params;
+    params.first_stage = op.first_stage;
+    params.last_stage = op.last_stage;
+    if (plan->x_bf16) {
+      gemv_plan_kernel<true><<<plan->grid, kThreads, plan->smem, s>>>(params);
+    } else {
+      gemv_plan_kernel<false><<<plan->grid, kThreads, plan->smem, s>>>(params);
+    }
+    DQ_CHECK_LAUNCH("plan");
+    note_kernel("gemv_plan_kernel");
   }
-  DQ_CHECK_LAUNCH("plan");
-  note_kernel("gemv_plan_kernel");
   return DQ_OK;
 }
 
@@ -893,6 +1032,7 @@ int32_t dq_plan_describe(const dq_plan* plan, dq_plan_info* info) {
   info->grid = plan->grid;
   info->threads = dq::plank::kThreads;
   info->ring_slots = plan->params.nb;
+  info->launches = static_cast<int32_t>(plan->ops.size());
   info->shared_bytes = static_cast<int64_t>(plan->smem);
   return DQ_OK;
 }
@@ -911,5 +1051,17 @@ int32_t dq_plan_stage_shape(const dq_plan* plan, int32_t stage, int32_t* k_slice
 }
 
 void dq_plan_destroy(dq_plan* plan) { delete plan; }
+
+#ifdef DQ_PLAN_TRACE
+// Diagnostic builds only: device buffer of nstages * 2 * 8 timestamps (see trace_point).
+__attribute__((visibility("default"))) void dq_plan_set_trace(dq_plan* plan, unsigned long long* buffer) {
+  plan->params.trace = buffer;
+}
+__attribute__((visibility("default"))) void dq_plan_set_debug(dq_plan* plan, int flags) {
+  plan->params.debug_flags = flags;
+  const int relaxed = (flags & 2) ? 1 : 0;
+  cudaMemcpyToSymbol(dq::plank::g_debug_relaxed_poll, &relaxed, sizeof(int));
+}
+#endif
 
 }  // extern "C"

@@ -85,6 +85,7 @@ __device__ __forceinline__ void stage_units(const GemvArgs& a, int s_first, int 
   constexpr bool QUADS = G64 && BITS == 3;   // groups = quad-lane pairs
   const int total = a.m * nsteps * 4;
   const int rounds = (total + nthreads - 1) / nthreads;
+#pragma unroll 1
   for (int r = 0; r < rounds; ++r) {
     const int id = tid + r * nthreads;
     const bool live = id < total;

@@ -85,6 +85,41 @@ class FusedPackedGeometry:
     def __iter__(self):
         return iter(self._plans)
 
+    def plan_for_rows(self, dest_row: int, num_rows: int) -> ShardPlan:
+        """The shard whose rows contain ``[dest_row, dest_row + num_rows)`` of the fused output --
+        what a framework's weight loader names when it places (part of) one checkpoint module."""
+        for plan in self._plans:
+            if plan.row_offset <= dest_row and dest_row + num_rows <= plan.row_offset + plan.spec.out_features:
+                return plan
+        raise ValueError(
+            f"rows [{dest_row}, {dest_row + num_rows}) do not lie inside one shard of "
+            f"{[(p.spec.name, p.row_offset, p.spec.out_features) for p in self._plans]}"
+        )
+
+    def place(self, flat: torch.Tensor, kind: str, loaded: torch.Tensor, *, dest_row: int, num_rows: int,
+              src_row: int, columns: slice | None = None) -> None:
+        """Copy ``loaded[src_row : src_row + num_rows]`` (optionally a column slice of it: an input
+        shard) into rows ``[dest_row, +num_rows)`` of the flat ``qweight`` or ``scales``/``offsets``
+        buffer.  Pure placement: shapes must match exactly, nothing is repacked or converted
+        (reference ``integration/vllm_plugin/parameter.py:158-183``)."""
+        if kind not in ("qweight", "scale"):
+            raise ValueError(f"unknown buffer kind {kind!r}")
+        plan = self.plan_for_rows(dest_row, num_rows)
+        per_row = plan.words_per_row if kind == "qweight" else plan.num_groups
+        base = plan.qweight_offset if kind == "qweight" else plan.scale_offset
+        start = base + (dest_row - plan.row_offset) * per_row
+        dest = flat[start : start + num_rows * per_row].view(num_rows, per_row)
+        source = loaded.narrow(0, src_row, num_rows)
+        if columns is not None:
+            source = source[:, columns]
+        if source.shape != dest.shape:
+            raise ValueError(
+                f"{plan.spec.name}: the checkpoint tensor gives {tuple(source.shape)} for this rank but "
+                f"{plan.spec.bits}-bit at group_size={plan.spec.group_size} needs {tuple(dest.shape)}; the "
+                f"quantization map and the weights were written by different runs"
+            )
+        dest.copy_(source)
+
     def view_qweight(self, flat: torch.Tensor, shard_id: int) -> torch.Tensor:
         p = self._plans[shard_id]
         return flat[p.qweight_offset : p.qweight_offset + p.qweight_numel].view(p.spec.out_features, p.words_per_row)
@@ -92,6 +127,49 @@ class FusedPackedGeometry:
     def view_scale(self, flat: torch.Tensor, shard_id: int) -> torch.Tensor:
         p = self._plans[shard_id]
         return flat[p.scale_offset : p.scale_offset + p.scale_numel].view(p.spec.out_features, p.num_groups)
+
+
+@dataclass(frozen=True)
+class InputSplit:
+    """A packed row divided over ranks along its INPUT axis (the o_proj / down_proj placement)."""
+
+    in_features: int  # per rank
+    num_groups: int   # per rank
+    words: int        # per rank
+
+    def word_slice(self, rank: int) -> slice:
+        return slice(rank * self.words, (rank + 1) * self.words)
+
+    def group_slice(self, rank: int) -> slice:
+        return slice(rank * self.num_groups, (rank + 1) * self.num_groups)
+
+
+def input_axis_split(bits: int, group_size: int, in_features: int, world: int, name: str = "<layer>") -> InputSplit:
+    """Words and groups each of ``world`` ranks owns of a row of ``in_features`` values.  Legal
+    only on group boundaries -- a group's words, scale and offset move together -- and never for a
+    per-row-grouped tensor (reference ``integration/serving_common/geometry.py:481-551``)."""
+    full = row_geometry(bits, group_size, in_features)
+    if world <= 0:
+        raise ValueError(f"the number of ranks must be positive, got {world}")
+    if world == 1:
+        return InputSplit(in_features, full.num_groups, full.words_per_row)
+    if full.is_per_row:
+        raise ValueError(
+            f"{name} has one group spanning its {in_features} inputs and cannot be split over {world} ranks: "
+            f"every rank would need the one scale of a group it holds a part of"
+        )
+    if in_features % world:
+        raise ValueError(f"{name}: in_features={in_features} is not divisible by {world} ranks")
+    per = in_features // world
+    if per % full.effective_group:
+        raise ValueError(
+            f"{name}: {world} ranks get {per} of {in_features} inputs each, not a whole number of "
+            f"{full.effective_group}-value groups; use a rank count dividing {in_features // full.effective_group}"
+        )
+    part = row_geometry(bits, group_size, per)
+    if part.words_per_row * world != full.words_per_row:
+        raise ValueError(f"{name}: {world} slices of {part.words_per_row} words do not tile {full.words_per_row}")
+    return InputSplit(per, part.num_groups, part.words_per_row)
 
 
 def match_shards_to_partitions(shards: Sequence[ShardSpec], output_partition_sizes: Sequence[int]) -> list[ShardSpec]:
@@ -125,20 +203,23 @@ class DynQuantLinearMethod:
         **extra_weight_attrs: Any,
     ) -> None:
         del output_size
+        specs = match_shards_to_partitions(self.shards, output_partition_sizes)
+        split = None
         if input_size_per_partition != input_size:
             # row-parallel placement: this rank holds a slice of the input axis, legal only on
             # group boundaries (reference serving_common/geometry.py:481-551); the framework's
             # RowParallelLinear all-reduces the partial sums apply() returns
-            for spec in self.shards:
-                if spec.group_size <= 0 or input_size_per_partition % spec.group_size:
-                    raise ValueError(
-                        f"shard {spec.name}: an input slice of {input_size_per_partition} values is not a whole "
-                        f"number of groups of {spec.group_size}; split the input axis on group boundaries"
-                    )
-        specs = match_shards_to_partitions(self.shards, output_partition_sizes)
+            if len(specs) != 1:
+                raise ValueError(
+                    f"the input-sharded layer {[s.name for s in specs]} has more than one fused shard: every "
+                    f"width implies its own words per rank, so the word axis has no single split"
+                )
+            split = input_axis_split(specs[0].bits, specs[0].group_size, input_size,
+                                     input_size // input_size_per_partition, specs[0].name)
         geometry = FusedPackedGeometry(specs, input_size_per_partition)
         device = extra_weight_attrs.get("device")
         layer.dynquant_geometry = geometry
+        layer.dynquant_row_split = split
         layer.dynquant_in_features = input_size_per_partition
         for name, numel, dtype in (
             ("qweight", geometry.qweight_numel, torch.int32),

@@ -25,8 +25,9 @@ class GemvPlan:
     """A job list compiled into ONE persistent kernel (``dq_plan_*`` of the C ABI).
 
     Same results as ``dq_gemv_sequence`` over the same ``dq_gemv_job`` array; the jobs' tensors
-    are referenced, not copied, and must outlive the plan.  ``launch()`` enqueues exactly one
-    kernel on torch's current stream and may be captured in a CUDA graph; ``check()``
+    are referenced, not copied, and must outlive the plan.  ``launch()`` enqueues
+    ``info()["launches"]`` kernels on torch's current stream (one persistent kernel per run of
+    stages, plus one streaming GEMV per very long matrix) and may be captured in a CUDA graph; ``check()``
     synchronises and raises if a stage's bounded wait ran out.
     """
 
@@ -54,7 +55,7 @@ class GemvPlan:
     def info(self) -> dict:
         out = _lib.PlanInfo()
         _lib.check(_lib.load().dq_plan_describe(self._handle, ctypes.byref(out)))
-        return {name: int(getattr(out, name)) for name, _ in out._fields_ if name != "reserved"}
+        return {name: int(getattr(out, name)) for name, _ in out._fields_}
 
     def stage_shape(self, stage: int) -> dict:
         kw, cs = ctypes.c_int32(), ctypes.c_int32()

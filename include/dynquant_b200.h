@@ -196,7 +196,10 @@ DQ_API int32_t dq_gemv_sequence(const dq_gemv_job* jobs, int32_t num_jobs, void*
  * that must stay alive and untouched for the life of the plan; the job list's tensors are
  * referenced, not copied.  A plan belongs to the device that was current at creation.
  * Launches of ONE plan must not overlap on the GPU (they share the counters); launches of
- * different plans may.  dq_plan_launch enqueues exactly one kernel and is capturable. */
+ * different plans may.  dq_plan_launch enqueues one persistent kernel per run of consecutive
+ * stages, and hands a matrix long enough to fill the machine many row tiles deep (a vocabulary
+ * projection) to the streaming GEMV as a launch of its own -- dq_plan_info.launches in all,
+ * two for a decoder stack followed by its lm_head; all of it is capturable. */
 typedef struct dq_plan dq_plan;
 typedef struct dq_plan_info {
   int32_t num_stages;
@@ -204,7 +207,7 @@ typedef struct dq_plan_info {
   int32_t grid;       /* CTAs = SMs of the device */
   int32_t threads;    /* per CTA */
   int32_t ring_slots; /* weight slots each warp keeps in flight */
-  int32_t reserved;
+  int32_t launches;   /* kernels one dq_plan_launch enqueues (see below) */
   int64_t shared_bytes;
 } dq_plan_info;
 DQ_API int32_t dq_plan_workspace_bytes(int32_t num_jobs, int64_t* bytes);

@@ -9,7 +9,9 @@ themselves.  Otherwise the C restatement ``dq_oracle.c`` is timed (``kind:
 
     python oracle/cpu_baseline.py '<json spec>'
 
-spec = {"modules": [[rows, in_features, bits], ...], "m": 1, "repeat": 1, "seed": 7}
+spec = {"modules": [[rows, in_features, bits], ...], "m": 1, "repeat": 1, "seed": 7, "threads": 16}
+("threads": host threads torch may use -- set explicitly so the figure does not depend on an
+OMP_NUM_THREADS a launcher put into the environment)
 prints {"kind", "cores", "seconds", "bytes", "gbps", "modules"} as one JSON line.
 """
 
@@ -30,6 +32,8 @@ def main() -> None:
     import numpy as np
     import torch
 
+    if spec.get("threads"):
+        torch.set_num_threads(int(spec["threads"]))
     gen = torch.Generator().manual_seed(int(spec.get("seed", 7)))
     m = int(spec.get("m", 1))
     group = 128

@@ -66,3 +66,26 @@ def make_quant(rows: int, in_features: int, group_size: int, bits: int, dtype: t
     if not with_offsets:
         qt.offsets = None
     return qt
+
+
+_VLLM_STATE = {"stack": None}
+
+
+def vllm_world_of_one():
+    """Once per process: a vLLM config context and a one-rank gloo world, which is all vLLM's
+    parameter base class needs in order to construct (it reads the tensor-parallel rank off the
+    process group).  The context stays open for the rest of the process."""
+    import contextlib
+
+    if _VLLM_STATE["stack"] is None:
+        from vllm.config import DeviceConfig, VllmConfig, set_current_vllm_config
+        from vllm.distributed import init_distributed_environment, initialize_model_parallel
+
+        # (an explicit device: without a GPU vLLM cannot infer one, and none is needed for placement)
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+        stack = contextlib.ExitStack()
+        stack.enter_context(set_current_vllm_config(VllmConfig(device_config=DeviceConfig(device=device))))
+        init_distributed_environment(world_size=1, rank=0, distributed_init_method="tcp://127.0.0.1:29541",
+                                     local_rank=0, backend="gloo")
+        initialize_model_parallel(1, 1)
+        _VLLM_STATE["stack"] = stack

@@ -178,3 +178,39 @@ def test_step_graph_with_its_copies_matches_the_plain_step():
     assert torch.equal(host_out, expect.cpu())
     with pytest.raises(ValueError, match="pinned"):
         runner.capture_with_io({k: v.cpu() for k, v in runner.inputs.items()}, last, host_out)
+
+
+def test_vllm_adapter_layer_loads_through_the_placement_hooks_and_runs_one_launch():
+    """The adapter vLLM builds layers from: parameters created by ``create_weights`` on the GPU,
+    filled through vLLM's v2 loader hooks (a fused q/k/v layer of three widths), applied with a
+    bias -- one kernel launch -- and compared with the oracle."""
+    pytest.importorskip("vllm", reason="the adapter needs vLLM")
+    from conftest import vllm_world_of_one
+
+    from dynquant_b200 import ops
+    from dynquant_b200.checkpoint import ModuleSpec
+    from dynquant_b200.vllm_plugin import DynQuantLinearMethod
+
+    vllm_world_of_one()
+    k = 1024
+    widths = [("q_proj", 4, 512), ("k_proj", 2, 128), ("v_proj", 3, 128)]
+    parts = [make_quant(rows, k, 128, bits, torch.float16, seed=20 + bits) for _, bits, rows in widths]
+    layer = torch.nn.Module()
+    method = DynQuantLinearMethod(None, [(f"l.{n}", ModuleSpec(bits=b)) for n, b, _ in widths])
+    with torch.device("cuda"):
+        method.create_weights(layer, input_size_per_partition=k, output_partition_sizes=[r for *_, r in widths],
+                              input_size=k, output_size=768, params_dtype=torch.float16, weight_loader=None)
+    assert layer.qweight.is_cuda
+    offset = 0
+    for (name, _, rows), qt in zip(widths, parts):
+        for attr, source in (("qweight", qt.packed), ("scales", qt.scales), ("offsets", qt.offsets)):
+            getattr(layer, attr).load_qkv_weight(loaded_weight=source.cuda(), shard_offset=offset, shard_size=rows,
+                                                 shard_id=name[0], num_heads=1)
+        offset += rows
+    bias = torch.randn(768, dtype=torch.bfloat16, device="cuda")
+    x = torch.randn(3, k, dtype=torch.bfloat16, device="cuda")
+    before = ops.launch_count()
+    got = method.apply(layer, x, bias)
+    assert ops.launch_count() - before == 1
+    want = torch.cat([dense_ref(x, qt) for qt in parts], dim=-1) + bias.float().cpu()
+    torch.testing.assert_close(got.float().cpu(), want, rtol=2e-2, atol=5e-3 * float(want.abs().max()))

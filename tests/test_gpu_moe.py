@@ -8,6 +8,7 @@ import pytest
 import torch
 
 from conftest import TAG, raw
+from test_gpu_parity import within_one_ulp_16
 
 pytestmark = pytest.mark.gpu
 
@@ -193,11 +194,9 @@ def test_moe_stage_by_stage(act, bits_gu, bits_dn):
             g, u = gu[:inter].astype(np.float64), gu[inter:].astype(np.float64)
             h32 = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
             got_h = h[aid].float().numpy()
-            rounded = torch.from_numpy(h32).to(act)
-            # one unit in the last place of the rounded value (the kernel's fp32 g, u differ from
-            # the oracle's double sums in the last bits, which can move a value across a tie)
-            ulp = np.maximum(np.abs(rounded.float().numpy()), 1e-4) * 2.0 ** (-(10 if act == torch.float16 else 7))
-            assert (np.abs(got_h - rounded.float().numpy()) <= ulp + 1e-6).all(), (t, k)
+            # the oracle's value rounded once, give or take one unit in the last place; plus the
+            # suite's usual absolute room for outputs that nearly cancel (2e-5 of the largest)
+            assert within_one_ulp_16(h[aid:aid + 1], h32[None, :]), (t, k)
             h_err2 += float(((got_h - h32) ** 2).sum())
             h_ref2 += float((h32 ** 2).sum())
             packed, scales, offsets, tag, geom = expert_rows(layer.down, e, hidden)
