@@ -120,10 +120,13 @@ def main() -> None:
     ap.add_argument("--m", default="1,4,16")
     ap.add_argument("--launches", type=int, default=50)
     ap.add_argument("--ring", type=int, default=None, help="distinct weight tensors (default: > 2x L2)")
+    ap.add_argument("--no-reference", action="store_true",
+                    help="skip the second baseline (the reference's own CUDA kernels, timed by a child process)")
     ns = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("the sweep needs a CUDA device: this library has no CPU path")
     shapes = ns.shape or ["14336x4096", "4096x14336", "4096x4096", "4097x4096"]
+    results = []
     for shape in shapes:
         rows, k = (int(v) for v in shape.lower().split("x"))
         for bits in (int(b) for b in ns.bits.split(",")):
@@ -132,7 +135,48 @@ def main() -> None:
                     print(json.dumps(run_dequant_point(rows, k, bits, group, launches=ns.launches)), flush=True)
                     continue
                 for m in (int(v) for v in ns.m.split(",")):
-                    print(json.dumps(run_point(rows, k, bits, group, m, launches=ns.launches, ring=ns.ring)), flush=True)
+                    point = run_point(rows, k, bits, group, m, launches=ns.launches, ring=ns.ring)
+                    if ns.no_reference:
+                        print(json.dumps(point), flush=True)
+                    results.append(point)
+    if ns.op == "dequant" or ns.no_reference:
+        return
+    # second baseline: the reference's own CUDA kernels, compiled for sm_100, on this GPU -- timed
+    # by a child process (its library registers the same operator namespace as this package)
+    reference = reference_cuda_points(results, ns.launches)
+    peak, _ = hbm_peak_gbs()
+    for point in results:
+        ref = reference.get(point_key(point))
+        if ref is not None:
+            point["reference_cuda_us"] = ref["reference_cuda_us"]
+            point["reference_cuda_pct_of_hbm_peak"] = round(100 * ref["reference_cuda_gbps"] / peak, 1)
+            point["speedup_vs_reference_cuda"] = round(ref["reference_cuda_us"] / point["us_per_call"], 2)
+        print(json.dumps(point), flush=True)
+
+
+def point_key(p: dict) -> tuple:
+    return (p["rows"], p["in_features"], p["bits"], p["group_size"], p["m"])
+
+
+def reference_cuda_points(results: list[dict], launches: int) -> dict:
+    import subprocess
+
+    spec = [{k: p[k] for k in ("rows", "in_features", "bits", "group_size", "m")} for p in results]
+    script = Path(__file__).resolve().parent / "reference_cuda.py"
+    try:
+        res = subprocess.run([sys.executable, str(script), json.dumps(spec), str(launches)], capture_output=True,
+                             text=True, timeout=3600)
+    except subprocess.TimeoutExpired:
+        return {}
+    out = {}
+    for line in res.stdout.splitlines():
+        try:
+            row = json.loads(line)
+        except ValueError:
+            continue
+        if "reference_cuda_us" in row:
+            out[point_key(row)] = row
+    return out
 
 
 if __name__ == "__main__":

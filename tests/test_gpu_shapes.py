@@ -275,3 +275,41 @@ def test_the_two_simt_paths_agree(tmp_path, bits):
     mma = ops.gemv(xb, qh.packed, qh.scales, qh.offsets, bits, 128, 2048, out_dtype=torch.float32)
     assert ops.last_kernel().startswith("gemv_mma")
     check_acc(mma, oracle_gemv(xb, qh))
+
+
+# ---- the reference's own CUDA kernel on the same inputs ------------------------------------------
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_agrees_with_the_references_own_cuda_gemv(tmp_path, bits):
+    """``oracle/_ref/libdynquant_ref_cuda.so`` is the reference's gemv.cu / dequant.cu compiled
+    where they lie (oracle/build_ref.py).  It runs in a child process (it registers the same
+    operator namespace) on a tensor saved to disk; both outputs are bf16, compared at the
+    reference's own bar for that dtype (rtol = atol = 2e-2, tests/test_kernels_parity.py:198-203),
+    and the dequantized weights bit for bit."""
+    lib = ROOT / "oracle" / "_ref" / "libdynquant_ref_cuda.so"
+    if not lib.exists():
+        pytest.skip("the reference's CUDA kernels are not built here")
+    from dynquant_b200 import ops
+
+    qt = make_quant(260, 2048, 128, bits, torch.bfloat16, seed=77)
+    x = torch.randn(4, 2048, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16)
+    torch.save({"packed": qt.packed, "scales": qt.scales, "offsets": qt.offsets, "x": x}, tmp_path / "in.pt")
+    body = textwrap.dedent(
+        f"""
+        import torch
+        torch.ops.load_library({str(lib)!r})
+        d = torch.load({str(tmp_path / "in.pt")!r})
+        args = [d[k].cuda() for k in ("packed", "scales", "offsets")]
+        y = torch.ops.dynquant.gemv(d["x"].cuda(), *args, {bits}, 128, 2048)
+        w = torch.ops.dynquant.dequant(*args, {bits}, 128, 2048)
+        torch.save({{"y": y.cpu(), "w": w.cpu()}}, {str(tmp_path / "out.pt")!r})
+        """
+    )
+    subprocess.run([sys.executable, "-c", body], check=True)
+    ref = torch.load(tmp_path / "out.pt")
+    dev = qt.to("cuda")
+    got = ops.gemv(x.cuda(), dev.packed, dev.scales, dev.offsets, bits, 128, 2048)
+    torch.testing.assert_close(got.float().cpu(), ref["y"].float(), rtol=2e-2, atol=2e-2)
+    dense = ops.dequant(dev.packed, dev.scales, dev.offsets, bits, 128, 2048)
+    assert torch.equal(dense.cpu().view(torch.int16), ref["w"].view(torch.int16))
