@@ -490,7 +490,7 @@ def run_ours(args) -> None:
             "frac": round(achieved / peak, 4),
             "kernel": kernel, "bytes_per_launch": round(kernel_bytes), "launch_us": round(kernel_seconds * 1e6, 3),
             "per_gpu": world > 1,
-            "traffic": None, "traffic_source": "ncu capture of this command, summarised under profiles/ (not measured in this run)",
+            "traffic": None, "traffic_source": "not measured in this run (needs a profiler pass)",
             "step_average": {"bytes_per_launch": round(local_bytes / launches_per_step),
                              "launch_us": round(per_step / launches_per_step * 1e6, 3),
                              "frac": round(local_bytes / per_step / 1e9 / peak, 4)},

@@ -46,7 +46,9 @@ def _stale(target: Path, deps: list[Path]) -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
+def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False, tuning: bool = False) -> Path:
+    """``tuning``: compile in the launch-shape overrides (``DQ_B200_*`` environment variables read
+    at every launch) that the sweeps behind the built-in heuristics used; not for normal use."""
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     headers = sorted(CSRC.glob("*.cuh")) + sorted(INCLUDE.glob("*.h")) + [Path(__file__)]
     sources = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
@@ -54,7 +56,7 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     for src in sources:
         obj = OBJ_DIR / (src.stem + ".o")
         if force or _stale(obj, [src, *headers]):
-            cmd = [nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc(), *NVCC_FLAGS, *(["-DDQ_TUNING"] if tuning else []), "-c", str(src), "-o", str(obj)]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append(cmd)
@@ -79,5 +81,6 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
 
 
 if __name__ == "__main__":
-    path = build_library(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas-info" in sys.argv)
+    path = build_library(force="--force" in sys.argv or "--tuning" in sys.argv, verbose=True,
+                         ptxas_info="--ptxas-info" in sys.argv, tuning="--tuning" in sys.argv)
     print(path)

@@ -252,9 +252,12 @@ def load_packed_checkpoint(path: str | Path, *, device: str | torch.device = "cp
                            in_features: Mapping[str, int] | None = None) -> PackedCheckpoint:
     """Read a packed checkpoint directory.
 
-    ``in_features`` overrides, per module, the input width implied by the stored shapes
-    (``groups * group_size``): only a module whose rows end in a zero-padded partial group
-    needs it.  Tensors are moved to ``device`` as stored.
+    The input width of a module is taken, in this order, from ``in_features`` (an explicit
+    per-module override), from the exporter's ``dynquant_manifest.json`` when the directory has
+    one (``layers[name].in_features``; the reference writes it beside the weights,
+    ``quant/checkpoint.py:109-200``), and otherwise from the stored shapes
+    (``groups * group_size``) -- which over-states it for a module whose rows end in a
+    zero-padded partial group.  Tensors are moved to ``device`` as stored.
     """
     from safetensors import safe_open
 
@@ -288,7 +291,8 @@ def load_packed_checkpoint(path: str | Path, *, device: str | torch.device = "cp
         else:
             dense[key] = value.to(device)
 
-    widths = dict(in_features or {})
+    widths = _manifest_widths(path)
+    widths.update(in_features or {})
     modules: dict[str, list[QuantTensor]] = {}
     for name, spec in quantization.modules.items():
         if name in quantization.modules_to_not_convert:
@@ -314,6 +318,25 @@ def load_packed_checkpoint(path: str | Path, *, device: str | torch.device = "cp
             raise CheckpointError(f"{name}: the map says {spec.out_features} rows, the tensors hold {row}")
         modules[name] = shards
     return PackedCheckpoint(quantization, modules, dense, config)
+
+
+MANIFEST_FILENAME = "dynquant_manifest.json"
+
+
+def _manifest_widths(path: Path) -> dict[str, int]:
+    """``in_features`` per module from the exporter's manifest, if the directory has one."""
+    manifest = path / MANIFEST_FILENAME
+    if not manifest.exists():
+        return {}
+    try:
+        layers = json.loads(manifest.read_text(encoding="utf-8")).get("layers", {})
+    except ValueError as exc:
+        raise CheckpointError(f"{manifest} is not valid JSON: {exc}") from exc
+    out = {}
+    for name, entry in layers.items():
+        if isinstance(entry, Mapping) and "in_features" in entry:
+            out[name] = int(entry["in_features"])
+    return out
 
 
 def save_packed_checkpoint(

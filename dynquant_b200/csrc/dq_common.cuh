@@ -8,6 +8,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "dynquant_b200.h"
 
@@ -102,6 +103,20 @@ struct DeviceInfo {
 };
 // Cached per device; returns nullptr and sets the error on failure.
 const DeviceInfo* device_info();
+
+// Launch-shape overrides used by the sweeps that chose the built-in heuristics.  They exist only in
+// a tuning build (-DDQ_TUNING, `python -m dynquant_b200.build --tuning`), where they are read from
+// the environment at every launch; a normal build returns the fallback and reads nothing.  The
+// switches a user may need (DQ_B200_GEMV_PATH, DQ_B200_NO_PDL, DYNQUANT_GEMV_SCALAR) are not here.
+inline int tuning_int(const char* name, int fallback = 0) {
+#ifdef DQ_TUNING
+  const char* v = std::getenv(name);
+  return v != nullptr ? std::atoi(v) : fallback;
+#else
+  (void)name;
+  return fallback;
+#endif
+}
 
 // Process-wide count of the kernels this library has launched (dq_launch_count).
 void count_launch();

@@ -5,8 +5,8 @@
 // and groups that are a multiple of 128 values.  The SIMT kernel spends about
 // two instructions per weight VALUE (one logic op, half a packed add, half a
 // packed FMA per activation row), which at 2 and 3 bits per value is more
-// instruction issue than the memory system needs time to deliver the bytes;
-// the measured ceiling is in profiles/.  Here a weight value costs 0.6-0.9
+// instruction issue than the memory system needs time to deliver the bytes
+// (measured: 17-55 % of the HBM peak depending on width).  Here a weight value costs 0.6-0.9
 // integer instructions and 1/8 of an mma, whatever M is:
 //
 //   * out tile = 16 weight rows x 8 activation rows = one m16n8k16 accumulator.
@@ -494,24 +494,16 @@ int32_t launch_mma_bits(const GemvArgs& a, const MmaParams& p, int threads, size
 template <int BITS>
 bool stream_ok(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps) {
   using C = stream::Cfg<BITS>;
-  static const bool off = [] {
-    const char* v = std::getenv("DQ_B200_NO_STREAM");
-    return v != nullptr && v[0] != '\0' && v[0] != '0';
-  }();
-  if (off) return false;
-  // Measured on B200 (profiles/): with 16-byte block copies and running source pointers the
-  // cp.async ring is as fast or faster than the register ring of gemv_mma_kernel<FAST> at
-  // every width (it fits three CTAs per SM).
-  static const bool ring_at_2bit = [] {  // measurement switch: the register ring instead, at 2 bits
-    const char* v = std::getenv("DQ_B200_RING_2BIT");
-    return v != nullptr && v[0] == '1';
-  }();
-  if (BITS == 2 && ring_at_2bit) return false;
+  if (tuning_int("DQ_B200_NO_STREAM") != 0) return false;
+  // Measured on B200: with 16-byte block copies and running source pointers the cp.async ring is
+  // as fast or faster than the register ring of gemv_mma_kernel<FAST> at every width (it fits
+  // three CTAs per SM).
+  if (BITS == 2 && tuning_int("DQ_B200_RING_2BIT") == 1) return false;
   if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) {
     return false;  // whole steps are copied in 16-byte pieces
   }
   if (a.group_values != kStepValues || steps % C::P != 0 || a.num_groups % C::P != 0) return false;
-  if (tiles < dev.sm_count * stream::kWarps) return false;
+  if (tiles < dev.sm_count * tuning_int("DQ_B200_STREAM_MIN_TILES_PER_SM", stream::kWarps)) return false;
   const auto align = static_cast<uintptr_t>(C::META_BYTES);
   if (reinterpret_cast<uintptr_t>(a.scales) % align != 0 || reinterpret_cast<uintptr_t>(a.offsets) % align != 0) {
     return false;
@@ -574,36 +566,14 @@ int32_t try_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int step
 
 // ---- tiled kernel (dq_gemv_mma_tile.cuh): short and middle-sized matrices, fused shards ----
 
-int env_int(const char* name) {
-  const char* v = std::getenv(name);
-  return v != nullptr ? std::atoi(v) : 0;
-}
-
-// A measurement switch: read once per process -- unless DQ_B200_LIVE_KNOBS is set, in which
-// case every launch reads it again so that one process can time several settings.
-struct Knob {
-  const char* name;
-  int cached = 0;
-  bool have = false;
-  int get() {
-    static const bool live = std::getenv("DQ_B200_LIVE_KNOBS") != nullptr;
-    if (live || !have) {
-      cached = env_int(name);
-      have = true;
-    }
-    return cached;
-  }
-};
-
 // One launch for `n` matrices sharing the activation.  *taken stays false (and nothing is
 // launched) when the jobs do not meet the kernel's requirements.
 int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo& dev, cudaStream_t stream_h,
                  bool* taken) {
   *taken = false;
-  static const bool off = env_int("DQ_B200_NO_TILE") != 0;
-  static Knob knob_kw{"DQ_B200_TILE_KW"}, knob_nb{"DQ_B200_TILE_NB"}, knob_per_sm{"DQ_B200_TILE_PER_SM"},
-      knob_ctas{"DQ_B200_TILE_CTAS"};
-  const int force_kw = knob_kw.get(), force_nb = knob_nb.get(), force_per_sm = knob_per_sm.get();
+  const bool off = tuning_int("DQ_B200_NO_TILE") != 0;
+  const int force_kw = tuning_int("DQ_B200_TILE_KW"), force_nb = tuning_int("DQ_B200_TILE_NB"),
+            force_per_sm = tuning_int("DQ_B200_TILE_PER_SM");
   if (off || n < 1 || n > tilek::kMaxJobs) return DQ_OK;
   const GemvArgs& a0 = jobs[0];
   const int steps = a0.words_per_row / (4 * bits[0]);
@@ -630,7 +600,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
   // Long matrices with one group per step have leaner kernels of their own (the streaming
   // kernel, or the register ring at 2 bits): this one is for what does not fill the machine
   // eight tiles per SM deep, for fused shards and for 64-value groups.
-  static const bool tile_all = env_int("DQ_B200_TILE_ALL") != 0;
+  const bool tile_all = tuning_int("DQ_B200_TILE_ALL") != 0;
   if (n == 1 && !g64_jobs && !tile_all && max_tiles_total >= dev.sm_count * tilek::kWarps) return DQ_OK;
   // Shape of the CTAs.  First choice: ONE wave in which every warp's whole share of the
   // weights is in flight before the activation arrives -- the finest slicing of the reduction
@@ -722,7 +692,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     return best;
   };
   // The three-CTA build only where its third CTA per SM buys a finer one-wave slicing.
-  const int force_ctas = knob_ctas.get();
+  const int force_ctas = tuning_int("DQ_B200_TILE_CTAS");
   ctas_by_registers = 3;
   Shape pick = choose();
   const bool needs_three = pick.kw != 0 && pick.ipc == 1 && pick.nb == (steps / pick.kw) / pick.ch &&
@@ -891,9 +861,7 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
     p.kw = best_kw;
   }
   {
-    // tuning overrides (measurement only)
-    static const int force_kw = [] { const char* v = std::getenv("DQ_B200_MMA_KW"); return v ? std::atoi(v) : 0; }();
-    static const int force_rw = [] { const char* v = std::getenv("DQ_B200_MMA_RW"); return v ? std::atoi(v) : 0; }();
+    const int force_kw = tuning_int("DQ_B200_MMA_KW"), force_rw = tuning_int("DQ_B200_MMA_RW");
     if (force_kw > 0) p.kw = std::min(force_kw, floor_pow2(p.steps));
     if (force_rw > 0) p.rw = std::min(force_rw, kMaxWarps / p.kw);
   }

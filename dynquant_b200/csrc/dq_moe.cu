@@ -533,22 +533,8 @@ int32_t static_scratch_address(void** out) {
   return DQ_OK;
 }
 
-// Measurement switches of the MoE launcher (integers from the environment; 0 / unset = the
-// built-in choice).  Read once per process -- unless DQ_B200_MOE_LIVE_KNOBS is set, in which
-// case every launch reads them again so that one process can time several settings.
-inline int moe_knob(const char* name, int* cached, bool* have) {
-  static const bool live = std::getenv("DQ_B200_MOE_LIVE_KNOBS") != nullptr;
-  if (!live && *have) return *cached;
-  const char* v = std::getenv(name);
-  const int value = v ? std::atoi(v) : 0;
-  *cached = value;
-  *have = true;
-  return value;
-}
-#define DQ_MOE_KNOB(var, name)            \
-  static int var##_cached = 0;            \
-  static bool var##_have = false;         \
-  const int var = ::dq::moe_knob(name, &var##_cached, &var##_have)
+// Launch-shape overrides of the MoE launcher (tuning builds only, see tuning_int; 0 = the built-in choice).
+#define DQ_MOE_KNOB(var, name) const int var = ::dq::tuning_int(name)
 
 template <typename Kernel>
 int32_t launch_pdl(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t stream, const MoeArgs& args,

@@ -163,8 +163,8 @@ def input_axis_split(bits: int, group_size: int, in_features: int, world: int, n
     per = in_features // world
     if per % full.effective_group:
         raise ValueError(
-            f"{name}: {world} ranks get {per} of {in_features} inputs each, not a whole number of "
-            f"{full.effective_group}-value groups; use a rank count dividing {in_features // full.effective_group}"
+            f"{name}: {world} ranks get {per} of {in_features} inputs each, which is not a whole number of groups "
+            f"of {full.effective_group} values; use a rank count dividing {in_features // full.effective_group}"
         )
     part = row_geometry(bits, group_size, per)
     if part.words_per_row * world != full.words_per_row:

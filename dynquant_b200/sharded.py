@@ -148,7 +148,7 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, gate_up_local: QuantTensor, down_local: QuantTensor, *, num_experts: int,
-                 group=None, compute: Callable | None = None) -> None:
+                 group=None, compute: Callable | None = None, max_tokens: int = 64) -> None:
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -165,6 +165,7 @@ class ExpertParallelMoE:
                 return ops.moe_gemv(x, ids, w, gate_up, down, num_experts=num_experts, out_dtype=torch.float32)
 
         self.compute = compute
+        self.max_tokens = max_tokens
 
     def _localise(self, ids: torch.Tensor) -> torch.Tensor:
         """Global expert ids -> this rank's local numbering, -1 for experts held elsewhere."""
@@ -173,8 +174,17 @@ class ExpertParallelMoE:
         return torch.where((local >= 0) & (local < self.local_experts), local, torch.full_like(ids, -1)).to(torch.int32)
 
     def _local_partial(self, x: torch.Tensor, ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        return self.compute(x.contiguous(), self._localise(ids).contiguous(), w.contiguous(), self.gate_up,
-                            self.down, self.local_experts)
+        """Partial sums of this rank's experts for every gathered token, at most ``max_tokens`` tokens
+        per call of the grouped kernel (the gathered batch is ``world`` times a rank's own)."""
+        local = self._localise(ids)
+        limit = self.max_tokens
+        if x.shape[0] <= limit:
+            return self.compute(x.contiguous(), local.contiguous(), w.contiguous(), self.gate_up, self.down,
+                                self.local_experts)
+        parts = [self.compute(x[s : s + limit].contiguous(), local[s : s + limit].contiguous(),
+                              w[s : s + limit].contiguous(), self.gate_up, self.down, self.local_experts)
+                 for s in range(0, x.shape[0], limit)]
+        return torch.cat(parts)
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, mode: str = "all_to_all") -> torch.Tensor:
         t, h = x.shape

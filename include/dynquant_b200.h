@@ -249,7 +249,8 @@ DQ_API int32_t dq_gemv_host(const void* x_host, int32_t x_dtype, int64_t m, cons
  *
  * x [tokens, hidden] in x_dtype (fp16 or bf16), tokens <= DQ_MOE_MAX_TOKENS;
  * topk_ids [tokens, topk] int32, ids outside [0, num_experts) are skipped (an
- * expert-parallel rank passes its local expert numbers and -1 for the rest);
+ * expert-parallel rank passes its local expert numbers and -1 for the rest); the ids of one
+ * token must be distinct, so that no expert receives more than `tokens` assignments;
  * topk_w [tokens, topk] fp32; y [tokens, hidden] in y_dtype.  The intermediate
  * silu(g)*u is rounded once to x_dtype.  fp32 accumulation, no atomics: bit-identical
  * run to run.  `scratch` is caller-owned device memory of at least
@@ -279,11 +280,14 @@ DQ_API int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const
  *
  * The first call on each device looks up the buffer's device address
  * (cudaGetSymbolAddress, with that device current); make that first call before any
- * stream capture begins.  Every call on a device shares the one buffer: it still holds the
- * previous call's routing tables and intermediates when the next call starts (each call
- * rewrites everything it reads, nothing has to start at zero), so two calls that may
- * overlap on the GPU -- different streams, no ordering between them -- race on it.
- * Order them, or give the overlapping one its own scratch through dq_moe_gemv. */
+ * stream capture begins.  On EVERY call the device that owns `stream`, x and y must be the
+ * current device: the address is looked up for the current device, and kernels launched on
+ * another device's stream would be handed an address that is not theirs.  Every call on a device shares the one buffer: it still holds the
+ * previous call's intermediates (the rounded silu(g)*u rows and the per-assignment down
+ * projections) when the next call starts -- each call rewrites everything it reads, nothing
+ * has to start at zero -- so two calls that may overlap on the GPU (different streams, no
+ * ordering between them) race on it.  Order them, or give the overlapping one its own scratch
+ * through dq_moe_gemv. */
 DQ_API int32_t dq_moe_gemv_static(const void* x, int32_t x_dtype, int64_t tokens,
                                   const int32_t* topk_ids, const float* topk_w, int64_t topk,
                                   int64_t num_experts, const dq_weight* gate_up,

@@ -101,6 +101,25 @@ def _worker(rank: int, world: int, port: int, results):
             y = ep(x_all[mine], ids_all[mine], w_all[mine], mode=mode).float()
             ref = want[mine].to(torch.bfloat16).float()
             errs[mode] = float((y - ref).abs().max() / (ref.abs().max() + 1e-30))
+        # ---- more gathered tokens than one call of the grouped kernel takes: chunks of 64 ----
+        t_big = 40  # 80 gathered tokens over two ranks
+        ids_big, w_big = seeded_routing(world * t_big, experts, topk, seed=9)
+        x_big = torch.randn(world * t_big, hidden, generator=gen).to(torch.bfloat16)
+        want_big = _oracle_moe(hidden, inter)(x_big, ids_big, w_big, gate_up, down, experts)
+        inner = _oracle_moe(hidden, inter)
+
+        def bounded(x, ids, w, gu, dn, n):
+            assert x.shape[0] <= 64, f"{x.shape[0]} tokens in one call"
+            return inner(x, ids, w, gu, dn, n)
+
+        ep_big = ExpertParallelMoE(expert_shard(gate_up, 2 * inter, experts, rank, world),
+                                   expert_shard(down, hidden, experts, rank, world), num_experts=experts,
+                                   compute=bounded, max_tokens=64)
+        big = slice(rank * t_big, (rank + 1) * t_big)
+        for mode in ("all_to_all", "replicated"):
+            y = ep_big(x_big[big], ids_big[big], w_big[big], mode=mode).float()
+            ref = want_big[big].to(torch.bfloat16).float()
+            errs[mode + "/80 tokens"] = float((y - ref).abs().max() / (ref.abs().max() + 1e-30))
         results[rank] = (ok_dense, errs, errs_in)
     finally:
         dist.destroy_process_group()

@@ -48,9 +48,16 @@ def test_static_scratch_entry_point_matches_the_allocating_one_twice():
         x = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(call)).to(torch.bfloat16).cuda()
         want = ops.moe_gemv(x, ids, w, layer.gate_up, layer.down, num_experts=experts)
         got = torch.empty_like(want)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        held_before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
         rc = _call_static(lib, _lib, ops, x, ids, w, layer, experts, got)
         assert rc == _lib.DQ_OK, _lib.last_error()
         torch.cuda.synchronize()
+        if call > 0:  # (the very first call may load the kernels' code; after that nothing may move)
+            # the claim itself: the call obtained no device memory, from the driver or from torch
+            assert torch.cuda.mem_get_info()[0] == free_before
+            assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == held_before
         # same kernels, same order of operations: bit-identical, not merely close
         assert torch.equal(got, want)
 
