@@ -40,6 +40,19 @@ def is_available() -> bool:
     return torch.cuda.is_available()
 
 
+def install_kernel_shim() -> str:
+    """Make the reference runtime (``dynquant.runtime``) find THESE kernels: put the stand-in for
+    its ``dynquant_kernels`` package (``dynquant_b200/shim``) first on ``sys.path``.  Call it
+    before ``dynquant.runtime`` resolves its backend.  Returns the directory added."""
+    import sys
+    from pathlib import Path
+
+    shim = str(Path(__file__).resolve().parent / "shim")
+    if shim not in sys.path:
+        sys.path.insert(0, shim)
+    return shim
+
+
 __all__ = [
     "ABI_VERSION",
     "BIT_OPTIONS",
@@ -52,6 +65,7 @@ __all__ = [
     "dequantize",
     "embedding_lookup",
     "gemv_max_rows",
+    "install_kernel_shim",
     "is_available",
     "load_packed_checkpoint",
     "ops",

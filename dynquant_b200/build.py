@@ -80,7 +80,45 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     return LIB_PATH
 
 
+TORCH_SHIM_PATH = PKG / "lib" / "libdynquant_b200_torch.so"
+
+
+def build_torch_shim(force: bool = False, verbose: bool = False) -> Path | None:
+    """Compile ``csrc/dq_torch_shim.cpp`` -- the C++ CUDA backend of ``torch.ops.dynquant.{gemv,
+    dequant}`` -- against the installed torch and link it to the C-ABI library beside it.  It is
+    optional: without it the operators are implemented by a Python function over ctypes (same
+    kernels, more host time per call).  Returns None when no C++ compiler is available."""
+    src = CSRC / "dq_torch_shim.cpp"
+    if not force and not _stale(TORCH_SHIM_PATH, [src, INCLUDE / "dynquant_b200.h", LIB_PATH]):
+        return TORCH_SHIM_PATH
+    gxx = shutil.which("g++")
+    if gxx is None or not LIB_PATH.exists():
+        return None
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension
+
+    torch_lib = Path(torch.__file__).parent / "lib"
+    cmd = [gxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI),
+           "-I", str(INCLUDE), "-I", sysconfig.get_paths()["include"], "-I", "/usr/local/cuda/include"]
+    for p in cpp_extension.include_paths():
+        cmd += ["-isystem", p]
+    cmd += [str(src), "-o", str(TORCH_SHIM_PATH), "-L", str(LIB_PATH.parent), "-ldynquant_b200",
+            "-L", str(torch_lib), "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+            "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("g++ failed on dq_torch_shim.cpp")
+    return TORCH_SHIM_PATH
+
+
 if __name__ == "__main__":
     path = build_library(force="--force" in sys.argv or "--tuning" in sys.argv, verbose=True,
                          ptxas_info="--ptxas-info" in sys.argv, tuning="--tuning" in sys.argv)
     print(path)
+    print(build_torch_shim(force="--force" in sys.argv, verbose=True))

@@ -451,7 +451,9 @@ def quantized_matmul(x: torch.Tensor, qt: QuantTensor, bias: torch.Tensor | None
     args = _kernel_args(qt)
     if flat.shape[0] <= gemv_max_rows():
         if bias is None:
-            out = gemv(flat.contiguous(), *args)
+            # the operator's C++ backend when it is loaded: a third of the host time of the
+            # Python route over ctypes (same entry point of the library underneath)
+            out = torch.ops.dynquant.gemv(flat.contiguous(), *args) if _native_backend else gemv(flat.contiguous(), *args)
         else:
             out = gemv_shards(flat.contiguous(), [qt], bias.contiguous())
     elif flat.shape[0] <= GEMV_CHUNKED_MAX_ROWS and flat.is_cuda:
@@ -481,6 +483,33 @@ def embedding_lookup(qt: QuantTensor, ids: torch.Tensor) -> torch.Tensor:
 
 _registered = False
 _libs: list[torch.library.Library] = []
+
+
+_native_backend = False
+
+
+def torch_ops_backend() -> str:
+    """``"c++"`` when ``torch.ops.dynquant.{gemv,dequant}`` run through the compiled shim
+    (``lib/libdynquant_b200_torch.so``, built by ``python -m dynquant_b200.build``), ``"python"``
+    when they are Python functions over ctypes."""
+    return "c++" if _native_backend else "python"
+
+
+def _load_torch_shim() -> bool:
+    import os
+    from pathlib import Path
+
+    if os.environ.get("DQ_B200_TORCH_SHIM", "1") == "0":
+        return False
+    path = Path(__file__).resolve().parent / "lib" / "libdynquant_b200_torch.so"
+    if not path.exists():
+        return False
+    try:
+        _lib.load()
+        torch.ops.load_library(str(path))
+    except (OSError, RuntimeError, _lib.LibraryUnavailableError):
+        return False  # built against another torch, or the C-ABI library is missing: Python backend
+    return True
 
 
 def register_torch_ops() -> bool:
@@ -530,8 +559,13 @@ def register_torch_ops() -> bool:
 
         return raiser
 
-    lib.impl("dequant", _dequant_cuda, "CUDA")
-    lib.impl("gemv", _gemv_cuda, "CUDA")
+    # CUDA backend: the compiled C++ shim when it has been built (one dispatcher hop and one C
+    # call per operator call), else these Python functions over ctypes.  Same kernels either way.
+    global _native_backend
+    _native_backend = _load_torch_shim()
+    if not _native_backend:
+        lib.impl("dequant", _dequant_cuda, "CUDA")
+        lib.impl("gemv", _gemv_cuda, "CUDA")
     lib.impl("dequant", _no_cpu("dequant"), "CPU")
     lib.impl("gemv", _no_cpu("gemv"), "CPU")
 

@@ -1,0 +1,83 @@
+"""The sharded paths on real GPUs: this library's kernels + NCCL together (needs two devices).
+
+The gloo tests (``test_sharded_gloo.py``) cover the placement logic with the oracle as the
+compute; here every rank runs the CUDA kernels on its shard and the exchange is NCCL over
+NVLink, and the reassembled result is compared with the same computation on one GPU:
+
+* column-sharded dense: the all-gathered output equals the unsharded kernel's, bit for bit
+  (rows are independent: a shard's rows are computed exactly as in the whole matrix);
+* expert-parallel MoE, both exchange modes: equal to the single-GPU layer up to the order of
+  the fp32 sum over ranks.
+
+No rank faults or hangs on purpose: process groups carry a short timeout, NVLS is off.
+"""
+
+from __future__ import annotations
+
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank: int, world: int, port: int, results) -> None:
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=60))
+    try:
+        from dynquant_b200 import ops
+        from dynquant_b200.sharded import ColumnShardedLinear, ExpertParallelMoE, column_shard, expert_shard
+        from dynquant_b200.workloads import qwen3_moe_layer, random_quant_tensor, seeded_routing
+
+        out = {}
+        # ---- column-sharded dense, every width, a long and a short matrix ----
+        for bits, rows in ((2, 40960), (3, 2048), (4, 6144), (8, 40960)):
+            gen = torch.Generator(device=dev).manual_seed(100 + bits)  # same seed: same tensor on every rank
+            qt = random_quant_tensor(rows, 2048, bits, device=dev, generator=gen)
+            x = torch.randn(1, 2048, device=dev, generator=gen).to(torch.bfloat16)
+            full = ops.quantized_matmul(x, qt)
+            got = ColumnShardedLinear(column_shard(qt, rank, world))(x)
+            out[f"dense{bits}"] = bool(torch.equal(got, full))
+        # ---- expert parallel ----
+        layer = qwen3_moe_layer(dev, seed=77, bits_gate_up=3, bits_down=4, num_experts=16, hidden=1024, inter=512, topk=4)
+        t_local = 6
+        ids_all, w_all = seeded_routing(world * t_local, 16, 4, seed=5)
+        x_all = torch.randn(world * t_local, 1024, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).to(dev)
+        want = ops.moe_gemv(x_all, ids_all.to(dev), w_all.to(dev), layer.gate_up, layer.down, num_experts=16,
+                            out_dtype=torch.float32)
+        ep = ExpertParallelMoE(expert_shard(layer.gate_up, 2 * 512, 16, rank, world),
+                               expert_shard(layer.down, 1024, 16, rank, world), num_experts=16)
+        mine = slice(rank * t_local, (rank + 1) * t_local)
+        for mode in ("all_to_all", "replicated"):
+            y = ep(x_all[mine], ids_all[mine].to(dev), w_all[mine].to(dev), mode=mode).float()
+            ref = want[mine].to(torch.bfloat16).float()
+            out[mode] = float((y - ref).abs().max() / ref.abs().max())
+        results[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_paths_on_two_gpus_match_one_gpu():
+    world = 2
+    port = 29600 + (os.getpid() % 1000)
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    assert len(results) == world
+    for rank in range(world):
+        for key, value in results[rank].items():
+            if key.startswith("dense"):
+                assert value, f"rank {rank}: gathered {key} differs from the unsharded result"
+            else:
+                assert value <= 1e-2, f"rank {rank} {key}: {value}"  # one bf16 rounding of the output
