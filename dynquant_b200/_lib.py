@@ -81,6 +81,19 @@ class PlanInfo(ctypes.Structure):
     ]
 
 
+class PeerGroup(ctypes.Structure):
+    """``dq_peer_group``."""
+
+    _fields_ = [
+        ("buffers", ctypes.c_void_p),
+        ("buffer_bytes", ctypes.c_int64),
+        ("world", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("spin_limit", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+    ]
+
+
 _P = ctypes.c_void_p
 _I32 = ctypes.c_int32
 _I64 = ctypes.c_int64
@@ -114,6 +127,10 @@ SIGNATURES = {
     "dq_plan_stage_shape": (_I32, [_P, _I32, ctypes.POINTER(_I32), ctypes.POINTER(_I32), ctypes.POINTER(_I32)]),
     "dq_plan_set_wait": (_I32, [_P, _I32, _I32, _I32, _P]),
     "dq_plan_destroy": (None, [_P]),
+    "dq_peer_header_bytes": (_I64, []),
+    "dq_peer_all_gather": (_I32, [ctypes.POINTER(PeerGroup), _P, _I64, _P, _P]),
+    "dq_peer_reduce_scatter_f32": (_I32, [ctypes.POINTER(PeerGroup), _P, _I64, _P, _I32, _P]),
+    "dq_peer_status": (_I32, [ctypes.POINTER(PeerGroup), _P, _P]),
     "dq_gemv_host": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P, _P, _P]),
 }
 

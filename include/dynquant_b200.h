@@ -294,6 +294,45 @@ DQ_API int32_t dq_moe_gemv_static(const void* x, int32_t x_dtype, int64_t tokens
                                   const dq_weight* down, int64_t hidden, int64_t inter, void* y,
                                   int32_t y_dtype, void* stream);
 
+/* ---- exchanges of the sharded paths over peer memory ------------------------------------
+ * No reference counterpart: the reference issues no collective (tensor parallelism there is
+ * weight placement only, integration/vllm_plugin/parameter.py:102-154; the gathers are the
+ * host framework's).  These replace a host-issued library collective where the payload is a
+ * few KB and the call is made hundreds of times per decode step: the output slabs of a
+ * column-sharded layer (all-gather) and the partial sums of an expert-parallel layer
+ * (reduce-scatter).  Each enqueues ordinary kernels on `stream` (capturable): a rank STORES
+ * its piece into every peer's exchange buffer through peer-mapped pointers, raises a flag
+ * there, and waits -- a bounded number of polls -- for the peers' flags in its own buffer.
+ * Only local memory is ever read; no TMA, no multicast.
+ *
+ * `buffers`: DEVICE array of `world` pointers, entry i = rank i's exchange buffer as mapped
+ * into this process (CUDA IPC / symmetric memory), every buffer `buffer_bytes` long, zeroed
+ * before first use, 16-byte aligned.  The first dq_peer_header_bytes() bytes hold flags,
+ * epochs and a status word; the rest is two halves used alternately, each of which must hold
+ * `world` pieces.  All ranks must issue the same sequence of exchanges on a group.  If a
+ * peer's flag does not arrive within `spin_limit` polls (0: a default of about a second) the
+ * kernel sets the status word and returns; dq_peer_status then reports DQ_ERR_DEVICE. */
+typedef struct dq_peer_group {
+  void* const* buffers;
+  int64_t buffer_bytes;
+  int32_t world, rank;
+  int32_t spin_limit;
+  int32_t reserved;
+} dq_peer_group;
+DQ_API int64_t dq_peer_header_bytes(void);
+/* Every rank contributes `bytes` (a multiple of 16) at `src`; `out` receives world * bytes,
+ * rank i's piece at out + i * bytes. */
+DQ_API int32_t dq_peer_all_gather(const dq_peer_group* group, const void* src, int64_t bytes,
+                                  void* out, void* stream);
+/* `partial` holds world * count floats: the rows this rank computed for rank i's elements at
+ * partial + i * count.  `out` (count elements of out_dtype) receives the sum over source ranks
+ * of the rows that belong to this rank, added in rank order, rounded once. */
+DQ_API int32_t dq_peer_reduce_scatter_f32(const dq_peer_group* group, const float* partial,
+                                          int64_t count, void* out, int32_t out_dtype, void* stream);
+/* Synchronises `stream` and reads the status word of this rank's own buffer (`local_buffer` =
+ * the pointer that is buffers[rank]). */
+DQ_API int32_t dq_peer_status(const dq_peer_group* group, const void* local_buffer, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
