@@ -250,28 +250,27 @@ def full_sharded_names(full, world: int, shard_min_bytes: int = 32 << 20) -> lis
 def config3_block(args, rank, world, device, dist, peak) -> dict:
     """BASELINE's third configuration: the Qwen3-14B-shaped linear set (40 layers, hidden 5120,
     intermediate 17408, seeded 3/4-bit map), every module column-sharded over the ranks (each
-    rank generates and holds only its slab of rows), M = 1.  The per-rank step is one plan
-    kernel; under N > 1 the slabs' outputs are all-gathered after it (one NCCL call per module,
-    issued after the step -- the synthetic set's activations are resident, so nothing in the
-    step waits for a gather)."""
+    rank generates and holds only its slab of rows), M = 1.  Under N > 1 every stage's output
+    slabs are all-gathered right after the stage, before the next stage's launch."""
     import torch
 
     from dynquant_b200.stack import StepRunner
     from dynquant_b200.workloads import qwen14b_linear_set
 
     local = qwen14b_linear_set(device=device, shard=(rank, world))
-    runner = StepRunner(local, 1, device=device)
-    mode = capture_runner(runner, args.graph_mode)
-    gathers = []
-    if world > 1:
-        for mod in local.modules:
-            piece = runner.outputs[mod.name]
-            gathers.append((piece, torch.empty(world, piece.shape[1], dtype=piece.dtype, device=device)))
+    if world == 1:
+        runner = StepRunner(local, 1, device=device)
+        mode = capture_runner(runner, args.graph_mode)
+        step = runner.replay
+        exchange = None
+    else:
+        from dynquant_b200.sharded import ShardedStepRunner
 
-    def step():
-        runner.replay()
-        for piece, full in gathers:
-            dist.all_gather_into_tensor(full, piece)
+        mode = "dataflow" if args.graph_mode == "plan" else args.graph_mode
+        runner = ShardedStepRunner(local, 1, rank=rank, world=world, device=device, graph_mode=mode,
+                                   exchange=args.exchange, presharded=True)
+        step = runner.run
+        exchange = runner.exchange
 
     def sync():
         torch.cuda.synchronize(device)
@@ -282,11 +281,16 @@ def config3_block(args, rank, world, device, dist, peak) -> dict:
 
     steps = max(5, args.steps // 3)
     seconds = max_over_ranks(time_steps(step, steps, 3, sync, barrier), dist, device) / steps
+    if world > 1:
+        runner.check()
     local_bytes = local.algorithmic_bytes(1)
     total_bytes = local_bytes * world
     return {
         "workload": "qwen3-14b-shaped linear set (BASELINE config 3: 40 layers x 7 modules, 3/4-bit, M=1)",
-        "placement": "single gpu" if world == 1 else f"every module column-sharded x{world}, NCCL all-gather per module",
+        "placement": ("single gpu" if world == 1 else
+                      f"every module column-sharded x{world}; each stage's output slabs all-gathered right after the "
+                      f"stage ({'library kernels over peer memory, in the graph' if exchange == 'peer' else 'NCCL'})"),
+        "exchanges_per_step": 0 if world == 1 else runner.gathers_per_step,
         "launch": f"cuda graph, {mode}", "launches_per_step": runner.launches_per_step,
         "ms_per_step": round(seconds * 1e3, 4), "weight_bytes_per_gpu": local.weight_bytes,
         "gbps_aggregate": round(total_bytes / seconds / 1e9, 1),
@@ -328,7 +332,7 @@ def run_ours(args) -> None:
         from dynquant_b200.sharded import ShardedStepRunner
 
         runner = ShardedStepRunner(full, m, rank=rank, world=world, device=device,
-                                   graph_mode=args.graph_mode if use_graph else None)
+                                   graph_mode=args.graph_mode if use_graph else None, exchange=args.exchange)
         step_fn = runner.run
         mode = runner.graph_mode
         local_bytes = runner.local_stack.algorithmic_bytes(m)
@@ -361,6 +365,8 @@ def run_ours(args) -> None:
     value = step_bytes / per_step / 1e9
     if world == 1 and mode == "plan":
         runner.plan().check()  # no stage's bounded wait ran out during the timed steps
+    if world > 1:
+        runner.check()  # nor an exchange's
 
     # ---- sharded runs: the gathered output against the same module computed unsharded ----
     if world > 1 and runner.sharded:
@@ -448,8 +454,9 @@ def run_ours(args) -> None:
     # ---- the rest of the metric: expert layer (config 4) and the 14B linear set (config 3) ----
     extras = {}
     parallelism = ("single gpu" if world == 1 else
-                   f"large layers ({', '.join(full_sharded_names(full, world))}) column-sharded x{world} with an NCCL "
-                   f"all-gather, small layers computed on every rank")
+                   f"large layers ({', '.join(full_sharded_names(full, world))}) column-sharded x{world}, their outputs "
+                   f"all-gathered {'by the library over peer memory, inside the graph' if args.exchange == 'peer' else 'with NCCL'}; "
+                   f"small layers computed on every rank")
     weight_bytes = full.weight_bytes
     cpu_modules = [(mod.weight.num_rows, mod.weight.in_features, mod.weight.bits) for mod in full.modules[:56]]
     if not args.no_extras and args.layers == 28:
@@ -536,6 +543,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-probe", action="store_true", help="skip the read/copy bandwidth probe")
     ap.add_argument("--no-extras", action="store_true", help="skip the moe and config3 blocks")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: exchanges by the library's kernels over peer memory (in the graph) or by NCCL calls")
     ap.add_argument("--e2e-eager-copies", action="store_true",
                     help="end-to-end arm: issue the host<->device copies as separate calls around the step's graph")
     ap.add_argument("--graph-mode", choices=["plan", "dataflow", "chain", "independent"], default="dataflow",

@@ -46,7 +46,7 @@ def hbm_peak_gbs() -> tuple[float, str]:
 
 
 def measure(tokens_list, *, layers: int = 6, steps: int = 20, rank: int = 0, world: int = 1, device=None,
-            dist=None, mode: str = "all_to_all") -> list[dict]:
+            dist=None, mode: str = "peer") -> list[dict]:
     """One result per token count.  ``dist`` given: expert-parallel over its ranks (every rank
     must call this with the same arguments); otherwise the whole layer on ``device``."""
     dev = torch.device(device if device is not None else "cuda")
@@ -57,9 +57,14 @@ def measure(tokens_list, *, layers: int = 6, steps: int = 20, rank: int = 0, wor
     if ep:
         from dynquant_b200.sharded import ExpertParallelMoE, expert_shard
 
+        peer = None
+        if mode == "peer":
+            from dynquant_b200.peer import PeerExchange
+
+            peer = PeerExchange(max(tokens_list) * 2048 * 4, device=dev)  # the largest piece: fp32 partial rows
         eps = [ExpertParallelMoE(expert_shard(l.gate_up, 2 * l.inter, l.num_experts, rank, world).to(dev),
                                  expert_shard(l.down, l.hidden, l.num_experts, rank, world).to(dev),
-                                 num_experts=l.num_experts) for l in banks]
+                                 num_experts=l.num_experts, peer=peer) for l in banks]
     results = []
     for tokens in tokens_list:
         if ep and (tokens % world or tokens // world == 0):
@@ -84,11 +89,12 @@ def measure(tokens_list, *, layers: int = 6, steps: int = 20, rank: int = 0, wor
             step()
         launches_per_layer = (ops.launch_count() - before) / 3 / layers
         torch.cuda.synchronize(dev)
-        # Single GPU: replay a CUDA graph of the step, so that the time is the device's.  Expert
-        # parallel: the step runs eagerly, its NCCL exchanges are issued from Python rank by rank
-        # and the time includes that host work.
+        # A CUDA graph of the step is replayed, so that the time is the device's -- on one GPU and,
+        # with the exchanges over peer memory (kernel launches), expert-parallel too.  With the NCCL
+        # exchanges the step runs eagerly: they are issued from Python rank by rank and the time
+        # includes that host work.
         run, launch = step, "eager"
-        if not ep:
+        if not ep or mode == "peer":  # (peer exchanges are kernel launches: the layer captures whole)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 step()
@@ -108,6 +114,8 @@ def measure(tokens_list, *, layers: int = 6, steps: int = 20, rank: int = 0, wor
             t = torch.tensor([seconds], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             seconds = float(t.item())
+        if ep and mode == "peer":
+            peer.check()  # no exchange's bounded wait ran out
         nbytes = sum(l.bytes_for(ids_all, tokens) for l in banks) / layers
         results.append({
             "workload": "qwen3-30b-a3b expert layer (128 experts, top-8, hidden 2048, inter 768, 2/3/4-bit banks)",
@@ -130,7 +138,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=6)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--ep", action="store_true", help="expert-parallel over the torchrun ranks")
-    ap.add_argument("--mode", default="all_to_all", choices=["all_to_all", "replicated"])
+    ap.add_argument("--mode", default="peer", choices=["peer", "all_to_all", "replicated"])
     ns = ap.parse_args()
     rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("WORLD_SIZE", 1), ("LOCAL_RANK", 0)))
     torch.cuda.set_device(local)

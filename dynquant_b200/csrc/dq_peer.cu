@@ -54,6 +54,11 @@ struct Args {
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ unsigned int ld_relaxed_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -96,24 +101,30 @@ __global__ void __launch_bounds__(kThreads) peer_exchange_kernel(const Args a) {
   const unsigned char* src = a.src + (a.scatter ? static_cast<int64_t>(p) * a.piece_bytes : 0);
   unsigned char* slot = theirs + kHeaderBytes + half + static_cast<int64_t>(a.rank) * a.piece_bytes;
   copy_span(slot, src, lo, hi);
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned int before = atomicAdd(&arrived[p], 1u);
-    if (before == static_cast<unsigned int>(a.ctas_per_peer) - 1u) {
+    // Ordering without a fence per thread: the barrier above orders the CTA's stores before this
+    // thread; the counter is added with release / acquire semantics at GPU scope (cumulative over
+    // what each CTA's thread 0 has observed), and the flag is stored with release at SYSTEM scope.
+    bool last = true;
+    if (a.ctas_per_peer > 1) {
+      unsigned int before;
+      asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(&arrived[p]) : "memory");
+      last = before == static_cast<unsigned int>(a.ctas_per_peer) - 1u;
+    }
+    if (last) {
       // the last CTA of the group: everything of this piece is on its way, and every CTA of the
       // group has read the epoch (it did so before pushing) -- record it for the next exchange
-      arrived[p] = 0u;
+      if (a.ctas_per_peer > 1) arrived[p] = 0u;
       epochs[p] = epoch;
-      __threadfence_system();
       st_release_sys(reinterpret_cast<unsigned int*>(theirs + kFlagsAt) + a.rank, epoch);
     }
     // ---- wait, bounded, for rank p's piece of the same epoch in my own buffer ----
     const unsigned int* flag = reinterpret_cast<const unsigned int*>(mine + kFlagsAt) + p;
     int ok = 0;
     for (int it = 0; it < a.spin_limit; ++it) {
-      if (ld_acquire_sys(flag) >= epoch) {
-        ok = 1;
+      if (ld_relaxed_sys(flag) >= epoch) {
+        ok = ld_acquire_sys(flag) >= epoch ? 1 : 0;  // (one acquire once the flag is up)
         break;
       }
       if ((it & 255) == 255 && *reinterpret_cast<volatile unsigned int*>(status) != 0u) break;

@@ -8,7 +8,8 @@ framework's.  Placement rules kept from it: a column shard is a contiguous slab 
 ``packed`` / ``scales`` / ``offsets`` (rows are independent under group-wise packing,
 ``docs/format-spec.md:355-358``); experts are contiguous row slabs of a bank.
 
-No kernel here touches a peer's memory; every exchange is a library collective.
+The dense step exchanges over peer memory with the library's own kernels by default
+(``dynquant_b200/peer.py``); NCCL is the checked alternative and the expert layer's default.
 """
 
 from __future__ import annotations
@@ -143,13 +144,18 @@ class ExpertParallelMoE:
       ``tokens_local`` rows to every rank -- so no size has to travel to the host first.
     * ``mode="replicated"``: all-gather tokens and routing, local partial sums for all tokens,
       reduce-scatter back.  Fewer messages; same bytes.
+    * ``mode="peer"``: the replicated scheme with the library's own exchanges over peer memory
+      (``peer=`` a :class:`~dynquant_b200.peer.PeerExchange`): three small all-gathers (token rows,
+      ids, weights), the grouped kernels, one reduce-scatter that adds the source ranks in rank
+      order -- kernel launches only, so a whole layer can sit in a CUDA graph.
 
-    Both produce the same numbers up to the order of the final fp32 sum over ranks.
+    All produce the same numbers up to the order of the final fp32 sum over ranks.
     """
 
     def __init__(self, gate_up_local: QuantTensor, down_local: QuantTensor, *, num_experts: int,
-                 group=None, compute: Callable | None = None, max_tokens: int = 64) -> None:
+                 group=None, compute: Callable | None = None, max_tokens: int = 64, peer=None) -> None:
         self.group = group
+        self.peer = peer
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if num_experts % self.world:
@@ -205,6 +211,19 @@ class ExpertParallelMoE:
                 out = torch.empty(t, h, dtype=torch.float32, device=x.device)
                 dist.reduce_scatter_tensor(out, partial.contiguous(), group=self.group)
             return out.to(x.dtype)
+        if mode == "peer":
+            if self.peer is None:
+                raise ValueError('mode="peer" needs the layer to be built with peer=PeerExchange(...)')
+            xs = torch.empty(world * t, h, dtype=x.dtype, device=x.device)
+            ids = torch.empty(world * t, k, dtype=topk_ids.dtype, device=x.device)
+            ws = torch.empty(world * t, k, dtype=topk_w.dtype, device=x.device)
+            self.peer.all_gather(x.contiguous(), xs)
+            self.peer.all_gather(topk_ids.contiguous(), ids)
+            self.peer.all_gather(topk_w.contiguous(), ws)
+            partial = self._local_partial(xs, ids, ws).to(torch.float32).contiguous()  # [world*t, h]
+            out = torch.empty(t, h, dtype=x.dtype, device=x.device)
+            self.peer.reduce_scatter(partial.view(-1), out)
+            return out
         if mode != "all_to_all":
             raise ValueError(mode)
         # dispatch: rank r receives [world, t, ...] = every rank's tokens and routing
@@ -233,55 +252,106 @@ class ShardedStepRunner:
     """One decode step of a :class:`~dynquant_b200.workloads.LinearStack` on ``world`` GPUs.
 
     Large modules -- those whose per-rank slab of packed rows is still at least
-    ``shard_min_bytes`` -- are column-sharded (row slabs) and their ``[M, N/world]`` outputs
-    all-gathered over NCCL; everything smaller is computed by every rank, because a gather
-    costs more than the whole small GEMV.  The local kernels of a step replay from one CUDA
-    graph (:class:`~dynquant_b200.stack.StepRunner`); the gathers follow on the same stream.
+    ``shard_min_bytes`` -- are column-sharded (row slabs); everything smaller is computed by
+    every rank, because exchanging costs more than the whole small GEMV.  A stage (q/k/v,
+    gate/up, or a single module) whose modules are all sharded writes its ``[M, rows/world]``
+    outputs into one buffer, and that buffer is all-gathered right after the stage:
+
+    * ``exchange="peer"`` (default): the library's own kernels over peer memory
+      (:class:`~dynquant_b200.peer.PeerExchange`), enqueued between the stages and captured in
+      the step's CUDA graph -- a step is one graph replay, exchanges included;
+    * ``exchange="nccl"``: one ``all_gather_into_tensor`` per sharded stage, issued eagerly after
+      the graph of local kernels (the checked fallback; NCCL calls are kept out of the capture).
     """
 
     def __init__(self, stack, m: int, *, rank: int, world: int, device, act_dtype=torch.bfloat16,
-                 shard_min_bytes: int = 32 << 20, graph_mode: str | None = "dataflow") -> None:
+                 shard_min_bytes: int = 32 << 20, graph_mode: str | None = "dataflow", exchange: str = "peer",
+                 presharded: bool = False) -> None:
+        """``presharded``: ``stack`` already holds this rank's row slabs of every module (a set
+        too large to generate whole on every rank); every module then counts as sharded."""
         from .stack import StepRunner
         from .workloads import LinearStack, Module
 
+        if exchange not in ("peer", "nccl"):
+            raise ValueError(exchange)
         self.rank, self.world, self.device = rank, world, torch.device(device)
         modules, self.sharded = [], []
         for mod in stack.modules:
             qt = mod.weight
-            if world > 1 and qt.num_rows % world == 0 and qt.nbytes // world >= shard_min_bytes:
+            if presharded:
+                modules.append(mod)
+                self.sharded.append(mod.name)
+            elif world > 1 and qt.num_rows % world == 0 and qt.nbytes // world >= shard_min_bytes:
                 modules.append(Module(mod.name, column_shard(qt, rank, world), mod.input))
                 self.sharded.append(mod.name)
             else:
                 modules.append(mod)
         self.local_stack = LinearStack(stack.name + f"[{rank}/{world}]", stack.hidden, stack.intermediate, modules,
                                        stack.bit_map)
-        self.runner = StepRunner(self.local_stack, m, act_dtype=act_dtype, device=self.device)
+        self.runner = StepRunner(self.local_stack, m, act_dtype=act_dtype, device=self.device, stage_outputs=True)
         self.inputs = self.runner.inputs
         self.outputs = dict(self.runner.outputs)
-        self._gathers = []
-        for name in self.sharded:
-            piece = self.runner.outputs[name]
-            full = torch.empty(world * m, piece.shape[1], dtype=piece.dtype, device=self.device)
-            self._gathers.append((piece, full))
-            self.outputs[name] = full  # [world*m, N/world]: rank-major pieces of the [m, N] result
+        # stages whose modules are all sharded exchange their (one) output buffer
+        sharded = set(self.sharded)
+        self._gathers = {}  # stage index -> (piece [m, cols], full [world, m, cols])
+        self._columns = {}  # module name -> (stage index, first column, rows) inside its stage's buffer
+        for index, stage in enumerate(self.local_stack.stages()):
+            names = [self.local_stack.modules[i].name for i in stage]
+            hit = [n in sharded for n in names]
+            if any(hit) and not all(hit):
+                raise ValueError(f"stage {names} mixes sharded and replicated modules")
+            if world > 1 and all(hit):
+                piece = self.runner.stage_buffers[index]
+                self._gathers[index] = (piece, torch.empty(world, *piece.shape, dtype=piece.dtype, device=self.device))
+                col = 0
+                for i in stage:
+                    rows = self.local_stack.modules[i].weight.num_rows
+                    self._columns[self.local_stack.modules[i].name] = (index, col, rows)
+                    col += rows
+        for name, (index, col, rows) in self._columns.items():
+            self.outputs[name] = self._gathers[index][1][:, :, col:col + rows]  # [world, m, rows/world]
         self.gathers_per_step = len(self._gathers)
+        self.exchange = exchange if self._gathers else "none"
+        self._peer = None
+        if self.exchange == "peer":
+            from .peer import PeerExchange
+
+            biggest = max(p.numel() * p.element_size() for p, _ in self._gathers.values())
+            self._peer = PeerExchange(-(-biggest // 16) * 16, device=self.device)
         self.graph_mode = graph_mode
+        in_graph = self.exchange == "peer" and graph_mode == "dataflow"
         if graph_mode is not None:
-            self.runner.capture(graph_mode)
+            self.runner.capture(graph_mode, after_stage=self._exchange_stage if in_graph else None)
         else:
             self.runner.count_launches()
+        self._exchanges_in_graph = in_graph
         self.launches_per_step = self.runner.launches_per_step
+
+    def _exchange_stage(self, index: int) -> None:
+        pair = self._gathers.get(index)
+        if pair is None:
+            return
+        piece, full = pair
+        if self._peer is not None:
+            self._peer.all_gather(piece, full)
+        else:
+            dist.all_gather_into_tensor(full, piece)
 
     def run(self) -> None:
         if self.graph_mode is not None:
             self.runner.replay()
         else:
             self.runner.run()
-        for piece, full in self._gathers:
-            dist.all_gather_into_tensor(full, piece)
+        if not self._exchanges_in_graph:
+            for index in self._gathers:
+                self._exchange_stage(index)
+
+    def check(self) -> None:
+        """Raises if an exchange's bounded wait ran out (peer exchanges only)."""
+        if self._peer is not None:
+            self._peer.check()
 
     def gathered(self, name: str) -> torch.Tensor:
         """The full ``[m, N]`` output of a sharded module, reassembled from the rank-major pieces."""
-        full = self.outputs[name]
-        m = full.shape[0] // self.world
-        return full.view(self.world, m, -1).permute(1, 0, 2).reshape(m, -1)
+        full = self.outputs[name]  # [world, m, rows/world]
+        return full.permute(1, 0, 2).reshape(full.shape[1], -1)

@@ -87,7 +87,11 @@ class StepRunner:
     to a resident ``[m, K]`` tensor; every module writes ``outputs[name]``.
     """
 
-    def __init__(self, stack: LinearStack, m: int, *, act_dtype=torch.bfloat16, out_dtype=None, device="cuda"):
+    def __init__(self, stack: LinearStack, m: int, *, act_dtype=torch.bfloat16, out_dtype=None, device="cuda",
+                 stage_outputs: bool = False):
+        """``stage_outputs``: the modules of a stage (q/k/v, gate/up) write side by side into ONE
+        ``[m, sum of their rows]`` buffer (``stage_buffers[i]``), so that a sharded runner can
+        exchange a stage's output with one call; ``outputs[name]`` is then a column slice of it."""
         self.stack = stack
         self.m = m
         self.device = torch.device(device)
@@ -101,22 +105,35 @@ class StepRunner:
         self.inputs = {
             name: torch.randn(m, k, device=self.device, generator=gen).to(act_dtype) for name, k in widths.items()
         }
-        self.outputs = {
-            mod.name: torch.empty(m, mod.weight.num_rows, dtype=out_dtype, device=self.device)
-            for mod in stack.modules
-        }
+        placement = {}  # module index -> (buffer, row stride, first column)
+        self.stage_buffers: list[torch.Tensor] = []
+        if stage_outputs:
+            for stage in stack.stages():
+                total = sum(stack.modules[i].weight.num_rows for i in stage)
+                buf = torch.empty(m, total, dtype=out_dtype, device=self.device)
+                self.stage_buffers.append(buf)
+                col = 0
+                for i in stage:
+                    placement[i] = (buf, total, col)
+                    col += stack.modules[i].weight.num_rows
+        else:
+            for i, mod in enumerate(stack.modules):
+                placement[i] = (torch.empty(m, mod.weight.num_rows, dtype=out_dtype, device=self.device),
+                                mod.weight.num_rows, 0)
+        self.outputs = {mod.name: placement[i][0][:, placement[i][2]:placement[i][2] + mod.weight.num_rows]
+                        for i, mod in enumerate(stack.modules)}
         self._jobs = (_lib.GemvJob * len(stack.modules))()
         for i, mod in enumerate(stack.modules):
             qt = mod.weight
             x = self.inputs[mod.input]
-            out = self.outputs[mod.name]
+            out, stride, col0 = placement[i]
             job = self._jobs[i]
             job.x = x.data_ptr()
             job.out = out.data_ptr()
             job.bias = None
             job.m = m
-            job.out_stride = qt.num_rows
-            job.out_col0 = 0
+            job.out_stride = stride
+            job.out_col0 = col0
             job.x_dtype = _tag(act_dtype, "x")
             job.out_dtype = _tag(out_dtype, "out")
             job.weight = weight_descriptor(
@@ -155,16 +172,19 @@ class StepRunner:
         jobs = ctypes.cast(ctypes.byref(self._jobs, first * ctypes.sizeof(_lib.GemvJob)), ctypes.POINTER(_lib.GemvJob))
         _lib.check(lib.dq_gemv_sequence(jobs, count, _stream(self.device)))
 
-    def run_dataflow(self, side_streams: list[torch.cuda.Stream] | None = None) -> None:
+    def run_dataflow(self, side_streams: list[torch.cuda.Stream] | None = None, after_stage=None) -> None:
         """Enqueue the step as its dependency graph: stage after stage, the members of a stage
         (q/k/v, gate/up: contiguous jobs reading one activation) in ONE library call, which
         issues them as one fused launch.  Stages whose members are not contiguous fork onto
-        ``side_streams``."""
+        ``side_streams``.  ``after_stage(i)`` (optional) is called after stage ``i`` has been
+        enqueued -- where a sharded runner enqueues the exchange of that stage's output."""
         main = torch.cuda.current_stream(self.device)
         with torch.cuda.device(self.device):
-            for stage in self.stack.stages():
+            for index, stage in enumerate(self.stack.stages()):
                 if list(stage) == list(range(stage[0], stage[0] + len(stage))):
                     self._run_jobs(stage[0], len(stage))
+                    if after_stage is not None:
+                        after_stage(index)
                     continue
                 fork = torch.cuda.Event()
                 fork.record(main)
@@ -177,8 +197,8 @@ class StepRunner:
                     join.record(side)
                     main.wait_event(join)
 
-    def capture(self, mode: str = "dataflow") -> None:
-        """Record the step into a CUDA graph.
+    def capture(self, mode: str = "dataflow", after_stage=None) -> None:
+        """Record the step into a CUDA graph (``after_stage``: see :meth:`run_dataflow`; dataflow mode only).
 
         ``"dataflow"``: stages in order, the members of a stage in one fused launch (what a
         decoder layer's dependencies allow).  ``"chain"``: the whole job list in stream order through
@@ -204,7 +224,7 @@ class StepRunner:
             elif mode == "plan":
                 self.run_plan()
             elif mode == "dataflow":
-                self.run_dataflow(sides)
+                self.run_dataflow(sides, after_stage)
             elif mode == "independent":
                 main = torch.cuda.current_stream(self.device)
                 fork = torch.cuda.Event()

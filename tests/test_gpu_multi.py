@@ -58,7 +58,10 @@ def _worker(rank: int, world: int, port: int, results) -> None:
         ep = ExpertParallelMoE(expert_shard(layer.gate_up, 2 * 512, 16, rank, world),
                                expert_shard(layer.down, 1024, 16, rank, world), num_experts=16)
         mine = slice(rank * t_local, (rank + 1) * t_local)
-        for mode in ("all_to_all", "replicated"):
+        from dynquant_b200.peer import PeerExchange
+
+        ep.peer = PeerExchange(t_local * 1024 * 4, device=dev)
+        for mode in ("all_to_all", "replicated", "peer"):
             y = ep(x_all[mine], ids_all[mine].to(dev), w_all[mine].to(dev), mode=mode).float()
             ref = want[mine].to(torch.bfloat16).float()
             out[mode] = float((y - ref).abs().max() / ref.abs().max())
