@@ -514,11 +514,20 @@ bool stream_ok(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps) {
 template <int BITS>
 int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps, cudaStream_t stream_h) {
   using C = stream::Cfg<BITS>;
+  // The fp16-operand plan at 8 bits, where a code no longer has to be split into nibbles: half
+  // the fragment registers, half the mma and half the staged activation per step.  (At 2 and 4
+  // bits it saves one or two integer instructions per word but adds a sub.f16x2 per register;
+  // measured on 262144 x 2048 it is slower there -- 43 vs 49 % and 72 vs 80 % of the copy
+  // bandwidth -- so those widths keep the bf16-safe plan.)  Needs the unit-per-lane staging:
+  // a 16-byte aligned 16-bit activation.
+  const bool plan16 = (BITS == 8 || (BITS != 3 && tuning_int("DQ_B200_PLAN16_ALL") != 0)) &&
+                      (a.in_features & 7) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&
+                      tuning_int("DQ_B200_NO_PLAN16") == 0;
   stream::Params p = {};
   p.steps = steps;
   p.tiles = tiles;
-  p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
-  const int aregs = BITS == 8 ? 32 : 16;
+  p.magic = (plan16 || a.x_dtype != DQ_BF16) ? 0x64006400u : 0x43004300u;
+  const int aregs = plan16 ? 16 : (BITS == 8 ? 32 : 16);
   p.m_stride_u4 = steps * aregs + 4;
   const size_t smem = C::RING_BYTES + (static_cast<size_t>(a.m) * p.m_stride_u4 + aregs) * 16 +
                       static_cast<size_t>(steps) * 8 * 4 * 2;
@@ -547,6 +556,19 @@ int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int s
   };
   const bool xbf = a.x_dtype == DQ_BF16;
   const bool mbf = a.meta_dtype == DQ_BF16;
+#ifdef DQ_TUNING
+  constexpr bool kHasPlan16 = BITS != 3;
+#else
+  constexpr bool kHasPlan16 = BITS == 8;
+#endif
+  if constexpr (kHasPlan16) {
+    if (plan16) {
+      if (xbf && mbf) return run(stream::gemv_mma_stream_kernel<BITS, true, true, true>);
+      if (xbf) return run(stream::gemv_mma_stream_kernel<BITS, true, false, true>);
+      if (mbf) return run(stream::gemv_mma_stream_kernel<BITS, false, true, true>);
+      return run(stream::gemv_mma_stream_kernel<BITS, false, false, true>);
+    }
+  }
   if (xbf && mbf) return run(stream::gemv_mma_stream_kernel<BITS, true, true>);
   if (xbf) return run(stream::gemv_mma_stream_kernel<BITS, true, false>);
   if (mbf) return run(stream::gemv_mma_stream_kernel<BITS, false, true>);

@@ -18,6 +18,7 @@
 #include "dq_gemv.cuh"
 #include "dq_mma_plan.cuh"
 #include "dq_mma_stage.cuh"
+#include "dq_mma_plan16.cuh"
 
 namespace dq {
 namespace stream {
@@ -116,13 +117,15 @@ struct Params {
   uint32_t magic;   // a parameter so it stays a register operand of the decode
 };
 
-template <int BITS, bool XBF16, bool MBF16>
+// P16: the fp16-operand plan (dq_mma_plan16.cuh; 2-, 4- and 8-bit codes, aligned 16-bit activations).
+template <int BITS, bool XBF16, bool MBF16, bool P16 = false>
 __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const GemvArgs a, const Params p) {
   using Plan = MmaPlan<BITS>;
   using C = Cfg<BITS>;
   constexpr int P = C::P;
   constexpr int NB = C::NB;
-  constexpr int NA = Plan::kARegs;
+  constexpr int NA = P16 ? 16 : Plan::kARegs;
+  constexpr bool MMA_BF16 = P16 ? false : XBF16;  // operand type of the contraction
   constexpr int QU = NA / 4;
   constexpr int STEP_WORDS = 4 * BITS;
   constexpr int kTileRows = 16;
@@ -237,7 +240,15 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
 
   // ---- stage the activation (the only part that depends on the previous kernel) ----
   pdl_wait_prior_grid();
-  stage_activation<BITS, XBF16>(a, p.steps, p.m_stride_u4, xb, xsum, xneg, tid, kThreads);
+  if constexpr (P16) {
+    if constexpr (BITS != 3) {
+      // (xneg holds the steps' inverse power-of-two factors in this plan, not a bias sum)
+      stage_zero_fill<4, false>(a.m, p.steps, p.m_stride_u4, xb, xsum, xneg, tid, kThreads);
+      stage_units16<BITS, XBF16>(a, 0, p.steps, p.m_stride_u4, xb, xsum, xneg, tid, kThreads, nullptr);
+    }
+  } else {
+    stage_activation<BITS, XBF16>(a, p.steps, p.m_stride_u4, xb, xsum, xneg, tid, kThreads);
+  }
   __syncthreads();
 
   // ---- compute loop: one block of P steps per iteration ----
@@ -281,21 +292,26 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
         read_unit<BITS>(wsrc + (j * 2 + 0) * (C::UNIT * kThreads), wa);
         read_unit<BITS>(wsrc + (j * 2 + 1) * (C::UNIT * kThreads), wb);
         uint32_t aa[NA], ab[NA];
-        decode_unit<BITS>(wa, magic, aa);
-        decode_unit<BITS>(wb, magic, ab);
-        unbias_fragments<XBF16, NA>(aa);
-        unbias_fragments<XBF16, NA>(ab);
+        if constexpr (P16 && BITS != 3) {
+          decode_unit16<BITS>(wa, magic, aa);
+          decode_unit16<BITS>(wb, magic, ab);
+        } else {
+          decode_unit<BITS>(wa, magic, aa);
+          decode_unit<BITS>(wb, magic, ab);
+          unbias_fragments<XBF16, NA>(aa);
+          unbias_fragments<XBF16, NA>(ab);
+        }
         const uint4* bsrc = bblk + j * xb_step_u4;
         float d[4];
 #pragma unroll
         for (int q = 0; q < QU; ++q) {
           const uint4 b = bsrc[q * 4];
           if (q == 0) {
-            mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
+            mma_16816<MMA_BF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
           } else {
-            mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
+            mma_16816<MMA_BF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
           }
-          mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
+          mma_16816<MMA_BF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
         }
         auto meta_f32 = [&](int i) -> float {
           const uint32_t reg = mc[i][j / 2];
@@ -309,10 +325,18 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
         const float2 xs2 = *reinterpret_cast<const float2*>(xs_blk + j * 8);
         const float2 xn2 = *reinterpret_cast<const float2*>(xn_blk + j * 8);
         const float sc_a = meta_f32(0), sc_b = meta_f32(2);
-        acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
-        acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
-        acc[2] = fmaf(sc_b, d[2] + xn2.x, acc[2]);
-        acc[3] = fmaf(sc_b, d[3] + xn2.y, acc[3]);
+        if constexpr (P16) {
+          // xn2: the step's inverse power-of-two factor per activation row
+          acc[0] = fmaf(sc_a * xn2.x, d[0], acc[0]);
+          acc[1] = fmaf(sc_a * xn2.y, d[1], acc[1]);
+          acc[2] = fmaf(sc_b * xn2.x, d[2], acc[2]);
+          acc[3] = fmaf(sc_b * xn2.y, d[3], acc[3]);
+        } else {
+          acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
+          acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
+          acc[2] = fmaf(sc_b, d[2] + xn2.x, acc[2]);
+          acc[3] = fmaf(sc_b, d[3] + xn2.y, acc[3]);
+        }
         if (has_off) {
           const float of_a = meta_f32(1), of_b = meta_f32(3);
           acc[0] = fmaf(of_a, xs2.x, acc[0]);
