@@ -62,6 +62,11 @@ def measured_peak() -> tuple[float, str]:
     return FALLBACK_HBM_GBS, "fallback"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the 112 gemv_mma_tile_kernel launches of one
+# step (638.2 MB), per launch, from an ncu launch list of the default command on a B200.
+TILE_KERNEL_DRAM_BYTES_PER_LAUNCH = 5_698_000
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
 
@@ -75,6 +80,7 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.proc = None
         self.file = None
+        self.skip = 0
 
     def __enter__(self):
         try:
@@ -87,6 +93,22 @@ class ClockSampler:
         except OSError:
             self.proc = None
         return self
+
+    def rows_so_far(self) -> int:
+        if self.file is None:
+            return 0
+        return sum(1 for r in Path(self.file.name).read_text().splitlines() if r.count(",") >= 8)
+
+    def wait_for_first_sample(self, limit_s: float = 8.0) -> None:
+        """nvidia-smi takes a while to start (longer with one per rank on an eight-GPU box): the
+        timed region begins only once it is sampling."""
+        end = time.time() + limit_s
+        while self.proc is not None and self.rows_so_far() == 0 and time.time() < end:
+            time.sleep(0.05)
+
+    def mark_load_start(self) -> None:
+        """Samples taken before this call are idle ones and are left out of the summary."""
+        self.skip = self.rows_so_far()
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -102,6 +124,7 @@ class ClockSampler:
             return out
         self.file.flush()
         rows = [r.split(",") for r in Path(self.file.name).read_text().splitlines() if r.count(",") >= 8]
+        rows = rows[self.skip:]
         os.unlink(self.file.name)
         sm, reasons = [], set()
         for r in rows:
@@ -116,9 +139,7 @@ class ClockSampler:
                 if r[col].lower().startswith("active"):
                     reasons.add(name)
         if sm:
-            # under load = the upper half of the samples (idle samples bracket the region)
-            sm.sort()
-            out["sm_mhz"] = statistics.median(sm[len(sm) // 2:])
+            out["sm_mhz"] = statistics.median(sm)
         out["reasons"] = sorted(reasons)
         out["samples"] = len(sm)
         return out
@@ -198,7 +219,7 @@ def run_reference(args) -> None:
     }))
 
 
-def time_steps(fn, steps: int, warmup: int, sync, barrier):
+def time_steps(fn, steps: int, warmup: int, sync, barrier, on_start=None):
     """W untimed steps, then exactly K steps between CUDA events on the current stream."""
     import torch
 
@@ -208,6 +229,8 @@ def time_steps(fn, steps: int, warmup: int, sync, barrier):
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync()
+    if on_start is not None:
+        on_start()
     start.record()
     for _ in range(steps):
         fn()
@@ -357,10 +380,17 @@ def run_ours(args) -> None:
             dist.barrier()
 
     with ClockSampler(local) as clocks:
-        seconds = time_steps(step_fn, args.steps, args.warmup, sync, barrier)
-        time.sleep(0.15)
+        clocks.wait_for_first_sample()
+        seconds = time_steps(step_fn, args.steps, args.warmup, sync, barrier, on_start=clocks.mark_load_start)
+        seconds = max_over_ranks(seconds, dist, device)
+        # The timed region can be shorter than the sampling period: the same steps keep running,
+        # untimed, for ~0.35 s (the same count on every rank) so that samples are taken under
+        # this very load.
+        for _ in range(max(1, int(0.35 / (seconds / args.steps)))):
+            step_fn()
+        sync()
+        barrier()
     clock_summary = clocks.summary()
-    seconds = max_over_ranks(seconds, dist, device)
     per_step = seconds / args.steps
     value = step_bytes / per_step / 1e9
     if world == 1 and mode == "plan":
@@ -441,6 +471,13 @@ def run_ours(args) -> None:
                  "us": round(head_seconds * 1e6, 2), "frac": round(head_bytes / head_seconds / 1e9 / peak, 4)}
         del hr
     achieved = kernel_bytes / kernel_seconds / 1e9
+    # DRAM bytes per launch of that kernel: from a profiler's launch list of this very command
+    # (1 GPU, the full stack, a launch per stage), not from this run -- and said so.
+    traffic, traffic_source = None, "not measured in this run (needs a profiler pass)"
+    if world == 1 and args.layers == 28 and m == 1 and kernel == "gemv_mma_tile_kernel":
+        traffic = TILE_KERNEL_DRAM_BYTES_PER_LAUNCH
+        traffic_source = ("separate ncu launch list of this command (dram read + write bytes of the 112 "
+                          "tiled launches of one step / 112); a constant of that capture, not measured in this run")
 
     # The second denominator: what a read-only stream and a copy reach on this GPU, now, through
     # this library's own launch path (the reference quotes against the same pair, measured in
@@ -468,7 +505,9 @@ def run_ours(args) -> None:
         tokens = [t for t in (1, 8, 64) if world == 1 or (t % world == 0)]
         extras["moe"] = {
             "metric": "moe_decode_tokens_per_s", "n_gpus": world,
-            "placement": "single gpu" if world == 1 else f"experts placed over {world} ranks, all-to-all exchange (NCCL)",
+            "placement": "single gpu" if world == 1 else (
+                f"experts placed over {world} ranks; tokens gathered and partial sums reduce-scattered by the "
+                "library's kernels over peer memory, the layer in one cuda graph"),
             "points": moe_bench.measure(tokens, layers=6, steps=20, rank=rank, world=world, device=device, dist=dist),
         }
         torch.cuda.empty_cache()
@@ -497,7 +536,7 @@ def run_ours(args) -> None:
             "frac": round(achieved / peak, 4),
             "kernel": kernel, "bytes_per_launch": round(kernel_bytes), "launch_us": round(kernel_seconds * 1e6, 3),
             "per_gpu": world > 1,
-            "traffic": None, "traffic_source": "not measured in this run (needs a profiler pass)",
+            "traffic": traffic, "traffic_source": traffic_source,
             "step_average": {"bytes_per_launch": round(local_bytes / launches_per_step),
                              "launch_us": round(per_step / launches_per_step * 1e6, 3),
                              "frac": round(local_bytes / per_step / 1e9 / peak, 4)},
