@@ -67,6 +67,16 @@ def measured_peak() -> tuple[float, str]:
 TILE_KERNEL_DRAM_BYTES_PER_LAUNCH = 5_698_000
 
 
+EXCHANGE_WORDS = {
+    "fused": "by the producing GEMV launch itself: stores into every rank's window over peer memory and a bounded "
+             "wait, in the graph",
+    "peer": "library exchange kernels over peer memory, in the graph",
+    "nccl": "NCCL, issued after the graph",
+    "none": "nothing to exchange",
+    None: "nothing to exchange",
+}
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
 
@@ -312,8 +322,9 @@ def config3_block(args, rank, world, device, dist, peak) -> dict:
         "workload": "qwen3-14b-shaped linear set (BASELINE config 3: 40 layers x 7 modules, 3/4-bit, M=1)",
         "placement": ("single gpu" if world == 1 else
                       f"every module column-sharded x{world}; each stage's output slabs all-gathered right after the "
-                      f"stage ({'library kernels over peer memory, in the graph' if exchange == 'peer' else 'NCCL'})"),
+                      f"stage ({EXCHANGE_WORDS[exchange]})"),
         "exchanges_per_step": 0 if world == 1 else runner.gathers_per_step,
+        "stages_exchanged_by_their_own_launch": 0 if world == 1 else runner.fused_stages,
         "launch": f"cuda graph, {mode}", "launches_per_step": runner.launches_per_step,
         "ms_per_step": round(seconds * 1e3, 4), "weight_bytes_per_gpu": local.weight_bytes,
         "gbps_aggregate": round(total_bytes / seconds / 1e9, 1),
@@ -419,8 +430,11 @@ def run_ours(args) -> None:
     # ---- end to end: activations in from pinned host memory, logits back ----
     host_in = {k: v.cpu().pin_memory() for k, v in runner.inputs.items()}
     last_name = full.modules[-1].name
-    logits_dev = runner.outputs[last_name]  # sharded runs: the gathered pieces, same bytes
-    host_out = torch.empty_like(logits_dev, device="cpu").pin_memory()
+    # sharded runs: the gathered pieces, the same bytes (a view that may alternate between steps)
+    logits = (lambda: runner.full_output(last_name)) if world > 1 and last_name in runner.sharded else (
+        lambda: runner.outputs[last_name])
+    logits_dev = logits()
+    host_out = torch.empty(logits_dev.shape, dtype=logits_dev.dtype, device="cpu").pin_memory()
     h2d = sum(v.numel() * v.element_size() for v in host_in.values())
     d2h = host_out.numel() * host_out.element_size()
 
@@ -436,7 +450,7 @@ def run_ours(args) -> None:
             for k, v in host_in.items():
                 runner.inputs[k].copy_(v, non_blocking=True)
             step_fn()
-            host_out.copy_(logits_dev, non_blocking=True)
+            host_out.copy_(logits(), non_blocking=True)
         torch.cuda.current_stream(device).synchronize()
 
     for _ in range(args.warmup):
@@ -492,12 +506,12 @@ def run_ours(args) -> None:
     extras = {}
     parallelism = ("single gpu" if world == 1 else
                    f"large layers ({', '.join(full_sharded_names(full, world))}) column-sharded x{world}, their outputs "
-                   f"all-gathered {'by the library over peer memory, inside the graph' if args.exchange == 'peer' else 'with NCCL'}; "
+                   f"all-gathered ({EXCHANGE_WORDS[args.exchange]}); "
                    f"small layers computed on every rank")
     weight_bytes = full.weight_bytes
     cpu_modules = [(mod.weight.num_rows, mod.weight.in_features, mod.weight.bits) for mod in full.modules[:56]]
     if not args.no_extras and args.layers == 28:
-        del runner, step_fn, full, host_in, host_out, logits_dev
+        del runner, step_fn, full, host_in, host_out, logits_dev, logits
         torch.cuda.empty_cache()
         sys.path.insert(0, str(ROOT / "benchmarks"))
         import moe_bench
@@ -582,8 +596,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-probe", action="store_true", help="skip the read/copy bandwidth probe")
     ap.add_argument("--no-extras", action="store_true", help="skip the moe and config3 blocks")
-    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
-                    help="N > 1: exchanges by the library's kernels over peer memory (in the graph) or by NCCL calls")
+    ap.add_argument("--exchange", choices=["fused", "peer", "nccl"], default="fused",
+                    help="N > 1: a sharded stage's output is exchanged by the GEMV launch itself (stores into the peers' "
+                         "windows), by the library's exchange kernels over peer memory (both in the graph), or by NCCL calls")
     ap.add_argument("--e2e-eager-copies", action="store_true",
                     help="end-to-end arm: issue the host<->device copies as separate calls around the step's graph")
     ap.add_argument("--graph-mode", choices=["plan", "dataflow", "chain", "independent"], default="dataflow",

@@ -94,6 +94,23 @@ class PeerGroup(ctypes.Structure):
     ]
 
 
+class PeerPush(ctypes.Structure):
+    """``dq_peer_push``."""
+
+    _fields_ = [
+        ("windows", ctypes.POINTER(ctypes.c_void_p)),
+        ("world", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("data_offset", ctypes.c_int64),
+        ("piece_bytes", ctypes.c_int64),
+        ("flags_offset", ctypes.c_int64),
+        ("state_offset", ctypes.c_int64),
+        ("status_offset", ctypes.c_int64),
+        ("spin_limit", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+    ]
+
+
 _P = ctypes.c_void_p
 _I32 = ctypes.c_int32
 _I64 = ctypes.c_int64
@@ -131,6 +148,8 @@ SIGNATURES = {
     "dq_peer_all_gather": (_I32, [ctypes.POINTER(PeerGroup), _P, _I64, _P, _P]),
     "dq_peer_reduce_scatter_f32": (_I32, [ctypes.POINTER(PeerGroup), _P, _I64, _P, _I32, _P]),
     "dq_peer_status": (_I32, [ctypes.POINTER(PeerGroup), _P, _P]),
+    "dq_gemv_stage_push": (_I32, [ctypes.POINTER(GemvJob), _I32, ctypes.POINTER(PeerPush), _P]),
+    "dq_peer_push_status": (_I32, [ctypes.POINTER(PeerPush), _P]),
     "dq_gemv_host": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P, _P, _P]),
 }
 

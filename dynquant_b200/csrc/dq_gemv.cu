@@ -31,6 +31,7 @@
 
 #include "dq_decode.cuh"
 #include "dq_gemv.cuh"
+#include "dq_peer_push.cuh"
 
 namespace dq {
 namespace {
@@ -655,6 +656,88 @@ int32_t dq_gemv_sequence(const dq_gemv_job* jobs, int32_t num_jobs, void* stream
       }
     }
     i = end;
+  }
+  return DQ_OK;
+}
+
+int32_t dq_gemv_stage_push(const dq_gemv_job* jobs, int32_t num_jobs, const dq_peer_push* push, void* stream) {
+  using dq::peerpush::Push;
+  constexpr int kBatch = 4;
+  DQ_REQUIRE(jobs != nullptr && num_jobs >= 1 && num_jobs <= kBatch, "gemv_stage_push: 1..%d jobs, got %d", kBatch, num_jobs);
+  DQ_REQUIRE(push != nullptr && push->windows != nullptr, "gemv_stage_push: null push descriptor");
+  DQ_REQUIRE(push->world >= 1 && push->world <= dq::peerpush::kMaxWorld && push->rank >= 0 && push->rank < push->world,
+             "gemv_stage_push: rank %d of %d (at most %d ranks)", push->rank, push->world, dq::peerpush::kMaxWorld);
+  const dq_gemv_job& head = jobs[0];
+  dq::GemvArgs args[kBatch];
+  dq_geometry geo[kBatch];
+  int bits[kBatch];
+  for (int i = 0; i < num_jobs; ++i) {
+    const dq_gemv_job& j = jobs[i];
+    if (const int32_t rc = dq_resolve_geometry("gemv_stage_push", &j.weight, &geo[i])) return rc;
+    if (const int32_t rc = dq::check_activation(j.x, j.x_dtype, j.m, j.out, j.out_dtype)) return rc;
+    DQ_REQUIRE(j.m >= 1 && j.weight.rows >= 1, "gemv_stage_push: job %d is empty", i);
+    DQ_REQUIRE(j.out_col0 >= 0 && j.out_stride >= j.out_col0 + j.weight.rows,
+               "gemv_stage_push: job %d writes columns [%lld, %lld) of a row of %lld", i,
+               static_cast<long long>(j.out_col0), static_cast<long long>(j.out_col0 + j.weight.rows),
+               static_cast<long long>(j.out_stride));
+    DQ_REQUIRE(j.x == head.x && j.m == head.m && j.x_dtype == head.x_dtype && j.out_dtype == head.out_dtype &&
+                   j.out == head.out && j.out_stride == head.out_stride,
+               "gemv_stage_push: job %d does not share the activation and the output buffer of job 0", i);
+    args[i] = dq::make_args(j.x, j.x_dtype, j.m, j.weight, geo[i], j.bias, j.out, j.out_stride, j.out_col0, j.out_dtype);
+    bits[i] = j.weight.bits;
+  }
+  const int64_t need = head.m * head.out_stride * static_cast<int64_t>(dq::dtype_size(head.out_dtype));
+  DQ_REQUIRE(push->piece_bytes >= need && push->piece_bytes % 16 == 0 && push->data_offset % 16 == 0 &&
+                 reinterpret_cast<uintptr_t>(head.out) % 16 == 0,
+             "gemv_stage_push: the piece is %lld bytes (a multiple of 16, 16-byte aligned), the output buffer needs %lld",
+             static_cast<long long>(push->piece_bytes), static_cast<long long>(need));
+  DQ_REQUIRE(push->flags_offset % 4 == 0 && push->state_offset % 8 == 0 && push->status_offset % 4 == 0 &&
+                 push->flags_offset >= 0 && push->state_offset >= 0 && push->status_offset >= 0 && push->data_offset >= 0 &&
+                 push->flags_offset < (1LL << 31) && push->state_offset < (1LL << 31) && push->status_offset < (1LL << 31),
+             "gemv_stage_push: misaligned or out-of-range flag / state / status offsets");
+  Push P = {};
+  for (int r = 0; r < push->world; ++r) {
+    DQ_REQUIRE(push->windows[r] != nullptr && reinterpret_cast<uintptr_t>(push->windows[r]) % 16 == 0,
+               "gemv_stage_push: window %d is null or not 16-byte aligned", r);
+    P.window[r] = static_cast<unsigned char*>(push->windows[r]);
+  }
+  P.data_off = push->data_offset;
+  P.piece_bytes = push->piece_bytes;
+  P.flags_off = static_cast<int>(push->flags_offset);
+  P.state_off = static_cast<int>(push->state_offset);
+  P.status_off = static_cast<int>(push->status_offset);
+  P.world = push->world;
+  P.rank = push->rank;
+  P.spin_limit = push->spin_limit > 0 ? push->spin_limit : (1 << 21);
+  P.enabled = 1;
+  auto s = static_cast<cudaStream_t>(stream);
+  if (dq::force_general()) return dq::fail(DQ_ERR_UNSUPPORTED, "gemv_stage_push: the general SIMT kernel is forced; it does not push");
+  int32_t rc = DQ_OK;
+  bool taken = false;
+  if (num_jobs == 1) {
+    rc = dq::mma_path_supports(args[0], bits[0]) ? dq::launch_gemv_mma(args[0], bits[0], s, &P) : DQ_ERR_UNSUPPORTED;
+    taken = rc == DQ_OK;
+  } else {
+    rc = dq::launch_gemv_mma_fused(args, bits, num_jobs, s, &taken, &P);
+  }
+  if (rc != DQ_OK && rc != DQ_ERR_UNSUPPORTED) return rc;
+  if (!taken) {
+    return dq::fail(DQ_ERR_UNSUPPORTED,
+                    "gemv_stage_push: these jobs do not leave as one launch of the tiled or the streaming kernel");
+  }
+  return DQ_OK;
+}
+
+int32_t dq_peer_push_status(const dq_peer_push* push, void* stream) {
+  DQ_REQUIRE(push != nullptr && push->windows != nullptr && push->rank >= 0 && push->rank < push->world,
+             "peer_push_status: null or inconsistent descriptor");
+  auto s = static_cast<cudaStream_t>(stream);
+  unsigned int word = 0;
+  DQ_CUDA(cudaMemcpyAsync(&word, static_cast<const unsigned char*>(push->windows[push->rank]) + push->status_offset,
+                          sizeof(word), cudaMemcpyDeviceToHost, s));
+  DQ_CUDA(cudaStreamSynchronize(s));
+  if (word != 0u) {
+    return dq::fail(DQ_ERR_DEVICE, "stage push: rank %d gave up waiting for the rows of rank %u", push->rank, word >> 8);
   }
   return DQ_OK;
 }

@@ -21,14 +21,22 @@ struct GemvArgs {
   int chunks_per_row, chunks_per_group;  // fast path only
 };
 
+namespace peerpush {
+struct Push;  // dq_peer_push.cuh
+}
+
 // Tensor-core path (dq_gemv_mma.cu).  Returns DQ_ERR_UNSUPPORTED without touching
 // the error buffer when the geometry or dtype is not one it handles, so the
 // caller can fall through to the SIMT kernels.
 bool mma_path_supports(const GemvArgs& a, int bits);
-int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream);
+// `push` (optional): the launch also replicates its output rows into every rank's window and
+// ends with the bounded wait for the other ranks' rows; only the streaming and the tiled kernel
+// do that, so with `push` every other geometry returns DQ_ERR_UNSUPPORTED, nothing launched.
+int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const peerpush::Push* push = nullptr);
 // Up to four matrices that share one activation, in ONE launch.  *taken is false (and nothing
 // was launched) when the jobs do not qualify; the caller then launches them one by one.
-int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken);
+int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken,
+                              const peerpush::Push* push = nullptr);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void store_out(const GemvArgs& a, int m, int row, float v) {

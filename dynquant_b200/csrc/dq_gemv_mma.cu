@@ -512,7 +512,8 @@ bool stream_ok(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps) {
 }
 
 template <int BITS>
-int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps, cudaStream_t stream_h) {
+int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps, cudaStream_t stream_h,
+                      const peerpush::Push* push) {
   using C = stream::Cfg<BITS>;
   // The fp16-operand plan at 8 bits, where a code no longer has to be split into nibbles: half
   // the fragment registers, half the mma and half the staged activation per step.  (At 2 and 4
@@ -527,6 +528,7 @@ int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int s
   p.steps = steps;
   p.tiles = tiles;
   p.magic = (plan16 || a.x_dtype != DQ_BF16) ? 0x64006400u : 0x43004300u;
+  if (push != nullptr) p.push = *push;
   const int aregs = plan16 ? 16 : (BITS == 8 ? 32 : 16);
   p.m_stride_u4 = steps * aregs + 4;
   const size_t smem = C::RING_BYTES + (static_cast<size_t>(a.m) * p.m_stride_u4 + aregs) * 16 +
@@ -561,26 +563,25 @@ int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int s
 #else
   constexpr bool kHasPlan16 = BITS == 8;
 #endif
+  auto pick = [&](auto p16, auto pushing) -> int32_t {
+    constexpr bool P = decltype(p16)::value, Q = decltype(pushing)::value;
+    if (xbf && mbf) return run(stream::gemv_mma_stream_kernel<BITS, true, true, P, Q>);
+    if (xbf) return run(stream::gemv_mma_stream_kernel<BITS, true, false, P, Q>);
+    if (mbf) return run(stream::gemv_mma_stream_kernel<BITS, false, true, P, Q>);
+    return run(stream::gemv_mma_stream_kernel<BITS, false, false, P, Q>);
+  };
   if constexpr (kHasPlan16) {
-    if (plan16) {
-      if (xbf && mbf) return run(stream::gemv_mma_stream_kernel<BITS, true, true, true>);
-      if (xbf) return run(stream::gemv_mma_stream_kernel<BITS, true, false, true>);
-      if (mbf) return run(stream::gemv_mma_stream_kernel<BITS, false, true, true>);
-      return run(stream::gemv_mma_stream_kernel<BITS, false, false, true>);
-    }
+    if (plan16) return push != nullptr ? pick(std::true_type{}, std::true_type{}) : pick(std::true_type{}, std::false_type{});
   }
-  if (xbf && mbf) return run(stream::gemv_mma_stream_kernel<BITS, true, true>);
-  if (xbf) return run(stream::gemv_mma_stream_kernel<BITS, true, false>);
-  if (mbf) return run(stream::gemv_mma_stream_kernel<BITS, false, true>);
-  return run(stream::gemv_mma_stream_kernel<BITS, false, false>);
+  return push != nullptr ? pick(std::false_type{}, std::true_type{}) : pick(std::false_type{}, std::false_type{});
 }
 
 template <int BITS>
 int32_t try_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps, cudaStream_t stream_h,
-                   bool* taken) {
+                   bool* taken, const peerpush::Push* push) {
   *taken = false;
   if (!stream_ok<BITS>(a, dev, tiles, steps)) return DQ_OK;
-  const int32_t rc = launch_stream<BITS>(a, dev, tiles, steps, stream_h);
+  const int32_t rc = launch_stream<BITS>(a, dev, tiles, steps, stream_h, push);
   if (rc == DQ_ERR_UNSUPPORTED) return DQ_OK;  // does not fit: the generic kernel takes it
   *taken = true;
   return rc;
@@ -591,7 +592,7 @@ int32_t try_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int step
 // One launch for `n` matrices sharing the activation.  *taken stays false (and nothing is
 // launched) when the jobs do not meet the kernel's requirements.
 int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo& dev, cudaStream_t stream_h,
-                 bool* taken) {
+                 bool* taken, const peerpush::Push* push = nullptr) {
   *taken = false;
   const bool off = tuning_int("DQ_B200_NO_TILE") != 0;
   const int force_kw = tuning_int("DQ_B200_TILE_KW"), force_nb = tuning_int("DQ_B200_TILE_NB"),
@@ -738,6 +739,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
   L.wide_stage = wide ? 1 : 0;
   L.meta_bf16 = a0.meta_dtype == DQ_BF16 ? 1 : 0;
   L.magic = a0.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
+  if (push != nullptr) L.push = *push;
   for (int i = 0; i < n; ++i) {
     L.job[i].a = jobs[i];
     L.job[i].bits = bits[i];
@@ -811,22 +813,23 @@ bool mma_path_supports(const GemvArgs& a, int bits) {
   return smem <= static_cast<size_t>(dev->max_smem_optin);
 }
 
-int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken) {
+int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken,
+                              const peerpush::Push* push) {
   *taken = false;
   const DeviceInfo* dev = device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
   for (int i = 0; i < n; ++i) {
     if (!mma_path_supports(jobs[i], bits[i])) return DQ_OK;
   }
-  return try_tile(jobs, bits, n, *dev, stream, taken);
+  return try_tile(jobs, bits, n, *dev, stream, taken, push);
 }
 
-int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
+int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const peerpush::Push* push) {
   const DeviceInfo* dev = device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
   if (a.group_values == kStepValues / 2) {  // two groups per step: only the tiled kernel does that
     bool taken = false;
-    const int32_t rc = try_tile(&a, &bits, 1, *dev, stream, &taken);
+    const int32_t rc = try_tile(&a, &bits, 1, *dev, stream, &taken, push);
     return (rc == DQ_OK && !taken) ? DQ_ERR_UNSUPPORTED : rc;
   }
   MmaParams p = {};
@@ -838,22 +841,23 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream) {
     int32_t rc = DQ_OK;
     switch (bits) {
       case 2:
-        rc = try_stream<2>(a, *dev, p.tiles, p.steps, stream, &taken);
+        rc = try_stream<2>(a, *dev, p.tiles, p.steps, stream, &taken, push);
         break;
       case 3:
-        rc = try_stream<3>(a, *dev, p.tiles, p.steps, stream, &taken);
+        rc = try_stream<3>(a, *dev, p.tiles, p.steps, stream, &taken, push);
         break;
       case 4:
-        rc = try_stream<4>(a, *dev, p.tiles, p.steps, stream, &taken);
+        rc = try_stream<4>(a, *dev, p.tiles, p.steps, stream, &taken, push);
         break;
       default:
-        rc = try_stream<8>(a, *dev, p.tiles, p.steps, stream, &taken);
+        rc = try_stream<8>(a, *dev, p.tiles, p.steps, stream, &taken, push);
         break;
     }
     if (taken || rc != DQ_OK) return rc;
-    rc = try_tile(&a, &bits, 1, *dev, stream, &taken);
+    rc = try_tile(&a, &bits, 1, *dev, stream, &taken, push);
     if (taken || rc != DQ_OK) return rc;
   }
+  if (push != nullptr) return DQ_ERR_UNSUPPORTED;  // the register-ring kernel below does not push
   // Shape of a CTA: rw row tiles x kw slices of the reduction axis, 8 or 16 warps.  A short
   // matrix is over in one dependent chain of latencies (launch, activation staging, a few
   // steps, reduction), so what matters is that EVERY CTA is resident at once -- a second

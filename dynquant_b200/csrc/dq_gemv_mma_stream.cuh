@@ -16,6 +16,7 @@
 #pragma once
 
 #include "dq_gemv.cuh"
+#include "dq_peer_push.cuh"
 #include "dq_mma_plan.cuh"
 #include "dq_mma_stage.cuh"
 #include "dq_mma_plan16.cuh"
@@ -115,10 +116,14 @@ struct Params {
   int tiles;        // ceil(rows / 16)
   int m_stride_u4;  // uint4 per activation row of the staged B buffer
   uint32_t magic;   // a parameter so it stays a register operand of the decode
+  peerpush::Push push;  // enabled: the output rows also go to every rank's window (dq_peer_push.cuh)
 };
 
 // P16: the fp16-operand plan (dq_mma_plan16.cuh; 2-, 4- and 8-bit codes, aligned 16-bit activations).
-template <int BITS, bool XBF16, bool MBF16, bool P16 = false>
+// PUSH: the launch also copies its output rows into every rank's window and ends with the bounded
+// wait for the other ranks' rows (dq_peer_push.cuh).  A template parameter, not a flag: this
+// kernel sits at its register limit and the plain build must stay exactly what it was.
+template <int BITS, bool XBF16, bool MBF16, bool P16 = false, bool PUSH = false>
 __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const GemvArgs a, const Params p) {
   using Plan = MmaPlan<BITS>;
   using C = Cfg<BITS>;
@@ -371,6 +376,18 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
     }
   }
   cp_async_wait<0>();
+  if constexpr (PUSH) {
+    // This CTA's warps took runs of kWarps consecutive row tiles: copy them, as stored, to every window.
+    // (Every thread reads the epoch itself: no static shared memory, which would cost the third CTA per SM.)
+    const unsigned int epoch = peerpush::next_epoch(p.push);
+    __syncthreads();  // the output stores above are visible to the whole CTA
+    constexpr int kRun = kWarps * kTileRows;
+    for (int row = static_cast<int>(blockIdx.x) * kRun; row < a.rows; row += static_cast<int>(gridDim.x) * kRun) {
+      peerpush::push_rows(p.push, a, epoch, row, min(row + kRun, a.rows), tid, kThreads);
+    }
+    __syncthreads();
+    if (tid < kWarp) peerpush::arrive(p.push, epoch, gridDim.x, tid);
+  }
 }
 
 }  // namespace stream

@@ -26,6 +26,7 @@
 #pragma once
 
 #include "dq_gemv.cuh"
+#include "dq_peer_push.cuh"
 #include "dq_gemv_mma_stream.cuh"
 #include "dq_mma_plan.cuh"
 #include "dq_mma_stage.cuh"
@@ -58,6 +59,7 @@ struct Launch {
   int wide_stage;  // 1: the CTA stages the whole activation; 0: every warp its own slice
   int meta_bf16;
   uint32_t magic;
+  peerpush::Push push;  // enabled: the output rows also go to every rank's window (dq_peer_push.cuh)
 };
 
 template <int BITS, int CH, bool G64 = false>
@@ -494,6 +496,19 @@ __global__ void __launch_bounds__(kThreads, CTAS) gemv_mma_tile_kernel(const __g
     default:
       tile_body<8, XBF16, CH, G64>(L, J, smem_raw);
       break;
+  }
+  if (L.push.enabled) {
+    // This CTA's items are whole runs of rw row tiles: copy them, as stored, to every window.
+    // (Every thread reads the epoch itself: no static shared memory beside the tuned dynamic layout.)
+    const unsigned int epoch = peerpush::next_epoch(L.push);
+    __syncthreads();  // the body's output stores are visible to the whole CTA
+    const int rows_per_item = L.rw * 16;
+    for (int item = static_cast<int>(blockIdx.x) - J.cta_begin; item < J.items; item += J.cta_count) {
+      peerpush::push_rows(L.push, J.a, epoch, item * rows_per_item, min((item + 1) * rows_per_item, J.a.rows),
+                          threadIdx.x, kThreads);
+    }
+    __syncthreads();
+    if (threadIdx.x < kWarp) peerpush::arrive(L.push, epoch, gridDim.x, threadIdx.x);
   }
 }
 

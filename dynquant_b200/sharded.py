@@ -257,7 +257,11 @@ class ShardedStepRunner:
     gate/up, or a single module) whose modules are all sharded writes its ``[M, rows/world]``
     outputs into one buffer, and that buffer is all-gathered right after the stage:
 
-    * ``exchange="peer"`` (default): the library's own kernels over peer memory
+    * ``exchange="fused"`` (default): the stage's GEMV launch itself stores its output rows into
+      every rank's window and ends with a bounded wait for the other ranks' rows
+      (``dq_gemv_stage_push``, :class:`~dynquant_b200.peer.PushWindow`): no exchange launch at
+      all.  A stage the pushing kernels do not take falls back to ``"peer"`` for that stage;
+    * ``exchange="peer"``: the library's own exchange kernels over peer memory
       (:class:`~dynquant_b200.peer.PeerExchange`), enqueued between the stages and captured in
       the step's CUDA graph -- a step is one graph replay, exchanges included;
     * ``exchange="nccl"``: one ``all_gather_into_tensor`` per sharded stage, issued eagerly after
@@ -265,14 +269,14 @@ class ShardedStepRunner:
     """
 
     def __init__(self, stack, m: int, *, rank: int, world: int, device, act_dtype=torch.bfloat16,
-                 shard_min_bytes: int = 32 << 20, graph_mode: str | None = "dataflow", exchange: str = "peer",
+                 shard_min_bytes: int = 32 << 20, graph_mode: str | None = "dataflow", exchange: str = "fused",
                  presharded: bool = False) -> None:
         """``presharded``: ``stack`` already holds this rank's row slabs of every module (a set
         too large to generate whole on every rank); every module then counts as sharded."""
         from .stack import StepRunner
         from .workloads import LinearStack, Module
 
-        if exchange not in ("peer", "nccl"):
+        if exchange not in ("fused", "peer", "nccl"):
             raise ValueError(exchange)
         self.rank, self.world, self.device = rank, world, torch.device(device)
         modules, self.sharded = [], []
@@ -313,19 +317,46 @@ class ShardedStepRunner:
         self.gathers_per_step = len(self._gathers)
         self.exchange = exchange if self._gathers else "none"
         self._peer = None
-        if self.exchange == "peer":
+        self._window = None
+        self._slot = {}       # stage index -> exchange of the push window
+        self._unfused = set()  # stages the pushing kernels refused: exchanged by the peer kernels instead
+        if self.exchange in ("peer", "fused"):
             from .peer import PeerExchange
 
             biggest = max(p.numel() * p.element_size() for p, _ in self._gathers.values())
             self._peer = PeerExchange(-(-biggest // 16) * 16, device=self.device)
+        if self.exchange == "fused":
+            from .peer import PushWindow
+
+            order = sorted(self._gathers)
+            self._slot = {index: k for k, index in enumerate(order)}
+            self._window = PushWindow([self._gathers[i][0].numel() * self._gathers[i][0].element_size() for i in order],
+                                      device=self.device)
         self.graph_mode = graph_mode
-        in_graph = self.exchange == "peer" and graph_mode == "dataflow"
+        in_graph = self.exchange in ("peer", "fused") and graph_mode == "dataflow"
         if graph_mode is not None:
-            self.runner.capture(graph_mode, after_stage=self._exchange_stage if in_graph else None)
+            self.runner.capture(graph_mode, after_stage=self._exchange_stage if in_graph else None,
+                                launch_stage=self._launch_stage if in_graph and self._window is not None else None)
         else:
             self.runner.count_launches()
         self._exchanges_in_graph = in_graph
         self.launches_per_step = self.runner.launches_per_step
+        self.fused_stages = len(self._slot) - len(self._unfused)
+        # what the windows hold now (the capture's own warm-up ran no exchange; an eager pass may have)
+        self._runs = 0
+        self._base_epoch = 0
+        if self._window is not None and self.fused_stages:
+            first = next(i for i in sorted(self._slot) if i not in self._unfused)
+            self._base_epoch = self._window.epoch(self._slot[first])
+
+    def _launch_stage(self, index: int, first: int, count: int) -> bool:
+        slot = self._slot.get(index)
+        if slot is None or index in self._unfused:
+            return False
+        if self._window.run_stage(slot, self.runner.jobs_at(first), count):
+            return True
+        self._unfused.add(index)
+        return False
 
     def _exchange_stage(self, index: int) -> None:
         pair = self._gathers.get(index)
@@ -340,18 +371,35 @@ class ShardedStepRunner:
     def run(self) -> None:
         if self.graph_mode is not None:
             self.runner.replay()
+        elif self._window is not None:
+            self.runner.run_dataflow(None, self._exchange_stage, self._launch_stage)
         else:
             self.runner.run()
-        if not self._exchanges_in_graph:
+        self._runs += 1
+        if not self._exchanges_in_graph and self._window is None:
             for index in self._gathers:
                 self._exchange_stage(index)
 
     def check(self) -> None:
-        """Raises if an exchange's bounded wait ran out (peer exchanges only)."""
+        """Raises if an exchange's bounded wait ran out (exchanges over peer memory only)."""
         if self._peer is not None:
             self._peer.check()
+        if self._window is not None:
+            self._window.check()
+
+    def full_output(self, name: str) -> torch.Tensor:
+        """``[world, m, rows/world]``: every rank's piece of a sharded module's output after the
+        last :meth:`run`.  For a stage exchanged by its own launch this is a view into the window
+        half the last step wrote (it alternates from step to step)."""
+        index, col, rows = self._columns[name]
+        if self._window is None or index not in self._slot or index in self._unfused:
+            return self.outputs[name]
+        piece = self._gathers[index][0]  # this rank's [m, columns] stage buffer: shape and dtype of a piece
+        raw = self._window.piece(self._slot[index], self._base_epoch + self._runs)
+        nbytes = piece.numel() * piece.element_size()
+        return raw[:, :nbytes].view(piece.dtype).view(self.world, *piece.shape)[:, :, col:col + rows]
 
     def gathered(self, name: str) -> torch.Tensor:
         """The full ``[m, N]`` output of a sharded module, reassembled from the rank-major pieces."""
-        full = self.outputs[name]  # [world, m, rows/world]
+        full = self.full_output(name)  # [world, m, rows/world]
         return full.permute(1, 0, 2).reshape(full.shape[1], -1)

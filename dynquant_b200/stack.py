@@ -172,16 +172,25 @@ class StepRunner:
         jobs = ctypes.cast(ctypes.byref(self._jobs, first * ctypes.sizeof(_lib.GemvJob)), ctypes.POINTER(_lib.GemvJob))
         _lib.check(lib.dq_gemv_sequence(jobs, count, _stream(self.device)))
 
-    def run_dataflow(self, side_streams: list[torch.cuda.Stream] | None = None, after_stage=None) -> None:
+    def jobs_at(self, first: int):
+        """Pointer to job ``first`` of the step's ``dq_gemv_job`` array."""
+        return ctypes.cast(ctypes.byref(self._jobs, first * ctypes.sizeof(_lib.GemvJob)), ctypes.POINTER(_lib.GemvJob))
+
+    def run_dataflow(self, side_streams: list[torch.cuda.Stream] | None = None, after_stage=None,
+                     launch_stage=None) -> None:
         """Enqueue the step as its dependency graph: stage after stage, the members of a stage
         (q/k/v, gate/up: contiguous jobs reading one activation) in ONE library call, which
         issues them as one fused launch.  Stages whose members are not contiguous fork onto
         ``side_streams``.  ``after_stage(i)`` (optional) is called after stage ``i`` has been
-        enqueued -- where a sharded runner enqueues the exchange of that stage's output."""
+        enqueued -- where a sharded runner enqueues the exchange of that stage's output.
+        ``launch_stage(i, first, count)`` (optional) may enqueue stage ``i`` itself (a launch that
+        also exchanges the output) and return True; on False the stage is enqueued as usual."""
         main = torch.cuda.current_stream(self.device)
         with torch.cuda.device(self.device):
             for index, stage in enumerate(self.stack.stages()):
                 if list(stage) == list(range(stage[0], stage[0] + len(stage))):
+                    if launch_stage is not None and launch_stage(index, stage[0], len(stage)):
+                        continue
                     self._run_jobs(stage[0], len(stage))
                     if after_stage is not None:
                         after_stage(index)
@@ -197,8 +206,9 @@ class StepRunner:
                     join.record(side)
                     main.wait_event(join)
 
-    def capture(self, mode: str = "dataflow", after_stage=None) -> None:
-        """Record the step into a CUDA graph (``after_stage``: see :meth:`run_dataflow`; dataflow mode only).
+    def capture(self, mode: str = "dataflow", after_stage=None, launch_stage=None) -> None:
+        """Record the step into a CUDA graph (``after_stage``, ``launch_stage``: see
+        :meth:`run_dataflow`; dataflow mode only).
 
         ``"dataflow"``: stages in order, the members of a stage in one fused launch (what a
         decoder layer's dependencies allow).  ``"chain"``: the whole job list in stream order through
@@ -224,7 +234,7 @@ class StepRunner:
             elif mode == "plan":
                 self.run_plan()
             elif mode == "dataflow":
-                self.run_dataflow(sides, after_stage)
+                self.run_dataflow(sides, after_stage, launch_stage)
             elif mode == "independent":
                 main = torch.cuda.current_stream(self.device)
                 fork = torch.cuda.Event()

@@ -333,6 +333,48 @@ DQ_API int32_t dq_peer_reduce_scatter_f32(const dq_peer_group* group, const floa
  * the pointer that is buffers[rank]). */
 DQ_API int32_t dq_peer_status(const dq_peer_group* group, const void* local_buffer, void* stream);
 
+/* ---- a column-sharded stage and its all-gather as ONE launch ----
+ *
+ * Replaces, for a stage of a tensor-parallel decode step, the pair "GEMV over this rank's row
+ * slab, then the host framework's all-gather" (vLLM: the gather after a ColumnParallelLinear
+ * whose weights were placed by integration/vllm_plugin/parameter.py:102-154) -- and this
+ * library's own pair dq_gemv_sequence + dq_peer_all_gather.  The GEMV kernel's CTAs copy their
+ * output rows into EVERY rank's window with ordinary stores through peer-mapped pointers
+ * (nothing is read from a peer; no TMA, no multicast), the launch's last CTA raises this rank's
+ * flag in every window and waits, a bounded number of polls, for the other ranks' flags in its
+ * own.  When the launch completes, the stage's gathered output is complete on this GPU.
+ *
+ * `windows`: HOST array of `world` (<= 8) device pointers, every rank's window as mapped on this
+ * GPU (symmetric memory, IPC), windows[rank] the local one; all offsets below are bytes from a
+ * window's base and identical on every rank.  Data of this exchange: 2 halves x world pieces of
+ * `piece_bytes` at `data_offset`; the exchange with epoch e (1, 2, ... counted on the device in
+ * state[0]) lands in half e & 1, rank r's piece at + r * piece_bytes, laid out exactly like the
+ * jobs' output buffer.  `flags_offset`: u32[world]; `state_offset`: u32[2] {epoch, arrived};
+ * `status_offset`: u32, nonzero once a wait ran out (1 | rank waited for << 8).  The host zeroes
+ * flags, state and status once before first use; every exchange needs its own data, flags and
+ * state; the status word may be shared. */
+typedef struct dq_peer_push {
+  void* const* windows;
+  int32_t world, rank;
+  int64_t data_offset;
+  int64_t piece_bytes;
+  int64_t flags_offset;
+  int64_t state_offset;
+  int64_t status_offset;
+  int32_t spin_limit; /* polls per awaited rank; <= 0: a default of about a second */
+  int32_t reserved;
+} dq_peer_push;
+/* `jobs`: 1..4 jobs of one stage -- the same x, m and dtypes, and the same out / out_stride
+ * (distinct columns): that [m, out_stride] buffer is the piece (piece_bytes >= its size).  They
+ * must leave as ONE launch of the tiled or the streaming tensor-core kernel; otherwise
+ * DQ_ERR_UNSUPPORTED is returned and nothing was launched (the caller then uses
+ * dq_gemv_sequence + dq_peer_all_gather).  Every rank must issue the same exchanges in the same
+ * order.  Captures into CUDA graphs. */
+DQ_API int32_t dq_gemv_stage_push(const dq_gemv_job* jobs, int32_t num_jobs, const dq_peer_push* push,
+                                  void* stream);
+/* Synchronises `stream` and reads the window's status word. */
+DQ_API int32_t dq_peer_push_status(const dq_peer_push* push, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -98,6 +98,45 @@ def _worker(rank: int, world: int, port: int, results) -> None:
         ex.check()
         want = torch.cat([torch.full((2048,), float(r + 1), device=dev) for r in range(world)])
         out["graph"] = bool(torch.equal(gathered, want))
+        # ---- a whole sharded decode step: every stage's all-gather folded into its GEMV launch ----
+        from dynquant_b200.sharded import ShardedStepRunner
+        from dynquant_b200.stack import StepRunner
+        from dynquant_b200.workloads import qwen2b_stack
+
+        stack = qwen2b_stack(device=dev, vocab=40960, layers=2)
+        single = StepRunner(stack, 2, device=dev)
+        single.run()
+        torch.cuda.synchronize()
+        for exchange in ("fused", "peer"):
+            runner = ShardedStepRunner(stack, 2, rank=rank, world=world, device=dev, shard_min_bytes=0,
+                                       exchange=exchange)
+            for name, t in single.inputs.items():
+                runner.inputs[name].copy_(t)
+            same, close = True, True
+            for step in range(3):  # the window halves alternate from step to step
+                runner.run()
+                runner.check()
+                for name in runner.sharded:
+                    # the transfer is exact: what arrived is what every rank computed (NCCL as the witness)
+                    piece = runner.runner.outputs[name].contiguous()
+                    witness = torch.empty(world, *piece.shape, dtype=piece.dtype, device=dev)
+                    dist.all_gather_into_tensor(witness, piece)
+                    if not torch.equal(runner.full_output(name), witness):
+                        same = False
+                        bad = (runner.full_output(name) != witness).nonzero()
+                        out[f"step/{exchange}: {name}, step {step}: {bad.shape[0]} of {witness.numel()} values differ from "
+                            f"what the ranks computed, first at {bad[0].tolist()}, last at {bad[-1].tolist()}"] = False
+                    # and the values are the single-GPU ones up to the summation order of a differently
+                    # sliced reduction axis (a slab is a smaller matrix): one rounding of the bf16 output
+                    got, ref = runner.gathered(name).float(), single.outputs[name].float()
+                    close = close and bool(((got - ref).abs() <= 2.0 ** -7 * ref.abs() + 1e-6).all())
+            out[f"step/{exchange}"] = same
+            out[f"step/{exchange}/within one rounding of the single-GPU step"] = close
+            out[f"step/{exchange}/all modules sharded"] = len(runner.sharded) == len(stack.modules)
+            if exchange == "fused":
+                out["step/fused/no stage fell back"] = runner.fused_stages == runner.gathers_per_step
+                out["step/fused/one launch per stage"] = runner.launches_per_step == runner.gathers_per_step
+            del runner
         results[rank] = out
     finally:
         dist.destroy_process_group()
