@@ -43,6 +43,17 @@ def hbm_peak_gbs() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
+def check_block(x: torch.Tensor, qt, out: torch.Tensor, rows_checked: int = 256) -> float:
+    """Largest error of the LAST ``rows_checked`` output rows (the ragged tail included) against
+    plain fp32 torch arithmetic on the dequantized rows, relative to the block's largest value.
+    A timed number for a wrong result would be worthless; the parity tests proper are in tests/."""
+    lo = max(0, qt.num_rows - rows_checked)
+    dense = ops.dequantize(qt.rows(lo, qt.num_rows)).float()  # [rows_checked, K]
+    want = x.float() @ dense.t()
+    got = out[:, lo:].float()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
 def run_point(rows: int, k: int, bits: int, group: int, m: int, *, launches: int, ring: int | None,
               device="cuda") -> dict:
     probe = random_quant_tensor(rows, k, bits, group_size=group, device=device)
@@ -56,8 +67,12 @@ def run_point(rows: int, k: int, bits: int, group: int, m: int, *, launches: int
         return ops.quantized_matmul(x, qt)
 
     for qt in weights[: min(3, ring)]:
-        step(qt)
+        out = step(qt)
     torch.cuda.synchronize()
+    # the output is rounded once to bf16 (2^-8 relative), the fp32 sums differ in their last bits
+    err = check_block(x, weights[min(3, ring) - 1], out)
+    if not err <= 1e-2:
+        raise SystemExit(f"{rows}x{k} bits={bits} group={group} m={m}: result differs from fp32 torch arithmetic ({err:.3e})")
     # one CUDA graph of `launches` back-to-back calls over the ring: device time only, no Python
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
@@ -80,7 +95,7 @@ def run_point(rows: int, k: int, bits: int, group: int, m: int, *, launches: int
                  "gemv x%d" % -(-m // ops.gemv_max_rows()) if m <= ops.GEMV_CHUNKED_MAX_ROWS else "dequant+dense"),
         "us_per_call": round(seconds * 1e6, 2), "gbps": round(gbs, 1),
         "pct_of_hbm_peak": round(100 * gbs / peak, 1), "peak": f"{peak} GB/s ({kind})",
-        "ring": ring, "ring_bytes": probe.nbytes * ring, "launches": launches,
+        "ring": ring, "ring_bytes": probe.nbytes * ring, "launches": launches, "max_err_vs_fp32_torch": float(f"{err:.2e}"),
     }
 
 

@@ -132,6 +132,7 @@ SIGNATURES = {
     "dq_probe_copy": (_I32, [_P, _P, _I64, _P]),
     "dq_gemv": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P]),
     "dq_gemv_shards": (_I32, [_P, _I32, _I64, _WP, _I32, _P, _P, _I64, _I32, _P]),
+    "dq_gemv_shards_rows": (_I32, [_P, _I32, _I64, _WP, _I32, _P, _P, _I64, _I32, _P]),
     "dq_gemv_sequence": (_I32, [ctypes.POINTER(GemvJob), _I32, _P]),
     "dq_moe_scratch_bytes": (_I32, [_I64, _I64, _I64, _I64, _I64, _I32, ctypes.POINTER(ctypes.c_int64)]),
     "dq_moe_gemv": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _WP, _WP, _I64, _I64, _P, _I32, _P, _I64, _P]),

@@ -474,6 +474,13 @@ GemvArgs activation_rows(const GemvArgs& a, int first, int count) {
   return b;
 }
 
+// Row chunks over one matrix share a launch only where the tiled kernel is the right kernel for
+// the matrix anyway; a matrix long enough for the streaming kernel goes chunk by chunk.
+bool fusable_rows(const GemvArgs& a) {
+  const DeviceInfo* dev = device_info();
+  return dev != nullptr && ceil_div(a.rows, 16) < static_cast<int64_t>(dev->sm_count) * 8;
+}
+
 int32_t gemv_args(GemvArgs a, const dq_weight& w, const dq_geometry& g, cudaStream_t stream) {
   if (!force_general()) {
     if (mma_path_supports(a, w.bits)) {
@@ -605,6 +612,82 @@ int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const dq_weigh
     }
   }
   return DQ_OK;
+}
+
+int32_t dq_gemv_shards_rows(const void* x, int32_t x_dtype, int64_t m, const dq_weight* shards, int32_t num_shards,
+                            const void* bias, void* out, int64_t out_stride, int32_t out_dtype, void* stream) {
+  constexpr int64_t kMaxRows = DQ_GEMV_CHUNKED_MAX_ROWS;
+  DQ_REQUIRE(shards != nullptr && num_shards > 0, "gemv_shards_rows: need at least one shard");
+  DQ_REQUIRE(m >= 0 && m <= kMaxRows,
+             "gemv_shards_rows: %lld activation rows exceeds the limit of %lld; above it a quantized matmul is "
+             "compute-bound and the dequant + dense GEMM path is faster",
+             static_cast<long long>(m), static_cast<long long>(kMaxRows));
+  if (m <= DQ_GEMV_MAX_ROWS) {
+    return dq_gemv_shards(x, x_dtype, m, shards, num_shards, bias, out, out_stride, out_dtype, stream);
+  }
+  DQ_REQUIRE(dq::dtype_ok(x_dtype) && dq::dtype_ok(out_dtype) && x != nullptr && out != nullptr,
+             "gemv_shards_rows: bad dtype tag or null pointer");
+  int64_t total = 0;
+  for (int i = 0; i < num_shards; ++i) {
+    dq_geometry g;
+    if (const int32_t rc = dq_resolve_geometry("gemv_shards_rows", &shards[i], &g)) return rc;
+    DQ_REQUIRE(shards[i].in_features == shards[0].in_features, "gemv_shards_rows: shard %d has in_features=%lld but shard 0 has %lld",
+               i, static_cast<long long>(shards[i].in_features), static_cast<long long>(shards[0].in_features));
+    total += shards[i].rows;
+  }
+  DQ_REQUIRE(out_stride >= total, "gemv_shards_rows: out_stride=%lld is smaller than the %lld rows of the shards",
+             static_cast<long long>(out_stride), static_cast<long long>(total));
+  // Row chunks of at most eight rows, as equal as possible (the members of one launch must have
+  // the same number of rows); chunk after chunk, shard after shard, up to four jobs per launch.
+  const int64_t chunks = dq::ceil_div(m, DQ_GEMV_MAX_ROWS);
+  const int64_t base = m / chunks, longer = m % chunks;  // the first `longer` chunks take base + 1 rows
+  const size_t x_row = static_cast<size_t>(shards[0].in_features) * dq::dtype_size(x_dtype);
+  const size_t out_row = static_cast<size_t>(out_stride) * dq::dtype_size(out_dtype);
+  auto s = static_cast<cudaStream_t>(stream);
+  constexpr int kBatch = 4;
+  dq::GemvArgs args[kBatch];
+  dq_geometry geo[kBatch];
+  int bits[kBatch];
+  const dq_weight* which[kBatch];
+  int live = 0;
+  auto flush = [&]() -> int32_t {
+    if (live == 0) return DQ_OK;
+    bool taken = false;
+    // (matrices long enough for the streaming kernel go out one by one: it is the faster kernel there)
+    bool fusable = live > 1 && !dq::force_general();
+    for (int k = 0; k < live && fusable; ++k) fusable = dq::fusable_rows(args[k]);
+    if (fusable) {
+      if (const int32_t rc = dq::launch_gemv_mma_fused(args, bits, live, s, &taken)) return rc;
+    }
+    if (!taken) {
+      for (int k = 0; k < live; ++k) {
+        if (const int32_t rc = dq::gemv_args(args[k], *which[k], geo[k], s)) return rc;
+      }
+    }
+    live = 0;
+    return DQ_OK;
+  };
+  int64_t row0 = 0;
+  for (int64_t c = 0; c < chunks; ++c) {
+    const int64_t rows_here = base + (c < longer ? 1 : 0);
+    int64_t col0 = 0;
+    for (int i = 0; i < num_shards; ++i) {
+      if (shards[i].rows > 0) {
+        if (live == kBatch || (live > 0 && args[0].m != rows_here)) {
+          if (const int32_t rc = flush()) return rc;
+        }
+        dq_resolve_geometry("gemv_shards_rows", &shards[i], &geo[live]);
+        args[live] = dq::make_args(static_cast<const unsigned char*>(x) + row0 * x_row, x_dtype, rows_here, shards[i], geo[live],
+                                   bias, static_cast<unsigned char*>(out) + row0 * out_row, out_stride, col0, out_dtype);
+        bits[live] = shards[i].bits;
+        which[live] = &shards[i];
+        ++live;
+      }
+      col0 += shards[i].rows;
+    }
+    row0 += rows_here;
+  }
+  return flush();
 }
 
 int32_t dq_gemv_sequence(const dq_gemv_job* jobs, int32_t num_jobs, void* stream) {

@@ -604,7 +604,9 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
   const bool g64_jobs = a0.group_values == kStepValues / 2;
   for (int i = 0; i < n; ++i) {
     const GemvArgs& a = jobs[i];
-    if (a.x != a0.x || a.m != a0.m || a.x_dtype != a0.x_dtype || a.meta_dtype != a0.meta_dtype ||
+    // (The activations may differ -- row chunks of one activation over the same matrix -- as long
+    // as they have the same shape: every CTA stages the activation of its own job.)
+    if (a.m != a0.m || a.x_dtype != a0.x_dtype || a.meta_dtype != a0.meta_dtype ||
         a.in_features != a0.in_features || a.out_dtype != a0.out_dtype) {
       return DQ_OK;
     }

@@ -200,14 +200,10 @@ def gemv_row_chunks(
     *,
     out_dtype: torch.dtype | None = None,
 ) -> torch.Tensor:
-    """``gemv_shards`` for more rows than one launch takes: ``gemv_max_rows()`` rows per launch."""
-    step = gemv_max_rows()
-    out_dtype = out_dtype or x.dtype
-    total = sum(qt.num_rows for qt in shards)
-    out = torch.empty((x.shape[0], total), dtype=out_dtype, device=x.device)
-    for start in range(0, x.shape[0], step):  # each launch writes its rows of `out` in place
-        gemv_shards(x[start : start + step], shards, bias, out_dtype=out_dtype, out=out[start : start + step])
-    return out
+    """``gemv_shards`` for more rows than one launch takes, up to ``GEMV_CHUNKED_MAX_ROWS``: the
+    library cuts the rows into chunks of at most ``gemv_max_rows()`` and issues up to four
+    (chunk, shard) pairs per launch (``dq_gemv_shards_rows``)."""
+    return gemv_shards(x, shards, bias, out_dtype=out_dtype, _entry="dq_gemv_shards_rows")
 
 
 def gemv_shards(
@@ -217,6 +213,7 @@ def gemv_shards(
     *,
     out_dtype: torch.dtype | None = None,
     out: torch.Tensor | None = None,
+    _entry: str = "dq_gemv_shards",
 ) -> torch.Tensor:
     """All shards of a fused layer against one activation; outputs concatenated along the last dim.
 
@@ -243,7 +240,7 @@ def gemv_shards(
         raise RuntimeError(f"gemv_shards: out must be a contiguous [{m}, {total}] {out_dtype} tensor on {x.device}")
     with torch.cuda.device(x.device):
         _lib.check(
-            lib.dq_gemv_shards(
+            getattr(lib, _entry)(
                 x.data_ptr(), _tag(x.dtype, "gemv_shards: x"), m, arr, len(shards),
                 None if bias is None else bias.data_ptr(), out.data_ptr(), total,
                 _tag(out_dtype, "gemv_shards: out"), _stream(x.device),

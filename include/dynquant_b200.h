@@ -34,6 +34,7 @@ extern "C" {
 #define DQ_ABI_VERSION 2
 #define DQ_GROUP_SIZE_ALIGNMENT 32
 #define DQ_GEMV_MAX_ROWS 8
+#define DQ_GEMV_CHUNKED_MAX_ROWS 64 /* dq_gemv_shards_rows: row chunks of <= 8, above it dequant + dense wins */
 /* Most tokens one expert may receive in a single dq_moe_* call. */
 #define DQ_MOE_MAX_TOKENS 64
 /* Size of the scratch buffer built into the library for dq_moe_gemv_static (2 MiB). */
@@ -147,6 +148,15 @@ DQ_API int32_t dq_gemv(const void* x, int32_t x_dtype, int64_t m, const dq_weigh
 DQ_API int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const dq_weight* shards,
                               int32_t num_shards, const void* bias, void* out, int64_t out_stride,
                               int32_t out_dtype, void* stream);
+/* dq_gemv_shards for up to DQ_GEMV_CHUNKED_MAX_ROWS activation rows (the 9..64-row band in which
+ * the reference already pays for dequantize + dense matmul, runtime/ops.py:205-231): the rows
+ * are cut into ceil(m / 8) chunks of equal size (+-1) and up to four (chunk, shard) pairs leave
+ * as one launch of the tiled kernel, so that a matrix is read from HBM once and by the other
+ * chunks from L2; matrices long enough for the streaming kernel go chunk by chunk.  Same
+ * arguments and results as dq_gemv_shards. */
+DQ_API int32_t dq_gemv_shards_rows(const void* x, int32_t x_dtype, int64_t m, const dq_weight* shards,
+                                   int32_t num_shards, const void* bias, void* out, int64_t out_stride,
+                                   int32_t out_dtype, void* stream);
 
 /* One GEMV of a sequence; see dq_gemv_sequence. */
 typedef struct dq_gemv_job {

@@ -142,6 +142,40 @@ def test_sweep_shapes(bits, group, shape):
     assert out.dtype == torch.bfloat16 and within_one_ulp_16(out, want)
 
 
+@pytest.mark.parametrize(("m", "launches"), [(9, 2), (16, 1), (20, 2), (32, 1), (33, 2), (64, 2)])
+def test_row_chunks_share_launches(m, launches):
+    """9..64 activation rows: chunks of equal size (+-1), up to four of them per launch of the tiled
+    kernel (chunks of different sizes cannot share one), every row against the oracle."""
+    from dynquant_b200 import _lib, ops
+
+    qt = random_qt(1000, 1024, 3, seed=m)  # a ragged row count
+    x = torch.randn(m, 1024, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16).cuda()
+    before = int(_lib.load().dq_launch_count())
+    acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
+    assert int(_lib.load().dq_launch_count()) - before == launches
+    assert ops.last_kernel() == "gemv_mma_tile_kernel"
+    check_acc(acc, oracle_gemv(x, qt))
+    # fused shards x row chunks, with a bias, against the same rows one chunk at a time
+    shards = [random_qt(256, 1024, 4, seed=1), random_qt(128, 1024, 2, seed=2), random_qt(384, 1024, 8, seed=3)]
+    bias = torch.randn(768, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
+    got = ops.gemv_row_chunks(x, shards, bias)
+    want = torch.cat([ops.gemv_shards(x[i:i + 8].contiguous(), shards, bias) for i in range(0, m, 8)])
+    assert got.shape == (m, 768) and within_one_ulp_16(got, want.float().cpu().numpy())
+
+
+def test_row_chunks_of_a_long_matrix_go_one_by_one():
+    from dynquant_b200 import _lib, ops
+
+    qt = random_qt(20480, 512, 4, seed=9)
+    x = torch.randn(16, 512, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).cuda()
+    before = int(_lib.load().dq_launch_count())
+    acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
+    assert int(_lib.load().dq_launch_count()) - before == 2 and ops.last_kernel() == "gemv_mma_stream_kernel"
+    check_acc(acc, oracle_gemv(x, qt))
+    with pytest.raises(RuntimeError, match="exceeds the limit of 64"):
+        ops.gemv_row_chunks(torch.zeros(65, 512, dtype=torch.bfloat16, device="cuda"), [qt])
+
+
 # ---- (d) the head of the decode stack -----------------------------------------------------------
 
 
