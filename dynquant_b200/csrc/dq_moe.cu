@@ -473,6 +473,216 @@ __global__ void __launch_bounds__(kMoeThreads, CTAS) moe_grouped_kernel(const __
   stream::cp_async_wait<0>();
 }
 
+// ---- few tokens: the down projection token by token, the combine folded in ----
+//
+// With a handful of tokens a layer is a chain of launch latencies, not a stream of bytes, and
+// almost every assignment has an expert to itself.  One CTA = (16 output rows, one token):
+// warp k takes the token's k-th expert -- its 16 rows over the whole reduction axis, with
+// h[token, k] as the activation -- and the cross-warp sum that the sliced kernels need anyway
+// IS the combine: y[token, rows] = sum over k, in slot order, of p[token, k] * (partial of warp
+// k).  No per-assignment fp32 scratch, no combine launch.  A warp's whole share (a few steps)
+// is requested before the dependency wait; topk_ids are inputs of the layer, so the addresses
+// do not depend on the gate_up launch.  An expert shared by two tokens is read twice (the
+// second time from L2): the host takes this path only for token counts at which that is rare.
+struct MoeTokenArgs {
+  const void* h;           // [assignments, inter] in act_dtype (gate_up's output)
+  const uint32_t* packed;  // the down bank, [E * hidden, words_per_row]
+  const void* scales;
+  const void* offsets;     // may be null
+  const int32_t* ids;      // [assignments]
+  const float* weights;    // [assignments] routing weights
+  void* y;                 // [tokens, hidden]
+  int y_dtype, act_dtype, meta_dtype;
+  int topk, num_experts;
+  int hidden, inter;
+  int words_per_row, num_groups;
+  int steps;               // padded inter / 128, even, <= kTokenMaxSteps
+  int m_stride_u4;
+  uint32_t magic;
+};
+constexpr int kTokenMaxSteps = 8;
+
+template <int BITS>
+__host__ __device__ inline size_t moe_token_smem(int steps) {
+  const int na = BITS == 8 ? 32 : 16;
+  const size_t ring_w = static_cast<size_t>(steps) * 2 * (4 * BITS) * kMoeThreads;
+  const size_t ring_m = static_cast<size_t>(steps) * 2 * kMoeThreads;
+  const size_t red = static_cast<size_t>(kMoeWarps) * 128 * 4 + kMoeWarps * 4;
+  const size_t stride = static_cast<size_t>(steps) * na + 4;
+  const size_t stage = steps * 256 + (stride + na) * 16 + steps * 64;
+  return ring_w + ring_m + red + kMoeWarps * stage + 16;
+}
+
+template <int BITS, bool XBF16>
+__global__ void __launch_bounds__(kMoeThreads, 2) moe_down_token_kernel(const __grid_constant__ MoeTokenArgs a) {
+  using Plan = MmaPlan<BITS>;
+  constexpr int NA = Plan::kARegs;
+  constexpr int QU = NA / 4;
+  constexpr int UNIT = 4 * BITS;
+  constexpr int STEP_BYTES = 4 * BITS * 4;
+  constexpr int CH = 2;
+  constexpr int STAGE_W = CH * 2 * UNIT * kMoeThreads;
+  constexpr int STAGE_M = CH * 2 * kMoeThreads;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int steps = a.steps, nstages = steps / CH;
+  unsigned char* ring_w = smem_raw;
+  unsigned char* ring_m = ring_w + static_cast<size_t>(nstages) * STAGE_W;
+  float* red = reinterpret_cast<float*>(ring_m + static_cast<size_t>(nstages) * STAGE_M);
+  float* wts = red + kMoeWarps * 128;
+  const int tid = threadIdx.x;
+  const int lane = tid & (kWarp - 1);
+  const int warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const size_t stage_one = static_cast<size_t>(steps) * 256 + (static_cast<size_t>(a.m_stride_u4) + NA) * 16 +
+                           static_cast<size_t>(steps) * 64;
+  unsigned char* mine = reinterpret_cast<unsigned char*>(wts + kMoeWarps) + 8 + warp * stage_one;
+  mine = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(mine) + 15) & ~static_cast<uintptr_t>(15));
+  unsigned short* raw = reinterpret_cast<unsigned short*>(mine);
+  uint4* xb = reinterpret_cast<uint4*>(mine + steps * 256);
+  float* xsum = reinterpret_cast<float*>(xb + a.m_stride_u4 + NA);
+  float* xneg = xsum + steps * 8;
+
+  const int tile = blockIdx.x, token = blockIdx.y;
+  const int aid = token * a.topk + warp;
+  // (inputs of the whole layer: readable before the dependency wait)
+  const int e = warp < a.topk ? __ldg(a.ids + aid) : -1;
+  const bool live = e >= 0 && e < a.num_experts;
+  if (lane == 0) wts[warp] = live ? __ldg(a.weights + aid) : 0.0f;
+  pdl_launch_dependents();
+
+  // ---- request this warp's whole share: 16 rows of its expert, every step ----
+  constexpr int PIECES = 2 * UNIT;
+  constexpr int PER_ROW = UNIT / 4;
+  constexpr int NSRC = (PIECES + kWarp - 1) / kWarp;
+  const bool has_off = a.offsets != nullptr;
+  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * UNIT + lane * 16;
+  const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * (CH * 2);
+  if (live) {
+    const int64_t row0 = static_cast<int64_t>(e) * a.hidden + tile * 16;
+    const int64_t last = static_cast<int64_t>(e) * a.hidden + a.hidden - 1;
+    const bool meta_lane = has_off || (t & 1) == 0;
+    const unsigned short* meta_arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
+    const int64_t mrow = min(row0 + g + ((t & 2) ? 8 : 0), last);
+    const unsigned short* meta = meta_arr + mrow * a.num_groups;
+    for (int s = 0; s < nstages; ++s) {
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+          for (int i = 0; i < NSRC; ++i) {
+            const int piece = i * kWarp + lane;
+            if ((PIECES % kWarp == 0) || piece < PIECES) {
+              const int pg = piece / PER_ROW;
+              const int part = piece - pg * PER_ROW;
+              const int64_t row = min(row0 + hh * 8 + pg, last);
+              const unsigned char* src = reinterpret_cast<const unsigned char*>(a.packed + row * a.words_per_row + part * 4) +
+                                         (s * CH + j) * STEP_BYTES;
+              stream::cp_async_n<16>(ring_w_s + s * STAGE_W + (j * 2 + hh) * (UNIT * kMoeThreads) + i * (kWarp * 16), src);
+            }
+          }
+        }
+      }
+      if (meta_lane) stream::cp_async_n<CH * 2>(ring_m_s + s * STAGE_M, meta + s * CH);
+      stream::cp_async_commit();
+    }
+  }
+  stage_zero_fill<BITS, false>(1, steps, a.m_stride_u4, xb, xsum, xneg, lane, kWarp);
+
+  pdl_wait_prior_grid();  // h
+
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (live) {
+    GemvArgs stage = {};
+    stage.x = static_cast<const unsigned char*>(a.h) + static_cast<size_t>(aid) * a.inter * 2;
+    stage.x_dtype = a.act_dtype;
+    stage.in_features = a.inter;
+    stage.m = 1;
+    stage_warp_slice<BITS, XBF16, false>(stage, 0, steps, a.m_stride_u4, raw, xb, xsum, xneg, lane, true);
+    const bool mbf = a.meta_dtype == DQ_BF16;
+    const uint32_t magic = a.magic;
+    const unsigned char* wslot = ring_w + tid * UNIT;
+    const unsigned char* mslot = ring_m + (tid & ~3) * (CH * 2);
+    const bool b_live = g < 1;
+    const uint4* xb_lane = b_live ? xb + t : xb + a.m_stride_u4;
+    const int xb_step_u4 = b_live ? QU * 4 : 0;
+    const float* xsum_w = xsum + 2 * t;
+    const float* xneg_w = xneg + 2 * t;
+    for (int s = 0; s < nstages; ++s) {
+      moe_wait_pending(nstages - 1 - s);  // groups complete in issue order
+      __syncwarp();
+      uint32_t mc[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (has_off || (i & 1) == 0) mc[i] = *reinterpret_cast<const uint32_t*>(mslot + i * (CH * 2));
+      }
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int sl = s * CH + j;
+        uint32_t wa[BITS], wb[BITS];
+        stream::read_unit<BITS>(wslot + (j * 2 + 0) * (UNIT * kMoeThreads), wa);
+        stream::read_unit<BITS>(wslot + (j * 2 + 1) * (UNIT * kMoeThreads), wb);
+        uint32_t aa[NA], ab[NA];
+        decode_unit<BITS>(wa, magic, aa);
+        decode_unit<BITS>(wb, magic, ab);
+        unbias_fragments<XBF16, NA>(aa);
+        unbias_fragments<XBF16, NA>(ab);
+        const uint4* bsrc = xb_lane + sl * xb_step_u4;
+        float d[4], f[4];
+#pragma unroll
+        for (int q = 0; q < QU; ++q) {
+          const uint4 b = bsrc[q * 4];
+          if (q == 0) {
+            mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
+            mma_16816<XBF16, true>(f, aa[2], ab[2], aa[3], ab[3], b.z, b.w);
+          } else {
+            mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
+            mma_16816<XBF16, false>(f, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d[i] += f[i];
+        auto meta_f32 = [&](int i) -> float {
+          const uint32_t reg = mc[i];
+          if (mbf) return __uint_as_float((j & 1) ? (reg & 0xFFFF0000u) : (reg << 16));
+          const __half2 hh2 = *reinterpret_cast<const __half2*>(&reg);
+          return (j & 1) ? __high2float(hh2) : __low2float(hh2);
+        };
+        const float2 xs2 = *reinterpret_cast<const float2*>(xsum_w + sl * 8);
+        const float2 xn2 = *reinterpret_cast<const float2*>(xneg_w + sl * 8);
+        const float sc_a = meta_f32(0), sc_b = meta_f32(2);
+        acc[0] = fmaf(sc_a, d[0] + xn2.x, acc[0]);
+        acc[1] = fmaf(sc_a, d[1] + xn2.y, acc[1]);
+        acc[2] = fmaf(sc_b, d[2] + xn2.x, acc[2]);
+        acc[3] = fmaf(sc_b, d[3] + xn2.y, acc[3]);
+        if (has_off) {
+          const float of_a = meta_f32(1), of_b = meta_f32(3);
+          acc[0] = fmaf(of_a, xs2.x, acc[0]);
+          acc[1] = fmaf(of_a, xs2.y, acc[1]);
+          acc[2] = fmaf(of_b, xs2.x, acc[2]);
+          acc[3] = fmaf(of_b, xs2.y, acc[3]);
+        }
+      }
+      wslot += STAGE_W;
+      mslot += STAGE_M;
+    }
+  }
+  // ---- the combine: the token is column 0 of the accumulator (lanes t == 0: rows g and g + 8) ----
+  if (t == 0) {
+    red[warp * 128 + g] = acc[0];
+    red[warp * 128 + 8 + g] = acc[2];
+  }
+  __syncthreads();
+  if (tid < 16) {
+    const int row = tile * 16 + tid;
+    if (row < a.hidden) {
+      float sum = 0.0f;
+      for (int k = 0; k < a.topk; ++k) sum = fmaf(wts[k], red[k * 128 + tid], sum);  // slot order, like moe_combine_kernel
+      store_f32(a.y, static_cast<int64_t>(token) * a.hidden + row, a.y_dtype, sum);
+    }
+  }
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ d, const float* __restrict__ w,
                                    const int32_t* __restrict__ ids, int tokens, int topk, int hidden,
                                    int num_experts, void* y, int y_dtype) {
@@ -554,6 +764,7 @@ int32_t launch_pdl(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStrea
   cfg.numAttrs = 1;
   DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, args));
   DQ_CHECK_LAUNCH(what);
+  note_kernel("moe_grouped_kernel");
   return DQ_OK;
 }
 
@@ -656,6 +867,82 @@ int32_t launch_bank(const dq_weight& w, const dq_geometry& g, MoeArgs a, int slo
   }
 }
 
+// *taken stays false (nothing launched) when the layer does not qualify: more tokens than the
+// threshold, more than eight experts per token, a reduction axis longer than kTokenMaxSteps
+// steps or with an odd number of them, metadata rows that are not whole 32-bit words.
+int32_t launch_down_by_token(const dq_weight& w, const dq_geometry& g, const MoeArgs& base, const float* topk_w,
+                             const void* h, void* y, int y_dtype, int hidden, int inter, cudaStream_t stream,
+                             bool* taken) {
+  *taken = false;
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr) return DQ_ERR_CUDA;
+  // Up to this many tokens nearly every assignment has its expert to itself (128 experts,
+  // top-8: 30 distinct experts for 32 assignments at four tokens), so reading per assignment
+  // costs no extra bytes and saves the combine launch.
+  const int max_tokens = tuning_int("DQ_B200_MOE_BY_TOKEN_MAX", 4);
+  const int steps = g.words_per_row / (4 * w.bits);
+  if (base.tokens > max_tokens || base.topk > kMoeWarps || steps > kTokenMaxSteps || steps % 2 != 0 || steps == 0) {
+    return DQ_OK;
+  }
+  if (g.num_groups != steps || g.num_groups % 2 != 0 || reinterpret_cast<uintptr_t>(w.scales) % 4 != 0 ||
+      reinterpret_cast<uintptr_t>(w.offsets) % 4 != 0) {
+    return DQ_OK;
+  }
+  MoeTokenArgs t = {};
+  t.h = h;
+  t.packed = static_cast<const uint32_t*>(w.packed);
+  t.scales = w.scales;
+  t.offsets = w.offsets;
+  t.ids = base.ids;
+  t.weights = topk_w;
+  t.y = y;
+  t.y_dtype = y_dtype;
+  t.act_dtype = base.act_dtype;
+  t.meta_dtype = w.meta_dtype;
+  t.topk = base.topk;
+  t.num_experts = base.num_experts;
+  t.hidden = hidden;
+  t.inter = inter;
+  t.words_per_row = g.words_per_row;
+  t.num_groups = g.num_groups;
+  t.steps = steps;
+  t.m_stride_u4 = steps * (w.bits == 8 ? 32 : 16) + 4;
+  t.magic = base.act_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
+  const dim3 grid(static_cast<unsigned>(ceil_div(hidden, 16)), static_cast<unsigned>(base.tokens));
+  auto run = [&](auto kernel, size_t smem) -> int32_t {
+    if (smem > static_cast<size_t>(dev->max_smem_optin)) return DQ_OK;  // not taken
+    if (smem > 48 * 1024) {
+      DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kMoeThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, t));
+    DQ_CHECK_LAUNCH("moe_gemv(down by token)");
+    note_kernel("moe_down_token_kernel");
+    *taken = true;
+    return DQ_OK;
+  };
+  const bool xbf = base.act_dtype == DQ_BF16;
+  switch (w.bits) {
+    case 2:
+      return xbf ? run(moe_down_token_kernel<2, true>, moe_token_smem<2>(steps)) : run(moe_down_token_kernel<2, false>, moe_token_smem<2>(steps));
+    case 3:
+      return xbf ? run(moe_down_token_kernel<3, true>, moe_token_smem<3>(steps)) : run(moe_down_token_kernel<3, false>, moe_token_smem<3>(steps));
+    case 4:
+      return xbf ? run(moe_down_token_kernel<4, true>, moe_token_smem<4>(steps)) : run(moe_down_token_kernel<4, false>, moe_token_smem<4>(steps));
+    default:
+      return xbf ? run(moe_down_token_kernel<8, true>, moe_token_smem<8>(steps)) : run(moe_down_token_kernel<8, false>, moe_token_smem<8>(steps));
+  }
+}
+
 }  // namespace
 }  // namespace dq
 
@@ -733,6 +1020,16 @@ int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_
   a.out = base + lay.h;
   a.rows = static_cast<int>(inter);
   if (const int32_t rc = dq::launch_bank<true>(*gate_up, g_gu, a, slots, s)) return rc;
+  // Few tokens: the down projection token by token with the combine folded in (two launches a
+  // layer instead of three).  Measured on B200, Qwen3-30B-A3B shape: see launch_down_by_token.
+  {
+    bool taken = false;
+    if (const int32_t rc = dq::launch_down_by_token(*down, g_dn, a, topk_w, base + lay.h, y, y_dtype,
+                                                    static_cast<int>(hidden), static_cast<int>(inter), s, &taken)) {
+      return rc;
+    }
+    if (taken) return DQ_OK;
+  }
   // down: h -> d
   a.act = base + lay.h;
   a.out = base + lay.d;
@@ -755,6 +1052,7 @@ int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_
                                topk_ids, static_cast<int>(tokens), static_cast<int>(topk), static_cast<int>(hidden),
                                static_cast<int>(num_experts), y, y_dtype));
     DQ_CHECK_LAUNCH("moe_gemv(combine)");
+    dq::note_kernel("moe_combine_kernel");
   }
   return DQ_OK;
 }

@@ -208,3 +208,33 @@ def test_moe_stage_by_stage(act, bits_gu, bits_dn):
         assert (h_err2 / h_ref2) ** 0.5 <= 1e-3  # fp16's rounding itself is inside the bar
     combined = (w.double().reshape(n_assign, 1) * d.double()).reshape(tokens, topk, hidden).sum(1)
     assert float((y.cpu().double() - combined).abs().max()) <= 1e-5 * float(combined.abs().max())
+
+
+@pytest.mark.parametrize(("tokens", "launches"), [(1, 2), (2, 2), (4, 2), (5, 3)])
+def test_few_tokens_take_the_down_projection_with_the_combine_folded_in(tokens, launches):
+    """Up to four tokens the layer is two launches: the down projection runs token by token (a
+    warp per expert of the token) and its cross-warp sum is the combine.  Real expert shape."""
+    from dynquant_b200 import _lib, ops
+
+    before = int(_lib.load().dq_launch_count())
+    got, want, *_ = run_case(tokens, 128, 2048, 768, 8, 3, 4, seed=40 + tokens)
+    assert int(_lib.load().dq_launch_count()) - before == launches
+    if launches == 2:
+        assert ops.last_kernel() == "moe_down_token_kernel"
+    scale = np.abs(want).max() + 1e-30
+    assert np.abs(got - want).max() / scale <= 4e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3
+
+
+@pytest.mark.parametrize("bits_dn", [2, 3, 4, 8])
+def test_few_tokens_every_width_dtype_and_absent_experts(bits_dn):
+    from dynquant_b200 import ops
+
+    for act in (torch.bfloat16, torch.float16):
+        got, want, *_ = run_case(3, 16, 512, 256, 4, 4, bits_dn, act=act, seed=50 + bits_dn, local=(4, 12))
+        assert ops.last_kernel() == "moe_down_token_kernel"
+        assert np.linalg.norm(got - want) / (np.linalg.norm(want) + 1e-30) <= 2e-3
+    # a reduction axis of three steps (odd): not this kernel's; the three-launch path takes it
+    got, want, *_ = run_case(2, 8, 256, 384, 2, 4, bits_dn, seed=60)
+    assert ops.last_kernel() != "moe_down_token_kernel"
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3
