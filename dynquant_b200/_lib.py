@@ -149,6 +149,8 @@ SIGNATURES = {
     "dq_peer_all_gather": (_I32, [ctypes.POINTER(PeerGroup), _P, _I64, _P, _P]),
     "dq_peer_reduce_scatter_f32": (_I32, [ctypes.POINTER(PeerGroup), _P, _I64, _P, _I32, _P]),
     "dq_peer_status": (_I32, [ctypes.POINTER(PeerGroup), _P, _P]),
+    "dq_peer_all_gather_parts": (_I32, [ctypes.POINTER(PeerGroup), ctypes.POINTER(ctypes.c_void_p),
+                                        ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_void_p), _I32, _P]),
     "dq_gemv_stage_push": (_I32, [ctypes.POINTER(GemvJob), _I32, ctypes.POINTER(PeerPush), _P]),
     "dq_peer_push_status": (_I32, [ctypes.POINTER(PeerPush), _P]),
     "dq_gemv_host": (_I32, [_P, _I32, _I64, _WP, _P, _I32, _P, _P, _P]),

@@ -32,6 +32,7 @@ namespace peer {
 constexpr int kThreads = 256;
 constexpr int kMaxWorld = 64;
 constexpr int kMaxCtasPerPeer = 8;
+constexpr int kMaxParts = 4;
 // header of every exchange buffer (bytes)
 constexpr int kFlagsAt = 0;        // u32 [world]: epoch of the last piece that arrived from each source
 constexpr int kEpochsAt = 1024;    // u32 [world]: epoch this rank last used towards each destination
@@ -49,6 +50,13 @@ struct Args {
   int64_t piece_bytes;
   unsigned char* out;             // all-gather: [world * piece_bytes]
   int scatter;                    // 1: piece p of src goes to rank p (reduce-scatter); 0: the one piece goes to everyone
+  // all-gather of several tensors in one exchange: the piece is their concatenation (every part a
+  // multiple of 16 bytes); part i comes from part_src[i] and rank p's copy of it goes to
+  // part_out[i] + p * part_bytes[i].  parts == 0: the single src / out above.
+  int parts;
+  const unsigned char* part_src[kMaxParts];
+  unsigned char* part_out[kMaxParts];
+  int64_t part_bytes[kMaxParts];
 };
 
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
@@ -98,9 +106,18 @@ __global__ void __launch_bounds__(kThreads) peer_exchange_kernel(const Args a) {
   const int64_t hi = std::min<int64_t>(a.piece_bytes, (words * (c + 1) / a.ctas_per_peer) * 16);
 
   // ---- push: my piece (gather) or my partial rows for rank p (scatter) into p's buffer, slot [rank] ----
-  const unsigned char* src = a.src + (a.scatter ? static_cast<int64_t>(p) * a.piece_bytes : 0);
   unsigned char* slot = theirs + kHeaderBytes + half + static_cast<int64_t>(a.rank) * a.piece_bytes;
-  copy_span(slot, src, lo, hi);
+  if (a.parts == 0) {
+    const unsigned char* src = a.src + (a.scatter ? static_cast<int64_t>(p) * a.piece_bytes : 0);
+    copy_span(slot, src, lo, hi);
+  } else {
+    int64_t at = 0;  // offset of the part inside the piece
+    for (int i = 0; i < a.parts; ++i) {
+      const int64_t from = max(lo, at), to = min(hi, at + a.part_bytes[i]);
+      if (from < to) copy_span(slot + at, a.part_src[i], from - at, to - at);
+      at += a.part_bytes[i];
+    }
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     // Ordering without a fence per thread: the barrier above orders the CTA's stores before this
@@ -134,8 +151,17 @@ __global__ void __launch_bounds__(kThreads) peer_exchange_kernel(const Args a) {
   }
   __syncthreads();
   if (s_ok && !a.scatter) {
-    copy_span(a.out + static_cast<int64_t>(p) * a.piece_bytes,
-              mine + kHeaderBytes + half + static_cast<int64_t>(p) * a.piece_bytes, lo, hi);
+    const unsigned char* got = mine + kHeaderBytes + half + static_cast<int64_t>(p) * a.piece_bytes;
+    if (a.parts == 0) {
+      copy_span(a.out + static_cast<int64_t>(p) * a.piece_bytes, got, lo, hi);
+    } else {
+      int64_t at = 0;
+      for (int i = 0; i < a.parts; ++i) {
+        const int64_t from = max(lo, at), to = min(hi, at + a.part_bytes[i]);
+        if (from < to) copy_span(a.part_out[i] + static_cast<int64_t>(p) * a.part_bytes[i], got + at, from - at, to - at);
+        at += a.part_bytes[i];
+      }
+    }
   }
 }
 
@@ -169,18 +195,14 @@ int32_t check_group(const char* op, const dq_peer_group* g, int64_t piece_bytes)
   return DQ_OK;
 }
 
-int32_t launch_exchange(const dq_peer_group* g, const void* src, int64_t piece_bytes, void* out, int scatter,
-                        cudaStream_t stream) {
-  Args a = {};
+int32_t launch_exchange(const dq_peer_group* g, Args a, int64_t piece_bytes, int scatter, cudaStream_t stream) {
   a.buffers = reinterpret_cast<unsigned char* const*>(g->buffers);
   a.half_bytes = ((g->buffer_bytes - kHeaderBytes) / 2) / 16 * 16;
   a.world = g->world;
   a.rank = g->rank;
   a.ctas_per_peer = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(kMaxCtasPerPeer, piece_bytes / 16384)));
   a.spin_limit = g->spin_limit > 0 ? g->spin_limit : (1 << 22);
-  a.src = static_cast<const unsigned char*>(src);
   a.piece_bytes = piece_bytes;
-  a.out = static_cast<unsigned char*>(out);
   a.scatter = scatter;
   peer_exchange_kernel<<<g->world * a.ctas_per_peer, kThreads, 0, stream>>>(a);
   DQ_CHECK_LAUNCH("peer exchange");
@@ -201,7 +223,33 @@ int32_t dq_peer_all_gather(const dq_peer_group* group, const void* src, int64_t 
   DQ_REQUIRE(bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0,
              "peer_all_gather: the piece must be a multiple of 16 bytes and both pointers 16-byte aligned");
   if (bytes == 0) return DQ_OK;
-  return peer::launch_exchange(group, src, bytes, out, 0, static_cast<cudaStream_t>(stream));
+  peer::Args a = {};
+  a.src = static_cast<const unsigned char*>(src);
+  a.out = static_cast<unsigned char*>(out);
+  return peer::launch_exchange(group, a, bytes, 0, static_cast<cudaStream_t>(stream));
+}
+
+int32_t dq_peer_all_gather_parts(const dq_peer_group* group, const void* const* srcs, const int64_t* bytes,
+                                 void* const* outs, int32_t parts, void* stream) {
+  using namespace dq;
+  DQ_REQUIRE(parts >= 1 && parts <= peer::kMaxParts && srcs != nullptr && bytes != nullptr && outs != nullptr,
+             "peer_all_gather_parts: 1..%d parts, got %d", peer::kMaxParts, parts);
+  int64_t total = 0;
+  for (int i = 0; i < parts; ++i) {
+    DQ_REQUIRE(bytes[i] > 0 && bytes[i] % 16 == 0 && srcs[i] != nullptr && outs[i] != nullptr &&
+                   reinterpret_cast<uintptr_t>(srcs[i]) % 16 == 0 && reinterpret_cast<uintptr_t>(outs[i]) % 16 == 0,
+               "peer_all_gather_parts: part %d must be a positive multiple of 16 bytes with 16-byte aligned pointers", i);
+    total += bytes[i];
+  }
+  if (const int32_t rc = peer::check_group("peer_all_gather_parts", group, total)) return rc;
+  peer::Args a = {};
+  a.parts = parts;
+  for (int i = 0; i < parts; ++i) {
+    a.part_src[i] = static_cast<const unsigned char*>(srcs[i]);
+    a.part_out[i] = static_cast<unsigned char*>(outs[i]);
+    a.part_bytes[i] = bytes[i];
+  }
+  return peer::launch_exchange(group, a, total, 0, static_cast<cudaStream_t>(stream));
 }
 
 int32_t dq_peer_reduce_scatter_f32(const dq_peer_group* group, const float* partial, int64_t count, void* out,
@@ -215,7 +263,9 @@ int32_t dq_peer_reduce_scatter_f32(const dq_peer_group* group, const float* part
              "peer_reduce_scatter: count must be a multiple of 4 and the source 16-byte aligned");
   if (count == 0) return DQ_OK;
   auto s = static_cast<cudaStream_t>(stream);
-  if (const int32_t rc = peer::launch_exchange(group, partial, bytes, nullptr, 1, s)) return rc;
+  peer::Args a = {};
+  a.src = reinterpret_cast<const unsigned char*>(partial);
+  if (const int32_t rc = peer::launch_exchange(group, a, bytes, 1, s)) return rc;
   const int grid = static_cast<int>(std::min<int64_t>(148, ceil_div(count, peer::kThreads)));
   peer::peer_sum_kernel<<<grid, peer::kThreads, 0, s>>>(reinterpret_cast<const unsigned char* const*>(group->buffers),
                                                         group->rank, group->world,

@@ -67,6 +67,22 @@ class PeerExchange:
                                                       _stream(self.device)))
         return out
 
+    def all_gather_parts(self, pieces: list[torch.Tensor], outs: list[torch.Tensor]) -> list[torch.Tensor]:
+        """Up to four tensors in ONE exchange launch: ``outs[i]`` (``world`` times ``pieces[i]``)
+        receives every rank's ``pieces[i]`` in rank order."""
+        n = len(pieces)
+        sizes = [p.numel() * p.element_size() for p in pieces]
+        for p, o, b in zip(pieces, outs, sizes):
+            if not p.is_contiguous() or not o.is_contiguous() or o.numel() * o.element_size() != b * self.world:
+                raise RuntimeError("peer all_gather_parts: pieces and outs must be contiguous and outs hold world pieces")
+        srcs = (ctypes.c_void_p * n)(*[p.data_ptr() for p in pieces])
+        dsts = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outs])
+        nbytes = (ctypes.c_int64 * n)(*sizes)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().dq_peer_all_gather_parts(ctypes.byref(self._desc), srcs, nbytes, dsts, n,
+                                                            _stream(self.device)))
+        return outs
+
     def reduce_scatter(self, partial: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """``partial``: fp32 ``[world * n]`` (rank i's rows first-to-last at ``[i * n, (i + 1) * n)``);
         ``out``: ``n`` elements receiving the sum over source ranks of this rank's rows."""

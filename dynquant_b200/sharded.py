@@ -145,8 +145,8 @@ class ExpertParallelMoE:
     * ``mode="replicated"``: all-gather tokens and routing, local partial sums for all tokens,
       reduce-scatter back.  Fewer messages; same bytes.
     * ``mode="peer"``: the replicated scheme with the library's own exchanges over peer memory
-      (``peer=`` a :class:`~dynquant_b200.peer.PeerExchange`): three small all-gathers (token rows,
-      ids, weights), the grouped kernels, one reduce-scatter that adds the source ranks in rank
+      (``peer=`` a :class:`~dynquant_b200.peer.PeerExchange`): one all-gather launch for token rows,
+      ids and weights together, the grouped kernels, one reduce-scatter that adds the source ranks in rank
       order -- kernel launches only, so a whole layer can sit in a CUDA graph.
 
     All produce the same numbers up to the order of the final fp32 sum over ranks.
@@ -174,10 +174,9 @@ class ExpertParallelMoE:
         self.max_tokens = max_tokens
 
     def _localise(self, ids: torch.Tensor) -> torch.Tensor:
-        """Global expert ids -> this rank's local numbering, -1 for experts held elsewhere."""
-        lo = self.rank * self.local_experts
-        local = ids - lo
-        return torch.where((local >= 0) & (local < self.local_experts), local, torch.full_like(ids, -1)).to(torch.int32)
+        """Global expert ids -> this rank's local numbering.  Experts held elsewhere come out
+        negative or >= ``local_experts``, which the grouped kernels skip: one elementwise op."""
+        return (ids - self.rank * self.local_experts).to(torch.int32)
 
     def _local_partial(self, x: torch.Tensor, ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """Partial sums of this rank's experts for every gathered token, at most ``max_tokens`` tokens
@@ -217,9 +216,12 @@ class ExpertParallelMoE:
             xs = torch.empty(world * t, h, dtype=x.dtype, device=x.device)
             ids = torch.empty(world * t, k, dtype=topk_ids.dtype, device=x.device)
             ws = torch.empty(world * t, k, dtype=topk_w.dtype, device=x.device)
-            self.peer.all_gather(x.contiguous(), xs)
-            self.peer.all_gather(topk_ids.contiguous(), ids)
-            self.peer.all_gather(topk_w.contiguous(), ws)
+            pieces = [x.contiguous(), topk_ids.contiguous(), topk_w.contiguous()]
+            if all((p.numel() * p.element_size()) % 16 == 0 for p in pieces):
+                self.peer.all_gather_parts(pieces, [xs, ids, ws])  # one launch for the three
+            else:
+                for p, o in zip(pieces, (xs, ids, ws)):
+                    self.peer.all_gather(p, o)
             partial = self._local_partial(xs, ids, ws).to(torch.float32).contiguous()  # [world*t, h]
             out = torch.empty(t, h, dtype=x.dtype, device=x.device)
             self.peer.reduce_scatter(partial.view(-1), out)

@@ -335,6 +335,13 @@ DQ_API int64_t dq_peer_header_bytes(void);
  * rank i's piece at out + i * bytes. */
 DQ_API int32_t dq_peer_all_gather(const dq_peer_group* group, const void* src, int64_t bytes,
                                   void* out, void* stream);
+/* Up to four tensors gathered by ONE exchange launch (an expert layer's token rows, expert ids and
+ * routing weights travel together): part i contributes bytes[i] (a multiple of 16) from srcs[i],
+ * and outs[i] receives world * bytes[i], rank r's copy at outs[i] + r * bytes[i].  srcs, bytes and
+ * outs are HOST arrays. */
+DQ_API int32_t dq_peer_all_gather_parts(const dq_peer_group* group, const void* const* srcs,
+                                        const int64_t* bytes, void* const* outs, int32_t parts,
+                                        void* stream);
 /* `partial` holds world * count floats: the rows this rank computed for rank i's elements at
  * partial + i * count.  `out` (count elements of out_dtype) receives the sum over source ranks
  * of the rows that belong to this rank, added in rank order, rounded once. */

@@ -172,3 +172,20 @@ def test_stages_the_pushing_kernels_do_not_take_are_refused_without_a_launch():
     assert not win.run_stage(0, _stage_jobs([qt], x, out, 1), 1)
     assert int(_lib.load().dq_launch_count()) == before
     assert win.epoch(0) == 0
+
+
+def test_world_of_one_gathers_several_tensors_in_one_launch():
+    from dynquant_b200 import _lib
+    from dynquant_b200.peer import PeerExchange
+
+    ex = PeerExchange.from_buffers(_buffers(1, 1 << 19), rank=0)
+    for sizes in ((4096, 32, 32), (16, 16), (131072, 64, 48, 16)):  # the last: several CTAs, a part inside one CTA's span
+        pieces = [torch.randint(0, 255, (n,), dtype=torch.uint8, device="cuda") for n in sizes]
+        outs = [torch.zeros_like(p) for p in pieces]
+        before = int(_lib.load().dq_launch_count())
+        ex.all_gather_parts(pieces, outs)
+        assert int(_lib.load().dq_launch_count()) - before == 1
+        ex.check()
+        assert all(torch.equal(o, p) for o, p in zip(outs, pieces)), sizes
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        ex.all_gather_parts([torch.zeros(24, dtype=torch.uint8, device="cuda")], [torch.zeros(24, dtype=torch.uint8, device="cuda")])
