@@ -136,6 +136,7 @@ SIGNATURES = {
     "dq_gemv_sequence": (_I32, [ctypes.POINTER(GemvJob), _I32, _P]),
     "dq_moe_scratch_bytes": (_I32, [_I64, _I64, _I64, _I64, _I64, _I32, ctypes.POINTER(ctypes.c_int64)]),
     "dq_moe_gemv": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _WP, _WP, _I64, _I64, _P, _I32, _P, _I64, _P]),
+    "dq_moe_gemv_shard": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _I64, _WP, _WP, _I64, _I64, _P, _I32, _P, _I64, _P]),
     "dq_moe_gemv_static": (_I32, [_P, _I32, _I64, _P, _P, _I64, _I64, _WP, _WP, _I64, _I64, _P, _I32, _P]),
     "dq_plan_workspace_bytes": (_I32, [_I32, ctypes.POINTER(ctypes.c_int64)]),
     "dq_plan_create": (_I32, [ctypes.POINTER(GemvJob), _I32, _P, _I64, _P, ctypes.POINTER(_P)]),

@@ -50,7 +50,8 @@ struct MoeArgs {
   const void* scales;
   const void* offsets;      // may be null
   void* out;                // gate_up: h [assignments, inter] act dtype; down: d [assignments, hidden] fp32
-  const int32_t* ids;       // [assignments] expert of every (token, slot)
+  const int32_t* ids;       // [assignments] expert of every (token, slot), minus first_expert
+  int first_expert;         // ids are global; this call holds experts [first_expert, first_expert + num_experts)
   int assignments, num_experts;
   int act_dtype, meta_dtype;
   int topk;
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(kMoeThreads, CTAS) moe_grouped_kernel(const __
 
   // ---- routing, by every CTA for itself ----
   for (int i = tid; i < a.num_experts; i += kMoeThreads) cnt[i] = 0;
-  for (int i = tid; i < a.assignments; i += kMoeThreads) ids_s[i] = __ldcg(a.ids + i);
+  for (int i = tid; i < a.assignments; i += kMoeThreads) ids_s[i] = __ldcg(a.ids + i) - a.first_expert;
   if (tid == 0) misc[0] = -1;
   __syncthreads();
   for (int i = tid; i < a.assignments; i += kMoeThreads) {
@@ -489,7 +490,8 @@ struct MoeTokenArgs {
   const uint32_t* packed;  // the down bank, [E * hidden, words_per_row]
   const void* scales;
   const void* offsets;     // may be null
-  const int32_t* ids;      // [assignments]
+  const int32_t* ids;      // [assignments], global numbers
+  int first_expert;        // this call holds experts [first_expert, first_expert + num_experts)
   const float* weights;    // [assignments] routing weights
   void* y;                 // [tokens, hidden]
   int y_dtype, act_dtype, meta_dtype;
@@ -545,7 +547,7 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_down_token_kernel(const __
   const int tile = blockIdx.x, token = blockIdx.y;
   const int aid = token * a.topk + warp;
   // (inputs of the whole layer: readable before the dependency wait)
-  const int e = warp < a.topk ? __ldg(a.ids + aid) : -1;
+  const int e = warp < a.topk ? __ldg(a.ids + aid) - a.first_expert : -1;
   const bool live = e >= 0 && e < a.num_experts;
   if (lane == 0) wts[warp] = live ? __ldg(a.weights + aid) : 0.0f;
   pdl_launch_dependents();
@@ -684,7 +686,7 @@ __global__ void __launch_bounds__(kMoeThreads, 2) moe_down_token_kernel(const __
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ d, const float* __restrict__ w,
-                                   const int32_t* __restrict__ ids, int tokens, int topk, int hidden,
+                                   const int32_t* __restrict__ ids, int first_expert, int tokens, int topk, int hidden,
                                    int num_experts, void* y, int y_dtype) {
   pdl_launch_dependents();
   pdl_wait_prior_grid();
@@ -696,7 +698,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ d, const float* __r
     float acc = 0.0f;
     for (int k = 0; k < topk; ++k) {
       const int aid = tkn * topk + k;
-      const int e = ids[aid];
+      const int e = ids[aid] - first_expert;
       if (e >= 0 && e < num_experts) {
         acc = fmaf(w[aid], d[static_cast<int64_t>(aid) * hidden + col], acc);
       }
@@ -894,6 +896,7 @@ int32_t launch_down_by_token(const dq_weight& w, const dq_geometry& g, const Moe
   t.scales = w.scales;
   t.offsets = w.offsets;
   t.ids = base.ids;
+  t.first_expert = base.first_expert;
   t.weights = topk_w;
   t.y = y;
   t.y_dtype = y_dtype;
@@ -965,6 +968,16 @@ int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_
                     int64_t topk, int64_t num_experts, const dq_weight* gate_up, const dq_weight* down,
                     int64_t hidden, int64_t inter, void* y, int32_t y_dtype, void* scratch, int64_t scratch_bytes,
                     void* stream) {
+  return dq_moe_gemv_shard(x, x_dtype, tokens, topk_ids, topk_w, topk, 0, num_experts, gate_up, down, hidden, inter, y,
+                           y_dtype, scratch, scratch_bytes, stream);
+}
+
+int32_t dq_moe_gemv_shard(const void* x, int32_t x_dtype, int64_t tokens, const int32_t* topk_ids, const float* topk_w,
+                          int64_t topk, int64_t first_expert, int64_t num_experts, const dq_weight* gate_up,
+                          const dq_weight* down, int64_t hidden, int64_t inter, void* y, int32_t y_dtype, void* scratch,
+                          int64_t scratch_bytes, void* stream) {
+  DQ_REQUIRE(first_expert >= 0 && first_expert < (1LL << 30), "moe_gemv: first_expert=%lld out of range",
+             static_cast<long long>(first_expert));
   int64_t need = 0;
   if (const int32_t rc = dq_moe_scratch_bytes(tokens, topk, hidden, inter, num_experts, x_dtype, &need)) return rc;
   DQ_REQUIRE(gate_up != nullptr && down != nullptr, "moe_gemv: null bank descriptor");
@@ -1003,6 +1016,7 @@ int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_
   const int slots = static_cast<int>(std::min<int64_t>(num_experts, assignments));
   dq::MoeArgs a = {};
   a.ids = topk_ids;
+  a.first_expert = static_cast<int>(first_expert);
   a.assignments = assignments;
   a.num_experts = static_cast<int>(num_experts);
   // Activation rows staged at once: the eight columns of one mma.  An expert with more tokens
@@ -1049,7 +1063,7 @@ int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const int32_
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     DQ_CUDA(cudaLaunchKernelEx(&cfg, dq::moe_combine_kernel, reinterpret_cast<const float*>(base + lay.d), topk_w,
-                               topk_ids, static_cast<int>(tokens), static_cast<int>(topk), static_cast<int>(hidden),
+                               topk_ids, static_cast<int>(first_expert), static_cast<int>(tokens), static_cast<int>(topk), static_cast<int>(hidden),
                                static_cast<int>(num_experts), y, y_dtype));
     DQ_CHECK_LAUNCH("moe_gemv(combine)");
     dq::note_kernel("moe_combine_kernel");

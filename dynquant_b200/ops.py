@@ -289,8 +289,13 @@ def moe_gemv(
     num_experts: int,
     out_dtype: torch.dtype | None = None,
     scratch: torch.Tensor | None = None,
+    first_expert: int = 0,
 ) -> torch.Tensor:
     """Expert layer over packed banks: ``sum_k w[t,k] * down_e(silu(gate_e(x_t)) * up_e(x_t))``.
+
+    ``first_expert``: the banks hold experts ``[first_expert, first_expert + num_experts)`` of a
+    larger layer and ``topk_ids`` carry the layer's global numbers (one rank of an
+    expert-parallel layer); ids outside that range are skipped.
 
     ``gate_up`` is the bank ``[E, 2*inter, hidden]`` folded to rows (gate rows of an expert
     first), ``down`` is ``[E, hidden, inter]`` folded to rows; ``topk_ids`` int32
@@ -321,9 +326,9 @@ def moe_gemv(
     y = torch.empty((tokens, hidden), dtype=out_dtype, device=x.device)
     with torch.cuda.device(x.device):
         _lib.check(
-            lib.dq_moe_gemv(
+            lib.dq_moe_gemv_shard(
                 x.data_ptr(), _tag(x.dtype, "moe_gemv: x"), tokens, topk_ids.data_ptr(), topk_weights.data_ptr(),
-                topk, num_experts, ctypes.byref(wgu), ctypes.byref(wdn), hidden, inter, y.data_ptr(),
+                topk, first_expert, num_experts, ctypes.byref(wgu), ctypes.byref(wdn), hidden, inter, y.data_ptr(),
                 _tag(out_dtype, "moe_gemv: out"), scratch.data_ptr(), scratch.numel(), _stream(x.device),
             )
         )

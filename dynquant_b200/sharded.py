@@ -156,6 +156,7 @@ class ExpertParallelMoE:
                  group=None, compute: Callable | None = None, max_tokens: int = 64, peer=None) -> None:
         self.group = group
         self.peer = peer
+        self._takes_global_ids = False
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if num_experts % self.world:
@@ -167,9 +168,11 @@ class ExpertParallelMoE:
         if compute is None:
             from . import ops
 
-            def compute(x, ids, w, gate_up, down, num_experts):
-                return ops.moe_gemv(x, ids, w, gate_up, down, num_experts=num_experts, out_dtype=torch.float32)
+            def compute(x, ids, w, gate_up, down, num_experts, first_expert=0):
+                return ops.moe_gemv(x, ids, w, gate_up, down, num_experts=num_experts, out_dtype=torch.float32,
+                                    first_expert=first_expert)
 
+            self._takes_global_ids = True  # the kernels renumber the ids themselves
         self.compute = compute
         self.max_tokens = max_tokens
 
@@ -181,13 +184,16 @@ class ExpertParallelMoE:
     def _local_partial(self, x: torch.Tensor, ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """Partial sums of this rank's experts for every gathered token, at most ``max_tokens`` tokens
         per call of the grouped kernel (the gathered batch is ``world`` times a rank's own)."""
-        local = self._localise(ids)
         limit = self.max_tokens
+        if self._takes_global_ids:  # no renumbering pass: the kernels subtract the first local expert
+            local, extra = ids.to(torch.int32), {"first_expert": self.rank * self.local_experts}
+        else:
+            local, extra = self._localise(ids), {}
         if x.shape[0] <= limit:
             return self.compute(x.contiguous(), local.contiguous(), w.contiguous(), self.gate_up, self.down,
-                                self.local_experts)
+                                self.local_experts, **extra)
         parts = [self.compute(x[s : s + limit].contiguous(), local[s : s + limit].contiguous(),
-                              w[s : s + limit].contiguous(), self.gate_up, self.down, self.local_experts)
+                              w[s : s + limit].contiguous(), self.gate_up, self.down, self.local_experts, **extra)
                  for s in range(0, x.shape[0], limit)]
         return torch.cat(parts)
 

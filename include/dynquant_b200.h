@@ -274,6 +274,15 @@ DQ_API int32_t dq_moe_gemv(const void* x, int32_t x_dtype, int64_t tokens, const
                            int64_t inter, void* y, int32_t y_dtype, void* scratch,
                            int64_t scratch_bytes, void* stream);
 
+/* dq_moe_gemv for one rank of an expert-parallel layer: topk_ids carry GLOBAL expert numbers and
+ * the banks hold experts [first_expert, first_expert + num_experts) only; every other id is
+ * skipped, so y is this rank's partial sum.  Saves the host framework the elementwise pass that
+ * renumbers the ids per rank. */
+DQ_API int32_t dq_moe_gemv_shard(const void* x, int32_t x_dtype, int64_t tokens, const int32_t* topk_ids,
+                                 const float* topk_w, int64_t topk, int64_t first_expert,
+                                 int64_t num_experts, const dq_weight* gate_up, const dq_weight* down,
+                                 int64_t hidden, int64_t inter, void* y, int32_t y_dtype, void* scratch,
+                                 int64_t scratch_bytes, void* stream);
 /* dq_moe_gemv without a scratch argument and without any allocation.  This entry point has
  * no counterpart in the reference.
  *

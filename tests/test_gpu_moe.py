@@ -238,3 +238,22 @@ def test_few_tokens_every_width_dtype_and_absent_experts(bits_dn):
     got, want, *_ = run_case(2, 8, 256, 384, 2, 4, bits_dn, seed=60)
     assert ops.last_kernel() != "moe_down_token_kernel"
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3
+
+
+@pytest.mark.parametrize("tokens", [2, 12])
+def test_a_shard_of_the_experts_takes_global_ids(tokens):
+    """One rank of an expert-parallel layer: banks of experts [4, 12) only, global ids and
+    ``first_expert=4`` -- bit-identical to renumbering the ids on the host first."""
+    from dynquant_b200 import ops
+    from dynquant_b200.workloads import qwen3_moe_layer, seeded_routing
+
+    layer = qwen3_moe_layer("cuda", seed=9, bits_gate_up=3, bits_down=4, num_experts=16, hidden=512, inter=256, topk=4)
+    gate_up = layer.gate_up.rows(4 * 512, 12 * 512)
+    down = layer.down.rows(4 * 512, 12 * 512)
+    ids, w = seeded_routing(tokens, 16, 4, seed=tokens)
+    x = torch.randn(tokens, 512, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    local = torch.where((ids >= 4) & (ids < 12), ids - 4, torch.full_like(ids, -1)).to(torch.int32)
+    want = ops.moe_gemv(x, local.cuda(), w.cuda(), gate_up, down, num_experts=8, out_dtype=torch.float32)
+    got = ops.moe_gemv(x, ids.to(torch.int32).cuda(), w.cuda(), gate_up, down, num_experts=8, out_dtype=torch.float32,
+                       first_expert=4)
+    assert torch.equal(got, want) and bool(want.abs().max() > 0)
