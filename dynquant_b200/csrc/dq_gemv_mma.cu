@@ -540,7 +540,33 @@ int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int s
     DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     int per_sm = 0;
     DQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, stream::kThreads, smem));
-    const int grid = std::min(static_cast<int>(ceil_div(tiles, stream::kWarps)), std::max(1, per_sm) * dev.sm_count);
+    const int resident = std::max(1, per_sm) * dev.sm_count;
+    int grid = std::min(static_cast<int>(ceil_div(tiles, stream::kWarps)), resident);
+    // Strided tiles unless that leaves the busiest SM well above the average.  Several rounds:
+    // with f = the fraction of CTAs that get one round more, an SM holds per_sm * f of them on
+    // average and ceil(per_sm * f) at worst, each worth a round of kWarps tiles -- runs when that
+    // excess is more than 3 % of an SM's share.  A single round that does not fill the machine
+    // (fewer CTAs than fit): whole CTAs of kWarps tiles land unevenly on the SMs (20,480 rows:
+    // 160 CTAs on 148 SMs, 16 tiles on some against 8.6 on average) -- then every resident CTA
+    // slot gets a run of a few tiles instead.
+    stream::Params q = p;
+    {
+      const int64_t per_round = static_cast<int64_t>(grid) * stream::kWarps;
+      const int64_t rounds = ceil_div(tiles, per_round);
+      const double average = static_cast<double>(tiles) / dev.sm_count;
+      if (rounds > 1) {
+        const double f = static_cast<double>(ceil_div(tiles - (rounds - 1) * per_round, stream::kWarps)) / grid;
+        const double held = std::max(1, per_sm);
+        const double excess = (std::ceil(held * f - 1e-9) - held * f) * stream::kWarps;
+        q.runs = excess > 0.03 * average ? 1 : 0;
+      } else if (grid < resident && ceil_div(grid, dev.sm_count) * stream::kWarps > 1.10 * average) {
+        q.runs = 1;
+        grid = std::min(tiles, resident);
+      }
+      const int forced = tuning_int("DQ_B200_STREAM_RUNS", -1);
+      if (forced == 0) q.runs = 0, grid = std::min(static_cast<int>(ceil_div(tiles, stream::kWarps)), resident);
+      if (forced == 1) q.runs = 1;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
     cfg.blockDim = dim3(stream::kThreads);
@@ -551,7 +577,7 @@ int32_t launch_stream(const GemvArgs& a, const DeviceInfo& dev, int tiles, int s
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
+    DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, q));
     DQ_CHECK_LAUNCH("gemv");
     note_kernel("gemv_mma_stream_kernel");
     return DQ_OK;

@@ -116,6 +116,7 @@ struct Params {
   int tiles;        // ceil(rows / 16)
   int m_stride_u4;  // uint4 per activation row of the staged B buffer
   uint32_t magic;   // a parameter so it stays a register operand of the decode
+  int runs;         // 1: every CTA takes a contiguous run of tiles; 0: tiles strided over the grid
   peerpush::Push push;  // enabled: the output rows also go to every rank's window (dq_peer_push.cuh)
 };
 
@@ -152,14 +153,17 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
   const uint32_t magic = p.magic;
   const bool has_off = a.offsets != nullptr;
   const int nblocks = p.steps / P;
-  // A CTA takes a contiguous run of row tiles, the runs as equal as the tile count allows (+-1),
-  // its warps interleaved over the run: what every SM streams is then equal to within a tile per
-  // CTA, where a stride over the whole grid left some SMs a full round of tiles more than others
-  // (248,320 rows on 444 CTAs: 14 against 13 rounds, 7 % of the launch).
-  const int tile_lo = static_cast<int>(static_cast<int64_t>(p.tiles) * blockIdx.x / gridDim.x);
-  const int tile_end = static_cast<int>(static_cast<int64_t>(p.tiles) * (blockIdx.x + 1) / gridDim.x);
-  constexpr int tile_stride = kWarps;
-  const int first_tile = tile_lo + warp;
+  // Two ways to deal the row tiles.  Strided (tile = CTA * warps + warp, + grid * warps, ...): the
+  // whole grid moves through the matrix as one window, which the memory system likes best (4-bit
+  // 262,144 rows: 80.1 % against 78.7 %), but a tile count that is not a multiple of the grid's
+  // warps leaves some SMs a full round more than others (248,320 rows on 444 CTAs: 14 against 13
+  // rounds, 7 % of the launch).  Runs (p.runs): a CTA takes a contiguous run of tiles, the runs
+  // equal to within a tile, its warps interleaved over the run.  The host picks per launch.
+  const bool runs = p.runs != 0;
+  const int tile_lo = runs ? static_cast<int>(static_cast<int64_t>(p.tiles) * blockIdx.x / gridDim.x) : 0;
+  const int tile_end = runs ? static_cast<int>(static_cast<int64_t>(p.tiles) * (blockIdx.x + 1) / gridDim.x) : p.tiles;
+  const int tile_stride = runs ? kWarps : static_cast<int>(gridDim.x) * kWarps;
+  const int first_tile = runs ? tile_lo + warp : static_cast<int>(blockIdx.x) * kWarps + warp;
 
   const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * C::UNIT;
   const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * C::META_BYTES;
@@ -383,11 +387,19 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
   }
   cp_async_wait<0>();
   if constexpr (PUSH) {
-    // This CTA took the row tiles [tile_lo, tile_end): copy their rows, as stored, to every window.
+    // Copy this CTA's rows, as stored, to every window: one run of tiles, or runs of kWarps tiles
+    // at the grid's stride.
     // (Every thread reads the epoch itself: no static shared memory, which would cost the third CTA per SM.)
     const unsigned int epoch = peerpush::next_epoch(p.push);
     __syncthreads();  // the output stores above are visible to the whole CTA
-    peerpush::push_rows(p.push, a, epoch, tile_lo * kTileRows, min(tile_end * kTileRows, a.rows), tid, kThreads);
+    if (runs) {
+      peerpush::push_rows(p.push, a, epoch, tile_lo * kTileRows, min(tile_end * kTileRows, a.rows), tid, kThreads);
+    } else {
+      constexpr int kRun = kWarps * kTileRows;
+      for (int row = static_cast<int>(blockIdx.x) * kRun; row < a.rows; row += static_cast<int>(gridDim.x) * kRun) {
+        peerpush::push_rows(p.push, a, epoch, row, min(row + kRun, a.rows), tid, kThreads);
+      }
+    }
     __syncthreads();
     if (tid < kWarp) peerpush::arrive(p.push, epoch, gridDim.x, tid);
   }
