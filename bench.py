@@ -25,9 +25,12 @@ fraction of the roofline at 1, 8 and 64 tokens) and ``config3`` (the Qwen3-14B-
 shaped linear set of the third configuration).
 
 Under torchrun (N > 1) the modules whose per-rank slab is still large (the
-lm_head) are column-sharded over the ranks and their outputs all-gathered over
-NCCL; small modules are computed by every rank; ``value`` is whole-job, and the
-line says whether the gathered output equals the unsharded result.
+lm_head) are column-sharded over the ranks and their outputs all-gathered by the
+producing launch itself over peer memory (``--exchange fused``; ``peer``: the
+library's exchange kernels, ``nccl``: NCCL calls); small modules are computed by
+every rank; ``value`` is whole-job, and the line says whether the gathered
+output equals the unsharded result.  The ``config3`` block shards every module
+and the ``moe`` block places the experts over the ranks.
 """
 
 from __future__ import annotations
