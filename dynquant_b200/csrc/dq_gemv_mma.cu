@@ -660,7 +660,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
   constexpr size_t kSmemPerSm = 228 * 1024, kCtaReserve = 1024;
   int ctas_by_registers = 3;  // which build of the kernel: see gemv_mma_tile_kernel
   struct Shape {
-    int kw = 0, ch = 0, nb = 0, per_sm = 0, ipc = 0;
+    int kw = 0, ch = 0, nb = 0, per_sm = 0, ipc = 0, sb = 0;
     size_t smem = 0;
   };
   const bool g64 = a0.group_values == kStepValues / 2;
@@ -686,9 +686,30 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     const int spw = steps / kw;
     const bool wide = kw < tilek::kWarps;
     const size_t stage = static_cast<size_t>(ch) * 2 * (4 * max_bits) * tilek::kThreads + ch * gps * 2 * tilek::kThreads;
-    const size_t fixed = tilek::kRedFloats * 4 +
-                         (max_bits == 8 ? tilek::stage_bytes<8>(a0.m, steps, spw, kw, wide, a0.in_features, gps)
-                                        : tilek::stage_bytes<4>(a0.m, steps, spw, kw, wide, a0.in_features, gps));
+    auto fixed_with = [&](int sb) {
+      return tilek::kRedFloats * 4 +
+             (max_bits == 8 ? tilek::stage_bytes<8>(a0.m, steps, spw, kw, wide, a0.in_features, gps, sb)
+                            : tilek::stage_bytes<4>(a0.m, steps, spw, kw, wide, a0.in_features, gps, sb));
+    };
+    size_t fixed = fixed_with(spw);
+    int sb = spw;
+    // Per-warp staging whose whole slices do not fit beside a two-stage ring (many activation rows
+    // x a long reduction axis): the slices go through the staging area block by block -- the
+    // longest block with which two CTAs still fit on an SM, else the longest that fits at all.
+    if (!wide && 2 * stage + fixed > static_cast<size_t>(dev.max_smem_optin)) {
+      if (ch != 2) return sh;  // (the block-by-block kernel is built for stages of two steps only)
+      const size_t rooms[2] = {kSmemPerSm / 2 - kCtaReserve, static_cast<size_t>(dev.max_smem_optin)};
+      for (int r = 0; r < 2 && sb == spw; ++r) {
+        for (int cand = spw - ch; cand >= ch; cand -= ch) {
+          if (spw % cand == 0 && 2 * stage + fixed_with(cand) <= rooms[r]) {
+            sb = cand;
+            break;
+          }
+        }
+      }
+      if (sb == spw) return sh;
+      fixed = fixed_with(sb);
+    }
     const int stages = spw / ch;
     int nb = one_shot ? stages : std::min(stages * 2, ch == 4 ? 2 : 4);
     if (force_nb > 0 && !one_shot) nb = force_nb;
@@ -702,6 +723,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     sh.kw = kw;
     sh.ch = ch;
     sh.nb = nb;
+    sh.sb = sb;
     sh.smem = smem;
     sh.per_sm = std::min<int>(ctas_by_registers, static_cast<int>(kSmemPerSm / (smem + kCtaReserve)));
     if (force_per_sm > 0) sh.per_sm = std::min(sh.per_sm, force_per_sm);
@@ -763,6 +785,7 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
   L.rw = rw;
   L.kw = kw;
   L.spw = spw;
+  L.sb = pick.sb;
   L.nb = pick.nb;
   L.wide_stage = wide ? 1 : 0;
   L.meta_bf16 = a0.meta_dtype == DQ_BF16 ? 1 : 0;
@@ -817,6 +840,10 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
     if (ch == 4) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 4, false, N>) : run(tilek::gemv_mma_tile_kernel<false, 4, false, N>);
     return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2, false, N>) : run(tilek::gemv_mma_tile_kernel<false, 2, false, N>);
   };
+  if (pick.sb < spw) {  // slices staged block by block: its own build (two CTAs per SM, stages of two steps)
+    if (g64) return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2, true, 2, true>) : run(tilek::gemv_mma_tile_kernel<false, 2, true, 2, true>);
+    return xbf ? run(tilek::gemv_mma_tile_kernel<true, 2, false, 2, true>) : run(tilek::gemv_mma_tile_kernel<false, 2, false, 2, true>);
+  }
   if (ctas_by_registers == 3) return dispatch(std::integral_constant<int, 3>{});
   return dispatch(std::integral_constant<int, 2>{});
 }
@@ -833,12 +860,9 @@ bool mma_path_supports(const GemvArgs& a, int bits) {
   const auto addr = reinterpret_cast<uintptr_t>(a.packed);
   const int align = bits == 2 ? 8 : (bits == 3 ? 4 : 16);
   if (addr % align != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % align != 0) return false;
-  const DeviceInfo* dev = device_info();
-  if (dev == nullptr) return false;
-  int stride = 0;
-  const int steps = a.words_per_row / (4 * bits);
-  const size_t smem = mma_smem_bytes(a.m, steps, bits == 8 ? 32 : 16, 1, kMaxWarps, &stride);
-  return smem <= static_cast<size_t>(dev->max_smem_optin);
+  // (Whether the staged activation fits shared memory is each kernel's own question: the tiled
+  // kernel passes long slices through its staging area block by block, the others refuse.)
+  return device_info() != nullptr;
 }
 
 int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken,
@@ -928,6 +952,7 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const 
   p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
   const int aregs = bits == 8 ? 32 : 16;
   const size_t smem = mma_smem_bytes(a.m, p.steps, aregs, p.rw, p.kw, &p.m_stride_u4);
+  if (smem > static_cast<size_t>(dev->max_smem_optin)) return DQ_ERR_UNSUPPORTED;  // the caller halves the rows
   const int threads = p.rw * p.kw * kWarp;
   switch (bits) {
     case 2:

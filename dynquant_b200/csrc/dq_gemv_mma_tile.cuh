@@ -55,6 +55,8 @@ struct Launch {
   int steps;       // padded K / 128 (the jobs share the activation, hence K)
   int rw, kw;      // rw * kw == kWarps
   int spw;         // steps per slice = steps / kw, a multiple of CH
+  int sb;          // per-warp staging (kw == kWarps): steps of the slice staged at a time (spw: the whole slice;
+                   // less: the slice goes through the warp's staging area block by block, see tile_body)
   int nb;          // ring stages, 1..kMaxRing
   int wide_stage;  // 1: the CTA stages the whole activation; 0: every warp its own slice
   int meta_bf16;
@@ -75,14 +77,15 @@ struct Ring {
 // `gps`: groups per 128-value step (1, or 2 with 64-value groups): the sums are per group.
 template <int BITS>
 __host__ __device__ inline size_t stage_bytes(int m, int steps, int spw, int kw, bool wide, int in_features,
-                                              int gps = 1) {
+                                              int gps = 1, int sb = 0) {
   const int na = BITS == 8 ? 32 : 16;
   if (wide) {
     const size_t stride = static_cast<size_t>(steps) * na + 4;
     return (m * stride + na) * 16 + static_cast<size_t>(steps) * 64 * gps + 16;
   }
-  const size_t stride = static_cast<size_t>(spw) * na + 4;
-  return static_cast<size_t>(kw) * (spw * 256 + (m * stride + na) * 16 + spw * 64 * gps);
+  if (sb <= 0) sb = spw;
+  const size_t stride = static_cast<size_t>(sb) * na + 4;
+  return static_cast<size_t>(kw) * (sb * 256 + (m * stride + na) * 16 + sb * 64 * gps);
 }
 
 __device__ __forceinline__ void wait_pending(int n) {
@@ -122,7 +125,10 @@ __device__ __forceinline__ void read_lane_words(const unsigned char* src, uint32
   }
 }
 
-template <int BITS, bool XBF16, int CH, bool G64>
+// KBLK: per-warp staging goes through the staging area block by block (L.sb < L.spw).  A template
+// parameter, not a test of L.sb: the three-CTA build of the plain kernel sits at its register
+// limit, and the extra state in its chunk loop cost it a few hundred bytes of spills.
+template <int BITS, bool XBF16, int CH, bool G64, bool KBLK = false>
 __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigned char* smem) {
   // 64-value groups: at 2, 4 and 8 bits a lane owns 16 values of each group (HALVES: the two
   // halves of its registers are the two groups).  3-bit half units do not start on words, so
@@ -159,7 +165,8 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
   unsigned char* area = reinterpret_cast<unsigned char*>(red + kRedFloats);
 
   // staging area: CTA-wide (indexed by global step) or this warp's own (indexed within its slice)
-  const int span = wide ? L.steps : spw;
+  const int sb = KBLK ? L.sb : spw;  // (per-warp staging only)
+  const int span = wide ? L.steps : sb;
   const int m_stride_u4 = span * NA + 4;
   unsigned short* raw;
   uint4* xb;
@@ -170,9 +177,9 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
     xneg = xsum + span * 8 * GPS;
     raw = nullptr;  // CTA-wide staging reads the activation straight from global memory
   } else {
-    unsigned char* mine = area + kwi * (spw * 256 + (a.m * m_stride_u4 + NA) * 16 + spw * 64 * GPS);
+    unsigned char* mine = area + kwi * (sb * 256 + (a.m * m_stride_u4 + NA) * 16 + sb * 64 * GPS);
     raw = reinterpret_cast<unsigned short*>(mine);
-    xb = reinterpret_cast<uint4*>(mine + spw * 256);
+    xb = reinterpret_cast<uint4*>(mine + sb * 256);
     xsum = reinterpret_cast<float*>(xb + a.m * m_stride_u4 + NA);
     xneg = xsum + span * 8 * GPS;
   }
@@ -281,7 +288,7 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
     if (wide) {
       stage_zero_fill<BITS, G64>(a.m, L.steps, m_stride_u4, xb, xsum, xneg, tid, kThreads);
     } else {
-      stage_zero_fill<BITS, G64>(a.m, spw, m_stride_u4, xb, xsum, xneg, lane, kWarp);
+      stage_zero_fill<BITS, G64>(a.m, sb, m_stride_u4, xb, xsum, xneg, lane, kWarp);
     }
   }
   pdl_wait_prior_grid();
@@ -289,8 +296,12 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
     stage_activation<BITS, XBF16, G64>(a, L.steps, m_stride_u4, xb, xsum, xneg, tid, kThreads, nullptr, prefilled);
     __syncthreads();
   } else {
-    stage_warp_slice<BITS, XBF16, G64>(a, s_begin, spw, m_stride_u4, raw, xb, xsum, xneg, lane, prefilled);
+    stage_warp_slice<BITS, XBF16, G64>(a, s_begin, sb, m_stride_u4, raw, xb, xsum, xneg, lane, prefilled);
   }
+  // A slice longer than the staging area (many activation rows x a long reduction axis, which
+  // staged whole would not fit shared memory) passes through it `sb` steps at a time: the warp
+  // re-stages at every block boundary -- its own area, so a warp barrier is all it takes.
+  const bool blocked = KBLK && !wide && sb < spw;
 
   const unsigned char* wslot = ring_w_mine;  // ring slot being consumed
   const unsigned char* mslot = ring_m_quad;
@@ -304,6 +315,13 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
     const float* xs_chunk = xsum_w;
     const float* xn_chunk = xneg_w;
     for (int chunk = 0; chunk < nchunks; ++chunk) {
+      if (KBLK && blocked && (chunk * CH) % sb == 0 && (chunk != 0 || item != cta)) {
+        __syncwarp();  // every lane is done reading the block that is about to be replaced
+        stage_warp_slice<BITS, XBF16, G64>(a, s_begin + chunk * CH, sb, m_stride_u4, raw, xb, xsum, xneg, lane, prefilled);
+        bchunk = xb_lane;
+        xs_chunk = xsum_w;
+        xn_chunk = xneg_w;
+      }
       wait_pending(nb - 1);  // groups are consumed in issue order: all but the nb-1 youngest are done
       __syncwarp();          // copies of other lanes (units, the quad's metadata) are visible
       if (live) {
@@ -474,7 +492,7 @@ __device__ __forceinline__ void tile_body(const Launch& L, const Job& J, unsigne
 // is the faster build; three (80 registers, a few spills) exists for launches whose single
 // wave needs the third CTA per SM -- the alternative there is a coarser slicing of the
 // reduction axis, which costs more than the spills.
-template <bool XBF16, int CH, bool G64, int CTAS>
+template <bool XBF16, int CH, bool G64, int CTAS, bool KBLK = false>
 __global__ void __launch_bounds__(kThreads, CTAS) gemv_mma_tile_kernel(const __grid_constant__ Launch L) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int j = 0;
@@ -485,16 +503,16 @@ __global__ void __launch_bounds__(kThreads, CTAS) gemv_mma_tile_kernel(const __g
   const Job& J = L.job[j];
   switch (J.bits) {
     case 2:
-      tile_body<2, XBF16, CH, G64>(L, J, smem_raw);
+      tile_body<2, XBF16, CH, G64, KBLK>(L, J, smem_raw);
       break;
     case 3:
-      tile_body<3, XBF16, CH, G64>(L, J, smem_raw);
+      tile_body<3, XBF16, CH, G64, KBLK>(L, J, smem_raw);
       break;
     case 4:
-      tile_body<4, XBF16, CH, G64>(L, J, smem_raw);
+      tile_body<4, XBF16, CH, G64, KBLK>(L, J, smem_raw);
       break;
     default:
-      tile_body<8, XBF16, CH, G64>(L, J, smem_raw);
+      tile_body<8, XBF16, CH, G64, KBLK>(L, J, smem_raw);
       break;
   }
   if (L.push.enabled) {
