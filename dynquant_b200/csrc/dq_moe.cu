@@ -52,6 +52,7 @@ struct MoeArgs {
   void* out;                // gate_up: h [assignments, inter] act dtype; down: d [assignments, hidden] fp32
   const int32_t* ids;       // [assignments] expert of every (token, slot), minus first_expert
   int first_expert;         // ids are global; this call holds experts [first_expert, first_expert + num_experts)
+  int by_assignment;        // 1: slot s IS assignment s (few tokens: no routing to work out, an expert may be read twice)
   int assignments, num_experts;
   int act_dtype, meta_dtype;
   int topk;
@@ -152,6 +153,16 @@ __global__ void __launch_bounds__(kMoeThreads, CTAS) moe_grouped_kernel(const __
   pdl_launch_dependents();
 
   // ---- routing, by every CTA for itself ----
+  if (a.by_assignment) {
+    // few tokens: a slot per assignment, nothing to count or rank
+    if (tid == 0) {
+      const int mine = __ldcg(a.ids + slot) - a.first_expert;
+      misc[0] = (mine >= 0 && mine < a.num_experts) ? mine : -1;
+      misc[1] = 1;
+      list[0] = slot;
+    }
+    __syncthreads();
+  } else {
   for (int i = tid; i < a.num_experts; i += kMoeThreads) cnt[i] = 0;
   for (int i = tid; i < a.assignments; i += kMoeThreads) ids_s[i] = __ldcg(a.ids + i) - a.first_expert;
   if (tid == 0) misc[0] = -1;
@@ -177,6 +188,7 @@ __global__ void __launch_bounds__(kMoeThreads, CTAS) moe_grouped_kernel(const __
     }
   }
   __syncthreads();
+  }
   const int e = misc[0];
   if (e < 0) return;  // fewer active experts than slots
   const int count = misc[1];
@@ -285,6 +297,7 @@ __global__ void __launch_bounds__(kMoeThreads, CTAS) moe_grouped_kernel(const __
   for (int i = 0; i < nb; ++i) prefetch_stage();
 
   // ---- the expert's assignments in ascending order (so results do not depend on timing) ----
+  if (!a.by_assignment) {
   for (int base = 0; base < a.assignments; base += kMoeThreads) {
     const int i = base + tid;
     const bool mine = i < a.assignments && ids_s[i] == e;
@@ -302,6 +315,7 @@ __global__ void __launch_bounds__(kMoeThreads, CTAS) moe_grouped_kernel(const __
       for (int k = 0; k < upto; ++k) rank += ballots[k];
       if (rank < DQ_MOE_MAX_TOKENS) list[rank] = i;
     }
+  }
   }
 
   if (!GATE_UP) {
@@ -810,7 +824,8 @@ int32_t launch_grouped(MoeArgs a, int slots, cudaStream_t stream) {
   const int tiles = (a.rows + 15) / 16;
   const int items = static_cast<int>(ceil_div(tiles, a.rw));
   const double e_count = a.num_experts;
-  const double active = std::max(1.0, e_count * (1.0 - std::pow(1.0 - 1.0 / e_count, a.assignments)));
+  const double active = a.by_assignment ? static_cast<double>(a.assignments)
+                                        : std::max(1.0, e_count * (1.0 - std::pow(1.0 - 1.0 / e_count, a.assignments)));
   const int steps_per_item = (GATE_UP ? 2 : 1) * a.spw;
   const int items_per_cta = std::max(1, static_cast<int>(ceil_div(12, steps_per_item)));
   const int one_wave = static_cast<int>(std::ceil(static_cast<double>(ctas) * dev->sm_count / active));
@@ -1033,7 +1048,11 @@ int32_t dq_moe_gemv_shard(const void* x, int32_t x_dtype, int64_t tokens, const 
   a.act = x;
   a.out = base + lay.h;
   a.rows = static_cast<int>(inter);
-  if (const int32_t rc = dq::launch_bank<true>(*gate_up, g_gu, a, slots, s)) return rc;
+  // Few tokens (the threshold of the by-token down projection): a slot per assignment, so no CTA
+  // has to work out the routing before it can request its weights.
+  a.by_assignment = tokens <= dq::tuning_int("DQ_B200_MOE_BY_TOKEN_MAX", 4) ? 1 : 0;
+  if (const int32_t rc = dq::launch_bank<true>(*gate_up, g_gu, a, a.by_assignment ? assignments : slots, s)) return rc;
+  a.by_assignment = 0;
   // Few tokens: the down projection token by token with the combine folded in (two launches a
   // layer instead of three).  Measured on B200, Qwen3-30B-A3B shape: see launch_down_by_token.
   {
