@@ -50,6 +50,12 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     """``tuning``: compile in the launch-shape overrides (``DQ_B200_*`` environment variables read
     at every launch) that the sweeps behind the built-in heuristics used; not for normal use."""
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    # The objects remember which kind of build they are: switching between the normal and the
+    # tuning build recompiles everything (time stamps alone would keep the other kind's objects).
+    stamp = OBJ_DIR / "build_kind.txt"
+    kind = "tuning" if tuning else "normal"
+    if not stamp.exists() or stamp.read_text().strip() != kind:
+        force = True
     headers = sorted(CSRC.glob("*.cuh")) + sorted(INCLUDE.glob("*.h")) + [Path(__file__)]
     sources = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
     jobs = []
@@ -73,6 +79,7 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     if jobs:
         with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
             list(pool.map(run, jobs))
+    stamp.write_text(kind + "\n")
     objs = [OBJ_DIR / (s.stem + ".o") for s in sources]
     if jobs or force or _stale(LIB_PATH, objs):
         run([nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs),
