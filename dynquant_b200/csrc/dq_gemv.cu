@@ -667,12 +667,28 @@ int32_t dq_gemv_shards_rows(const void* x, int32_t x_dtype, int64_t m, const dq_
     live = 0;
     return DQ_OK;
   };
+  // A shard whose geometry the many-rows kernel takes goes through it whole: one pass over its
+  // weights for all the rows.  The others run as row chunks.
+  constexpr int kMaxShards = 64;
+  bool whole[kMaxShards] = {};
+  if (!dq::force_general() && dq::mma_enabled_for_rows()) {
+    int64_t col0 = 0;
+    for (int i = 0; i < num_shards; ++i) {
+      if (i < kMaxShards && shards[i].rows > 0) {
+        dq_geometry g;
+        dq_resolve_geometry("gemv_shards_rows", &shards[i], &g);
+        const dq::GemvArgs all = dq::make_args(x, x_dtype, m, shards[i], g, bias, out, out_stride, col0, out_dtype);
+        if (const int32_t rc = dq::launch_gemv_rows(all, shards[i].bits, s, &whole[i])) return rc;
+      }
+      col0 += shards[i].rows;
+    }
+  }
   int64_t row0 = 0;
   for (int64_t c = 0; c < chunks; ++c) {
     const int64_t rows_here = base + (c < longer ? 1 : 0);
     int64_t col0 = 0;
     for (int i = 0; i < num_shards; ++i) {
-      if (shards[i].rows > 0) {
+      if (shards[i].rows > 0 && !(i < kMaxShards && whole[i])) {
         if (live == kBatch || (live > 0 && args[0].m != rows_here)) {
           if (const int32_t rc = flush()) return rc;
         }

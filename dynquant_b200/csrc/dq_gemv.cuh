@@ -38,6 +38,14 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const 
 int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken,
                               const peerpush::Push* push = nullptr);
 
+// 9..64 activation rows against one matrix in one pass over the weights (dq_gemv_rows.cu).  *taken
+// stays false, nothing launched, when the matrix or the activation does not qualify.
+int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool* taken);
+// False when DQ_B200_GEMV_PATH=simt forces the SIMT kernels.
+bool mma_enabled_for_rows();
+// False when DQ_B200_NO_PDL drops the programmatic-dependent-launch attribute.
+bool pdl_enabled_for_rows();
+
 #ifdef __CUDACC__
 __device__ __forceinline__ void store_out(const GemvArgs& a, int m, int row, float v) {
   const int64_t col = a.out_col0 + row;

@@ -850,6 +850,9 @@ int32_t try_tile(const GemvArgs* jobs, const int* bits, int n, const DeviceInfo&
 
 }  // namespace
 
+bool mma_enabled_for_rows() { return mma_enabled(); }
+bool pdl_enabled_for_rows() { return pdl_enabled(); }
+
 bool mma_path_supports(const GemvArgs& a, int bits) {
   if (!mma_enabled()) return false;
   if (a.x_dtype != DQ_BF16 && a.x_dtype != DQ_F16) return false;

@@ -1,0 +1,373 @@
+// 9..64 activation rows against one packed matrix in ONE pass over the weights.
+//
+// The GEMV kernels take at most eight activation rows: the eight columns of one m16n8k16
+// accumulator.  More rows used to mean more passes (row chunks of eight, each decoding the
+// weights again, the later ones from L2).  Here a warp decodes the fragments of a 16-row x
+// 128-value step ONCE and feeds them to up to eight column blocks of eight activation rows each
+// -- the decode, which bounds the GEMV kernels, is amortised over the blocks, and the tensor
+// pipe becomes the busy unit, as it should in a small-batch matrix product.
+//
+//   CTA       8 warps = 8 row tiles of 16 weight rows; warp w streams its tile's rows over the
+//             whole reduction axis through a private cp.async ring (the streaming kernel's
+//             plumbing: blocks of P steps, no barrier for weights).
+//   x         too large to stage whole (64 rows x 4096 values in fragment order: 512 KB), so it
+//             passes through shared memory in blocks of P steps, shared by the CTA's warps and
+//             double buffered: all threads stage block b+1 (unit-per-lane staging, 16-bit
+//             aligned activations only), every warp computes block b, one CTA barrier per block.
+//   out       [m, rows] as the GEMV kernels write it; accumulation in fp32, scale and offset
+//             applied per step, one rounding.
+//
+// Replaces, for this band of row counts, the reference's dequantize + dense matmul
+// (runtime/ops.py:205-231): same result up to the summation order.  The host (dq_gemv.cu,
+// dq_gemv_shards_rows) falls back to row chunks when a matrix does not qualify.
+#include <algorithm>
+
+#include "dq_gemv.cuh"
+#include "dq_gemv_mma_stream.cuh"
+#include "dq_mma_plan.cuh"
+#include "dq_mma_stage.cuh"
+
+namespace dq {
+namespace rowsk {
+
+constexpr int kWarps = stream::kWarps;
+constexpr int kThreads = stream::kThreads;
+
+struct Params {
+  int steps;        // padded K / 128, a multiple of P
+  int tiles;        // ceil(rows / 16)
+  int m_stride_u4;  // uint4 per activation row of one staged block: P * NA + 4
+  int meta_bf16;
+  uint32_t magic;
+};
+
+// Bytes of one column block's staging region for one x block: 8 rows of fragments, the zero
+// block that lanes of absent rows read, and the two sums per (step, row).
+template <int BITS>
+__host__ __device__ constexpr size_t region_bytes() {
+  using C = stream::Cfg<BITS>;
+  constexpr int NA = BITS == 8 ? 32 : 16;
+  return (static_cast<size_t>(8) * (C::P * NA + 4) + NA) * 16 + static_cast<size_t>(C::P) * 8 * 4 * 2;
+}
+
+template <int BITS>
+size_t smem_bytes(int mb) {
+  return stream::Cfg<BITS>::RING_BYTES + 2 * static_cast<size_t>(mb) * region_bytes<BITS>();
+}
+
+template <int BITS, bool XBF16, int MB>
+__global__ void __launch_bounds__(kThreads, MB <= 2 ? 2 : 1) gemv_rows_kernel(const GemvArgs a, const Params p) {
+  using Plan = MmaPlan<BITS>;
+  using C = stream::Cfg<BITS>;
+  constexpr int P = C::P;
+  constexpr int NB = C::NB;
+  constexpr int NA = Plan::kARegs;
+  constexpr int QU = NA / 4;
+  constexpr int STEP_WORDS = 4 * BITS;
+  constexpr int STEP_BYTES = STEP_WORDS * 4;
+  constexpr size_t REGION = region_bytes<BITS>();
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned char* ring_w = smem_raw;
+  unsigned char* ring_m = ring_w + NB * C::BLOCK_BYTES * kThreads;
+  unsigned char* xarea = ring_m + NB * C::META_BYTES * kThreads;  // [2 buffers][MB regions]
+
+  const int tid = threadIdx.x;
+  const int lane = tid & (kWarp - 1);
+  const int warp = tid >> 5;
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const uint32_t magic = p.magic;
+  const bool mbf = p.meta_bf16 != 0;
+  const bool has_off = a.offsets != nullptr;
+  const int nblocks = p.steps / P;
+  const int tile = blockIdx.x * kWarps + warp;
+  const bool live = tile < p.tiles;
+  const int mbs = (a.m + 7) / 8;  // column blocks that have rows (the kernel is built for 2, 4 or 8)
+
+  const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * C::UNIT;
+  const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * C::META_BYTES;
+  const unsigned char* ring_w_mine = ring_w + tid * C::UNIT;
+  const unsigned char* ring_m_quad = ring_m + (tid & ~3) * C::META_BYTES;
+
+  pdl_launch_dependents();
+
+  // ---- prefetch cursor over the blocks of this warp's tile (running pointers, immediate offsets) ----
+  constexpr int PIECES = 2 * C::UNIT;
+  constexpr int PER_ROW = C::UNIT / 4;
+  constexpr int NSRC = (PIECES + kWarp - 1) / kWarp;
+  const unsigned char* pf_src[2][NSRC];
+  bool pf_lane[NSRC];
+#pragma unroll
+  for (int i = 0; i < NSRC; ++i) pf_lane[i] = (PIECES % kWarp == 0) || (i * kWarp + lane < PIECES);
+  const unsigned short* pf_meta = nullptr;
+  if (live) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int i = 0; i < NSRC; ++i) {
+        const int piece = i * kWarp + lane;
+        const int pg = piece / PER_ROW;
+        const int part = piece - pg * PER_ROW;
+        const int row = min(tile * 16 + h * 8 + pg, a.rows - 1);
+        pf_src[h][i] = reinterpret_cast<const unsigned char*>(a.packed + static_cast<int64_t>(row) * a.words_per_row + part * 4);
+      }
+    }
+    const int ra = min(tile * 16 + g, a.rows - 1);
+    const int rb = min(tile * 16 + g + 8, a.rows - 1);
+    const unsigned short* arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
+    pf_meta = arr + static_cast<int64_t>((t & 2) ? rb : ra) * a.num_groups;
+  }
+  const bool meta_lane = has_off || (t & 1) == 0;
+  uint32_t pf_w = ring_w_s + lane * 16, pf_m = ring_m_s;
+  const uint32_t ring_w_end = ring_w_s + lane * 16 + NB * (C::BLOCK_BYTES * kThreads);
+  int pf_blk = 0;
+  auto prefetch_block = [&]() {
+    if (live && pf_blk < nblocks) {
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < NSRC; ++i) {
+            if (pf_lane[i]) {
+              stream::cp_async_n<16>(pf_w + (j * 2 + h) * (C::UNIT * kThreads) + i * (kWarp * 16), pf_src[h][i] + j * STEP_BYTES);
+            }
+          }
+        }
+      }
+      if (meta_lane) stream::cp_async_n<C::META_BYTES>(pf_m, pf_meta);
+      ++pf_blk;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int i = 0; i < NSRC; ++i) pf_src[h][i] += P * STEP_BYTES;
+      }
+      pf_meta += P;
+    }
+    pf_w += C::BLOCK_BYTES * kThreads;
+    pf_m += C::META_BYTES * kThreads;
+    if (pf_w == ring_w_end) {
+      pf_w -= NB * (C::BLOCK_BYTES * kThreads);
+      pf_m -= NB * (C::META_BYTES * kThreads);
+    }
+    stream::cp_async_commit();  // an empty group keeps the wait arithmetic uniform
+  };
+#pragma unroll
+  for (int i = 0; i < NB - 1; ++i) prefetch_block();
+
+  // ---- staging of one x block: thread groups of 32 * P threads take the column blocks in turn ----
+  constexpr int kGroupThreads = 32 * P;             // one (row, step, quad lane) task per thread: 8 * P * 4
+  constexpr int kGroups = kThreads / kGroupThreads;  // 2 (P = 4) or 4 (P = 2)
+  const int sg = tid / kGroupThreads, stid = tid - sg * kGroupThreads;
+  auto stage_block = [&](int blk, int buf) {
+    for (int cb = sg; cb < mbs; cb += kGroups) {
+      unsigned char* region = xarea + (static_cast<size_t>(buf) * MB + cb) * REGION;
+      uint4* xb = reinterpret_cast<uint4*>(region);
+      float* xsum = reinterpret_cast<float*>(xb + 8 * p.m_stride_u4 + NA);
+      float* xneg = xsum + P * 8;
+      GemvArgs sub = {};
+      sub.x = static_cast<const unsigned short*>(a.x) + static_cast<int64_t>(cb) * 8 * a.in_features;
+      sub.x_dtype = a.x_dtype;
+      sub.in_features = a.in_features;
+      sub.m = min(8, a.m - cb * 8);
+      // (rows that do not exist: their fragments are the zero block, which sits after row `m`)
+      stage_units<BITS, XBF16, false>(sub, blk * P, P, p.m_stride_u4, xb, xsum, xneg, stid, kGroupThreads, nullptr, false);
+    }
+  };
+
+  pdl_wait_prior_grid();
+  stage_block(0, 0);
+  __syncthreads();
+
+  float acc[MB][4];
+#pragma unroll
+  for (int cb = 0; cb < MB; ++cb) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[cb][i] = 0.0f;
+  }
+  const unsigned char* wslot = ring_w_mine;
+  const unsigned char* mslot = ring_m_quad;
+  const unsigned char* const wslot_end = ring_w_mine + NB * (C::BLOCK_BYTES * kThreads);
+  for (int blk = 0; blk < nblocks; ++blk) {
+    const int buf = blk & 1;
+    if (blk + 1 < nblocks) stage_block(blk + 1, buf ^ 1);  // (the barrier below publishes it)
+    __syncwarp();
+    prefetch_block();
+    stream::cp_async_wait<NB - 1>();
+    __syncwarp();
+    if (live) {
+      uint32_t mc[4][P / 2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (has_off || (i & 1) == 0) {
+          if constexpr (P == 4) {
+            const uint2 v = *reinterpret_cast<const uint2*>(mslot + i * C::META_BYTES);
+            mc[i][0] = v.x, mc[i][1] = v.y;
+          } else {
+            mc[i][0] = *reinterpret_cast<const uint32_t*>(mslot + i * C::META_BYTES);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+        uint32_t wa[BITS], wb[BITS];
+        stream::read_unit<BITS>(wslot + (j * 2 + 0) * (C::UNIT * kThreads), wa);
+        stream::read_unit<BITS>(wslot + (j * 2 + 1) * (C::UNIT * kThreads), wb);
+        uint32_t aa[NA], ab[NA];
+        decode_unit<BITS>(wa, magic, aa);
+        decode_unit<BITS>(wb, magic, ab);
+        unbias_fragments<XBF16, NA>(aa);
+        unbias_fragments<XBF16, NA>(ab);
+        auto meta_f32 = [&](int i) -> float {
+          const uint32_t reg = mc[i][j / 2];
+          if (mbf) return __uint_as_float((j & 1) ? (reg & 0xFFFF0000u) : (reg << 16));
+          const __half2 hh = *reinterpret_cast<const __half2*>(&reg);
+          return (j & 1) ? __high2float(hh) : __low2float(hh);
+        };
+        const float sc_a = meta_f32(0), sc_b = meta_f32(2);
+        const float of_a = has_off ? meta_f32(1) : 0.0f, of_b = has_off ? meta_f32(3) : 0.0f;
+#pragma unroll
+        for (int cb = 0; cb < MB; ++cb) {
+          if (cb >= mbs) continue;  // (uniform over the CTA)
+          const unsigned char* region = xarea + (static_cast<size_t>(buf) * MB + cb) * REGION;
+          const uint4* xb = reinterpret_cast<const uint4*>(region);
+          const float* xsum = reinterpret_cast<const float*>(xb + 8 * p.m_stride_u4 + NA);
+          const float* xneg = xsum + P * 8;
+          const int m_here = a.m - cb * 8;  // rows of this column block that exist (>= 1)
+          const uint4* bsrc = (g < m_here ? xb + g * p.m_stride_u4 + t + j * (QU * 4) : xb + min(m_here, 8) * p.m_stride_u4);
+          const int bstep = g < m_here ? 4 : 0;
+          float d[4];
+#pragma unroll
+          for (int q = 0; q < QU; ++q) {
+            const uint4 b = bsrc[q * bstep];
+            if (q == 0) {
+              mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
+            } else {
+              mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
+            }
+            mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
+          }
+          const float2 xs2 = *reinterpret_cast<const float2*>(xsum + j * 8 + 2 * t);
+          const float2 xn2 = *reinterpret_cast<const float2*>(xneg + j * 8 + 2 * t);
+          acc[cb][0] = fmaf(sc_a, d[0] + xn2.x, acc[cb][0]);
+          acc[cb][1] = fmaf(sc_a, d[1] + xn2.y, acc[cb][1]);
+          acc[cb][2] = fmaf(sc_b, d[2] + xn2.x, acc[cb][2]);
+          acc[cb][3] = fmaf(sc_b, d[3] + xn2.y, acc[cb][3]);
+          if (has_off) {
+            acc[cb][0] = fmaf(of_a, xs2.x, acc[cb][0]);
+            acc[cb][1] = fmaf(of_a, xs2.y, acc[cb][1]);
+            acc[cb][2] = fmaf(of_b, xs2.x, acc[cb][2]);
+            acc[cb][3] = fmaf(of_b, xs2.y, acc[cb][3]);
+          }
+        }
+      }
+    }
+    wslot += C::BLOCK_BYTES * kThreads;
+    mslot += C::META_BYTES * kThreads;
+    if (wslot == wslot_end) {
+      wslot = ring_w_mine;
+      mslot = ring_m_quad;
+    }
+    __syncthreads();  // block b+1 is staged; everyone is done with block b's buffer
+  }
+  stream::cp_async_wait<0>();
+  if (live) {
+    const int row_a = tile * 16 + g, row_b = row_a + 8;
+#pragma unroll
+    for (int cb = 0; cb < MB; ++cb) {
+      const int m0 = cb * 8 + 2 * t;
+      if (m0 < a.m) {
+        if (row_a < a.rows) store_out(a, m0, row_a, acc[cb][0]);
+        if (row_b < a.rows) store_out(a, m0, row_b, acc[cb][2]);
+      }
+      if (m0 + 1 < a.m) {
+        if (row_a < a.rows) store_out(a, m0 + 1, row_a, acc[cb][1]);
+        if (row_b < a.rows) store_out(a, m0 + 1, row_b, acc[cb][3]);
+      }
+    }
+  }
+}
+
+template <int BITS, int MB>
+int32_t launch_mb(const GemvArgs& a, const Params& p, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
+  const size_t smem = smem_bytes<BITS>(MB);
+  if (smem > static_cast<size_t>(dev.max_smem_optin)) return DQ_OK;  // not taken
+  auto run = [&](auto kernel) -> int32_t {
+    DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(p.tiles, kWarps)));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream_h;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled_for_rows() ? 1 : 0;
+    DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
+    DQ_CHECK_LAUNCH("gemv rows");
+    note_kernel("gemv_rows_kernel");
+    *taken = true;
+    return DQ_OK;
+  };
+  return a.x_dtype == DQ_BF16 ? run(gemv_rows_kernel<BITS, true, MB>) : run(gemv_rows_kernel<BITS, false, MB>);
+}
+
+template <int BITS>
+int32_t launch_bits(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
+  using C = stream::Cfg<BITS>;
+  const int steps = a.words_per_row / (4 * BITS);
+  if (steps % C::P != 0 || a.num_groups != steps) return DQ_OK;
+  const auto align = static_cast<uintptr_t>(C::META_BYTES);
+  if (reinterpret_cast<uintptr_t>(a.scales) % align != 0 || reinterpret_cast<uintptr_t>(a.offsets) % align != 0 ||
+      (static_cast<int64_t>(a.num_groups) * 2) % C::META_BYTES != 0) {
+    return DQ_OK;
+  }
+  Params p = {};
+  p.steps = steps;
+  p.tiles = static_cast<int>(ceil_div(a.rows, 16));
+  p.m_stride_u4 = C::P * (BITS == 8 ? 32 : 16) + 4;
+  p.meta_bf16 = a.meta_dtype == DQ_BF16 ? 1 : 0;
+  p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
+  const int mb = static_cast<int>(ceil_div(a.m, 8));
+  if (mb <= 2) return launch_mb<BITS, 2>(a, p, dev, stream_h, taken);
+  if (mb <= 4) return launch_mb<BITS, 4>(a, p, dev, stream_h, taken);
+  return launch_mb<BITS, 8>(a, p, dev, stream_h, taken);
+}
+
+}  // namespace rowsk
+
+// 9..64 activation rows, one matrix, one pass.  *taken stays false (nothing launched) when the
+// matrix or the activation does not qualify: the caller then runs row chunks.
+int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool* taken) {
+  *taken = false;
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr) return DQ_ERR_CUDA;
+  if (a.m <= 8 || a.m > 64) return DQ_OK;
+  // Where this kernel wins today (measured on B200 against row chunks, 2/4/8 bits): from 25 rows
+  // on and with a CTA for at least two thirds of the SMs -- 14336 x 4096: 40 us against 50 at 32
+  // rows, 73 against 100 at 64.  At 16 rows (35 against 26) and on 4096 x 4096 (32 CTAs: 39
+  // against 18 at 32 rows) the chunks are faster: a block of x is staged with its global loads
+  // exposed, one CTA barrier per block, one CTA per SM.
+  const bool forced = tuning_int("DQ_B200_ROWS_KERNEL", -1) == 1;
+  if (tuning_int("DQ_B200_ROWS_KERNEL", -1) == 0) return DQ_OK;
+  if (!forced && (a.m < 25 || ceil_div(a.rows, 16 * rowsk::kWarps) * 3 < static_cast<int64_t>(dev->sm_count) * 2)) return DQ_OK;
+  if (a.x_dtype != DQ_BF16 && a.x_dtype != DQ_F16) return DQ_OK;
+  if (a.meta_dtype != DQ_BF16 && a.meta_dtype != DQ_F16) return DQ_OK;
+  if (a.group_values != 128) return DQ_OK;
+  if ((a.in_features & 7) != 0 || (reinterpret_cast<uintptr_t>(a.x) & 15) != 0) return DQ_OK;  // unit-per-lane staging
+  if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) return DQ_OK;
+  switch (bits) {
+    case 2:
+      return rowsk::launch_bits<2>(a, *dev, stream, taken);
+    case 3:
+      return rowsk::launch_bits<3>(a, *dev, stream, taken);
+    case 4:
+      return rowsk::launch_bits<4>(a, *dev, stream, taken);
+    default:
+      return rowsk::launch_bits<8>(a, *dev, stream, taken);
+  }
+}
+
+}  // namespace dq

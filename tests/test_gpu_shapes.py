@@ -142,25 +142,59 @@ def test_sweep_shapes(bits, group, shape):
     assert out.dtype == torch.bfloat16 and within_one_ulp_16(out, want)
 
 
-@pytest.mark.parametrize(("m", "launches"), [(9, 2), (16, 1), (20, 2), (32, 1), (33, 2), (64, 2)])
-def test_row_chunks_share_launches(m, launches):
-    """9..64 activation rows: chunks of equal size (+-1), up to four of them per launch of the tiled
-    kernel (chunks of different sizes cannot share one), every row against the oracle."""
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("m", [25, 33, 40, 64])
+def test_many_rows_on_a_large_matrix_take_one_pass_over_the_weights(m, bits):
+    """The many-rows kernel (from 25 rows on, matrices with a CTA for most SMs): the fragments of
+    a step decoded once and fed to up to eight column blocks of eight activation rows; one launch
+    per matrix, every row against the oracle."""
     from dynquant_b200 import _lib, ops
 
-    qt = random_qt(1000, 1024, 3, seed=m)  # a ragged row count
+    meta = torch.bfloat16 if (m + bits) % 2 else torch.float16
+    qt = random_qt(12809, 1024, bits, meta=meta, seed=m, offsets=bits != 3)  # a ragged row count
+    act = torch.float16 if m % 3 == 0 else torch.bfloat16
+    x = torch.randn(m, 1024, generator=torch.Generator().manual_seed(m)).to(act).cuda()
+    before = int(_lib.load().dq_launch_count())
+    acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
+    assert int(_lib.load().dq_launch_count()) - before == 1
+    assert ops.last_kernel() == "gemv_rows_kernel"
+    want = oracle_gemv(x, qt)
+    check_acc(acc, want)
+    out = ops.quantized_matmul(x, qt)
+    assert out.dtype == act and within_one_ulp_16(out, want)
+
+
+def test_many_rows_fused_shards_with_a_bias():
+    from dynquant_b200 import _lib, ops
+
+    m = 40
+    x = torch.randn(m, 512, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+    shards = [random_qt(12800, 512, 4, seed=1), random_qt(128, 512, 2, seed=2), random_qt(13000, 512, 8, seed=3)]
+    bias = torch.randn(25928, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
+    before = int(_lib.load().dq_launch_count())
+    got = ops.gemv_row_chunks(x, shards, bias)
+    # the two large shards one pass each; the small one as five chunks of eight rows in two launches
+    assert int(_lib.load().dq_launch_count()) - before == 4
+    want = torch.cat([ops.gemv_shards(x[i:i + 8].contiguous(), shards, bias) for i in range(0, m, 8)])
+    assert got.shape == (m, 25928) and within_one_ulp_16(got, want.float().cpu().numpy())
+    with pytest.raises(RuntimeError, match="exceeds the limit of 64"):
+        ops.gemv_row_chunks(torch.zeros(65, 512, dtype=torch.bfloat16, device="cuda"), shards)
+
+
+@pytest.mark.parametrize(("m", "launches"), [(9, 2), (16, 1), (20, 2), (32, 1), (33, 2), (64, 2)])
+def test_row_chunks_share_launches(m, launches):
+    """What the many-rows kernel does not take (here: a small matrix) runs as row chunks of equal
+    size (+-1), up to four of them per launch of the tiled kernel (chunks of different sizes
+    cannot share one), every row against the oracle."""
+    from dynquant_b200 import _lib, ops
+
+    qt = random_qt(1000, 1024, 3, seed=m)
     x = torch.randn(m, 1024, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16).cuda()
     before = int(_lib.load().dq_launch_count())
     acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
     assert int(_lib.load().dq_launch_count()) - before == launches
     assert ops.last_kernel() == "gemv_mma_tile_kernel"
     check_acc(acc, oracle_gemv(x, qt))
-    # fused shards x row chunks, with a bias, against the same rows one chunk at a time
-    shards = [random_qt(256, 1024, 4, seed=1), random_qt(128, 1024, 2, seed=2), random_qt(384, 1024, 8, seed=3)]
-    bias = torch.randn(768, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
-    got = ops.gemv_row_chunks(x, shards, bias)
-    want = torch.cat([ops.gemv_shards(x[i:i + 8].contiguous(), shards, bias) for i in range(0, m, 8)])
-    assert got.shape == (m, 768) and within_one_ulp_16(got, want.float().cpu().numpy())
 
 
 def test_row_chunks_of_a_long_matrix_go_one_by_one():
@@ -170,10 +204,8 @@ def test_row_chunks_of_a_long_matrix_go_one_by_one():
     x = torch.randn(16, 512, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).cuda()
     before = int(_lib.load().dq_launch_count())
     acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
-    assert int(_lib.load().dq_launch_count()) - before == 2 and ops.last_kernel() == "gemv_mma_stream_kernel"
+    assert int(_lib.load().dq_launch_count()) - before == 2 and ops.last_kernel().startswith("gemv_mma")
     check_acc(acc, oracle_gemv(x, qt))
-    with pytest.raises(RuntimeError, match="exceeds the limit of 64"):
-        ops.gemv_row_chunks(torch.zeros(65, 512, dtype=torch.bfloat16, device="cuda"), [qt])
 
 
 # ---- (d) the head of the decode stack -----------------------------------------------------------
