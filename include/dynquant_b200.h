@@ -102,7 +102,7 @@ DQ_API int32_t dq_gemv_max_rows(void);
 DQ_API int64_t dq_launch_count(void);
 /* Name of the kernel the calling thread's most recent GEMV or MoE entry point launched last
  * ("gemv_mma_stream_kernel", "gemv_mma_tile_kernel", "gemv_mma_kernel", "gemv_fast_kernel",
- * "gemv_general_kernel", "gemv_plan_kernel", "moe_grouped_kernel", "moe_combine_kernel",
+ * "gemv_general_kernel", "gemv_plan_kernel", "gemv_rows_kernel", "moe_grouped_kernel", "moe_combine_kernel",
  * "moe_down_token_kernel"; "" before the first launch).  No reference
  * counterpart: the reference has two kernels and a documented rule between them
  * (csrc/gemv/gemv.cu:566-598); here a test uses this to prove which kernel it exercised. */
@@ -150,11 +150,12 @@ DQ_API int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const d
                               int32_t num_shards, const void* bias, void* out, int64_t out_stride,
                               int32_t out_dtype, void* stream);
 /* dq_gemv_shards for up to DQ_GEMV_CHUNKED_MAX_ROWS activation rows (the 9..64-row band in which
- * the reference already pays for dequantize + dense matmul, runtime/ops.py:205-231): the rows
- * are cut into ceil(m / 8) chunks of equal size (+-1) and up to four (chunk, shard) pairs leave
- * as one launch of the tiled kernel, so that a matrix is read from HBM once and by the other
- * chunks from L2; matrices long enough for the streaming kernel go chunk by chunk.  Same
- * arguments and results as dq_gemv_shards. */
+ * the reference already pays for dequantize + dense matmul, runtime/ops.py:205-231).  From 25 rows
+ * on, a large shard goes through the many-rows kernel: one pass over its weights, a step's
+ * fragments decoded once for all the rows.  Otherwise the rows are cut into ceil(m / 8) chunks of
+ * equal size (+-1) and up to four (chunk, shard) pairs leave as one launch of the tiled kernel, so
+ * that a matrix is read from HBM once and by the other chunks from L2; matrices long enough for
+ * the streaming kernel go chunk by chunk.  Same arguments and results as dq_gemv_shards. */
 DQ_API int32_t dq_gemv_shards_rows(const void* x, int32_t x_dtype, int64_t m, const dq_weight* shards,
                                    int32_t num_shards, const void* bias, void* out, int64_t out_stride,
                                    int32_t out_dtype, void* stream);
