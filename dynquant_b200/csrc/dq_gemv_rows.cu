@@ -1,4 +1,4 @@
-// 9..64 activation rows against one packed matrix in ONE pass over the weights.
+// 9..64 activation rows against one packed matrix in one pass over the weights (two from 33 rows on).
 //
 // The GEMV kernels take at most eight activation rows: the eight columns of one m16n8k16
 // accumulator.  More rows used to mean more passes (row chunks of eight, each decoding the
@@ -10,10 +10,11 @@
 //   CTA       8 warps = 8 row tiles of 16 weight rows; warp w streams its tile's rows over the
 //             whole reduction axis through a private cp.async ring (the streaming kernel's
 //             plumbing: blocks of P steps, no barrier for weights).
-//   x         too large to stage whole (64 rows x 4096 values in fragment order: 512 KB), so it
-//             passes through shared memory in blocks of P steps, shared by the CTA's warps and
-//             double buffered: all threads stage block b+1 (unit-per-lane staging, 16-bit
-//             aligned activations only), every warp computes block b, one CTA barrier per block.
+//   x         too large to stage whole (32 rows x 4096 values in fragment order: 256 KB), so it
+//             passes through shared memory in blocks of P steps shared by the CTA's warps: the raw
+//             rows of block b+2 travel by cp.async while block b is computed, all threads convert
+//             raw block b+1 to fragment order (unit-per-lane staging, 16-bit aligned activations
+//             only) between two CTA barriers.  Up to 32 rows per launch (four column blocks).
 //   out       [m, rows] as the GEMV kernels write it; accumulation in fp32, scale and offset
 //             applied per step, one rounding.
 //
@@ -32,16 +33,19 @@ namespace rowsk {
 
 constexpr int kWarps = stream::kWarps;
 constexpr int kThreads = stream::kThreads;
+constexpr int kRingBlocks = 3;  // weight blocks in a warp's ring: requested two blocks ahead
+constexpr int kRawBuffers = 2;  // raw blocks of x in flight: requested two blocks ahead
+constexpr int kMaxRows = 32;    // activation rows per launch (four column blocks)
 
 struct Params {
-  int steps;        // padded K / 128, a multiple of P
+  int steps;        // K / 128, a multiple of P (no padded tail: in_features == steps * 128)
   int tiles;        // ceil(rows / 16)
-  int m_stride_u4;  // uint4 per activation row of one staged block: P * NA + 4
+  int m_stride_u4;  // uint4 per activation row of the staged block: P * NA + 4
   int meta_bf16;
   uint32_t magic;
 };
 
-// Bytes of one column block's staging region for one x block: 8 rows of fragments, the zero
+// Bytes of one column block's fragment region for one x block: 8 rows of fragments, the zero
 // block that lanes of absent rows read, and the two sums per (step, row).
 template <int BITS>
 __host__ __device__ constexpr size_t region_bytes() {
@@ -49,28 +53,44 @@ __host__ __device__ constexpr size_t region_bytes() {
   constexpr int NA = BITS == 8 ? 32 : 16;
   return (static_cast<size_t>(8) * (C::P * NA + 4) + NA) * 16 + static_cast<size_t>(C::P) * 8 * 4 * 2;
 }
+// One column block of a raw x block: 8 rows x P steps x 128 values of 16 bits.
+template <int BITS>
+__host__ __device__ constexpr size_t raw_bytes() {
+  return static_cast<size_t>(8) * stream::Cfg<BITS>::P * 256;
+}
 
 template <int BITS>
 size_t smem_bytes(int mb) {
-  return stream::Cfg<BITS>::RING_BYTES + 2 * static_cast<size_t>(mb) * region_bytes<BITS>();
+  using C = stream::Cfg<BITS>;
+  return static_cast<size_t>(kRingBlocks) * (C::BLOCK_BYTES + C::META_BYTES) * kThreads +
+         static_cast<size_t>(mb) * (kRawBuffers * raw_bytes<BITS>() + region_bytes<BITS>());
 }
 
+// Pipeline of one CTA, block b of P steps:
+//   weights   cp.async into the warp's ring, two blocks ahead (the streaming kernel's plumbing);
+//   x, raw    cp.async of the block's rows into one of two raw buffers, two blocks ahead -- the
+//             global latency of the activation is off the critical path;
+//   x, frags  after compute(b): all threads convert raw(b+1) into the (single) fragment buffer,
+//             between two CTA barriers;
+//   compute   every warp: decode a step once, feed it to the column blocks.
 template <int BITS, bool XBF16, int MB>
-__global__ void __launch_bounds__(kThreads, MB <= 2 ? 2 : 1) gemv_rows_kernel(const GemvArgs a, const Params p) {
+__global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a, const Params p) {
   using Plan = MmaPlan<BITS>;
   using C = stream::Cfg<BITS>;
   constexpr int P = C::P;
-  constexpr int NB = C::NB;
+  constexpr int NB = kRingBlocks;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
   constexpr int STEP_WORDS = 4 * BITS;
   constexpr int STEP_BYTES = STEP_WORDS * 4;
   constexpr size_t REGION = region_bytes<BITS>();
+  constexpr size_t RAW = raw_bytes<BITS>();
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* ring_w = smem_raw;
   unsigned char* ring_m = ring_w + NB * C::BLOCK_BYTES * kThreads;
-  unsigned char* xarea = ring_m + NB * C::META_BYTES * kThreads;  // [2 buffers][MB regions]
+  unsigned char* raw = ring_m + NB * C::META_BYTES * kThreads;   // [kRawBuffers][MB][8 rows][P * 128] 16-bit
+  unsigned char* frag = raw + kRawBuffers * MB * RAW;            // [MB] regions
 
   const int tid = threadIdx.x;
   const int lane = tid & (kWarp - 1);
@@ -83,16 +103,17 @@ __global__ void __launch_bounds__(kThreads, MB <= 2 ? 2 : 1) gemv_rows_kernel(co
   const int nblocks = p.steps / P;
   const int tile = blockIdx.x * kWarps + warp;
   const bool live = tile < p.tiles;
-  const int mbs = (a.m + 7) / 8;  // column blocks that have rows (the kernel is built for 2, 4 or 8)
+  const int mbs = (a.m + 7) / 8;  // column blocks that have rows (the kernel is built for 2 or 4)
 
   const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * C::UNIT;
   const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * C::META_BYTES;
+  const uint32_t raw_s = static_cast<uint32_t>(__cvta_generic_to_shared(raw));
   const unsigned char* ring_w_mine = ring_w + tid * C::UNIT;
   const unsigned char* ring_m_quad = ring_m + (tid & ~3) * C::META_BYTES;
 
   pdl_launch_dependents();
 
-  // ---- prefetch cursor over the blocks of this warp's tile (running pointers, immediate offsets) ----
+  // ---- weights: prefetch cursor over the blocks of this warp's tile ----
   constexpr int PIECES = 2 * C::UNIT;
   constexpr int PER_ROW = C::UNIT / 4;
   constexpr int NSRC = (PIECES + kWarp - 1) / kWarp;
@@ -122,7 +143,7 @@ __global__ void __launch_bounds__(kThreads, MB <= 2 ? 2 : 1) gemv_rows_kernel(co
   uint32_t pf_w = ring_w_s + lane * 16, pf_m = ring_m_s;
   const uint32_t ring_w_end = ring_w_s + lane * 16 + NB * (C::BLOCK_BYTES * kThreads);
   int pf_blk = 0;
-  auto prefetch_block = [&]() {
+  auto prefetch_weights = [&]() {  // (no commit: the caller commits weights and raw x together)
     if (live && pf_blk < nblocks) {
 #pragma unroll
       for (int j = 0; j < P; ++j) {
@@ -151,33 +172,56 @@ __global__ void __launch_bounds__(kThreads, MB <= 2 ? 2 : 1) gemv_rows_kernel(co
       pf_w -= NB * (C::BLOCK_BYTES * kThreads);
       pf_m -= NB * (C::META_BYTES * kThreads);
     }
-    stream::cp_async_commit();  // an empty group keeps the wait arithmetic uniform
   };
-#pragma unroll
-  for (int i = 0; i < NB - 1; ++i) prefetch_block();
 
-  // ---- staging of one x block: thread groups of 32 * P threads take the column blocks in turn ----
-  constexpr int kGroupThreads = 32 * P;             // one (row, step, quad lane) task per thread: 8 * P * 4
-  constexpr int kGroups = kThreads / kGroupThreads;  // 2 (P = 4) or 4 (P = 2)
+  // ---- x, raw: block `blk` of every existing row into raw buffer blk % kRawBuffers, 16 bytes a piece ----
+  constexpr int kRowPieces = P * 16;  // 16-byte pieces of one row of one block
+  auto request_raw = [&](int blk) {
+    if (blk < nblocks) {
+      const uint32_t dst0 = raw_s + static_cast<uint32_t>((blk % kRawBuffers) * MB * RAW);
+      const unsigned char* src0 = static_cast<const unsigned char*>(a.x) + static_cast<size_t>(blk) * P * 256;
+      const int pieces = a.m * kRowPieces;  // (raw rows are laid out 8 per column block, back to back: row r at r * P * 256)
+      for (int i = tid; i < pieces; i += kThreads) {
+        const int r = i / kRowPieces, c = i - r * kRowPieces;
+        stream::cp_async_n<16>(dst0 + r * (P * 256) + c * 16, src0 + static_cast<size_t>(r) * a.in_features * 2 + c * 16);
+      }
+    }
+  };
+
+  // ---- x, fragments: raw buffer of block `blk` -> the fragment regions; thread groups of 32 * P
+  // threads (one (row, step, quad lane) task per thread) take the column blocks in turn ----
+  constexpr int kGroupThreads = 32 * P;
+  constexpr int kGroups = kThreads / kGroupThreads;
   const int sg = tid / kGroupThreads, stid = tid - sg * kGroupThreads;
-  auto stage_block = [&](int blk, int buf) {
+  auto convert = [&](int blk) {
     for (int cb = sg; cb < mbs; cb += kGroups) {
-      unsigned char* region = xarea + (static_cast<size_t>(buf) * MB + cb) * REGION;
+      unsigned char* region = frag + cb * REGION;
       uint4* xb = reinterpret_cast<uint4*>(region);
       float* xsum = reinterpret_cast<float*>(xb + 8 * p.m_stride_u4 + NA);
       float* xneg = xsum + P * 8;
       GemvArgs sub = {};
-      sub.x = static_cast<const unsigned short*>(a.x) + static_cast<int64_t>(cb) * 8 * a.in_features;
+      sub.x = raw + (static_cast<size_t>(blk % kRawBuffers) * MB + cb) * RAW;
       sub.x_dtype = a.x_dtype;
-      sub.in_features = a.in_features;
+      sub.in_features = P * 128;  // the raw block's row pitch
       sub.m = min(8, a.m - cb * 8);
       // (rows that do not exist: their fragments are the zero block, which sits after row `m`)
-      stage_units<BITS, XBF16, false>(sub, blk * P, P, p.m_stride_u4, xb, xsum, xneg, stid, kGroupThreads, nullptr, false);
+      stage_units<BITS, XBF16, false, true>(sub, 0, P, p.m_stride_u4, xb, xsum, xneg, stid, kGroupThreads, nullptr, false);
     }
   };
 
+  // prologue: weights do not depend on the previous kernel, x does
+  prefetch_weights();
+  stream::cp_async_commit();
+  prefetch_weights();
   pdl_wait_prior_grid();
-  stage_block(0, 0);
+  request_raw(0);
+  stream::cp_async_commit();
+  request_raw(1);
+  stream::cp_async_commit();
+  // groups so far: {w0}, {w1, raw0}, {raw1}; from here on one group per block: {w(b+2), raw(b+2)}
+  stream::cp_async_wait<1>();  // raw0 (and w0, w1)
+  __syncthreads();
+  convert(0);
   __syncthreads();
 
   float acc[MB][4];
@@ -190,11 +234,11 @@ __global__ void __launch_bounds__(kThreads, MB <= 2 ? 2 : 1) gemv_rows_kernel(co
   const unsigned char* mslot = ring_m_quad;
   const unsigned char* const wslot_end = ring_w_mine + NB * (C::BLOCK_BYTES * kThreads);
   for (int blk = 0; blk < nblocks; ++blk) {
-    const int buf = blk & 1;
-    if (blk + 1 < nblocks) stage_block(blk + 1, buf ^ 1);  // (the barrier below publishes it)
-    __syncwarp();
-    prefetch_block();
-    stream::cp_async_wait<NB - 1>();
+    __syncwarp();  // every lane is done with the ring slot about to be refilled
+    prefetch_weights();
+    request_raw(blk + 2);  // into the buffer raw(blk) was converted from
+    stream::cp_async_commit();
+    stream::cp_async_wait<2>();  // all but the two youngest groups: w(blk) is in
     __syncwarp();
     if (live) {
       uint32_t mc[4][P / 2];
@@ -227,33 +271,49 @@ __global__ void __launch_bounds__(kThreads, MB <= 2 ? 2 : 1) gemv_rows_kernel(co
         };
         const float sc_a = meta_f32(0), sc_b = meta_f32(2);
         const float of_a = has_off ? meta_f32(1) : 0.0f, of_b = has_off ? meta_f32(3) : 0.0f;
+        // The column blocks' accumulators are independent: their mma are interleaved, so that a
+        // warp has MB chains in flight instead of one chain of 2 * QU dependent mma per block
+        // (with eight warps on the SM nothing else would hide that latency).
+        float d[MB][4];
+        const uint4* bsrc[MB];
+        int bstep[MB];
 #pragma unroll
         for (int cb = 0; cb < MB; ++cb) {
-          if (cb >= mbs) continue;  // (uniform over the CTA)
-          const unsigned char* region = xarea + (static_cast<size_t>(buf) * MB + cb) * REGION;
-          const uint4* xb = reinterpret_cast<const uint4*>(region);
+          const uint4* xb = reinterpret_cast<const uint4*>(frag + cb * REGION);
+          const int m_here = a.m - cb * 8;  // rows of this column block that exist (<= 0: none, the zero block)
+          const bool mine = g < m_here;
+          bsrc[cb] = mine ? xb + g * p.m_stride_u4 + t + j * (QU * 4) : xb + max(0, min(m_here, 8)) * p.m_stride_u4;
+          bstep[cb] = mine ? 4 : 0;
+        }
+#pragma unroll
+        for (int q = 0; q < QU; ++q) {
+          uint4 b[MB];
+#pragma unroll
+          for (int cb = 0; cb < MB; ++cb) b[cb] = bsrc[cb][q * bstep[cb]];
+#pragma unroll
+          for (int cb = 0; cb < MB; ++cb) {
+            if (q == 0) {
+              mma_16816<XBF16, true>(d[cb], aa[0], ab[0], aa[1], ab[1], b[cb].x, b[cb].y);
+            } else {
+              mma_16816<XBF16, false>(d[cb], aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b[cb].x, b[cb].y);
+            }
+          }
+#pragma unroll
+          for (int cb = 0; cb < MB; ++cb) {
+            mma_16816<XBF16, false>(d[cb], aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b[cb].z, b[cb].w);
+          }
+        }
+#pragma unroll
+        for (int cb = 0; cb < MB; ++cb) {
+          const uint4* xb = reinterpret_cast<const uint4*>(frag + cb * REGION);
           const float* xsum = reinterpret_cast<const float*>(xb + 8 * p.m_stride_u4 + NA);
           const float* xneg = xsum + P * 8;
-          const int m_here = a.m - cb * 8;  // rows of this column block that exist (>= 1)
-          const uint4* bsrc = (g < m_here ? xb + g * p.m_stride_u4 + t + j * (QU * 4) : xb + min(m_here, 8) * p.m_stride_u4);
-          const int bstep = g < m_here ? 4 : 0;
-          float d[4];
-#pragma unroll
-          for (int q = 0; q < QU; ++q) {
-            const uint4 b = bsrc[q * bstep];
-            if (q == 0) {
-              mma_16816<XBF16, true>(d, aa[0], ab[0], aa[1], ab[1], b.x, b.y);
-            } else {
-              mma_16816<XBF16, false>(d, aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b.x, b.y);
-            }
-            mma_16816<XBF16, false>(d, aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b.z, b.w);
-          }
           const float2 xs2 = *reinterpret_cast<const float2*>(xsum + j * 8 + 2 * t);
           const float2 xn2 = *reinterpret_cast<const float2*>(xneg + j * 8 + 2 * t);
-          acc[cb][0] = fmaf(sc_a, d[0] + xn2.x, acc[cb][0]);
-          acc[cb][1] = fmaf(sc_a, d[1] + xn2.y, acc[cb][1]);
-          acc[cb][2] = fmaf(sc_b, d[2] + xn2.x, acc[cb][2]);
-          acc[cb][3] = fmaf(sc_b, d[3] + xn2.y, acc[cb][3]);
+          acc[cb][0] = fmaf(sc_a, d[cb][0] + xn2.x, acc[cb][0]);
+          acc[cb][1] = fmaf(sc_a, d[cb][1] + xn2.y, acc[cb][1]);
+          acc[cb][2] = fmaf(sc_b, d[cb][2] + xn2.x, acc[cb][2]);
+          acc[cb][3] = fmaf(sc_b, d[cb][3] + xn2.y, acc[cb][3]);
           if (has_off) {
             acc[cb][0] = fmaf(of_a, xs2.x, acc[cb][0]);
             acc[cb][1] = fmaf(of_a, xs2.y, acc[cb][1]);
@@ -269,7 +329,12 @@ __global__ void __launch_bounds__(kThreads, MB <= 2 ? 2 : 1) gemv_rows_kernel(co
       wslot = ring_w_mine;
       mslot = ring_m_quad;
     }
-    __syncthreads();  // block b+1 is staged; everyone is done with block b's buffer
+    if (blk + 1 < nblocks) {
+      stream::cp_async_wait<1>();  // all but the youngest group: raw(blk + 1) is in
+      __syncthreads();             // ... for every thread's pieces; and every warp is done with the fragments
+      convert(blk + 1);
+      __syncthreads();
+    }
   }
   stream::cp_async_wait<0>();
   if (live) {
@@ -318,7 +383,7 @@ template <int BITS>
 int32_t launch_bits(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
   using C = stream::Cfg<BITS>;
   const int steps = a.words_per_row / (4 * BITS);
-  if (steps % C::P != 0 || a.num_groups != steps) return DQ_OK;
+  if (steps % C::P != 0 || a.num_groups != steps || a.in_features != steps * 128) return DQ_OK;
   const auto align = static_cast<uintptr_t>(C::META_BYTES);
   if (reinterpret_cast<uintptr_t>(a.scales) % align != 0 || reinterpret_cast<uintptr_t>(a.offsets) % align != 0 ||
       (static_cast<int64_t>(a.num_groups) * 2) % C::META_BYTES != 0) {
@@ -330,10 +395,22 @@ int32_t launch_bits(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t strea
   p.m_stride_u4 = C::P * (BITS == 8 ? 32 : 16) + 4;
   p.meta_bf16 = a.meta_dtype == DQ_BF16 ? 1 : 0;
   p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
-  const int mb = static_cast<int>(ceil_div(a.m, 8));
-  if (mb <= 2) return launch_mb<BITS, 2>(a, p, dev, stream_h, taken);
-  if (mb <= 4) return launch_mb<BITS, 4>(a, p, dev, stream_h, taken);
-  return launch_mb<BITS, 8>(a, p, dev, stream_h, taken);
+  // at most kMaxRows rows per launch (four column blocks): more rows, more passes
+  const size_t x_row = static_cast<size_t>(a.in_features) * 2, out_row = static_cast<size_t>(a.out_stride) * dtype_size(a.out_dtype);
+  const int passes = static_cast<int>(ceil_div(a.m, kMaxRows));
+  const int per = static_cast<int>(ceil_div(a.m, passes));
+  for (int r0 = 0; r0 < a.m; r0 += per) {
+    GemvArgs part = a;
+    part.m = std::min(per, a.m - r0);
+    part.x = static_cast<const unsigned char*>(a.x) + r0 * x_row;
+    part.out = static_cast<unsigned char*>(a.out) + r0 * out_row;
+    bool ok = false;
+    const int32_t rc = part.m <= 16 ? launch_mb<BITS, 2>(part, p, dev, stream_h, &ok) : launch_mb<BITS, 4>(part, p, dev, stream_h, &ok);
+    if (rc != DQ_OK) return rc;
+    if (!ok) return r0 == 0 ? DQ_OK : fail(DQ_ERR_UNSUPPORTED, "gemv rows: the second pass did not fit shared memory");
+  }
+  *taken = true;
+  return DQ_OK;
 }
 
 }  // namespace rowsk
@@ -345,14 +422,15 @@ int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool*
   const DeviceInfo* dev = device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
   if (a.m <= 8 || a.m > 64) return DQ_OK;
-  // Where this kernel wins today (measured on B200 against row chunks, 2/4/8 bits): from 25 rows
-  // on and with a CTA for at least two thirds of the SMs -- 14336 x 4096: 40 us against 50 at 32
-  // rows, 73 against 100 at 64.  At 16 rows (35 against 26) and on 4096 x 4096 (32 CTAs: 39
-  // against 18 at 32 rows) the chunks are faster: a block of x is staged with its global loads
-  // exposed, one CTA barrier per block, one CTA per SM.
-  const bool forced = tuning_int("DQ_B200_ROWS_KERNEL", -1) == 1;
-  if (tuning_int("DQ_B200_ROWS_KERNEL", -1) == 0) return DQ_OK;
-  if (!forced && (a.m < 25 || ceil_div(a.rows, 16 * rowsk::kWarps) * 3 < static_cast<int64_t>(dev->sm_count) * 2)) return DQ_OK;
+  // Where this kernel wins (measured on B200 against row chunks, 2/4/8 bits): matrices with a CTA
+  // for at least two thirds of the SMs -- 14336 x 4096: 19.5 / 19.9 / 37.9 us against 25.4 / 26.0 /
+  // 41.7 at 16 rows, 31 / 32 / 55 against 50 / 51 / 82 at 32 rows, 61 / 63 / 110 against 100 / 102 /
+  // 164 at 64 rows.  On 4096 x 4096 (32 CTAs of eight row tiles on 148 SMs) the chunks are faster
+  // (10 against 19 us at 16 rows): every CTA converts the whole activation for its own tiles, so
+  // smaller CTAs do not pay either.
+  const int rows_switch = tuning_int("DQ_B200_ROWS_KERNEL", -1);
+  if (rows_switch == 0) return DQ_OK;
+  if (rows_switch != 1 && ceil_div(a.rows, 16 * rowsk::kWarps) * 3 < static_cast<int64_t>(dev->sm_count) * 2) return DQ_OK;
   if (a.x_dtype != DQ_BF16 && a.x_dtype != DQ_F16) return DQ_OK;
   if (a.meta_dtype != DQ_BF16 && a.meta_dtype != DQ_F16) return DQ_OK;
   if (a.group_values != 128) return DQ_OK;

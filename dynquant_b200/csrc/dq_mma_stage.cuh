@@ -73,7 +73,9 @@ __device__ __forceinline__ void stage_zero_fill(int m, int nsteps, int m_stride_
 // (two shuffle levels, fixed order).  Tasks tid, tid + nthreads, ... ; consecutive tasks of
 // a quad are the four tt of one (m, j).  Steps are [s_first, s_first + nsteps) of the row and
 // are indexed from 0 in xb / xsum / xneg.  The caller synchronises afterwards.
-template <int BITS, bool XBF16, bool G64>
+// PLAIN_LOADS: `a.x` points into shared memory (a raw block of the activation that was copied there
+// asynchronously); ordinary loads instead of L2-coherent global ones.
+template <int BITS, bool XBF16, bool G64, bool PLAIN_LOADS = false>
 __device__ __forceinline__ void stage_units(const GemvArgs& a, int s_first, int nsteps, int m_stride_u4, uint4* xb,
                                             float* xsum, float* xneg, int tid, int nthreads,
                                             const int* row_map, bool prefilled = false) {
@@ -102,7 +104,12 @@ __device__ __forceinline__ void stage_units(const GemvArgs& a, int s_first, int 
       const int k = k_step + step_position<G64, BITS>(tt, 8 * c);
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (live && k < a.in_features) {
-        v = __ldcg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(a.x) + src_row * a.in_features + k));
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(a.x) + src_row * a.in_features + k);
+        if constexpr (PLAIN_LOADS) {
+          v = *src;
+        } else {
+          v = __ldcg(src);
+        }
       }
       w[4 * c] = v.x, w[4 * c + 1] = v.y, w[4 * c + 2] = v.z, w[4 * c + 3] = v.w;
     }

@@ -150,9 +150,9 @@ DQ_API int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const d
                               int32_t num_shards, const void* bias, void* out, int64_t out_stride,
                               int32_t out_dtype, void* stream);
 /* dq_gemv_shards for up to DQ_GEMV_CHUNKED_MAX_ROWS activation rows (the 9..64-row band in which
- * the reference already pays for dequantize + dense matmul, runtime/ops.py:205-231).  From 25 rows
- * on, a large shard goes through the many-rows kernel: one pass over its weights, a step's
- * fragments decoded once for all the rows.  Otherwise the rows are cut into ceil(m / 8) chunks of
+ * the reference already pays for dequantize + dense matmul, runtime/ops.py:205-231).  A large
+ * shard goes through the many-rows kernel: one pass over its weights per 32 rows, a step's
+ * fragments decoded once for all of them.  Otherwise the rows are cut into ceil(m / 8) chunks of
  * equal size (+-1) and up to four (chunk, shard) pairs leave as one launch of the tiled kernel, so
  * that a matrix is read from HBM once and by the other chunks from L2; matrices long enough for
  * the streaming kernel go chunk by chunk.  Same arguments and results as dq_gemv_shards. */
