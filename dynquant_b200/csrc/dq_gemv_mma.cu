@@ -503,7 +503,10 @@ bool stream_ok(const GemvArgs& a, const DeviceInfo& dev, int tiles, int steps) {
     return false;  // whole steps are copied in 16-byte pieces
   }
   if (a.group_values != kStepValues || steps % C::P != 0 || a.num_groups % C::P != 0) return false;
-  if (tiles < dev.sm_count * tuning_int("DQ_B200_STREAM_MIN_TILES_PER_SM", stream::kWarps)) return false;
+  // From eight row tiles per SM on; 8-bit matrices from six (measured with the threshold lowered:
+  // 14336 x 4096 at 8 bits 14.3 us here against 19.7 in the tiled kernel, at 4 bits 10.7 against
+  // 11.7 but 17408 x 5120 20.2 against 15.2, at 2 bits 12.0 against 10.2 and 24.7 against 12.8).
+  if (tiles < dev.sm_count * tuning_int("DQ_B200_STREAM_MIN_TILES_PER_SM", BITS == 8 ? 6 : stream::kWarps)) return false;
   const auto align = static_cast<uintptr_t>(C::META_BYTES);
   if (reinterpret_cast<uintptr_t>(a.scales) % align != 0 || reinterpret_cast<uintptr_t>(a.offsets) % align != 0) {
     return false;
