@@ -68,6 +68,7 @@ def run_point(rows: int, k: int, bits: int, group: int, m: int, *, launches: int
 
     for qt in weights[: min(3, ring)]:
         out = step(qt)
+    kernel = ops.last_kernel()
     torch.cuda.synchronize()
     # the output is rounded once to bf16 (2^-8 relative), the fp32 sums differ in their last bits
     err = check_block(x, weights[min(3, ring) - 1], out)
@@ -92,7 +93,9 @@ def run_point(rows: int, k: int, bits: int, group: int, m: int, *, launches: int
     return {
         "rows": rows, "in_features": k, "bits": bits, "group_size": group, "m": m,
         "path": ("gemv" if m <= ops.gemv_max_rows() else
-                 "gemv x%d" % -(-m // ops.gemv_max_rows()) if m <= ops.GEMV_CHUNKED_MAX_ROWS else "dequant+dense"),
+                 "dequant+dense" if m > ops.GEMV_CHUNKED_MAX_ROWS else
+                 "many-rows kernel" if kernel == "gemv_rows_kernel" else "row chunks"),
+        "kernel": kernel,
         "us_per_call": round(seconds * 1e6, 2), "gbps": round(gbs, 1),
         "pct_of_hbm_peak": round(100 * gbs / peak, 1), "peak": f"{peak} GB/s ({kind})",
         "ring": ring, "ring_bytes": probe.nbytes * ring, "launches": launches, "max_err_vs_fp32_torch": float(f"{err:.2e}"),
