@@ -38,6 +38,9 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const 
 int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken,
                               const peerpush::Push* push = nullptr);
 
+// Two to four long matrices that share an activation in one launch of the streaming kernel's body
+// (dq_gemv_stream_multi.cu).  *taken stays false, nothing launched, when they do not qualify.
+int32_t launch_gemv_stream_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken);
 // 9..64 activation rows against one matrix in one pass over the weights (dq_gemv_rows.cu).  *taken
 // stays false, nothing launched, when the matrix or the activation does not qualify.
 int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool* taken);

@@ -879,6 +879,11 @@ int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cuda
   for (int i = 0; i < n; ++i) {
     if (!mma_path_supports(jobs[i], bits[i])) return DQ_OK;
   }
+  if (push == nullptr && tuning_int("DQ_B200_NO_STREAM_MULTI") == 0) {
+    // matrices long enough to be streamed: the streaming body, a range of CTAs per matrix
+    if (const int32_t rc = launch_gemv_stream_fused(jobs, bits, n, stream, taken)) return rc;
+    if (*taken) return DQ_OK;
+  }
   return try_tile(jobs, bits, n, *dev, stream, taken, push);
 }
 

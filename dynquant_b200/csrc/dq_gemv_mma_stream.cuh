@@ -124,8 +124,13 @@ struct Params {
 // PUSH: the launch also copies its output rows into every rank's window and ends with the bounded
 // wait for the other ranks' rows (dq_peer_push.cuh).  A template parameter, not a flag: this
 // kernel sits at its register limit and the plain build must stay exactly what it was.
+//
+// The body is a device function of (CTA index, CTA count) so that one launch can also run several
+// matrices side by side, each on its own range of CTAs (gemv_mma_stream_multi_kernel,
+// dq_gemv_stream_multi.cu); the single-matrix kernel below passes blockIdx.x / gridDim.x.
 template <int BITS, bool XBF16, bool MBF16, bool P16 = false, bool PUSH = false>
-__global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const GemvArgs a, const Params p) {
+__device__ __forceinline__ void stream_body(const GemvArgs& a, const Params& p, const unsigned int cta,
+                                            const unsigned int ncta, unsigned char* smem_raw) {
   using Plan = MmaPlan<BITS>;
   using C = Cfg<BITS>;
   constexpr int P = C::P;
@@ -137,7 +142,6 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
   constexpr int kTileRows = 16;
   constexpr float kMagicValue = XBF16 ? 128.0f : 1024.0f;
 
-  extern __shared__ __align__(16) unsigned char smem_raw[];
   // [ring weights: NB][P][2 rows][threads][UNIT] [ring meta: NB][threads][META_BYTES] [xb] [zero] [xsum] [xneg]
   unsigned char* ring_w = smem_raw;
   unsigned char* ring_m = ring_w + NB * C::BLOCK_BYTES * kThreads;
@@ -160,10 +164,10 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
   // rounds, 7 % of the launch).  Runs (p.runs): a CTA takes a contiguous run of tiles, the runs
   // equal to within a tile, its warps interleaved over the run.  The host picks per launch.
   const bool runs = p.runs != 0;
-  const int tile_lo = runs ? static_cast<int>(static_cast<int64_t>(p.tiles) * blockIdx.x / gridDim.x) : 0;
-  const int tile_end = runs ? static_cast<int>(static_cast<int64_t>(p.tiles) * (blockIdx.x + 1) / gridDim.x) : p.tiles;
-  const int tile_stride = runs ? kWarps : static_cast<int>(gridDim.x) * kWarps;
-  const int first_tile = runs ? tile_lo + warp : static_cast<int>(blockIdx.x) * kWarps + warp;
+  const int tile_lo = runs ? static_cast<int>(static_cast<int64_t>(p.tiles) * cta / ncta) : 0;
+  const int tile_end = runs ? static_cast<int>(static_cast<int64_t>(p.tiles) * (cta + 1) / ncta) : p.tiles;
+  const int tile_stride = runs ? kWarps : static_cast<int>(ncta) * kWarps;
+  const int first_tile = runs ? tile_lo + warp : static_cast<int>(cta) * kWarps + warp;
 
   const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * C::UNIT;
   const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * C::META_BYTES;
@@ -396,13 +400,19 @@ __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const Gemv
       peerpush::push_rows(p.push, a, epoch, tile_lo * kTileRows, min(tile_end * kTileRows, a.rows), tid, kThreads);
     } else {
       constexpr int kRun = kWarps * kTileRows;
-      for (int row = static_cast<int>(blockIdx.x) * kRun; row < a.rows; row += static_cast<int>(gridDim.x) * kRun) {
+      for (int row = static_cast<int>(cta) * kRun; row < a.rows; row += static_cast<int>(ncta) * kRun) {
         peerpush::push_rows(p.push, a, epoch, row, min(row + kRun, a.rows), tid, kThreads);
       }
     }
     __syncthreads();
-    if (tid < kWarp) peerpush::arrive(p.push, epoch, gridDim.x, tid);
+    if (tid < kWarp) peerpush::arrive(p.push, epoch, ncta, tid);
   }
+}
+
+template <int BITS, bool XBF16, bool MBF16, bool P16 = false, bool PUSH = false>
+__global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const GemvArgs a, const Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  stream_body<BITS, XBF16, MBF16, P16, PUSH>(a, p, blockIdx.x, gridDim.x, smem_raw);
 }
 
 }  // namespace stream

@@ -208,6 +208,33 @@ def test_row_chunks_of_a_long_matrix_go_one_by_one():
     check_acc(acc, oracle_gemv(x, qt))
 
 
+@pytest.mark.parametrize(("widths", "m", "meta"), [
+    ((4, 3), 1, torch.float16), ((2, 8), 1, torch.bfloat16), ((3, 8, 4), 8, torch.float16), ((2, 2, 4, 8), 3, torch.float16),
+])
+def test_long_fused_shards_take_the_streaming_body(widths, m, meta):
+    """Two to four long matrices sharing an activation (a large model's gate / up): one launch,
+    every matrix on its own range of CTAs running the streaming body of its width."""
+    from dynquant_b200 import _lib, ops
+
+    # >= 296 row tiles each and a tile per resident warp (3552) together; one row count ragged
+    rows = {2: [28800, 28817], 3: [24000, 24017, 9600], 4: [19200, 19217, 9600, 9600]}[len(widths)]
+    shards = [random_qt(r, 512, b, meta=meta, seed=10 * i + b) for i, (r, b) in enumerate(zip(rows, widths))]
+    act = torch.bfloat16 if m != 3 else torch.float16
+    x = torch.randn(m, 512, generator=torch.Generator().manual_seed(m)).to(act).cuda()
+    before = int(_lib.load().dq_launch_count())
+    acc = ops.gemv_shards(x, shards, out_dtype=torch.float32)
+    assert int(_lib.load().dq_launch_count()) - before == 1
+    assert ops.last_kernel() == "gemv_mma_stream_multi_kernel"
+    col = 0
+    got = acc.cpu().numpy()
+    for s_, r in zip(shards, rows):
+        want = oracle_gemv(x, s_)
+        part = got[:, col:col + r]
+        scale = np.abs(want).max() + 1e-30
+        assert np.abs(part - want).max() / scale <= 1e-3, (s_.bits, r)
+        col += r
+
+
 # ---- (d) the head of the decode stack -----------------------------------------------------------
 
 
