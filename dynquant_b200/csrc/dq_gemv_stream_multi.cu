@@ -129,7 +129,11 @@ int32_t launch_gemv_stream_fused(const GemvArgs* jobs, const int* bits, int n, c
   // two to three blocks each) to cover the memory latency: below a row tile per resident warp it is
   // a chain of latencies per warp and the tiled kernel, which slices the reduction axis over warps,
   // is faster (measured, the gate / up pair of a 14B model, 2 x 17408 x 5120 at 3 and 4 bits, 14.7
-  // tiles per SM: the step of 40 such layers 3.22 ms here against 3.04 ms).
+  // tiles per SM: the step of 40 such layers 3.22 ms here against 3.04 ms).  A build with rings of
+  // six blocks and one CTA per SM -- the same bytes in flight from a third of the warps -- was
+  // measured on such sizes too: within +-9 % of the tiled kernel on single matrices (14336 x 4096,
+  // 17408 x 5120) and slower on the pair (35 against 29 us).  Those sizes sit at launch latency
+  // plus the decode-bound streaming rate in either kernel.
   if (total_tiles < static_cast<int64_t>(dev->sm_count) * stream::kWarps * 3) return DQ_OK;
   if (smem > static_cast<size_t>(dev->max_smem_optin)) return DQ_OK;
 
