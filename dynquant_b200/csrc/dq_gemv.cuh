@@ -41,9 +41,9 @@ int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cuda
 // Two to four long matrices that share an activation in one launch of the streaming kernel's body
 // (dq_gemv_stream_multi.cu).  *taken stays false, nothing launched, when they do not qualify.
 int32_t launch_gemv_stream_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken);
-// 9..64 activation rows against one matrix in one pass over the weights (dq_gemv_rows.cu).  *taken
-// stays false, nothing launched, when the matrix or the activation does not qualify.
-int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool* taken);
+// min_rows..64 activation rows against one matrix in one pass over the weights (dq_gemv_rows.cu).
+// *taken stays false, nothing launched, when the matrix or the activation does not qualify.
+int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool* taken, int min_rows = 9);
 // False when DQ_B200_GEMV_PATH=simt forces the SIMT kernels.
 bool mma_enabled_for_rows();
 // False when DQ_B200_NO_PDL drops the programmatic-dependent-launch attribute.

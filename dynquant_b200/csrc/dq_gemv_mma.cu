@@ -887,6 +887,30 @@ int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cuda
   return try_tile(jobs, bits, n, *dev, stream, taken, push);
 }
 
+// The tiled kernel slices the reduction axis 8, 4 or 2 ways over the warps of a CTA, in slices of
+// an even number of 128-value steps.  A step count with few such factors (K = 8960, 11008, 18944:
+// 70, 86 and 148 steps) on a matrix of few rows leaves it with CTAs for a fraction of the SMs; the
+// many-rows kernel, which slices the reduction axis over a cluster in any proportion, is then the
+// faster kernel at every number of activation rows (measured at 2 / 4 / 8 bits, one row: 3584 x
+// 18944 21 / 19 / 37 us against 25 / 26 / 52; 4096 x 11008 19 / 21 / 23 against 28 / 38 / 51;
+// 1536 x 8960 10 / 11 / 12 against 23 / 31 / 41).
+bool rows_kernel_first(const GemvArgs& a, int bits) {
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr || a.group_values != 128 || a.words_per_row % (4 * bits) != 0) return false;
+  const int steps = a.words_per_row / (4 * bits);
+  int kw = 8;
+  while (kw > 1 && (steps % kw != 0 || (steps / kw) % 2 != 0)) kw /= 2;
+  const int64_t ctas = ceil_div(ceil_div(a.rows, 16) * kw, 8);
+  if (ctas * 2 < dev->sm_count) return true;
+  // The tiled kernel stages the whole activation in fragment order (16 bytes per register of the
+  // plan, step and row).  Where that leaves little room for a ring (six rows x K = 14336; at 8 bits
+  // four rows) it passes the slices through shared memory block by block, every CTA again; the
+  // many-rows kernel does that once per eight row tiles and reads ahead meanwhile (4096 x 14336,
+  // eight rows, 2 / 3 / 4 / 8 bits: 21 / 28 / 16 / 30 us against 27 / 30 / 37 / 53).
+  const int64_t frag_bytes = static_cast<int64_t>(a.m) * steps * (bits == 8 ? 32 : 16) * 16;
+  return frag_bytes > (144 << 10);
+}
+
 int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const peerpush::Push* push) {
   const DeviceInfo* dev = device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
@@ -917,6 +941,13 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const 
         break;
     }
     if (taken || rc != DQ_OK) return rc;
+    // (not a stream of bytes for the streaming kernel:) the many-rows kernel where the tiled kernel
+    // is known to be the slower one
+    const int rows_switch = tuning_int("DQ_B200_ROWS_SMALL_M", -1);  // 0: never below nine rows; 1: wherever it qualifies
+    if (push == nullptr && (rows_switch == 1 || (rows_switch != 0 && rows_kernel_first(a, bits)))) {
+      rc = launch_gemv_rows(a, bits, stream, &taken, 1);
+      if (taken || rc != DQ_OK) return rc;
+    }
     rc = try_tile(&a, &bits, 1, *dev, stream, &taken, push);
     if (taken || rc != DQ_OK) return rc;
   }

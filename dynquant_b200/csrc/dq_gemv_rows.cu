@@ -1,15 +1,19 @@
-// 9..64 activation rows against one packed matrix in one pass over the weights (two from 33 rows on).
+// Many activation rows (9..64) against one packed matrix in one pass over the weights (two from 33
+// rows on) -- and the kernel for matrices the tiled kernel is a poor fit for, at any row count.
 //
 // The GEMV kernels take at most eight activation rows: the eight columns of one m16n8k16
 // accumulator.  More rows used to mean more passes (row chunks of eight, each decoding the
 // weights again, the later ones from L2).  Here a warp decodes the fragments of a 16-row x
-// 128-value step ONCE and feeds them to up to eight column blocks of eight activation rows each
+// 128-value step ONCE and feeds them to up to four column blocks of eight activation rows each
 // -- the decode, which bounds the GEMV kernels, is amortised over the blocks, and the tensor
 // pipe becomes the busy unit, as it should in a small-batch matrix product.
 //
 //   CTA       8 warps = 8 row tiles of 16 weight rows; warp w streams its tile's rows over the
-//             whole reduction axis through a private cp.async ring (the streaming kernel's
-//             plumbing: blocks of P steps, no barrier for weights).
+//             CTA's part of the reduction axis through a private cp.async ring (the streaming
+//             kernel's plumbing: blocks of P steps, no barrier for weights).
+//   cluster   matrices with too few rows for a CTA per SM (down-projections): the grid's y axis
+//             slices the reduction axis, the slices of one row group are a thread-block cluster
+//             and their sums meet in the cluster's first CTA through distributed shared memory.
 //   x         too large to stage whole (32 rows x 4096 values in fragment order: 256 KB), so it
 //             passes through shared memory in blocks of P steps shared by the CTA's warps: the raw
 //             rows of block b+2 travel by cp.async while block b is computed, all threads convert
@@ -18,10 +22,17 @@
 //   out       [m, rows] as the GEMV kernels write it; accumulation in fp32, scale and offset
 //             applied per step, one rounding.
 //
-// Replaces, for this band of row counts, the reference's dequantize + dense matmul
-// (runtime/ops.py:205-231): same result up to the summation order.  The host (dq_gemv.cu,
-// dq_gemv_shards_rows) falls back to row chunks when a matrix does not qualify.
+// Because the activation never has to fit shared memory whole and the reduction axis can be cut
+// in any proportion, this is also the faster kernel at 1..8 rows where the tiled kernel is not
+// at home (dq_gemv_mma.cu, rows_kernel_first): step counts with few factors of two (K = 8960,
+// 11008, 18944) on matrices of few rows, and activations of six to eight rows x K >= 12288.
+//
+// Replaces, above eight rows, the reference's dequantize + dense matmul (runtime/ops.py:205-231):
+// same result up to the summation order.  The hosts (dq_gemv.cu, dq_gemv_mma.cu) fall back to row
+// chunks / the tiled kernel when a matrix does not qualify.
 #include <algorithm>
+#include <atomic>
+#include <type_traits>
 
 #include "dq_gemv.cuh"
 #include "dq_gemv_mma_stream.cuh"
@@ -45,25 +56,36 @@ struct Params {
   uint32_t magic;
 };
 
+// Steps per block PP: the streaming kernel's (four at 2 / 3 / 4 bits, two at 8), or two at the low
+// widths too for reduction axes whose step count is even but not a multiple of four (K = 8960,
+// 11008: 70 and 86 steps) -- a row's metadata is then copied four bytes at a time.
+template <int BITS, int PP>
+struct Cfg {
+  static constexpr int P = PP;
+  static constexpr int UNIT = 4 * BITS;
+  static constexpr int BLOCK_BYTES = P * 2 * UNIT;
+  static constexpr int META_BYTES = 2 * P;
+};
+
 // Bytes of one column block's fragment region for one x block: 8 rows of fragments, the zero
 // block that lanes of absent rows read, and the two sums per (step, row).
-template <int BITS>
+template <int BITS, int PP>
 __host__ __device__ constexpr size_t region_bytes() {
-  using C = stream::Cfg<BITS>;
+  using C = Cfg<BITS, PP>;
   constexpr int NA = BITS == 8 ? 32 : 16;
   return (static_cast<size_t>(8) * (C::P * NA + 4) + NA) * 16 + static_cast<size_t>(C::P) * 8 * 4 * 2;
 }
 // One column block of a raw x block: 8 rows x P steps x 128 values of 16 bits.
-template <int BITS>
+template <int PP>
 __host__ __device__ constexpr size_t raw_bytes() {
-  return static_cast<size_t>(8) * stream::Cfg<BITS>::P * 256;
+  return static_cast<size_t>(8) * PP * 256;
 }
 
-template <int BITS>
+template <int BITS, int PP>
 size_t smem_bytes(int mb) {
-  using C = stream::Cfg<BITS>;
+  using C = Cfg<BITS, PP>;
   return static_cast<size_t>(kRingBlocks) * (C::BLOCK_BYTES + C::META_BYTES) * kThreads +
-         static_cast<size_t>(mb) * (kRawBuffers * raw_bytes<BITS>() + region_bytes<BITS>());
+         static_cast<size_t>(mb) * (kRawBuffers * raw_bytes<PP>() + region_bytes<BITS, PP>());
 }
 
 // Pipeline of one CTA, block b of P steps:
@@ -73,18 +95,46 @@ size_t smem_bytes(int mb) {
 //   x, frags  after compute(b): all threads convert raw(b+1) into the (single) fragment buffer,
 //             between two CTA barriers;
 //   compute   every warp: decode a step once, feed it to the column blocks.
-template <int BITS, bool XBF16, int MB>
+//
+// KSPLIT: the grid's y axis slices the reduction axis and the CTAs of one row group form a
+// thread-block cluster (1 x slices): every CTA runs the pipeline over its own range of blocks,
+// then the slices' sums meet in the first CTA of the cluster through distributed shared memory,
+// added in slice order (a fixed summation order: same bits on every run), and that CTA stores.
+// For matrices with too few rows to fill the SMs with one CTA per eight row tiles -- a
+// down-projection, 4096 x 14336.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
+}
+
+template <int BITS, bool XBF16, int MB, bool KSPLIT, int PP>
 __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a, const Params p) {
   using Plan = MmaPlan<BITS>;
-  using C = stream::Cfg<BITS>;
+  using C = Cfg<BITS, PP>;
   constexpr int P = C::P;
   constexpr int NB = kRingBlocks;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
   constexpr int STEP_WORDS = 4 * BITS;
   constexpr int STEP_BYTES = STEP_WORDS * 4;
-  constexpr size_t REGION = region_bytes<BITS>();
-  constexpr size_t RAW = raw_bytes<BITS>();
+  constexpr size_t REGION = region_bytes<BITS, PP>();
+  constexpr size_t RAW = raw_bytes<PP>();
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* ring_w = smem_raw;
@@ -104,6 +154,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
   const int tile = blockIdx.x * kWarps + warp;
   const bool live = tile < p.tiles;
   const int mbs = (a.m + 7) / 8;  // column blocks that have rows (the kernel is built for 2 or 4)
+  // this CTA's range of blocks of the reduction axis (all of them without KSPLIT)
+  const int slices = KSPLIT ? static_cast<int>(cluster_nctarank()) : 1;
+  const int slice = KSPLIT ? static_cast<int>(cluster_ctarank()) : 0;
+  const int blk_begin = KSPLIT ? (nblocks * slice) / slices : 0;
+  const int blk_end = KSPLIT ? (nblocks * (slice + 1)) / slices : nblocks;
 
   const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * C::UNIT;
   const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * C::META_BYTES;
@@ -131,20 +186,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
         const int pg = piece / PER_ROW;
         const int part = piece - pg * PER_ROW;
         const int row = min(tile * 16 + h * 8 + pg, a.rows - 1);
-        pf_src[h][i] = reinterpret_cast<const unsigned char*>(a.packed + static_cast<int64_t>(row) * a.words_per_row + part * 4);
+        pf_src[h][i] = reinterpret_cast<const unsigned char*>(a.packed + static_cast<int64_t>(row) * a.words_per_row + part * 4) +
+                       static_cast<size_t>(blk_begin) * P * STEP_BYTES;
       }
     }
     const int ra = min(tile * 16 + g, a.rows - 1);
     const int rb = min(tile * 16 + g + 8, a.rows - 1);
     const unsigned short* arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
-    pf_meta = arr + static_cast<int64_t>((t & 2) ? rb : ra) * a.num_groups;
+    pf_meta = arr + static_cast<int64_t>((t & 2) ? rb : ra) * a.num_groups + blk_begin * P;
   }
   const bool meta_lane = has_off || (t & 1) == 0;
   uint32_t pf_w = ring_w_s + lane * 16, pf_m = ring_m_s;
   const uint32_t ring_w_end = ring_w_s + lane * 16 + NB * (C::BLOCK_BYTES * kThreads);
-  int pf_blk = 0;
+  int pf_blk = blk_begin;
   auto prefetch_weights = [&]() {  // (no commit: the caller commits weights and raw x together)
-    if (live && pf_blk < nblocks) {
+    if (live && pf_blk < blk_end) {
 #pragma unroll
       for (int j = 0; j < P; ++j) {
 #pragma unroll
@@ -177,7 +233,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
   // ---- x, raw: block `blk` of every existing row into raw buffer blk % kRawBuffers, 16 bytes a piece ----
   constexpr int kRowPieces = P * 16;  // 16-byte pieces of one row of one block
   auto request_raw = [&](int blk) {
-    if (blk < nblocks) {
+    if (blk < blk_end) {
       const uint32_t dst0 = raw_s + static_cast<uint32_t>((blk % kRawBuffers) * MB * RAW);
       const unsigned char* src0 = static_cast<const unsigned char*>(a.x) + static_cast<size_t>(blk) * P * 256;
       const int pieces = a.m * kRowPieces;  // (raw rows are laid out 8 per column block, back to back: row r at r * P * 256)
@@ -214,14 +270,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
   stream::cp_async_commit();
   prefetch_weights();
   pdl_wait_prior_grid();
-  request_raw(0);
+  request_raw(blk_begin);
   stream::cp_async_commit();
-  request_raw(1);
+  request_raw(blk_begin + 1);
   stream::cp_async_commit();
   // groups so far: {w0}, {w1, raw0}, {raw1}; from here on one group per block: {w(b+2), raw(b+2)}
   stream::cp_async_wait<1>();  // raw0 (and w0, w1)
   __syncthreads();
-  convert(0);
+  convert(blk_begin);
   __syncthreads();
 
   float acc[MB][4];
@@ -233,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
   const unsigned char* wslot = ring_w_mine;
   const unsigned char* mslot = ring_m_quad;
   const unsigned char* const wslot_end = ring_w_mine + NB * (C::BLOCK_BYTES * kThreads);
-  for (int blk = 0; blk < nblocks; ++blk) {
+  for (int blk = blk_begin; blk < blk_end; ++blk) {
     __syncwarp();  // every lane is done with the ring slot about to be refilled
     prefetch_weights();
     request_raw(blk + 2);  // into the buffer raw(blk) was converted from
@@ -329,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
       wslot = ring_w_mine;
       mslot = ring_m_quad;
     }
-    if (blk + 1 < nblocks) {
+    if (blk + 1 < blk_end) {
       stream::cp_async_wait<1>();  // all but the youngest group: raw(blk + 1) is in
       __syncthreads();             // ... for every thread's pieces; and every warp is done with the fragments
       convert(blk + 1);
@@ -337,6 +393,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
     }
   }
   stream::cp_async_wait<0>();
+  if constexpr (KSPLIT) {
+    // Every CTA leaves its sums in its own shared memory ([MB][thread] float4, over the ring, which
+    // nobody reads any more); the cluster's first CTA adds them to its own in slice order.  Both
+    // cluster barriers are reached by every thread of every CTA: the second keeps a CTA's shared
+    // memory alive until the first CTA has read it.
+    __syncthreads();
+    float4* mine = reinterpret_cast<float4*>(smem_raw);
+#pragma unroll
+    for (int cb = 0; cb < MB; ++cb) mine[cb * kThreads + tid] = make_float4(acc[cb][0], acc[cb][1], acc[cb][2], acc[cb][3]);
+    cluster_sync_all();
+    if (slice == 0 && live) {
+      const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
+      for (int r = 1; r < slices; ++r) {
+#pragma unroll
+        for (int cb = 0; cb < MB; ++cb) {
+          const float4 v = ld_cluster_f4(base + (cb * kThreads + tid) * 16, static_cast<uint32_t>(r));
+          acc[cb][0] += v.x, acc[cb][1] += v.y, acc[cb][2] += v.z, acc[cb][3] += v.w;
+        }
+      }
+    }
+    cluster_sync_all();
+    if (slice != 0) return;
+  }
   if (live) {
     const int row_a = tile * 16 + g, row_b = row_a + 8;
 #pragma unroll
@@ -354,34 +433,98 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
   }
 }
 
-template <int BITS, int MB>
-int32_t launch_mb(const GemvArgs& a, const Params& p, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
-  const size_t smem = smem_bytes<BITS>(MB);
+// Clusters of `slices` CTAs of this kernel that the device holds at once (cached per kernel and
+// size: the query costs microseconds on a path whose launches take as long).
+// (TAG names the kernel build: every build has the same pointer type, so the type cannot.)
+template <int TAG, typename Kernel>
+int active_clusters(Kernel kernel, const cudaLaunchConfig_t& base, int slices) {
+  static std::atomic<int> cache[9] = {{-1}, {-1}, {-1}, {-1}, {-1}, {-1}, {-1}, {-1}, {-1}};
+  int n = cache[slices].load(std::memory_order_relaxed);
+  if (n >= 0) return n;
+  cudaLaunchConfig_t cfg = base;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = static_cast<unsigned>(slices);
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim.y = static_cast<unsigned>(slices);
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+  cache[slices].store(n, std::memory_order_relaxed);
+  return n;
+}
+
+// max_slices > 1: slice the reduction axis over a cluster.  The slice count is the largest one
+// (<= max_slices) whose clusters are all resident at once -- a second wave costs more than fewer
+// slices do (measured: 4096 x 14336, 32 row groups: 19 us with 4 slices, 36 with 8; clusters of
+// eight one-CTA-per-SM blocks also pack badly into the GPCs) -- and that still gives a CTA to half
+// of the SMs; `forced` takes max_slices as it is.
+template <int BITS, int MB, int PP>
+int32_t launch_mb(const GemvArgs& a, const Params& p, int max_slices, bool forced, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
+  const size_t smem = smem_bytes<BITS, PP>(MB);
   if (smem > static_cast<size_t>(dev.max_smem_optin)) return DQ_OK;  // not taken
-  auto run = [&](auto kernel) -> int32_t {
+  const int row_ctas = static_cast<int>(ceil_div(p.tiles, kWarps));
+  auto run = [&](auto kernel, auto tag) -> int32_t {
+    constexpr int TAG = decltype(tag)::value;
     DQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(p.tiles, kWarps)));
+    cfg.gridDim = dim3(static_cast<unsigned>(row_ctas));
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream_h;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    int slices = 1;
+    if (max_slices > 1) {
+      if (forced) {
+        if (active_clusters<TAG>(kernel, cfg, max_slices) < 1) return DQ_OK;
+        slices = max_slices;
+      } else {
+        for (int s = max_slices; s >= 2 && slices == 1; --s) {
+          if (active_clusters<TAG>(kernel, cfg, s) >= row_ctas) slices = s;
+        }
+        // ... and of the counts with the same longest slice, the smallest: same critical path, fewer CTAs
+        const int nblocks = p.steps / PP;
+        while (slices > 2 && ceil_div(nblocks, slices - 1) == ceil_div(nblocks, slices)) --slices;
+        if (slices == 1 || row_ctas * slices * 2 < dev.sm_count) return DQ_OK;  // not taken: the row chunks are faster
+      }
+    }
+    cfg.gridDim.y = static_cast<unsigned>(slices);
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
+    if (slices > 1) {  // the slices of one row group: one cluster
+      attr[nattr].id = cudaLaunchAttributeClusterDimension;
+      attr[nattr].val.clusterDim.x = 1;
+      attr[nattr].val.clusterDim.y = static_cast<unsigned>(slices);
+      attr[nattr].val.clusterDim.z = 1;
+      ++nattr;
+    }
+    if (pdl_enabled_for_rows()) {
+      attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+      ++nattr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled_for_rows() ? 1 : 0;
+    cfg.numAttrs = nattr;
     DQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, p));
     DQ_CHECK_LAUNCH("gemv rows");
     note_kernel("gemv_rows_kernel");
     *taken = true;
     return DQ_OK;
   };
-  return a.x_dtype == DQ_BF16 ? run(gemv_rows_kernel<BITS, true, MB>) : run(gemv_rows_kernel<BITS, false, MB>);
+  using Bf16 = std::integral_constant<int, BITS * 1000 + MB * 100 + PP * 10 + 1>;
+  using F16 = std::integral_constant<int, BITS * 1000 + MB * 100 + PP * 10>;
+  if (max_slices > 1) {
+    return a.x_dtype == DQ_BF16 ? run(gemv_rows_kernel<BITS, true, MB, true, PP>, Bf16{}) : run(gemv_rows_kernel<BITS, false, MB, true, PP>, F16{});
+  }
+  return a.x_dtype == DQ_BF16 ? run(gemv_rows_kernel<BITS, true, MB, false, PP>, Bf16{}) : run(gemv_rows_kernel<BITS, false, MB, false, PP>, F16{});
 }
 
-template <int BITS>
-int32_t launch_bits(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
-  using C = stream::Cfg<BITS>;
+template <int BITS, int PP>
+int32_t launch_blocks(const GemvArgs& a, int want_slices, bool forced, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
+  using C = Cfg<BITS, PP>;
   const int steps = a.words_per_row / (4 * BITS);
   if (steps % C::P != 0 || a.num_groups != steps || a.in_features != steps * 128) return DQ_OK;
   const auto align = static_cast<uintptr_t>(C::META_BYTES);
@@ -395,6 +538,9 @@ int32_t launch_bits(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t strea
   p.m_stride_u4 = C::P * (BITS == 8 ? 32 : 16) + 4;
   p.meta_bf16 = a.meta_dtype == DQ_BF16 ? 1 : 0;
   p.magic = a.x_dtype == DQ_BF16 ? 0x43004300u : 0x64006400u;
+  // slices of the reduction axis: at least two blocks each (the pipeline's prologue requests two)
+  const int slices = std::max(1, std::min(want_slices, (steps / C::P) / 2));
+  if (want_slices > 1 && slices < 2) return DQ_OK;  // too short to slice, too few rows not to
   // at most kMaxRows rows per launch (four column blocks): more rows, more passes
   const size_t x_row = static_cast<size_t>(a.in_features) * 2, out_row = static_cast<size_t>(a.out_stride) * dtype_size(a.out_dtype);
   const int passes = static_cast<int>(ceil_div(a.m, kMaxRows));
@@ -405,7 +551,9 @@ int32_t launch_bits(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t strea
     part.x = static_cast<const unsigned char*>(a.x) + r0 * x_row;
     part.out = static_cast<unsigned char*>(a.out) + r0 * out_row;
     bool ok = false;
-    const int32_t rc = part.m <= 16 ? launch_mb<BITS, 2>(part, p, dev, stream_h, &ok) : launch_mb<BITS, 4>(part, p, dev, stream_h, &ok);
+    const int32_t rc = part.m <= 8    ? launch_mb<BITS, 1, PP>(part, p, slices, forced, dev, stream_h, &ok)
+                       : part.m <= 16 ? launch_mb<BITS, 2, PP>(part, p, slices, forced, dev, stream_h, &ok)
+                                      : launch_mb<BITS, 4, PP>(part, p, slices, forced, dev, stream_h, &ok);
     if (rc != DQ_OK) return rc;
     if (!ok) return r0 == 0 ? DQ_OK : fail(DQ_ERR_UNSUPPORTED, "gemv rows: the second pass did not fit shared memory");
   }
@@ -413,24 +561,49 @@ int32_t launch_bits(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t strea
   return DQ_OK;
 }
 
+// Blocks of the streaming kernel's size where the step count allows, of two steps otherwise.
+template <int BITS>
+int32_t launch_bits(const GemvArgs& a, int want_slices, bool forced, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
+  constexpr int P = stream::Cfg<BITS>::P;
+  const int steps = a.words_per_row / (4 * BITS);
+  if constexpr (P > 2) {
+    if (steps % P != 0) return launch_blocks<BITS, 2>(a, want_slices, forced, dev, stream_h, taken);
+  }
+  return launch_blocks<BITS, P>(a, want_slices, forced, dev, stream_h, taken);
+}
+
 }  // namespace rowsk
 
-// 9..64 activation rows, one matrix, one pass.  *taken stays false (nothing launched) when the
-// matrix or the activation does not qualify: the caller then runs row chunks.
-int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool* taken) {
+// min_rows..64 activation rows, one matrix, one pass.  *taken stays false (nothing launched) when
+// the matrix or the activation does not qualify: the caller then runs row chunks (or, below nine
+// rows, the tiled kernel).
+int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool* taken, int min_rows) {
   *taken = false;
   const DeviceInfo* dev = device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
-  if (a.m <= 8 || a.m > 64) return DQ_OK;
+  if (a.m < min_rows || a.m > 64) return DQ_OK;
   // Where this kernel wins (measured on B200 against row chunks, 2/4/8 bits): matrices with a CTA
   // for at least two thirds of the SMs -- 14336 x 4096: 19.5 / 19.9 / 37.9 us against 25.4 / 26.0 /
   // 41.7 at 16 rows, 31 / 32 / 55 against 50 / 51 / 82 at 32 rows, 61 / 63 / 110 against 100 / 102 /
   // 164 at 64 rows.  On 4096 x 4096 (32 CTAs of eight row tiles on 148 SMs) the chunks are faster
   // (10 against 19 us at 16 rows): every CTA converts the whole activation for its own tiles, so
   // smaller CTAs do not pay either.
+  // Matrices with fewer rows than that and a long reduction axis (a down-projection, 4096 x 14336)
+  // slice the reduction axis over a cluster of up to eight CTAs per row group instead.
   const int rows_switch = tuning_int("DQ_B200_ROWS_KERNEL", -1);
   if (rows_switch == 0) return DQ_OK;
-  if (rows_switch != 1 && ceil_div(a.rows, 16 * rowsk::kWarps) * 3 < static_cast<int64_t>(dev->sm_count) * 2) return DQ_OK;
+  const int64_t row_ctas = ceil_div(a.rows, 16 * rowsk::kWarps);
+  int slices = 1;
+  if (row_ctas * 3 < static_cast<int64_t>(dev->sm_count) * 2) {
+    slices = static_cast<int>(std::min<int64_t>(8, dev->sm_count / row_ctas));
+  }
+  const int forced_slices = tuning_int("DQ_B200_ROWS_SLICES", -1);  // 0: never slice; n: n slices
+  if (forced_slices == 0 && slices > 1) {
+    if (rows_switch != 1) return DQ_OK;
+    slices = 1;
+  }
+  if (forced_slices > 0) slices = std::min(8, forced_slices);
+  const bool forced = rows_switch == 1 || forced_slices > 0;
   if (a.x_dtype != DQ_BF16 && a.x_dtype != DQ_F16) return DQ_OK;
   if (a.meta_dtype != DQ_BF16 && a.meta_dtype != DQ_F16) return DQ_OK;
   if (a.group_values != 128) return DQ_OK;
@@ -438,13 +611,13 @@ int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool*
   if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) return DQ_OK;
   switch (bits) {
     case 2:
-      return rowsk::launch_bits<2>(a, *dev, stream, taken);
+      return rowsk::launch_bits<2>(a, slices, forced, *dev, stream, taken);
     case 3:
-      return rowsk::launch_bits<3>(a, *dev, stream, taken);
+      return rowsk::launch_bits<3>(a, slices, forced, *dev, stream, taken);
     case 4:
-      return rowsk::launch_bits<4>(a, *dev, stream, taken);
+      return rowsk::launch_bits<4>(a, slices, forced, *dev, stream, taken);
     default:
-      return rowsk::launch_bits<8>(a, *dev, stream, taken);
+      return rowsk::launch_bits<8>(a, slices, forced, *dev, stream, taken);
   }
 }
 

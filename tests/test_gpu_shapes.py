@@ -164,6 +164,50 @@ def test_many_rows_on_a_large_matrix_take_one_pass_over_the_weights(m, bits):
     assert out.dtype == act and within_one_ulp_16(out, want)
 
 
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("rows,k,m", [(2048, 6144, 16), (4096 + 5, 14336, 9), (3072, 8192, 40), (8192, 8192, 64), (6144, 4096, 33)])
+def test_many_rows_on_a_matrix_with_few_rows_slice_the_reduction_axis(rows, k, m, bits):
+    """Matrices with too few rows for a CTA per SM (down-projections): the many-rows kernel's CTAs
+    of one row group form a thread-block cluster that slices the reduction axis; the slices' sums
+    are added in slice order by the cluster's first CTA -- every row against the oracle, and the
+    same bits on a second run."""
+    from dynquant_b200 import _lib, ops
+
+    meta = torch.bfloat16 if (m + bits) % 2 else torch.float16
+    qt = random_qt(rows, k, bits, meta=meta, seed=m + bits, offsets=bits != 2)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16).cuda()
+    before = int(_lib.load().dq_launch_count())
+    acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
+    assert int(_lib.load().dq_launch_count()) - before == (m + 31) // 32
+    assert ops.last_kernel() == "gemv_rows_kernel"
+    check_acc(acc, oracle_gemv(x, qt))
+    again = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
+    assert torch.equal(acc, again)
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("rows,k,m", [(1536, 8960, 1), (1536 + 3, 8960, 8), (2048, 11008, 3), (4096, 14336, 8), (4096, 14336, 6)])
+def test_matrices_the_tiled_kernel_is_a_poor_fit_for_take_the_many_rows_kernel(rows, k, m, bits):
+    """One to eight activation rows: step counts with few factors of two (70 and 86 steps -- blocks
+    of two steps at the low widths) on matrices of few rows, and six to eight rows x a long reduction
+    axis (the staged activation would fill the tiled kernel's shared memory).  Against the oracle,
+    with a bias, through the operator (16-bit output = the accumulator rounded once)."""
+    from dynquant_b200 import ops
+
+    meta = torch.float16 if (m + bits) % 2 else torch.bfloat16
+    act = torch.float16 if m == 3 else torch.bfloat16
+    qt = random_qt(rows, k, bits, meta=meta, seed=m * 10 + bits, offsets=bits != 8)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(act).cuda()
+    bias = torch.randn(rows, generator=torch.Generator().manual_seed(7)).to(act).cuda()
+    acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, 128, k, out_dtype=torch.float32)
+    assert ops.last_kernel() == "gemv_rows_kernel"
+    want = oracle_gemv(x, qt)
+    check_acc(acc, want)
+    out = ops.gemv_shards(x, [qt], bias)
+    assert ops.last_kernel() == "gemv_rows_kernel"
+    assert out.dtype == act and within_one_ulp_16(out, want + bias.float().cpu().numpy()[None, :])
+
+
 def test_many_rows_fused_shards_with_a_bias():
     from dynquant_b200 import _lib, ops
 
