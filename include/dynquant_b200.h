@@ -150,12 +150,14 @@ DQ_API int32_t dq_gemv_shards(const void* x, int32_t x_dtype, int64_t m, const d
                               int32_t num_shards, const void* bias, void* out, int64_t out_stride,
                               int32_t out_dtype, void* stream);
 /* dq_gemv_shards for up to DQ_GEMV_CHUNKED_MAX_ROWS activation rows (the 9..64-row band in which
- * the reference already pays for dequantize + dense matmul, runtime/ops.py:205-231).  A large
- * shard goes through the many-rows kernel: one pass over its weights per 32 rows, a step's
- * fragments decoded once for all of them.  Otherwise the rows are cut into ceil(m / 8) chunks of
- * equal size (+-1) and up to four (chunk, shard) pairs leave as one launch of the tiled kernel, so
- * that a matrix is read from HBM once and by the other chunks from L2; matrices long enough for
- * the streaming kernel go chunk by chunk.  Same arguments and results as dq_gemv_shards. */
+ * the reference already pays for dequantize + dense matmul, runtime/ops.py:205-231).  A shard
+ * with 128-value groups and enough work to fill half of the SMs goes through the many-rows kernel:
+ * one pass over its weights per 32 rows, a step's fragments decoded once for all of them (shards
+ * of few rows slice the reduction axis over a thread-block cluster).  Otherwise the rows are cut
+ * into ceil(m / 8) chunks of equal size (+-1) and up to four (chunk, shard) pairs leave as one
+ * launch of the tiled kernel, so that a matrix is read from HBM once and by the other chunks from
+ * L2; matrices long enough for the streaming kernel go chunk by chunk.  Same arguments and
+ * results as dq_gemv_shards. */
 DQ_API int32_t dq_gemv_shards_rows(const void* x, int32_t x_dtype, int64_t m, const dq_weight* shards,
                                    int32_t num_shards, const void* bias, void* out, int64_t out_stride,
                                    int32_t out_dtype, void* stream);
