@@ -2,8 +2,9 @@
 
 The fixed-shape tests pin the corners that were thought of; this one draws (rows, reduction
 length, width, group size, activation rows, dtypes, offsets) from the ranges the kernels split
-on -- short / tiled / streaming row counts with ragged tails, reduction axes of one to 112
-steps, 64- and 128-value groups, per-row groups, odd lengths that only the general kernel takes
+on -- short / tiled / streaming row counts with ragged tails, reduction axes of one to 148
+steps (with many and with few factors of two), 64- and 128-value groups, per-row groups, odd
+lengths that only the general kernel takes
 -- and checks fp32 accumulators within 1e-3 of the oracle (the reference's own definition,
 ``tests/test_kernels_parity.py:198-199``: ``x.float() @ dequant(fp32).T``).  It also records
 which kernel every case took and requires that the draw reached all of them, so a dispatch
@@ -28,7 +29,7 @@ PER_ROW = -1
 
 
 def _draw(rng: random.Random):
-    kind = rng.choice(["short", "tiled", "tiled", "stream", "rows_x_long_k", "general"])
+    kind = rng.choice(["short", "tiled", "tiled", "stream", "rows_x_long_k", "few_factors", "general"])
     bits = rng.choice([2, 3, 4, 8])
     x_dtype = rng.choice([torch.bfloat16, torch.float16])
     meta = rng.choice([torch.float16, torch.bfloat16])
@@ -45,6 +46,8 @@ def _draw(rng: random.Random):
         rows, k = rng.randint(18944, 36000), 512 * rng.choice([1, 2, 4])
     elif kind == "rows_x_long_k":
         rows, k, m = rng.randint(16, 700), 128 * rng.choice([56, 96, 112]), rng.choice([4, 8, 8])
+    elif kind == "few_factors":  # step counts the tiled kernel slices badly, few rows: the many-rows kernel, sliced over a cluster
+        rows, k = rng.randint(1300, 4200), 128 * rng.choice([70, 86, 148, 74, 106])
     else:  # lengths and groups only the SIMT kernels take
         rows = rng.randint(1, 200)
         k, group = rng.choice([(100, PER_ROW), (320, 32), (4304, 128), (72, PER_ROW), (2048 + 64, 64)])
@@ -59,7 +62,7 @@ def test_random_shapes_match_the_oracle_and_reach_every_kernel():
     seen: dict[str, int] = {}
     for case in range(160):
         kind, rows, k, bits, group, m, x_dtype, meta, offsets = _draw(rng)
-        if kind == "stream":  # (generated on the device: encoding 70 M values on the host takes seconds)
+        if kind in ("stream", "few_factors"):  # (generated on the device: encoding 70 M values on the host takes seconds)
             qt = random_qt(rows, k, bits, group=group, meta=meta, seed=case, offsets=offsets)
         else:
             qt = make_quant(rows, k, group, bits, meta, seed=case, with_offsets=offsets).to("cuda")
@@ -73,7 +76,7 @@ def test_random_shapes_match_the_oracle_and_reach_every_kernel():
         err = float(np.abs(got - want).max() / scale)
         assert err <= 1e-3, (case, kind, rows, k, bits, group, m, x_dtype, meta, offsets, name, err)
         assert np.linalg.norm(got - want) / (np.linalg.norm(want) + 1e-30) <= 1e-3, (case, kind, name)
-    for kernel in ("gemv_mma_tile_kernel", "gemv_mma_stream_kernel", "gemv_fast_kernel", "gemv_general_kernel"):
+    for kernel in ("gemv_mma_tile_kernel", "gemv_mma_stream_kernel", "gemv_rows_kernel", "gemv_fast_kernel", "gemv_general_kernel"):
         assert seen.get(kernel, 0) >= 3, (kernel, seen)
 
 
