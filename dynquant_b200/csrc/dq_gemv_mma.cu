@@ -896,7 +896,7 @@ int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cuda
 // 1536 x 8960 10 / 11 / 12 against 23 / 31 / 41).
 bool rows_kernel_first(const GemvArgs& a, int bits) {
   const DeviceInfo* dev = device_info();
-  if (dev == nullptr || a.group_values != 128 || a.words_per_row % (4 * bits) != 0) return false;
+  if (dev == nullptr || (a.group_values != 128 && a.group_values != 64) || a.words_per_row % (4 * bits) != 0) return false;
   const int steps = a.words_per_row / (4 * bits);
   int kw = 8;
   while (kw > 1 && (steps % kw != 0 || (steps / kw) % 2 != 0)) kw /= 2;
@@ -914,8 +914,15 @@ bool rows_kernel_first(const GemvArgs& a, int bits) {
 int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const peerpush::Push* push) {
   const DeviceInfo* dev = device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
-  if (a.group_values == kStepValues / 2) {  // two groups per step: only the tiled kernel does that
+  // the many-rows kernel where the tiled kernel is known to be the slower one (rows_kernel_first)
+  const int rows_switch = tuning_int("DQ_B200_ROWS_SMALL_M", -1);  // 0: never below nine rows; 1: wherever it qualifies
+  const bool rows_first = push == nullptr && (rows_switch == 1 || (rows_switch != 0 && rows_kernel_first(a, bits)));
+  if (a.group_values == kStepValues / 2) {  // two groups per step: the tiled and the many-rows kernel do that
     bool taken = false;
+    if (rows_first) {
+      const int32_t rc = launch_gemv_rows(a, bits, stream, &taken, 1);
+      if (taken || rc != DQ_OK) return rc;
+    }
     const int32_t rc = try_tile(&a, &bits, 1, *dev, stream, &taken, push);
     return (rc == DQ_OK && !taken) ? DQ_ERR_UNSUPPORTED : rc;
   }
@@ -941,10 +948,8 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const 
         break;
     }
     if (taken || rc != DQ_OK) return rc;
-    // (not a stream of bytes for the streaming kernel:) the many-rows kernel where the tiled kernel
-    // is known to be the slower one
-    const int rows_switch = tuning_int("DQ_B200_ROWS_SMALL_M", -1);  // 0: never below nine rows; 1: wherever it qualifies
-    if (push == nullptr && (rows_switch == 1 || (rows_switch != 0 && rows_kernel_first(a, bits)))) {
+    // (not a stream of bytes for the streaming kernel)
+    if (rows_first) {
       rc = launch_gemv_rows(a, bits, stream, &taken, 1);
       if (taken || rc != DQ_OK) return rc;
     }

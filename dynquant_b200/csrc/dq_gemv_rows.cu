@@ -59,21 +59,27 @@ struct Params {
 // Steps per block PP: the streaming kernel's (four at 2 / 3 / 4 bits, two at 8), or two at the low
 // widths too for reduction axes whose step count is even but not a multiple of four (K = 8960,
 // 11008: 70 and 86 steps) -- a row's metadata is then copied four bytes at a time.
-template <int BITS, int PP>
+//
+// G64: 64-value groups, two per step.  A row's metadata is twice as long, the activation's sums are
+// per (step, group), and a lane's fragments belong half to one group and half to the other (at 3
+// bits: the quad's lane pairs hold one group each) -- the layout of dq_mma_stage.cuh -- so a step's
+// mma feed two accumulators per column block, scaled separately.
+template <int BITS, int PP, bool G64 = false>
 struct Cfg {
   static constexpr int P = PP;
+  static constexpr int GPS = G64 ? 2 : 1;  // groups per step
   static constexpr int UNIT = 4 * BITS;
   static constexpr int BLOCK_BYTES = P * 2 * UNIT;
-  static constexpr int META_BYTES = 2 * P;
+  static constexpr int META_BYTES = 2 * P * GPS;
 };
 
 // Bytes of one column block's fragment region for one x block: 8 rows of fragments, the zero
 // block that lanes of absent rows read, and the two sums per (step, row).
-template <int BITS, int PP>
+template <int BITS, int PP, bool G64>
 __host__ __device__ constexpr size_t region_bytes() {
-  using C = Cfg<BITS, PP>;
+  using C = Cfg<BITS, PP, G64>;
   constexpr int NA = BITS == 8 ? 32 : 16;
-  return (static_cast<size_t>(8) * (C::P * NA + 4) + NA) * 16 + static_cast<size_t>(C::P) * 8 * 4 * 2;
+  return (static_cast<size_t>(8) * (C::P * NA + 4) + NA) * 16 + static_cast<size_t>(C::P) * C::GPS * 8 * 4 * 2;
 }
 // One column block of a raw x block: 8 rows x P steps x 128 values of 16 bits.
 template <int PP>
@@ -81,11 +87,11 @@ __host__ __device__ constexpr size_t raw_bytes() {
   return static_cast<size_t>(8) * PP * 256;
 }
 
-template <int BITS, int PP>
+template <int BITS, int PP, bool G64>
 size_t smem_bytes(int mb) {
-  using C = Cfg<BITS, PP>;
+  using C = Cfg<BITS, PP, G64>;
   return static_cast<size_t>(kRingBlocks) * (C::BLOCK_BYTES + C::META_BYTES) * kThreads +
-         static_cast<size_t>(mb) * (kRawBuffers * raw_bytes<PP>() + region_bytes<BITS, PP>());
+         static_cast<size_t>(mb) * (kRawBuffers * raw_bytes<PP>() + region_bytes<BITS, PP, G64>());
 }
 
 // Pipeline of one CTA, block b of P steps:
@@ -123,17 +129,39 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t ct
   return v;
 }
 
-template <int BITS, bool XBF16, int MB, bool KSPLIT, int PP>
+// One lane's fragment source of one row of one step with 64-value groups at 2 / 4 / 8 bits: the two
+// half units (16 values of each group), 2 * UNIT bytes apart.
+template <int BITS>
+__device__ __forceinline__ void read_half_units(const unsigned char* src, uint32_t* w) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const unsigned char* q = src + half * 2 * (4 * BITS);
+    if constexpr (BITS == 2) {
+      w[half] = *reinterpret_cast<const uint32_t*>(q);
+    } else if constexpr (BITS == 4) {
+      const uint2 v = *reinterpret_cast<const uint2*>(q);
+      w[2 * half] = v.x, w[2 * half + 1] = v.y;
+    } else {
+      const uint4 v = *reinterpret_cast<const uint4*>(q);
+      w[4 * half] = v.x, w[4 * half + 1] = v.y, w[4 * half + 2] = v.z, w[4 * half + 3] = v.w;
+    }
+  }
+}
+
+template <int BITS, bool XBF16, int MB, bool KSPLIT, int PP, bool G64>
 __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a, const Params p) {
   using Plan = MmaPlan<BITS>;
-  using C = Cfg<BITS, PP>;
+  using C = Cfg<BITS, PP, G64>;
+  constexpr int GPS = C::GPS;
+  constexpr bool HALVES = G64 && BITS != 3;  // groups = halves of a lane's registers
+  [[maybe_unused]] constexpr bool QUADS = G64 && BITS == 3;  // groups = the quad's lane pairs
   constexpr int P = C::P;
   constexpr int NB = kRingBlocks;
   constexpr int NA = Plan::kARegs;
   constexpr int QU = NA / 4;
   constexpr int STEP_WORDS = 4 * BITS;
   constexpr int STEP_BYTES = STEP_WORDS * 4;
-  constexpr size_t REGION = region_bytes<BITS, PP>();
+  constexpr size_t REGION = region_bytes<BITS, PP, G64>();
   constexpr size_t RAW = raw_bytes<PP>();
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -163,7 +191,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
   const uint32_t ring_w_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_w)) + (tid - lane) * C::UNIT;
   const uint32_t ring_m_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring_m)) + tid * C::META_BYTES;
   const uint32_t raw_s = static_cast<uint32_t>(__cvta_generic_to_shared(raw));
-  const unsigned char* ring_w_mine = ring_w + tid * C::UNIT;
+  const unsigned char* ring_w_mine = HALVES ? ring_w + (tid & ~3) * C::UNIT + t * (C::UNIT / 2) : ring_w + tid * C::UNIT;
   const unsigned char* ring_m_quad = ring_m + (tid & ~3) * C::META_BYTES;
 
   pdl_launch_dependents();
@@ -193,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
     const int ra = min(tile * 16 + g, a.rows - 1);
     const int rb = min(tile * 16 + g + 8, a.rows - 1);
     const unsigned short* arr = reinterpret_cast<const unsigned short*>((t & 1) ? a.offsets : a.scales);
-    pf_meta = arr + static_cast<int64_t>((t & 2) ? rb : ra) * a.num_groups + blk_begin * P;
+    pf_meta = arr + static_cast<int64_t>((t & 2) ? rb : ra) * a.num_groups + blk_begin * P * GPS;
   }
   const bool meta_lane = has_off || (t & 1) == 0;
   uint32_t pf_w = ring_w_s + lane * 16, pf_m = ring_m_s;
@@ -220,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
 #pragma unroll
         for (int i = 0; i < NSRC; ++i) pf_src[h][i] += P * STEP_BYTES;
       }
-      pf_meta += P;
+      pf_meta += P * GPS;
     }
     pf_w += C::BLOCK_BYTES * kThreads;
     pf_m += C::META_BYTES * kThreads;
@@ -254,14 +282,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
       unsigned char* region = frag + cb * REGION;
       uint4* xb = reinterpret_cast<uint4*>(region);
       float* xsum = reinterpret_cast<float*>(xb + 8 * p.m_stride_u4 + NA);
-      float* xneg = xsum + P * 8;
+      float* xneg = xsum + P * GPS * 8;
       GemvArgs sub = {};
       sub.x = raw + (static_cast<size_t>(blk % kRawBuffers) * MB + cb) * RAW;
       sub.x_dtype = a.x_dtype;
       sub.in_features = P * 128;  // the raw block's row pitch
       sub.m = min(8, a.m - cb * 8);
       // (rows that do not exist: their fragments are the zero block, which sits after row `m`)
-      stage_units<BITS, XBF16, false, true>(sub, 0, P, p.m_stride_u4, xb, xsum, xneg, stid, kGroupThreads, nullptr, false);
+      stage_units<BITS, XBF16, G64, true>(sub, 0, P, p.m_stride_u4, xb, xsum, xneg, stid, kGroupThreads, nullptr, false);
     }
   };
 
@@ -297,11 +325,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
     stream::cp_async_wait<2>();  // all but the two youngest groups: w(blk) is in
     __syncwarp();
     if (live) {
-      uint32_t mc[4][P / 2];
+      constexpr int MW = C::META_BYTES / 4;  // 32-bit words of one metadata array of a block
+      uint32_t mc[4][MW];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         if (has_off || (i & 1) == 0) {
-          if constexpr (P == 4) {
+          if constexpr (MW == 4) {
+            const uint4 v = *reinterpret_cast<const uint4*>(mslot + i * C::META_BYTES);
+            mc[i][0] = v.x, mc[i][1] = v.y, mc[i][2] = v.z, mc[i][3] = v.w;
+          } else if constexpr (MW == 2) {
             const uint2 v = *reinterpret_cast<const uint2*>(mslot + i * C::META_BYTES);
             mc[i][0] = v.x, mc[i][1] = v.y;
           } else {
@@ -312,21 +344,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
 #pragma unroll
       for (int j = 0; j < P; ++j) {
         uint32_t wa[BITS], wb[BITS];
-        stream::read_unit<BITS>(wslot + (j * 2 + 0) * (C::UNIT * kThreads), wa);
-        stream::read_unit<BITS>(wslot + (j * 2 + 1) * (C::UNIT * kThreads), wb);
+        if constexpr (HALVES) {
+          read_half_units<BITS>(wslot + (j * 2 + 0) * (C::UNIT * kThreads), wa);
+          read_half_units<BITS>(wslot + (j * 2 + 1) * (C::UNIT * kThreads), wb);
+        } else {
+          stream::read_unit<BITS>(wslot + (j * 2 + 0) * (C::UNIT * kThreads), wa);
+          stream::read_unit<BITS>(wslot + (j * 2 + 1) * (C::UNIT * kThreads), wb);
+        }
         uint32_t aa[NA], ab[NA];
         decode_unit<BITS>(wa, magic, aa);
         decode_unit<BITS>(wb, magic, ab);
         unbias_fragments<XBF16, NA>(aa);
         unbias_fragments<XBF16, NA>(ab);
-        auto meta_f32 = [&](int i) -> float {
-          const uint32_t reg = mc[i][j / 2];
-          if (mbf) return __uint_as_float((j & 1) ? (reg & 0xFFFF0000u) : (reg << 16));
+        // halfword `hw` of metadata array i of this block
+        auto meta_f32 = [&](int i, int hw) -> float {
+          const uint32_t reg = mc[i][hw / 2];
+          if (mbf) return __uint_as_float((hw & 1) ? (reg & 0xFFFF0000u) : (reg << 16));
           const __half2 hh = *reinterpret_cast<const __half2*>(&reg);
-          return (j & 1) ? __high2float(hh) : __low2float(hh);
+          return (hw & 1) ? __high2float(hh) : __low2float(hh);
         };
-        const float sc_a = meta_f32(0), sc_b = meta_f32(2);
-        const float of_a = has_off ? meta_f32(1) : 0.0f, of_b = has_off ? meta_f32(3) : 0.0f;
         // The column blocks' accumulators are independent: their mma are interleaved, so that a
         // warp has MB chains in flight instead of one chain of 2 * QU dependent mma per block
         // (with eight warps on the SM nothing else would hide that latency).
@@ -341,40 +377,126 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_rows_kernel(const GemvArgs a
           bsrc[cb] = mine ? xb + g * p.m_stride_u4 + t + j * (QU * 4) : xb + max(0, min(m_here, 8)) * p.m_stride_u4;
           bstep[cb] = mine ? 4 : 0;
         }
+        if constexpr (!G64) {
 #pragma unroll
-        for (int q = 0; q < QU; ++q) {
-          uint4 b[MB];
+          for (int q = 0; q < QU; ++q) {
+            uint4 b[MB];
 #pragma unroll
-          for (int cb = 0; cb < MB; ++cb) b[cb] = bsrc[cb][q * bstep[cb]];
+            for (int cb = 0; cb < MB; ++cb) b[cb] = bsrc[cb][q * bstep[cb]];
+#pragma unroll
+            for (int cb = 0; cb < MB; ++cb) {
+              if (q == 0) {
+                mma_16816<XBF16, true>(d[cb], aa[0], ab[0], aa[1], ab[1], b[cb].x, b[cb].y);
+              } else {
+                mma_16816<XBF16, false>(d[cb], aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b[cb].x, b[cb].y);
+              }
+            }
+#pragma unroll
+            for (int cb = 0; cb < MB; ++cb) {
+              mma_16816<XBF16, false>(d[cb], aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b[cb].z, b[cb].w);
+            }
+          }
+          const float sc_a = meta_f32(0, j), sc_b = meta_f32(2, j);
+          const float of_a = has_off ? meta_f32(1, j) : 0.0f, of_b = has_off ? meta_f32(3, j) : 0.0f;
 #pragma unroll
           for (int cb = 0; cb < MB; ++cb) {
-            if (q == 0) {
-              mma_16816<XBF16, true>(d[cb], aa[0], ab[0], aa[1], ab[1], b[cb].x, b[cb].y);
-            } else {
-              mma_16816<XBF16, false>(d[cb], aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b[cb].x, b[cb].y);
+            const uint4* xb = reinterpret_cast<const uint4*>(frag + cb * REGION);
+            const float* xsum = reinterpret_cast<const float*>(xb + 8 * p.m_stride_u4 + NA);
+            const float* xneg = xsum + P * 8;
+            const float2 xs2 = *reinterpret_cast<const float2*>(xsum + j * 8 + 2 * t);
+            const float2 xn2 = *reinterpret_cast<const float2*>(xneg + j * 8 + 2 * t);
+            acc[cb][0] = fmaf(sc_a, d[cb][0] + xn2.x, acc[cb][0]);
+            acc[cb][1] = fmaf(sc_a, d[cb][1] + xn2.y, acc[cb][1]);
+            acc[cb][2] = fmaf(sc_b, d[cb][2] + xn2.x, acc[cb][2]);
+            acc[cb][3] = fmaf(sc_b, d[cb][3] + xn2.y, acc[cb][3]);
+            if (has_off) {
+              acc[cb][0] = fmaf(of_a, xs2.x, acc[cb][0]);
+              acc[cb][1] = fmaf(of_a, xs2.y, acc[cb][1]);
+              acc[cb][2] = fmaf(of_b, xs2.x, acc[cb][2]);
+              acc[cb][3] = fmaf(of_b, xs2.y, acc[cb][3]);
+            }
+          }
+        } else {
+          // two accumulators per column block: d the step's first group, e its second
+          float e[MB][4];
+          if constexpr (HALVES) {  // the first half of a lane's registers is the first group's
+#pragma unroll
+            for (int q = 0; q < QU / 2; ++q) {
+              uint4 b0[MB], b1[MB];
+#pragma unroll
+              for (int cb = 0; cb < MB; ++cb) {
+                b0[cb] = bsrc[cb][q * bstep[cb]];
+                b1[cb] = bsrc[cb][(q + QU / 2) * bstep[cb]];
+              }
+#pragma unroll
+              for (int cb = 0; cb < MB; ++cb) {
+                if (q == 0) {
+                  mma_16816<XBF16, true>(d[cb], aa[0], ab[0], aa[1], ab[1], b0[cb].x, b0[cb].y);
+                  mma_16816<XBF16, true>(e[cb], aa[NA / 2], ab[NA / 2], aa[NA / 2 + 1], ab[NA / 2 + 1], b1[cb].x, b1[cb].y);
+                } else {
+                  mma_16816<XBF16, false>(d[cb], aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b0[cb].x, b0[cb].y);
+                  mma_16816<XBF16, false>(e[cb], aa[NA / 2 + 4 * q], ab[NA / 2 + 4 * q], aa[NA / 2 + 4 * q + 1], ab[NA / 2 + 4 * q + 1],
+                                          b1[cb].x, b1[cb].y);
+                }
+              }
+#pragma unroll
+              for (int cb = 0; cb < MB; ++cb) {
+                mma_16816<XBF16, false>(d[cb], aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b0[cb].z, b0[cb].w);
+                mma_16816<XBF16, false>(e[cb], aa[NA / 2 + 4 * q + 2], ab[NA / 2 + 4 * q + 2], aa[NA / 2 + 4 * q + 3],
+                                        ab[NA / 2 + 4 * q + 3], b1[cb].z, b1[cb].w);
+              }
+            }
+          } else {  // QUADS: lanes 0,1 of a quad hold the first group, 2,3 the second; the other pair feeds a zero B
+#pragma unroll
+            for (int q = 0; q < QU; ++q) {
+              uint4 b0[MB], b1[MB];
+#pragma unroll
+              for (int cb = 0; cb < MB; ++cb) {
+                const uint4 v = bsrc[cb][q * bstep[cb]];
+                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                b0[cb] = (t < 2) ? v : z;
+                b1[cb] = (t < 2) ? z : v;
+              }
+#pragma unroll
+              for (int cb = 0; cb < MB; ++cb) {
+                if (q == 0) {
+                  mma_16816<XBF16, true>(d[cb], aa[0], ab[0], aa[1], ab[1], b0[cb].x, b0[cb].y);
+                  mma_16816<XBF16, true>(e[cb], aa[0], ab[0], aa[1], ab[1], b1[cb].x, b1[cb].y);
+                } else {
+                  mma_16816<XBF16, false>(d[cb], aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b0[cb].x, b0[cb].y);
+                  mma_16816<XBF16, false>(e[cb], aa[4 * q], ab[4 * q], aa[4 * q + 1], ab[4 * q + 1], b1[cb].x, b1[cb].y);
+                }
+              }
+#pragma unroll
+              for (int cb = 0; cb < MB; ++cb) {
+                mma_16816<XBF16, false>(d[cb], aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b0[cb].z, b0[cb].w);
+                mma_16816<XBF16, false>(e[cb], aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b1[cb].z, b1[cb].w);
+              }
             }
           }
 #pragma unroll
-          for (int cb = 0; cb < MB; ++cb) {
-            mma_16816<XBF16, false>(d[cb], aa[4 * q + 2], ab[4 * q + 2], aa[4 * q + 3], ab[4 * q + 3], b[cb].z, b[cb].w);
-          }
-        }
+          for (int half = 0; half < 2; ++half) {
+            const float sc_a = meta_f32(0, 2 * j + half), sc_b = meta_f32(2, 2 * j + half);
+            const float of_a = has_off ? meta_f32(1, 2 * j + half) : 0.0f, of_b = has_off ? meta_f32(3, 2 * j + half) : 0.0f;
 #pragma unroll
-        for (int cb = 0; cb < MB; ++cb) {
-          const uint4* xb = reinterpret_cast<const uint4*>(frag + cb * REGION);
-          const float* xsum = reinterpret_cast<const float*>(xb + 8 * p.m_stride_u4 + NA);
-          const float* xneg = xsum + P * 8;
-          const float2 xs2 = *reinterpret_cast<const float2*>(xsum + j * 8 + 2 * t);
-          const float2 xn2 = *reinterpret_cast<const float2*>(xneg + j * 8 + 2 * t);
-          acc[cb][0] = fmaf(sc_a, d[cb][0] + xn2.x, acc[cb][0]);
-          acc[cb][1] = fmaf(sc_a, d[cb][1] + xn2.y, acc[cb][1]);
-          acc[cb][2] = fmaf(sc_b, d[cb][2] + xn2.x, acc[cb][2]);
-          acc[cb][3] = fmaf(sc_b, d[cb][3] + xn2.y, acc[cb][3]);
-          if (has_off) {
-            acc[cb][0] = fmaf(of_a, xs2.x, acc[cb][0]);
-            acc[cb][1] = fmaf(of_a, xs2.y, acc[cb][1]);
-            acc[cb][2] = fmaf(of_b, xs2.x, acc[cb][2]);
-            acc[cb][3] = fmaf(of_b, xs2.y, acc[cb][3]);
+            for (int cb = 0; cb < MB; ++cb) {
+              const float* dd = half == 0 ? d[cb] : e[cb];
+              const uint4* xb = reinterpret_cast<const uint4*>(frag + cb * REGION);
+              const float* xsum = reinterpret_cast<const float*>(xb + 8 * p.m_stride_u4 + NA);
+              const float* xneg = xsum + P * GPS * 8;
+              const float2 xs2 = *reinterpret_cast<const float2*>(xsum + (j * 2 + half) * 8 + 2 * t);
+              const float2 xn2 = *reinterpret_cast<const float2*>(xneg + (j * 2 + half) * 8 + 2 * t);
+              acc[cb][0] = fmaf(sc_a, dd[0] + xn2.x, acc[cb][0]);
+              acc[cb][1] = fmaf(sc_a, dd[1] + xn2.y, acc[cb][1]);
+              acc[cb][2] = fmaf(sc_b, dd[2] + xn2.x, acc[cb][2]);
+              acc[cb][3] = fmaf(sc_b, dd[3] + xn2.y, acc[cb][3]);
+              if (has_off) {
+                acc[cb][0] = fmaf(of_a, xs2.x, acc[cb][0]);
+                acc[cb][1] = fmaf(of_a, xs2.y, acc[cb][1]);
+                acc[cb][2] = fmaf(of_b, xs2.x, acc[cb][2]);
+                acc[cb][3] = fmaf(of_b, xs2.y, acc[cb][3]);
+              }
+            }
           }
         }
       }
@@ -463,9 +585,9 @@ int active_clusters(Kernel kernel, const cudaLaunchConfig_t& base, int slices) {
 // slices do (measured: 4096 x 14336, 32 row groups: 19 us with 4 slices, 36 with 8; clusters of
 // eight one-CTA-per-SM blocks also pack badly into the GPCs) -- and that still gives a CTA to half
 // of the SMs; `forced` takes max_slices as it is.
-template <int BITS, int MB, int PP>
+template <int BITS, int MB, int PP, bool G64>
 int32_t launch_mb(const GemvArgs& a, const Params& p, int max_slices, bool forced, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
-  const size_t smem = smem_bytes<BITS, PP>(MB);
+  const size_t smem = smem_bytes<BITS, PP, G64>(MB);
   if (smem > static_cast<size_t>(dev.max_smem_optin)) return DQ_OK;  // not taken
   const int row_ctas = static_cast<int>(ceil_div(p.tiles, kWarps));
   auto run = [&](auto kernel, auto tag) -> int32_t {
@@ -514,19 +636,21 @@ int32_t launch_mb(const GemvArgs& a, const Params& p, int max_slices, bool force
     *taken = true;
     return DQ_OK;
   };
-  using Bf16 = std::integral_constant<int, BITS * 1000 + MB * 100 + PP * 10 + 1>;
-  using F16 = std::integral_constant<int, BITS * 1000 + MB * 100 + PP * 10>;
+  using Bf16 = std::integral_constant<int, BITS * 10000 + MB * 1000 + PP * 100 + (G64 ? 10 : 0) + 1>;
+  using F16 = std::integral_constant<int, BITS * 10000 + MB * 1000 + PP * 100 + (G64 ? 10 : 0)>;
   if (max_slices > 1) {
-    return a.x_dtype == DQ_BF16 ? run(gemv_rows_kernel<BITS, true, MB, true, PP>, Bf16{}) : run(gemv_rows_kernel<BITS, false, MB, true, PP>, F16{});
+    return a.x_dtype == DQ_BF16 ? run(gemv_rows_kernel<BITS, true, MB, true, PP, G64>, Bf16{})
+                                : run(gemv_rows_kernel<BITS, false, MB, true, PP, G64>, F16{});
   }
-  return a.x_dtype == DQ_BF16 ? run(gemv_rows_kernel<BITS, true, MB, false, PP>, Bf16{}) : run(gemv_rows_kernel<BITS, false, MB, false, PP>, F16{});
+  return a.x_dtype == DQ_BF16 ? run(gemv_rows_kernel<BITS, true, MB, false, PP, G64>, Bf16{})
+                              : run(gemv_rows_kernel<BITS, false, MB, false, PP, G64>, F16{});
 }
 
-template <int BITS, int PP>
+template <int BITS, int PP, bool G64>
 int32_t launch_blocks(const GemvArgs& a, int want_slices, bool forced, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
-  using C = Cfg<BITS, PP>;
+  using C = Cfg<BITS, PP, G64>;
   const int steps = a.words_per_row / (4 * BITS);
-  if (steps % C::P != 0 || a.num_groups != steps || a.in_features != steps * 128) return DQ_OK;
+  if (steps % C::P != 0 || a.num_groups != steps * C::GPS || a.in_features != steps * 128) return DQ_OK;
   const auto align = static_cast<uintptr_t>(C::META_BYTES);
   if (reinterpret_cast<uintptr_t>(a.scales) % align != 0 || reinterpret_cast<uintptr_t>(a.offsets) % align != 0 ||
       (static_cast<int64_t>(a.num_groups) * 2) % C::META_BYTES != 0) {
@@ -541,9 +665,10 @@ int32_t launch_blocks(const GemvArgs& a, int want_slices, bool forced, const Dev
   // slices of the reduction axis: at least two blocks each (the pipeline's prologue requests two)
   const int slices = std::max(1, std::min(want_slices, (steps / C::P) / 2));
   if (want_slices > 1 && slices < 2) return DQ_OK;  // too short to slice, too few rows not to
-  // at most kMaxRows rows per launch (four column blocks): more rows, more passes
+  // at most kMaxRows rows per launch (four column blocks; two with 64-value groups, whose second
+  // accumulator per column block would not fit the registers): more rows, more passes
   const size_t x_row = static_cast<size_t>(a.in_features) * 2, out_row = static_cast<size_t>(a.out_stride) * dtype_size(a.out_dtype);
-  const int passes = static_cast<int>(ceil_div(a.m, kMaxRows));
+  const int passes = static_cast<int>(ceil_div(a.m, G64 ? kMaxRows / 2 : kMaxRows));
   const int per = static_cast<int>(ceil_div(a.m, passes));
   for (int r0 = 0; r0 < a.m; r0 += per) {
     GemvArgs part = a;
@@ -551,9 +676,16 @@ int32_t launch_blocks(const GemvArgs& a, int want_slices, bool forced, const Dev
     part.x = static_cast<const unsigned char*>(a.x) + r0 * x_row;
     part.out = static_cast<unsigned char*>(a.out) + r0 * out_row;
     bool ok = false;
-    const int32_t rc = part.m <= 8    ? launch_mb<BITS, 1, PP>(part, p, slices, forced, dev, stream_h, &ok)
-                       : part.m <= 16 ? launch_mb<BITS, 2, PP>(part, p, slices, forced, dev, stream_h, &ok)
-                                      : launch_mb<BITS, 4, PP>(part, p, slices, forced, dev, stream_h, &ok);
+    int32_t rc;
+    if (part.m <= 8) {
+      rc = launch_mb<BITS, 1, PP, G64>(part, p, slices, forced, dev, stream_h, &ok);
+    } else if (part.m <= 16) {
+      rc = launch_mb<BITS, 2, PP, G64>(part, p, slices, forced, dev, stream_h, &ok);
+    } else if constexpr (!G64) {
+      rc = launch_mb<BITS, 4, PP, false>(part, p, slices, forced, dev, stream_h, &ok);
+    } else {
+      rc = DQ_OK;  // (not reached: passes of at most 16 rows)
+    }
     if (rc != DQ_OK) return rc;
     if (!ok) return r0 == 0 ? DQ_OK : fail(DQ_ERR_UNSUPPORTED, "gemv rows: the second pass did not fit shared memory");
   }
@@ -566,10 +698,15 @@ template <int BITS>
 int32_t launch_bits(const GemvArgs& a, int want_slices, bool forced, const DeviceInfo& dev, cudaStream_t stream_h, bool* taken) {
   constexpr int P = stream::Cfg<BITS>::P;
   const int steps = a.words_per_row / (4 * BITS);
+  const bool g64 = a.group_values == 64;
   if constexpr (P > 2) {
-    if (steps % P != 0) return launch_blocks<BITS, 2>(a, want_slices, forced, dev, stream_h, taken);
+    if (steps % P != 0) {
+      return g64 ? launch_blocks<BITS, 2, true>(a, want_slices, forced, dev, stream_h, taken)
+                 : launch_blocks<BITS, 2, false>(a, want_slices, forced, dev, stream_h, taken);
+    }
   }
-  return launch_blocks<BITS, P>(a, want_slices, forced, dev, stream_h, taken);
+  return g64 ? launch_blocks<BITS, P, true>(a, want_slices, forced, dev, stream_h, taken)
+             : launch_blocks<BITS, P, false>(a, want_slices, forced, dev, stream_h, taken);
 }
 
 }  // namespace rowsk
@@ -606,7 +743,7 @@ int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool*
   const bool forced = rows_switch == 1 || forced_slices > 0;
   if (a.x_dtype != DQ_BF16 && a.x_dtype != DQ_F16) return DQ_OK;
   if (a.meta_dtype != DQ_BF16 && a.meta_dtype != DQ_F16) return DQ_OK;
-  if (a.group_values != 128) return DQ_OK;
+  if (a.group_values != 128 && a.group_values != 64) return DQ_OK;
   if ((a.in_features & 7) != 0 || (reinterpret_cast<uintptr_t>(a.x) & 15) != 0) return DQ_OK;  // unit-per-lane staging
   if (reinterpret_cast<uintptr_t>(a.packed) % 16 != 0 || (static_cast<int64_t>(a.words_per_row) * 4) % 16 != 0) return DQ_OK;
   switch (bits) {

@@ -48,6 +48,7 @@ def _draw(rng: random.Random):
         rows, k, m = rng.randint(16, 700), 128 * rng.choice([56, 96, 112]), rng.choice([4, 8, 8])
     elif kind == "few_factors":  # step counts the tiled kernel slices badly, few rows: the many-rows kernel, sliced over a cluster
         rows, k = rng.randint(1300, 4200), 128 * rng.choice([70, 86, 148, 74, 106])
+        group = rng.choice([64, 128])
     else:  # lengths and groups only the SIMT kernels take
         rows = rng.randint(1, 200)
         k, group = rng.choice([(100, PER_ROW), (320, 32), (4304, 128), (72, PER_ROW), (2048 + 64, 64)])

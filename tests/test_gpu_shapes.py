@@ -134,7 +134,7 @@ def test_sweep_shapes(bits, group, shape):
     want = oracle_gemv(x, qt)
     if m <= ops.gemv_max_rows():
         acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, group, k, out_dtype=torch.float32)
-        assert ops.last_kernel().startswith("gemv_mma")
+        assert ops.last_kernel().startswith(("gemv_mma", "gemv_rows"))  # a tensor-core kernel, not the SIMT fallback
     else:
         acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
     check_acc(acc, want)
@@ -143,20 +143,22 @@ def test_sweep_shapes(bits, group, shape):
 
 
 @pytest.mark.parametrize("bits", BITS)
-@pytest.mark.parametrize("m", [9, 16, 20, 32, 33, 40, 64])
-def test_many_rows_on_a_large_matrix_take_one_pass_over_the_weights(m, bits):
+@pytest.mark.parametrize("m,group", [(9, 128), (16, 128), (20, 128), (32, 128), (33, 128), (40, 128), (64, 128),
+                                     (9, 64), (16, 64), (17, 64), (40, 64)])
+def test_many_rows_on_a_large_matrix_take_one_pass_over_the_weights(m, group, bits):
     """The many-rows kernel (matrices with a CTA for most SMs): the fragments of a step decoded once
-    and fed to up to four column blocks of eight activation rows; one launch per 32 rows, every
-    row against the oracle."""
+    and fed to up to four column blocks of eight activation rows; one launch per 32 rows (per 16
+    with 64-value groups: two accumulators per column block), every row against the oracle."""
     from dynquant_b200 import _lib, ops
 
     meta = torch.bfloat16 if (m + bits) % 2 else torch.float16
-    qt = random_qt(12809, 1024, bits, meta=meta, seed=m, offsets=bits != 3)  # a ragged row count
+    qt = random_qt(12809, 1024, bits, group=group, meta=meta, seed=m, offsets=bits != 3)  # a ragged row count
     act = torch.float16 if m % 3 == 0 else torch.bfloat16
     x = torch.randn(m, 1024, generator=torch.Generator().manual_seed(m)).to(act).cuda()
     before = int(_lib.load().dq_launch_count())
     acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
-    assert int(_lib.load().dq_launch_count()) - before == (m + 31) // 32
+    per_launch = 32 if group == 128 else 16
+    assert int(_lib.load().dq_launch_count()) - before == (m + per_launch - 1) // per_launch
     assert ops.last_kernel() == "gemv_rows_kernel"
     want = oracle_gemv(x, qt)
     check_acc(acc, want)
@@ -165,8 +167,10 @@ def test_many_rows_on_a_large_matrix_take_one_pass_over_the_weights(m, bits):
 
 
 @pytest.mark.parametrize("bits", BITS)
-@pytest.mark.parametrize("rows,k,m", [(2048, 6144, 16), (4096 + 5, 14336, 9), (3072, 8192, 40), (8192, 8192, 64), (6144, 4096, 33)])
-def test_many_rows_on_a_matrix_with_few_rows_slice_the_reduction_axis(rows, k, m, bits):
+@pytest.mark.parametrize("rows,k,m,group", [(2048, 6144, 16, 128), (4096 + 5, 14336, 9, 128), (3072, 8192, 40, 128),
+                                            (8192, 8192, 64, 128), (6144, 4096, 33, 128),
+                                            (2048, 6144, 16, 64), (4096 + 5, 14336, 9, 64), (3072, 8192, 24, 64)])
+def test_many_rows_on_a_matrix_with_few_rows_slice_the_reduction_axis(rows, k, m, group, bits):
     """Matrices with too few rows for a CTA per SM (down-projections): the many-rows kernel's CTAs
     of one row group form a thread-block cluster that slices the reduction axis; the slices' sums
     are added in slice order by the cluster's first CTA -- every row against the oracle, and the
@@ -174,11 +178,12 @@ def test_many_rows_on_a_matrix_with_few_rows_slice_the_reduction_axis(rows, k, m
     from dynquant_b200 import _lib, ops
 
     meta = torch.bfloat16 if (m + bits) % 2 else torch.float16
-    qt = random_qt(rows, k, bits, meta=meta, seed=m + bits, offsets=bits != 2)
+    qt = random_qt(rows, k, bits, group=group, meta=meta, seed=m + bits, offsets=bits != 2)
     x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16).cuda()
     before = int(_lib.load().dq_launch_count())
     acc = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
-    assert int(_lib.load().dq_launch_count()) - before == (m + 31) // 32
+    per_launch = 32 if group == 128 else 16
+    assert int(_lib.load().dq_launch_count()) - before == (m + per_launch - 1) // per_launch
     assert ops.last_kernel() == "gemv_rows_kernel"
     check_acc(acc, oracle_gemv(x, qt))
     again = ops.gemv_row_chunks(x, [qt], out_dtype=torch.float32)
@@ -186,8 +191,10 @@ def test_many_rows_on_a_matrix_with_few_rows_slice_the_reduction_axis(rows, k, m
 
 
 @pytest.mark.parametrize("bits", BITS)
-@pytest.mark.parametrize("rows,k,m", [(1536, 8960, 1), (1536 + 3, 8960, 8), (2048, 11008, 3), (4096, 14336, 8), (4096, 14336, 6)])
-def test_matrices_the_tiled_kernel_is_a_poor_fit_for_take_the_many_rows_kernel(rows, k, m, bits):
+@pytest.mark.parametrize("rows,k,m,group", [(1536, 8960, 1, 128), (1536 + 3, 8960, 8, 128), (2048, 11008, 3, 128),
+                                            (4096, 14336, 8, 128), (4096, 14336, 6, 128),
+                                            (1536 + 3, 8960, 5, 64), (2048, 11008, 1, 64), (4096, 14336, 8, 64)])
+def test_matrices_the_tiled_kernel_is_a_poor_fit_for_take_the_many_rows_kernel(rows, k, m, group, bits):
     """One to eight activation rows: step counts with few factors of two (70 and 86 steps -- blocks
     of two steps at the low widths) on matrices of few rows, and six to eight rows x a long reduction
     axis (the staged activation would fill the tiled kernel's shared memory).  Against the oracle,
@@ -196,10 +203,10 @@ def test_matrices_the_tiled_kernel_is_a_poor_fit_for_take_the_many_rows_kernel(r
 
     meta = torch.float16 if (m + bits) % 2 else torch.bfloat16
     act = torch.float16 if m == 3 else torch.bfloat16
-    qt = random_qt(rows, k, bits, meta=meta, seed=m * 10 + bits, offsets=bits != 8)
+    qt = random_qt(rows, k, bits, group=group, meta=meta, seed=m * 10 + bits, offsets=bits != 8)
     x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(act).cuda()
     bias = torch.randn(rows, generator=torch.Generator().manual_seed(7)).to(act).cuda()
-    acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, 128, k, out_dtype=torch.float32)
+    acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, group, k, out_dtype=torch.float32)
     assert ops.last_kernel() == "gemv_rows_kernel"
     want = oracle_gemv(x, qt)
     check_acc(acc, want)
