@@ -21,7 +21,7 @@ INCLUDE = ROOT / "include"
 OBJ_DIR = PKG / "lib" / "obj"
 LIB_PATH = PKG / "lib" / "libdynquant_b200.so"
 
-SOURCES = ["dq_capi.cu", "dq_dequant.cu", "dq_gemv.cu", "dq_gemv_mma.cu", "dq_gemv_plan.cu", "dq_gemv_rows.cu", "dq_gemv_stream_multi.cu", "dq_moe.cu", "dq_peer.cu", "dq_probe.cu"]
+SOURCES = ["dq_capi.cu", "dq_dequant.cu", "dq_gemv.cu", "dq_gemv_mma.cu", "dq_gemv_plan.cu", "dq_gemv_rows.cu", "dq_gemv_stream_multi.cu", "dq_gemv_stream_sliced.cu", "dq_moe.cu", "dq_peer.cu", "dq_probe.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

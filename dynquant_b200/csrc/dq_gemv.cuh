@@ -41,6 +41,9 @@ int32_t launch_gemv_mma_fused(const GemvArgs* jobs, const int* bits, int n, cuda
 // Two to four long matrices that share an activation in one launch of the streaming kernel's body
 // (dq_gemv_stream_multi.cu).  *taken stays false, nothing launched, when they do not qualify.
 int32_t launch_gemv_stream_fused(const GemvArgs* jobs, const int* bits, int n, cudaStream_t stream, bool* taken);
+// One to eight activation rows against one matrix of too few rows for the streaming kernel: its
+// body with the reduction axis sliced over a thread-block cluster (dq_gemv_stream_sliced.cu).
+int32_t launch_gemv_stream_sliced(const GemvArgs& a, int bits, cudaStream_t stream, bool* taken);
 // min_rows..64 activation rows against one matrix in one pass over the weights (dq_gemv_rows.cu).
 // *taken stays false, nothing launched, when the matrix or the activation does not qualify.
 int32_t launch_gemv_rows(const GemvArgs& a, int bits, cudaStream_t stream, bool* taken, int min_rows = 9);

@@ -911,6 +911,27 @@ bool rows_kernel_first(const GemvArgs& a, int bits) {
   return frag_bytes > (144 << 10);
 }
 
+// Where the streaming body with the reduction axis sliced over a cluster (dq_gemv_stream_sliced.cu)
+// goes first: matrices of 16 MB and more on which the tiled kernel has about a CTA of eight warps
+// per SM or fewer -- the decode wants more resident warps than that -- or would be handed to the
+// many-rows kernel anyway.  Measured, one activation row, 2 / 3 / 4 / 8 bits: 5120 x 17408 17 / 24 /
+// 23 / 31 us against 21 / 29 / 26 / 46 in the tiled kernel; 3584 x 18944 17 / 23 / 22 / 30 against
+// 21 / 30 / 19 / 34 in the many-rows kernel; eight rows: 5120 x 17408 20 / 25 / 20 / 26 against 31 /
+// 44 / 25 / 43, 4096 x 14336 13 / 17 / 17 / 19 against 21 / 28 / 16 / 28.  Smaller matrices and those
+// the tiled kernel fills the SMs with twice over (4096 x 4096, 4096 x 14336 and 8192 x 8192 at one to
+// five rows, 2048 x 6144) are faster there: one CTA's eight slices share one staged activation.
+bool stream_sliced_first(const GemvArgs& a, int bits, bool rows_first) {
+  const DeviceInfo* dev = device_info();
+  if (dev == nullptr || a.group_values != kStepValues || a.words_per_row % (4 * bits) != 0) return false;
+  if (static_cast<int64_t>(a.rows) * a.words_per_row * 4 < (16 << 20)) return false;
+  if (rows_first) return true;
+  const int steps = a.words_per_row / (4 * bits);
+  int kw = 8;
+  while (kw > 1 && (steps % kw != 0 || (steps / kw) % 2 != 0)) kw /= 2;
+  const int64_t ctas = ceil_div(ceil_div(a.rows, 16) * kw, 8);
+  return ctas * 4 < static_cast<int64_t>(dev->sm_count) * 5;
+}
+
 int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const peerpush::Push* push) {
   const DeviceInfo* dev = device_info();
   if (dev == nullptr) return DQ_ERR_CUDA;
@@ -949,6 +970,11 @@ int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const 
     }
     if (taken || rc != DQ_OK) return rc;
     // (not a stream of bytes for the streaming kernel)
+    const int sliced_switch = tuning_int("DQ_B200_STREAM_SLICED", -1);  // 0: never; 1: wherever it qualifies
+    if (push == nullptr && (sliced_switch == 1 || (sliced_switch != 0 && stream_sliced_first(a, bits, rows_first)))) {
+      rc = launch_gemv_stream_sliced(a, bits, stream, &taken);
+      if (taken || rc != DQ_OK) return rc;
+    }
     if (rows_first) {
       rc = launch_gemv_rows(a, bits, stream, &taken, 1);
       if (taken || rc != DQ_OK) return rc;

@@ -128,9 +128,14 @@ struct Params {
 // The body is a device function of (CTA index, CTA count) so that one launch can also run several
 // matrices side by side, each on its own range of CTAs (gemv_mma_stream_multi_kernel,
 // dq_gemv_stream_multi.cu); the single-matrix kernel below passes blockIdx.x / gridDim.x.
-template <int BITS, bool XBF16, bool MBF16, bool P16 = false, bool PUSH = false>
+//
+// SLICED (gemv_mma_stream_sliced_kernel below): `a` and `p` describe one slice of the reduction
+// axis, every warp has at most one row tile, and the sums are not stored: they are left in acc_out
+// for the caller, which adds the slices of a thread-block cluster.
+template <int BITS, bool XBF16, bool MBF16, bool P16 = false, bool PUSH = false, bool SLICED = false>
 __device__ __forceinline__ void stream_body(const GemvArgs& a, const Params& p, const unsigned int cta,
-                                            const unsigned int ncta, unsigned char* smem_raw) {
+                                            const unsigned int ncta, unsigned char* smem_raw,
+                                            float* acc_out = nullptr) {
   using Plan = MmaPlan<BITS>;
   using C = Cfg<BITS>;
   constexpr int P = C::P;
@@ -374,15 +379,20 @@ __device__ __forceinline__ void stream_body(const GemvArgs& a, const Params& p, 
         mslot = ring_m_quad;
       }
     }
-    const int row_a = tile * kTileRows + g, row_b = row_a + 8;
-    const int m0 = 2 * t;
-    if (m0 < a.m) {
-      if (row_a < a.rows) store_out(a, m0, row_a, acc[0]);
-      if (row_b < a.rows) store_out(a, m0, row_b, acc[2]);
-    }
-    if (m0 + 1 < a.m) {
-      if (row_a < a.rows) store_out(a, m0 + 1, row_a, acc[1]);
-      if (row_b < a.rows) store_out(a, m0 + 1, row_b, acc[3]);
+    if constexpr (SLICED) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc_out[i] = acc[i];
+    } else {
+      const int row_a = tile * kTileRows + g, row_b = row_a + 8;
+      const int m0 = 2 * t;
+      if (m0 < a.m) {
+        if (row_a < a.rows) store_out(a, m0, row_a, acc[0]);
+        if (row_b < a.rows) store_out(a, m0, row_b, acc[2]);
+      }
+      if (m0 + 1 < a.m) {
+        if (row_a < a.rows) store_out(a, m0 + 1, row_a, acc[1]);
+        if (row_b < a.rows) store_out(a, m0 + 1, row_b, acc[3]);
+      }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -413,6 +423,69 @@ template <int BITS, bool XBF16, bool MBF16, bool P16 = false, bool PUSH = false>
 __global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_kernel(const GemvArgs a, const Params p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   stream_body<BITS, XBF16, MBF16, P16, PUSH>(a, p, blockIdx.x, gridDim.x, smem_raw);
+}
+
+// Matrices of too few rows to be a stream for the kernel above (a warp there owns whole rows): the
+// grid's y axis slices the reduction axis, the CTAs of one group of eight row tiles form a
+// thread-block cluster (1 x slices), each runs the streaming body over its own range of blocks
+// -- staging only its part of the activation -- and the sums meet in the cluster's first CTA
+// through distributed shared memory, added in slice order (a fixed summation order), which stores.
+// p.steps is the whole row's step count here; the slices are whole blocks, equal to within one.
+template <int BITS, bool XBF16, bool MBF16, bool P16 = false>
+__global__ void __launch_bounds__(kThreads, 3) gemv_mma_stream_sliced_kernel(const GemvArgs a, const Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int P = Cfg<BITS>::P;
+  constexpr int NA = P16 ? 16 : MmaPlan<BITS>::kARegs;
+  uint32_t slice, slices;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(slice));
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(slices));
+  const int nblocks = p.steps / P;
+  const int blk_begin = static_cast<int>(static_cast<unsigned>(nblocks) * slice / slices);
+  const int blk_end = static_cast<int>(static_cast<unsigned>(nblocks) * (slice + 1) / slices);
+  GemvArgs sa = a;
+  Params sp = p;
+  sp.steps = (blk_end - blk_begin) * P;
+  sp.m_stride_u4 = sp.steps * NA + 4;
+  sp.runs = 0;
+  const int s0 = blk_begin * P;  // first step of the slice
+  sa.packed = a.packed + s0 * (4 * BITS);
+  sa.scales = static_cast<const unsigned short*>(a.scales) + s0;
+  sa.offsets = a.offsets != nullptr ? static_cast<const unsigned short*>(a.offsets) + s0 : nullptr;
+  sa.x = static_cast<const unsigned short*>(a.x) + s0 * 128;  // (the row pitch stays a.in_features)
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  stream_body<BITS, XBF16, MBF16, P16, false, true>(sa, sp, blockIdx.x, gridDim.x, smem_raw, acc);
+
+  // Both cluster barriers are reached by every thread of every CTA; the second keeps a CTA's shared
+  // memory alive until the first CTA has read it.
+  const int tid = threadIdx.x;
+  __syncthreads();  // every warp is done with the ring and the staged activation
+  reinterpret_cast<float4*>(smem_raw)[tid] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (slice == 0) {
+    const uint32_t mine = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw)) + tid * 16;
+    for (uint32_t r = 1; r < slices; ++r) {
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(r));
+      float4 v;
+      asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+      acc[0] += v.x, acc[1] += v.y, acc[2] += v.z, acc[3] += v.w;
+    }
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (slice != 0) return;
+  const int lane = tid & (kWarp - 1), warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int tile = static_cast<int>(blockIdx.x) * kWarps + warp;
+  if (tile >= p.tiles) return;
+  const int row_a = tile * 16 + g, row_b = row_a + 8;
+  const int m0 = 2 * t;
+  if (m0 < a.m) {
+    if (row_a < a.rows) store_out(a, m0, row_a, acc[0]);
+    if (row_b < a.rows) store_out(a, m0, row_b, acc[2]);
+  }
+  if (m0 + 1 < a.m) {
+    if (row_a < a.rows) store_out(a, m0 + 1, row_a, acc[1]);
+    if (row_b < a.rows) store_out(a, m0 + 1, row_b, acc[3]);
+  }
 }
 
 }  // namespace stream

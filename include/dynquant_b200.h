@@ -101,7 +101,8 @@ DQ_API int32_t dq_gemv_max_rows(void);
  * matrices or several launches for one, and benchmarks report the real number. */
 DQ_API int64_t dq_launch_count(void);
 /* Name of the kernel the calling thread's most recent GEMV or MoE entry point launched last
- * ("gemv_mma_stream_kernel", "gemv_mma_stream_multi_kernel", "gemv_mma_tile_kernel", "gemv_mma_kernel", "gemv_fast_kernel",
+ * ("gemv_mma_stream_kernel", "gemv_mma_stream_multi_kernel", "gemv_mma_stream_sliced_kernel", "gemv_mma_tile_kernel",
+ * "gemv_mma_kernel", "gemv_fast_kernel",
  * "gemv_general_kernel", "gemv_plan_kernel", "gemv_rows_kernel", "moe_grouped_kernel", "moe_combine_kernel",
  * "moe_down_token_kernel"; "" before the first launch).  No reference
  * counterpart: the reference has two kernels and a documented rule between them

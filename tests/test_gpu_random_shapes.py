@@ -79,6 +79,7 @@ def test_random_shapes_match_the_oracle_and_reach_every_kernel():
         assert np.linalg.norm(got - want) / (np.linalg.norm(want) + 1e-30) <= 1e-3, (case, kind, name)
     for kernel in ("gemv_mma_tile_kernel", "gemv_mma_stream_kernel", "gemv_rows_kernel", "gemv_fast_kernel", "gemv_general_kernel"):
         assert seen.get(kernel, 0) >= 3, (kernel, seen)
+    assert seen.get("gemv_mma_stream_sliced_kernel", 0) >= 1, seen  # (few of the draws are matrices of 16 MB and more)
 
 
 def test_random_fused_shards_and_row_chunks_match_the_oracle():

@@ -206,12 +206,37 @@ def test_matrices_the_tiled_kernel_is_a_poor_fit_for_take_the_many_rows_kernel(r
     qt = random_qt(rows, k, bits, group=group, meta=meta, seed=m * 10 + bits, offsets=bits != 8)
     x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(act).cuda()
     bias = torch.randn(rows, generator=torch.Generator().manual_seed(7)).to(act).cuda()
+    cluster_kernels = ("gemv_rows_kernel", "gemv_mma_stream_sliced_kernel")  # (the second: from 16 MB on, 128-value groups)
     acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, group, k, out_dtype=torch.float32)
-    assert ops.last_kernel() == "gemv_rows_kernel"
+    assert ops.last_kernel() in cluster_kernels
     want = oracle_gemv(x, qt)
     check_acc(acc, want)
     out = ops.gemv_shards(x, [qt], bias)
-    assert ops.last_kernel() == "gemv_rows_kernel"
+    assert ops.last_kernel() in cluster_kernels
+    assert out.dtype == act and within_one_ulp_16(out, want + bias.float().cpu().numpy()[None, :])
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("rows,k,m", [(5120, 17408, 1), (5120 + 7, 17408, 8), (3584, 18944, 4), (5120, 13824, 2)])
+def test_large_matrices_of_few_rows_take_the_streaming_body_sliced_over_a_cluster(rows, k, m, bits):
+    """Matrices of 16 MB and more that leave the tiled kernel about a CTA per SM or fewer: the
+    streaming kernel's body, the reduction axis sliced over a thread-block cluster, the slices'
+    sums added in slice order by the cluster's first CTA.  Against the oracle, with a bias, and the
+    same bits on a second run."""
+    from dynquant_b200 import ops
+
+    meta = torch.float16 if (m + bits) % 2 else torch.bfloat16
+    act = torch.float16 if m == 4 else torch.bfloat16
+    qt = random_qt(rows, k, bits, meta=meta, seed=m * 10 + bits, offsets=bits != 4)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(act).cuda()
+    bias = torch.randn(rows, generator=torch.Generator().manual_seed(7)).to(act).cuda()
+    acc = ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, 128, k, out_dtype=torch.float32)
+    assert ops.last_kernel() == "gemv_mma_stream_sliced_kernel"
+    want = oracle_gemv(x, qt)
+    check_acc(acc, want)
+    assert torch.equal(acc, ops.gemv(x, qt.packed, qt.scales, qt.offsets, bits, 128, k, out_dtype=torch.float32))
+    out = ops.gemv_shards(x, [qt], bias)
+    assert ops.last_kernel() == "gemv_mma_stream_sliced_kernel"
     assert out.dtype == act and within_one_ulp_16(out, want + bias.float().cpu().numpy()[None, :])
 
 
