@@ -912,24 +912,37 @@ bool rows_kernel_first(const GemvArgs& a, int bits) {
 }
 
 // Where the streaming body with the reduction axis sliced over a cluster (dq_gemv_stream_sliced.cu)
-// goes first: matrices of 16 MB and more on which the tiled kernel has about a CTA of eight warps
-// per SM or fewer -- the decode wants more resident warps than that -- or would be handed to the
-// many-rows kernel anyway.  Measured, one activation row, 2 / 3 / 4 / 8 bits: 5120 x 17408 17 / 24 /
-// 23 / 31 us against 21 / 29 / 26 / 46 in the tiled kernel; 3584 x 18944 17 / 23 / 22 / 30 against
-// 21 / 30 / 19 / 34 in the many-rows kernel; eight rows: 5120 x 17408 20 / 25 / 20 / 26 against 31 /
-// 44 / 25 / 43, 4096 x 14336 13 / 17 / 17 / 19 against 21 / 28 / 16 / 28.  Smaller matrices and those
-// the tiled kernel fills the SMs with twice over (4096 x 4096, 4096 x 14336 and 8192 x 8192 at one to
-// five rows, 2048 x 6144) are faster there: one CTA's eight slices share one staged activation.
+// goes first, all measured against the tiled (or many-rows) kernel on matrices of 16 MB and more:
+//  * the many-rows kernel would be handed the matrix anyway (3584 x 18944 at one row, 2 / 3 / 4 / 8
+//    bits: 17 / 23 / 22 / 30 us against 21 / 30 / 19 / 34; 4096 x 14336 at eight rows 13 / 17 / 17 / 19
+//    against 21 / 28 / 16 / 28);
+//  * the tiled kernel has about a CTA of eight warps per SM or fewer -- the decode wants more
+//    resident warps (5120 x 17408 at one row 17 / 24 / 23 / 31 against 21 / 29 / 26 / 46);
+//  * it cannot slice the reduction axis eight ways (K = 5120: 40 steps) and has fewer than 2.5 CTAs
+//    per SM, from 20 MB on (10240 x 5120 at one row, 4 / 8 bits: 12.0 / 15.5 against 14.7 / 22.5;
+//    but 7168 x 5120 at 4 bits, 18 MB, 10.8 against 9.0, and 17408 x 5120, 544 CTAs, 14.0 / 19.5 /
+//    17.0 at 2 / 3 / 4 bits against 13.0 / 17.0 / 15.7);
+//  * seven or eight activation rows (8192 x 8192 13.7 / 16.9 / 16.8 / 22.9 against 18.5 / 20.7 / 20.6
+//    / 32; 11008 x 4096 11.1 / 13.7 / 11.7 / 14.1 against 13.9 / 14.5 / 13.7 / 21.1);
+//  * 8-bit codes with two or more rows from 24 MB on, with one row from 96 MB on (8192 x 8192 at
+//    four rows 18 against 44; 8192 x 28672 at one row 49 against 102; 4096 x 4096, 17 MB, at two rows
+//    9.6 against 8.6).
+// Elsewhere -- one to six rows on matrices the tiled kernel fills the SMs with twice over (4096 x
+// 4096, 4096 x 14336, 8192 x 8192, 12288 x 8192), small matrices (2048 x 6144) -- the tiled kernel
+// is faster by 5-40 %: its eight slices share one CTA's staged activation.
 bool stream_sliced_first(const GemvArgs& a, int bits, bool rows_first) {
   const DeviceInfo* dev = device_info();
   if (dev == nullptr || a.group_values != kStepValues || a.words_per_row % (4 * bits) != 0) return false;
-  if (static_cast<int64_t>(a.rows) * a.words_per_row * 4 < (16 << 20)) return false;
-  if (rows_first) return true;
+  const int64_t bytes = static_cast<int64_t>(a.rows) * a.words_per_row * 4;
+  if (bytes < (16 << 20)) return false;
+  if (rows_first || a.m >= 7) return true;
   const int steps = a.words_per_row / (4 * bits);
   int kw = 8;
   while (kw > 1 && (steps % kw != 0 || (steps / kw) % 2 != 0)) kw /= 2;
   const int64_t ctas = ceil_div(ceil_div(a.rows, 16) * kw, 8);
-  return ctas * 4 < static_cast<int64_t>(dev->sm_count) * 5;
+  if (ctas * 4 < static_cast<int64_t>(dev->sm_count) * 5) return true;
+  if (kw < 8 && bytes >= (20 << 20) && ctas * 2 < static_cast<int64_t>(dev->sm_count) * 5) return true;
+  return bits == 8 && ((a.m >= 2 && bytes >= (24 << 20)) || bytes >= (96 << 20));
 }
 
 int32_t launch_gemv_mma(const GemvArgs& a, int bits, cudaStream_t stream, const peerpush::Push* push) {
