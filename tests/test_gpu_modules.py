@@ -140,6 +140,40 @@ def test_gemv_sequence_and_step_runner_match_individual_calls():
                 assert torch.equal(runner.outputs[name], want), (mode, name)
 
 
+@pytest.mark.parametrize("rows_m", [1, 8])
+def test_a_step_with_cluster_launches_in_its_graph_matches_the_eager_step(rows_m):
+    """One layer of the 14B set: its down-projection (5120 x 17408) takes the streaming body sliced
+    over a thread-block cluster.  Cluster launches with programmatic dependent launch between
+    them, captured into a graph: the same bits as the eager step, every module within the
+    rounding of a re-sliced sum of the single call."""
+    from dynquant_b200 import ops
+    from dynquant_b200.stack import StepRunner
+    from dynquant_b200.workloads import qwen14b_linear_set
+
+    stack = qwen14b_linear_set(device="cuda", layers=1)
+    runner = StepRunner(stack, rows_m, device="cuda")
+    runner.run()
+    torch.cuda.synchronize()
+    eager = {k: v.clone() for k, v in runner.outputs.items()}
+    kernels = set()
+    for mod in stack.modules:
+        want = ops.quantized_matmul(runner.inputs[mod.input], mod.weight)
+        kernels.add(ops.last_kernel())
+        diff = (eager[mod.name].float() - want.float()).abs()
+        bound = want.float().abs() * 2.0**-7 + 1e-4 * want.float().abs().max()
+        assert bool((diff <= bound).all()), (mod.name, float(diff.max()))
+    assert "gemv_mma_stream_sliced_kernel" in kernels, kernels
+    for mode in ("dataflow", "chain"):
+        for v in runner.outputs.values():
+            v.zero_()
+        runner.capture(mode)
+        runner.replay()
+        runner.replay()
+        torch.cuda.synchronize()
+        for name, want in eager.items():
+            assert torch.equal(runner.outputs[name], want), (mode, name)
+
+
 def test_gemv_host_entry_point_round_trips_through_pinned_memory():
     from dynquant_b200 import ops
 
