@@ -901,7 +901,9 @@ bool rows_kernel_first(const GemvArgs& a, int bits) {
   int kw = 8;
   while (kw > 1 && (steps % kw != 0 || (steps / kw) % 2 != 0)) kw /= 2;
   const int64_t ctas = ceil_div(ceil_div(a.rows, 16) * kw, 8);
-  if (ctas * 2 < dev->sm_count) return true;
+  // (... and a long chain per warp: with 28 steps, K = 3584, two slices of 14 are over soon enough --
+  // 3584 x 3584 and 4608 x 3584 at 2 / 3 bits run 6.4-7.8 us there against 7.9-10.3 here)
+  if (ctas * 2 < dev->sm_count && steps / kw >= 24) return true;
   // The tiled kernel stages the whole activation in fragment order (16 bytes per register of the
   // plan, step and row).  Where that leaves little room for a ring (six rows x K = 14336; at 8 bits
   // four rows) it passes the slices through shared memory block by block, every CTA again; the
@@ -916,8 +918,9 @@ bool rows_kernel_first(const GemvArgs& a, int bits) {
 //  * the many-rows kernel would be handed the matrix anyway (3584 x 18944 at one row, 2 / 3 / 4 / 8
 //    bits: 17 / 23 / 22 / 30 us against 21 / 30 / 19 / 34; 4096 x 14336 at eight rows 13 / 17 / 17 / 19
 //    against 21 / 28 / 16 / 28);
-//  * the tiled kernel has about a CTA of eight warps per SM or fewer -- the decode wants more
-//    resident warps (5120 x 17408 at one row 17 / 24 / 23 / 31 against 21 / 29 / 26 / 46);
+//  * the tiled kernel has about a CTA of eight warps per SM or fewer and 24 steps or more per warp
+//    -- the decode wants more resident warps (5120 x 17408 at one row 17 / 24 / 23 / 31 against 21 /
+//    29 / 26 / 46);
 //  * it cannot slice the reduction axis eight ways (K = 5120: 40 steps) and has fewer than 2.5 CTAs
 //    per SM, from 20 MB on (10240 x 5120 at one row, 4 / 8 bits: 12.0 / 15.5 against 14.7 / 22.5;
 //    but 7168 x 5120 at 4 bits, 18 MB, 10.8 against 9.0, and 17408 x 5120, 544 CTAs, 14.0 / 19.5 /
@@ -940,7 +943,9 @@ bool stream_sliced_first(const GemvArgs& a, int bits, bool rows_first) {
   int kw = 8;
   while (kw > 1 && (steps % kw != 0 || (steps / kw) % 2 != 0)) kw /= 2;
   const int64_t ctas = ceil_div(ceil_div(a.rows, 16) * kw, 8);
-  if (ctas * 4 < static_cast<int64_t>(dev->sm_count) * 5) return true;
+  // (a CTA per SM AND a long chain per warp: 2048 x 16384 has 128 CTAs there but slices of 16 steps,
+  // and runs 9.0 us at 4 bits against 14.1 here, whose 16 row groups x 8 slices cannot fill the SMs)
+  if (ctas * 4 < static_cast<int64_t>(dev->sm_count) * 5 && steps / kw >= 24) return true;
   if (kw < 8 && bytes >= (20 << 20) && ctas * 2 < static_cast<int64_t>(dev->sm_count) * 5) return true;
   return bits == 8 && ((a.m >= 2 && bytes >= (24 << 20)) || bytes >= (96 << 20));
 }
