@@ -916,10 +916,10 @@ bool rows_kernel_first(const GemvArgs& a, int bits) {
 // Where the streaming body with the reduction axis sliced over a cluster (dq_gemv_stream_sliced.cu)
 // goes first, all measured against the tiled (or many-rows) kernel on matrices of 16 MB and more:
 //  * the many-rows kernel would be handed the matrix anyway (3584 x 18944 at one row, 2 / 3 / 4 / 8
-//    bits: 17 / 23 / 22 / 30 us against 21 / 30 / 19 / 34; 4096 x 14336 at eight rows 13 / 17 / 17 / 19
+//    bits: 13 / 18 / 15 / 18 us against 21 / 30 / 19 / 34; 4096 x 14336 at eight rows 13 / 17 / 17 / 19
 //    against 21 / 28 / 16 / 28);
 //  * the tiled kernel has about a CTA of eight warps per SM or fewer and 24 steps or more per warp
-//    -- the decode wants more resident warps (5120 x 17408 at one row 17 / 24 / 23 / 31 against 21 /
+//    -- the decode wants more resident warps (5120 x 17408 at one row 14 / 20 / 17 / 21 against 21 /
 //    29 / 26 / 46);
 //  * it cannot slice the reduction axis eight ways (K = 5120: 40 steps) and has fewer than 2.5 CTAs
 //    per SM, from 20 MB on (10240 x 5120 at one row, 4 / 8 bits: 12.0 / 15.5 against 14.7 / 22.5;

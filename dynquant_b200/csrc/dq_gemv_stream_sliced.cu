@@ -6,7 +6,7 @@
 // CTA (8, 4 or 2 ways, even slices), which leaves a down-projection such as 5120 x 17408 with 160
 // CTAs of eight warps on 148 SMs -- a third of the warps the streaming kernel keeps resident, and the
 // decode needs them.  Here the slices are CTAs of a cluster: a group of eight row tiles x up to
-// eight slices of whole blocks in any proportion, three CTAs per SM, every CTA staging only its own
+// eight slices of whole blocks in any proportion, two CTAs per SM, every CTA staging only its own
 // part of the activation; the slices' sums meet in the cluster's first CTA through distributed
 // shared memory in slice order.
 #include <algorithm>
@@ -77,7 +77,13 @@ int32_t launch_sliced(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t str
   auto smem_for = [&](int slices) {
     const int slice_steps = static_cast<int>(ceil_div(nblocks, slices)) * C::P;
     const size_t stride = static_cast<size_t>(slice_steps) * aregs + 4;
-    return C::RING_BYTES + (static_cast<size_t>(a.m) * stride + aregs) * 16 + static_cast<size_t>(slice_steps) * 8 * 4 * 2;
+    const size_t need = C::RING_BYTES + (static_cast<size_t>(a.m) * stride + aregs) * 16 + static_cast<size_t>(slice_steps) * 8 * 4 * 2;
+    // At least 80 KB: two CTAs per SM, not three.  With one activation row three would fit, and the
+    // CTAs of a cluster are then placed so unevenly over the SMs that the launch is slower and its
+    // time erratic in the slice count (measured at 2 / 3 / 4 / 8 bits, one row: 5120 x 17408 17 / 24 /
+    // 23 / 31 us with three per SM, 14 / 20 / 17 / 21 with two; 3584 x 18944 17 / 23 / 22 / 30 against
+    // 13 / 18 / 15 / 18; one per SM is level with two except on 10240 x 5120, 23 against 13 at 8 bits).
+    return std::max(need, static_cast<size_t>(tuning_int("DQ_B200_SLICED_MIN_SMEM_KB", 80)) << 10);
   };
   auto run = [&](auto kernel, int tag) -> int32_t {
     // The largest slice count (two blocks a slice at least) whose clusters are all resident at once,
