@@ -927,12 +927,17 @@ bool rows_kernel_first(const GemvArgs& a, int bits) {
 //    17.0 at 2 / 3 / 4 bits against 13.0 / 17.0 / 15.7);
 //  * seven or eight activation rows (8192 x 8192 13.7 / 16.9 / 16.8 / 22.9 against 18.5 / 20.7 / 20.6
 //    / 32; 11008 x 4096 11.1 / 13.7 / 11.7 / 14.1 against 13.9 / 14.5 / 13.7 / 21.1);
+//  * up to 8192 weight rows: four and more activation rows from 20 MB on (4096 x 14336 at 3 / 4 bits
+//    15.4 / 13.7 against 18.5 / 17.3; 8192 x 8192 15.8 / 13.9 against 18.2 / 16.5; but 12288 x 8192 26.7
+//    / 25.5 against 25.0 / 22.5), any number from 56 MB on (8192 x 28672 at one row, 2 / 3 / 4 bits: 28
+//    / 42 / 34 against 33 / 45 / 39; 4096 x 14336 and 8192 x 8192 at 8 bits 17 against 22);
 //  * 8-bit codes with two or more rows from 24 MB on, with one row from 96 MB on (8192 x 8192 at
 //    four rows 18 against 44; 8192 x 28672 at one row 49 against 102; 4096 x 4096, 17 MB, at two rows
 //    9.6 against 8.6).
-// Elsewhere -- one to six rows on matrices the tiled kernel fills the SMs with twice over (4096 x
-// 4096, 4096 x 14336, 8192 x 8192, 12288 x 8192), small matrices (2048 x 6144) -- the tiled kernel
-// is faster by 5-40 %: its eight slices share one CTA's staged activation.
+// Elsewhere -- one to three rows on matrices the tiled kernel fills the SMs with twice over (4096 x
+// 14336, 8192 x 8192 below 56 MB, 12288 x 8192 at any row count), small matrices (4096 x 4096, 2048 x
+// 6144, 7168 x 5120 at 2-4 bits) -- the tiled kernel is level or faster, by up to 50 % on the small
+// ones: its eight slices share one CTA's staged activation.
 bool stream_sliced_first(const GemvArgs& a, int bits, bool rows_first) {
   const DeviceInfo* dev = device_info();
   if (dev == nullptr || a.group_values != kStepValues || a.words_per_row % (4 * bits) != 0) return false;
@@ -947,6 +952,7 @@ bool stream_sliced_first(const GemvArgs& a, int bits, bool rows_first) {
   // and runs 9.0 us at 4 bits against 14.1 here, whose 16 row groups x 8 slices cannot fill the SMs)
   if (ctas * 4 < static_cast<int64_t>(dev->sm_count) * 5 && steps / kw >= 24) return true;
   if (kw < 8 && bytes >= (20 << 20) && ctas * 2 < static_cast<int64_t>(dev->sm_count) * 5) return true;
+  if (a.rows <= 8192 && ((a.m >= 4 && bytes >= (20 << 20)) || bytes >= (56 << 20))) return true;
   return bits == 8 && ((a.m >= 2 && bytes >= (24 << 20)) || bytes >= (96 << 20));
 }
 
