@@ -63,6 +63,10 @@ def main() -> None:
     ap.add_argument("--group", type=int, default=128)
     ap.add_argument("--m", default="1,4,8")
     args = ap.parse_args()
+    stamp = Path(__file__).resolve().parent.parent / "dynquant_b200" / "lib" / "obj" / "build_kind.txt"
+    if not stamp.exists() or stamp.read_text().strip() != "tuning":
+        print("note: not a tuning build -- the switches are ignored and both arms run the full dispatch "
+              "(python -m dynquant_b200.build --tuning)", file=sys.stderr)
     shapes = [tuple(int(v) for v in s.split("x")) for s in args.shape] if args.shape else SHAPES
     rows_m = [int(v) for v in args.m.split(",")]
     same = better = worse = 0
