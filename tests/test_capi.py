@@ -28,6 +28,19 @@ def test_library_exports_every_declared_symbol():
     assert set(names) == set(_lib.SIGNATURES), "ctypes signatures and the header disagree"
 
 
+def test_header_names_every_kernel_the_library_reports():
+    """dq_last_kernel()'s documentation lists the names a caller can see; every name the sources
+    pass to note_kernel() must be in that list (a new kernel is not silently undocumented)."""
+    csrc = ROOT / "dynquant_b200" / "csrc"
+    reported = set()
+    for path in list(csrc.glob("*.cu")) + list(csrc.glob("*.cuh")):
+        reported |= set(re.findall(r'note_kernel\("(\w+)"\)', path.read_text()))
+    assert len(reported) >= 8
+    doc = HEADER[HEADER.index("Name of the kernel the calling thread"):HEADER.index("dq_last_kernel(void)")]
+    missing = sorted(name for name in reported if f'"{name}"' not in doc)
+    assert not missing, f"kernel names missing from the dq_last_kernel documentation: {missing}"
+
+
 def test_abi_constants_match_the_reference_numbers():
     lib = _lib.load()
     assert lib.dq_abi_version() == 2  # csrc/include/dynquant/abi.h:23
